@@ -1,0 +1,48 @@
+"""Pack the reference's flash-attention golden vectors into one small .npz.
+
+The reference stores them as text (space separated floats, one file per
+tensor) under runtime/test/test_files/flash_attn_*.data; they were produced by
+runtime/test/test_files/generate_flash_attn_ground_truth.py with the upstream
+flash-attn package: b=1, seqlen=128, heads=3, head_dim=32, fp16, causal,
+softmax scale 0.5.  The reference's own tests round these values to fp16 and
+demand a bit-exact match (runtime/test/backends/cuda/providers/default/kernel/
+flash_attn_fwd_test.cc:142), so fp16 is a lossless container for them.
+
+Run in a checkout that has the reference mounted:
+    python tests/golden/make_flash_attn_golden.py /root/reference
+"""
+import sys
+from pathlib import Path
+
+import numpy as np
+
+SHAPE = (1, 128, 3, 32)
+NAMES = {
+    "q": "flash_attn_inputs_q.data",
+    "k": "flash_attn_inputs_k.data",
+    "v": "flash_attn_inputs_v.data",
+    "dout": "flash_attn_inputs_dout.data",
+    "out": "flash_attn_fwd_outputs.data",
+    "dq": "flash_attn_bwd_outputs_dq.data",
+    "dk": "flash_attn_bwd_outputs_dk.data",
+    "dv": "flash_attn_bwd_outputs_dv.data",
+}
+
+
+def main(ref_root: str) -> None:
+    src = Path(ref_root) / "runtime" / "test" / "test_files"
+    arrays = {}
+    for key, fname in NAMES.items():
+        vals = np.array((src / fname).read_text().split(), dtype=np.float64)
+        assert vals.size == int(np.prod(SHAPE)), (fname, vals.size)
+        f16 = vals.astype(np.float16)
+        # the text was printed from fp16 tensors: the round trip must be exact
+        assert np.array_equal(f16.astype(np.float64), vals), fname
+        arrays[key] = f16.reshape(SHAPE)
+    out = Path(__file__).with_name("flash_attn_b1_s128_h3_d32_f16.npz")
+    np.savez_compressed(out, **arrays)
+    print("wrote", out, out.stat().st_size, "bytes")
+
+
+if __name__ == "__main__":
+    main(sys.argv[1] if len(sys.argv) > 1 else "/root/reference")
