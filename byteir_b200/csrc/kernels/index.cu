@@ -1,0 +1,928 @@
+// IndexSelectOp (row gather) and IndexPutOp with accumulate (deterministic
+// scatter-add) for sm_100a.
+//
+// Gather.  out[a, ob, :] = in[a, idx[ob], :].  When a row is a multiple of 16
+// bytes the rows never pass through registers: one warp per block drives a
+// 4-stage ring of shared-memory tiles; each lane issues bulk (TMA) copies
+// global -> shared for its rows of the tile, the tile's mbarrier counts the
+// bytes, and one bulk copy shared -> global writes the tile, which is contiguous
+// in the output.  Other row sizes use vector loads sized to the row.
+//
+// Scatter-add.  out = in; out[idx[i], :] += upd[i, :].  The reference uses
+// atomicAdd, so its f32 result depends on scheduling.  Here the (index, i) pairs
+// are sorted by index with a stable LSD radix sort, which leaves the updates of
+// a row adjacent and in ascending i.  The sorted list is cut into chunks of 32
+// entries; one warp sums each chunk's runs in f32.  A run that lies inside one
+// chunk is finished at once (table value + sum, one rounding).  A run that
+// crosses chunk borders leaves f32 partials, and the warp of the chunk where the
+// run starts adds the partials of the following chunks in order.  The summation
+// tree is therefore a function of the index list alone.
+#include <algorithm>
+#include <map>
+#include <mutex>
+#include <type_traits>
+#include <utility>
+
+#include "common.cuh"
+#include "tma.cuh"
+
+namespace b200 {
+namespace {
+
+// =============================================================================
+// gather
+// =============================================================================
+constexpr int kGatherStages = 4;
+constexpr int kGatherMaxRowsPerTile = 128;
+
+template <typename IdxT>
+__global__ void __launch_bounds__(32)
+    gather_rows_bulk_kernel(const char *__restrict__ in, const IdxT *__restrict__ idx,
+                            char *__restrict__ out, int64_t IB, int64_t OB, uint32_t row_bytes,
+                            int rows_per_tile, int64_t tiles_per_a, int64_t num_tiles,
+                            int *status) {
+  extern __shared__ __align__(128) unsigned char smem[];
+  __shared__ uint64_t full[kGatherStages];
+  const int lane = threadIdx.x;
+  const uint32_t stage_bytes = (uint32_t)rows_per_tile * row_bytes;
+
+  if (lane == 0) {
+    for (int s = 0; s < kGatherStages; ++s)
+      mbar_init(&full[s], 1);
+    mbar_fence_init();
+  }
+  __syncwarp();
+
+  const int64_t my_tiles = (num_tiles - blockIdx.x + gridDim.x - 1) / gridDim.x;
+
+  auto issue = [&](int64_t k) {
+    const int64_t tile = blockIdx.x + k * gridDim.x;
+    const int stage = (int)(k % kGatherStages);
+    const int64_t a = tile / tiles_per_a;
+    const int64_t ob0 = (tile - a * tiles_per_a) * rows_per_tile;
+    const int nrows = (int)min((int64_t)rows_per_tile, OB - ob0);
+    unsigned char *dst = smem + (size_t)stage * stage_bytes;
+    const char *src = in + (size_t)a * IB * row_bytes;
+    int64_t my_idx[kGatherMaxRowsPerTile / 32];
+    int valid = 0;
+#pragma unroll
+    for (int u = 0; u < kGatherMaxRowsPerTile / 32; ++u) {
+      const int r = lane + 32 * u;
+      int64_t i = -1;
+      if (r < nrows) {
+        i = (int64_t)idx[ob0 + r];
+        if (i < 0 || i >= IB)
+          i = -1;
+        else
+          ++valid;
+      }
+      my_idx[u] = i;
+    }
+    valid = __reduce_add_sync(0xffffffffu, valid);
+    if (lane == 0)
+      mbar_arrive_expect_tx(&full[stage], (uint32_t)valid * row_bytes);
+    __syncwarp();
+    bool zero_filled = false;
+#pragma unroll
+    for (int u = 0; u < kGatherMaxRowsPerTile / 32; ++u) {
+      const int r = lane + 32 * u;
+      if (r >= nrows)
+        continue;
+      if (my_idx[u] >= 0) {
+        bulk_g2s(dst + (size_t)r * row_bytes, src + (size_t)my_idx[u] * row_bytes, row_bytes,
+                 &full[stage]);
+      } else {
+        uint4 *z = reinterpret_cast<uint4 *>(dst + (size_t)r * row_bytes);
+        for (uint32_t b = 0; b < row_bytes / 16; ++b)
+          z[b] = make_uint4(0, 0, 0, 0);
+        zero_filled = true;
+        if (status)
+          *status = 1;
+      }
+    }
+    if (zero_filled)
+      fence_proxy_async_smem();
+  };
+
+  const int prologue = (int)min((int64_t)(kGatherStages - 1), my_tiles);
+  for (int k = 0; k < prologue; ++k)
+    issue(k);
+
+  for (int64_t k = 0; k < my_tiles; ++k) {
+    const int stage = (int)(k % kGatherStages);
+    const uint32_t parity = (uint32_t)((k / kGatherStages) & 1);
+    if (!__all_sync(0xffffffffu, mbar_wait(&full[stage], parity))) {
+      if (status)
+        *status = 2; // a copy never arrived: give up instead of spinning
+      break;
+    }
+    if (lane == 0) {
+      const int64_t tile = blockIdx.x + k * gridDim.x;
+      const int64_t a = tile / tiles_per_a;
+      const int64_t ob0 = (tile - a * tiles_per_a) * rows_per_tile;
+      const int nrows = (int)min((int64_t)rows_per_tile, OB - ob0);
+      bulk_s2g(out + ((size_t)a * OB + ob0) * row_bytes, smem + (size_t)stage * stage_bytes,
+               (uint32_t)nrows * row_bytes);
+      bulk_commit();
+    }
+    if (k + kGatherStages - 1 < my_tiles) {
+      // the stage to refill was last read by the store of tile k - 1
+      if (lane == 0)
+        bulk_wait_read<1>();
+      __syncwarp();
+      issue(k + kGatherStages - 1);
+    }
+  }
+  if (lane == 0)
+    bulk_wait_all<0>();
+}
+
+// Vector gather for any row size: V is the widest type that divides a row.
+template <typename V, typename IdxT>
+__global__ void __launch_bounds__(256)
+    gather_generic_kernel(const V *__restrict__ in, const IdxT *__restrict__ idx,
+                          V *__restrict__ out, int64_t A, int64_t IB, int64_t OB, int64_t vpr,
+                          int tx_log2, int *status) {
+  const int TX = 1 << tx_log2, TY = 256 >> tx_log2;
+  const int tx = threadIdx.x & (TX - 1), ty = threadIdx.x >> tx_log2;
+  constexpr int U = 4;
+  for (int64_t a = blockIdx.y; a < A; a += gridDim.y) {
+    const V *src = in + a * IB * vpr;
+    V *dst = out + a * OB * vpr;
+    for (int64_t ob0 = (int64_t)blockIdx.x * TY * U; ob0 < OB; ob0 += (int64_t)gridDim.x * TY * U) {
+      int64_t row[U];
+      bool live[U];
+#pragma unroll
+      for (int u = 0; u < U; ++u) {
+        const int64_t ob = ob0 + u * TY + ty;
+        live[u] = ob < OB;
+        row[u] = live[u] ? (int64_t)idx[ob] : 0;
+        if (live[u] && (row[u] < 0 || row[u] >= IB)) {
+          row[u] = -1;
+          if (status && tx == 0)
+            *status = 1;
+        }
+      }
+      for (int64_t v = tx; v < vpr; v += TX) {
+        V val[U];
+#pragma unroll
+        for (int u = 0; u < U; ++u) {
+          val[u] = V{};
+          if (live[u] && row[u] >= 0)
+            val[u] = src[row[u] * vpr + v];
+        }
+#pragma unroll
+        for (int u = 0; u < U; ++u)
+          if (live[u])
+            dst[(ob0 + u * TY + ty) * vpr + v] = val[u];
+      }
+    }
+  }
+}
+
+template <typename V, typename IdxT>
+int launch_gather_generic(const void *in, const void *idx, void *out, int64_t A, int64_t IB,
+                          int64_t OB, int64_t row_bytes, int *status, cudaStream_t stream) {
+  const int64_t vpr = row_bytes / (int64_t)sizeof(V);
+  int tx_log2 = 0;
+  while ((1 << tx_log2) < vpr && tx_log2 < 8)
+    ++tx_log2;
+  const int TY = 256 >> tx_log2;
+  const int64_t row_blocks = ceil_div<int64_t>(OB, (int64_t)TY * 4);
+  dim3 grid((unsigned)std::min<int64_t>(row_blocks, 1 << 20), (unsigned)std::min<int64_t>(A, 65535));
+  gather_generic_kernel<V, IdxT><<<grid, 256, 0, stream>>>((const V *)in, (const IdxT *)idx, (V *)out,
+                                                           A, IB, OB, vpr, tx_log2, status);
+  return check_launch();
+}
+
+template <typename IdxT>
+int launch_gather(int path, const void *in, const void *idx, void *out, int64_t A, int64_t IB,
+                  int64_t OB, int64_t row_bytes, int *status, cudaStream_t stream) {
+  const bool bulk_ok = row_bytes % 16 == 0 && aligned16(in) && aligned16(out) && row_bytes <= 49152;
+  if (path == 1 && !bulk_ok)
+    return B200_ERR_ALIGNMENT;
+  if ((path == 0 && bulk_ok && row_bytes >= 64) || path == 1) {
+    int rows_per_tile =
+        (int)std::max<int64_t>(1, std::min<int64_t>(kGatherMaxRowsPerTile, 16384 / row_bytes));
+    rows_per_tile = (int)std::min<int64_t>(rows_per_tile, OB);
+    const int64_t tiles_per_a = ceil_div<int64_t>(OB, rows_per_tile);
+    const int64_t num_tiles = tiles_per_a * A;
+    const size_t smem = (size_t)kGatherStages * rows_per_tile * row_bytes;
+    static bool attr_set[2] = {false, false};
+    constexpr int which = sizeof(IdxT) == 8 ? 1 : 0;
+    if (!attr_set[which]) {
+      if (int rc = check_cuda(cudaFuncSetAttribute(gather_rows_bulk_kernel<IdxT>,
+                                                   cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                                   kGatherStages * 49152)))
+        return rc;
+      attr_set[which] = true;
+    }
+    const int ctas_per_sm = (int)std::max<size_t>(1, std::min<size_t>(8, (200 * 1024) / (smem + 1024)));
+    const unsigned grid = (unsigned)std::min<int64_t>(num_tiles, (int64_t)kNumSMs * ctas_per_sm);
+    gather_rows_bulk_kernel<IdxT><<<grid, 32, smem, stream>>>(
+        (const char *)in, (const IdxT *)idx, (char *)out, IB, OB, (uint32_t)row_bytes, rows_per_tile,
+        tiles_per_a, num_tiles, status);
+    return check_launch();
+  }
+  const uintptr_t both = reinterpret_cast<uintptr_t>(in) | reinterpret_cast<uintptr_t>(out) |
+                         (uintptr_t)row_bytes;
+  if (both % 16 == 0)
+    return launch_gather_generic<uint4, IdxT>(in, idx, out, A, IB, OB, row_bytes, status, stream);
+  if (both % 8 == 0)
+    return launch_gather_generic<uint2, IdxT>(in, idx, out, A, IB, OB, row_bytes, status, stream);
+  if (both % 4 == 0)
+    return launch_gather_generic<uint32_t, IdxT>(in, idx, out, A, IB, OB, row_bytes, status, stream);
+  if (both % 2 == 0)
+    return launch_gather_generic<uint16_t, IdxT>(in, idx, out, A, IB, OB, row_bytes, status, stream);
+  return launch_gather_generic<uint8_t, IdxT>(in, idx, out, A, IB, OB, row_bytes, status, stream);
+}
+
+// =============================================================================
+// scatter-add
+// =============================================================================
+constexpr int kRadixBits = 8;
+constexpr int kRadix = 1 << kRadixBits;
+constexpr int kSortTile = 2048; // keys per block: 8 warps x 8 rounds x 32 lanes
+constexpr int kChunk = 32;      // sorted entries per warp in the accumulate pass
+
+__device__ __forceinline__ uint32_t key_of_index(int64_t i, int64_t rows, int *status) {
+  if (i < 0 || i >= rows) {
+    if (status)
+      *status = 1;
+    return (uint32_t)rows; // sorts after every valid row, skipped later
+  }
+  return (uint32_t)i;
+}
+
+// per-block digit histogram; the first pass also turns int64 indices into keys
+template <bool FIRST>
+__global__ void __launch_bounds__(256)
+    radix_hist_kernel(const int64_t *__restrict__ idx, const uint32_t *__restrict__ keys_in,
+                      uint32_t *__restrict__ keys_first, uint32_t *__restrict__ block_hist, int64_t n,
+                      int64_t rows, int shift, int nblocks, int *status, uint32_t *leader_count) {
+  __shared__ uint32_t hist[kRadix];
+  if (FIRST && blockIdx.x == 0 && threadIdx.x == 0) {
+    leader_count[0] = 0; // work-list counters of the accumulate passes, which run
+    leader_count[1] = 0; // after the whole sort
+  }
+  hist[threadIdx.x] = 0;
+  __syncthreads();
+  const int64_t base = (int64_t)blockIdx.x * kSortTile;
+  for (int k = 0; k < kSortTile / 256; ++k) {
+    const int64_t i = base + k * 256 + threadIdx.x;
+    if (i < n) {
+      uint32_t key;
+      if (FIRST) {
+        key = key_of_index(idx[i], rows, status);
+        keys_first[i] = key;
+      } else {
+        key = keys_in[i];
+      }
+      atomicAdd(&hist[(key >> shift) & (kRadix - 1)], 1u);
+    }
+  }
+  __syncthreads();
+  block_hist[(size_t)threadIdx.x * nblocks + blockIdx.x] = hist[threadIdx.x];
+}
+
+// exclusive scan of the (digit-major, block-minor) histogram, one block;
+// m is a multiple of 4 (256 digits x blocks), 4096 entries per sweep
+__global__ void __launch_bounds__(1024) radix_scan_kernel(uint32_t *__restrict__ hist, int64_t m) {
+  __shared__ uint32_t warp_sums[32];
+  __shared__ uint32_t sweep_total;
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  uint32_t carry = 0;
+  for (int64_t base = 0; base < m; base += 4096) {
+    const int64_t i = base + (int64_t)threadIdx.x * 4;
+    uint4 v = make_uint4(0, 0, 0, 0);
+    if (i < m)
+      v = *reinterpret_cast<const uint4 *>(hist + i);
+    const uint32_t local = v.x + v.y + v.z + v.w;
+    uint32_t incl = local;
+    for (int off = 1; off < 32; off <<= 1) {
+      const uint32_t u = __shfl_up_sync(0xffffffffu, incl, off);
+      if (lane >= off)
+        incl += u;
+    }
+    if (lane == 31)
+      warp_sums[warp] = incl;
+    __syncthreads();
+    if (warp == 0) {
+      const uint32_t w = warp_sums[lane];
+      uint32_t wi = w;
+      for (int off = 1; off < 32; off <<= 1) {
+        const uint32_t u = __shfl_up_sync(0xffffffffu, wi, off);
+        if (lane >= off)
+          wi += u;
+      }
+      warp_sums[lane] = wi - w;
+      if (lane == 31)
+        sweep_total = wi;
+    }
+    __syncthreads();
+    uint32_t run = carry + warp_sums[warp] + incl - local;
+    if (i < m) {
+      uint4 o;
+      o.x = run;
+      o.y = run + v.x;
+      o.z = o.y + v.y;
+      o.w = o.z + v.z;
+      *reinterpret_cast<uint4 *>(hist + i) = o;
+    }
+    carry += sweep_total;
+    __syncthreads();
+  }
+}
+
+// stable scatter of one digit
+template <bool FIRST>
+__global__ void __launch_bounds__(256)
+    radix_scatter_kernel(const uint32_t *__restrict__ keys_in, const uint32_t *__restrict__ vals_in,
+                         uint32_t *__restrict__ keys_out, uint32_t *__restrict__ vals_out,
+                         const uint32_t *__restrict__ block_hist, int64_t n, int shift, int nblocks) {
+  __shared__ uint32_t whist[8][kRadix];
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  for (int i = threadIdx.x; i < 8 * kRadix; i += 256)
+    (&whist[0][0])[i] = 0;
+  __syncthreads();
+  const int64_t base = (int64_t)blockIdx.x * kSortTile + warp * 256;
+  uint32_t key[8], val[8], rank[8];
+  const uint32_t lt = (1u << lane) - 1u;
+#pragma unroll
+  for (int r = 0; r < 8; ++r) {
+    const int64_t i = base + r * 32 + lane;
+    const bool ok = i < n;
+    key[r] = ok ? keys_in[i] : 0u;
+    val[r] = ok ? (FIRST ? (uint32_t)i : vals_in[i]) : 0u;
+    const uint32_t d = ok ? ((key[r] >> shift) & (kRadix - 1)) : 0xffffffffu;
+    const uint32_t peers = __match_any_sync(0xffffffffu, d);
+    uint32_t prefix = 0;
+    if (ok)
+      prefix = whist[warp][d];
+    __syncwarp();
+    if (ok && (peers & lt) == 0)
+      whist[warp][d] = prefix + __popc(peers);
+    __syncwarp();
+    rank[r] = prefix + __popc(peers & lt);
+  }
+  __syncthreads();
+  {
+    const int d = threadIdx.x;
+    uint32_t run = block_hist[(size_t)d * nblocks + blockIdx.x];
+#pragma unroll
+    for (int w = 0; w < 8; ++w) {
+      const uint32_t c = whist[w][d];
+      whist[w][d] = run;
+      run += c;
+    }
+  }
+  __syncthreads();
+#pragma unroll
+  for (int r = 0; r < 8; ++r) {
+    const int64_t i = base + r * 32 + lane;
+    if (i < n) {
+      const uint32_t d = (key[r] >> shift) & (kRadix - 1);
+      const uint32_t dst = whist[warp][d] + rank[r];
+      keys_out[dst] = key[r];
+      vals_out[dst] = val[r];
+    }
+  }
+}
+
+__global__ void __launch_bounds__(256)
+    copy_table_kernel(const uint4 *__restrict__ in, uint4 *__restrict__ out, int64_t nvec) {
+  int64_t i = (int64_t)blockIdx.x * 256 * 4 + threadIdx.x;
+  if (i + 3 * 256 < nvec) {
+    uint4 a = ld_nc_v4(in + i), b = ld_nc_v4(in + i + 256), c = ld_nc_v4(in + i + 512),
+          d = ld_nc_v4(in + i + 768);
+    st_cs_v4(out + i, a), st_cs_v4(out + i + 256, b), st_cs_v4(out + i + 512, c),
+        st_cs_v4(out + i + 768, d);
+  } else {
+    for (int k = 0; k < 4; ++k, i += 256)
+      if (i < nvec)
+        out[i] = in[i];
+  }
+}
+
+// ---- accumulate pass --------------------------------------------------------
+// LV = elements per lane per feature tile (a lane loads LV * sizeof(T) bytes).
+template <typename T, int LV> struct LaneVec {
+  T v[LV];
+};
+
+template <typename T, int LV> struct LaneRaw {
+  using type = typename std::conditional<
+      LV * sizeof(T) == 16, uint4,
+      typename std::conditional<LV * sizeof(T) == 8, uint2,
+                                typename std::conditional<LV * sizeof(T) == 4, uint32_t, uint16_t>::type>::type>::type;
+};
+template <typename T, int LV>
+__device__ __forceinline__ typename LaneRaw<T, LV>::type load_raw(const T *p) {
+  return *reinterpret_cast<const typename LaneRaw<T, LV>::type *>(p);
+}
+template <typename T, int LV>
+__device__ __forceinline__ void unpack_raw(const typename LaneRaw<T, LV>::type &raw, float (&f)[LV]) {
+  const T *e = reinterpret_cast<const T *>(&raw);
+#pragma unroll
+  for (int j = 0; j < LV; ++j)
+    f[j] = Elt<T>::to_f32(e[j]);
+}
+
+template <typename T, int LV>
+__device__ __forceinline__ void load_lane(const T *p, float (&f)[LV]) {
+  using Raw = typename std::conditional<
+      LV * sizeof(T) == 16, uint4,
+      typename std::conditional<LV * sizeof(T) == 8, uint2,
+                                typename std::conditional<LV * sizeof(T) == 4, uint32_t, uint16_t>::type>::type>::type;
+  Raw raw = *reinterpret_cast<const Raw *>(p);
+  const T *e = reinterpret_cast<const T *>(&raw);
+#pragma unroll
+  for (int j = 0; j < LV; ++j)
+    f[j] = Elt<T>::to_f32(e[j]);
+}
+
+template <typename T, int LV>
+__device__ __forceinline__ void store_lane(T *p, const float (&f)[LV]) {
+  using Raw = typename std::conditional<
+      LV * sizeof(T) == 16, uint4,
+      typename std::conditional<LV * sizeof(T) == 8, uint2,
+                                typename std::conditional<LV * sizeof(T) == 4, uint32_t, uint16_t>::type>::type>::type;
+  Raw raw;
+  T *e = reinterpret_cast<T *>(&raw);
+#pragma unroll
+  for (int j = 0; j < LV; ++j)
+    e[j] = Elt<T>::from_f32(f[j]);
+  *reinterpret_cast<Raw *>(p) = raw;
+}
+
+// One warp per chunk of kChunk sorted entries.  part: [nchunks][2][feature] f32.
+// Entries are handled 8 at a time: the 8 update rows, and the table rows of the
+// runs that end (and are complete) inside those 8 entries, are all loaded before
+// any of them is used, so a warp keeps up to 16 row loads in flight.
+template <typename T, int LV>
+__global__ void __launch_bounds__(256)
+    scatter_chunk_kernel(const T *in, const T *__restrict__ upd, T *out,
+                         const uint32_t *__restrict__ keys, const uint32_t *__restrict__ vals,
+                         float *__restrict__ part, uint32_t *__restrict__ leaders, int64_t n,
+                         int64_t rows, int64_t feature) {
+  const int lane = threadIdx.x & 31;
+  const int64_t chunk = (int64_t)blockIdx.x * 8 + (threadIdx.x >> 5);
+  const int64_t e0 = chunk * kChunk;
+  if (e0 >= n)
+    return;
+  const int cnt = (int)min((int64_t)kChunk, n - e0);
+  const uint32_t invalid = (uint32_t)rows;
+  const uint32_t my_key = lane < cnt ? keys[e0 + lane] : 0xffffffffu;
+  const uint32_t my_pos = lane < cnt ? vals[e0 + lane] : 0u;
+  const uint32_t prev_key = e0 > 0 ? keys[e0 - 1] : 0xffffffffu;
+  const uint32_t next_key = e0 + kChunk < n ? keys[e0 + kChunk] : 0xffffffffu;
+  const uint32_t first_key = __shfl_sync(0xffffffffu, my_key, 0);
+  const uint32_t last_key = __shfl_sync(0xffffffffu, my_key, cnt - 1);
+  // per entry: does a run end here, and is that run complete inside this chunk?
+  const uint32_t key_after = __shfl_down_sync(0xffffffffu, my_key, 1);
+  const bool my_end = lane < cnt && (lane == cnt - 1 || key_after != my_key);
+  const bool my_open = (my_key == first_key && first_key == prev_key) ||
+                       (my_key == last_key && last_key == next_key);
+  const uint32_t end_mask = __ballot_sync(0xffffffffu, my_end);
+  const uint32_t closed_mask = __ballot_sync(0xffffffffu, my_end && !my_open && my_key != invalid);
+  float *part0 = part + (size_t)chunk * 2 * feature;
+  float *part1 = part0 + feature;
+  // a run that starts in this chunk and continues into the next one is finished by
+  // the span pass: put this chunk on its work list
+  if (lane == 0 && last_key != invalid && last_key == next_key &&
+      !(first_key == last_key && first_key == prev_key))
+    leaders[64 + atomicAdd(&leaders[0], 1u)] = (uint32_t)chunk;
+
+  // uniform over the warp (it contains shuffles); lanes past the end of a short
+  // row only skip their loads and stores
+  for (int64_t fbase = 0; fbase < feature; fbase += 32 * LV) {
+    const int64_t f0 = fbase + (int64_t)lane * LV;
+    const bool lane_on = f0 < feature;
+    float acc[LV];
+#pragma unroll
+    for (int j = 0; j < LV; ++j)
+      acc[j] = 0.f;
+    for (int i0 = 0; i0 < cnt; i0 += 8) {
+      // raw 16-bit/32-bit lanes stay packed until they are used: fewer registers,
+      // more warps per SM, more loads in flight
+      typename LaneRaw<T, LV>::type x[8], base[8];
+      uint32_t k[8];
+#pragma unroll
+      for (int u = 0; u < 8; ++u) {
+        const int i = i0 + u;
+        k[u] = __shfl_sync(0xffffffffu, my_key, i & 31);
+        const uint32_t pos = __shfl_sync(0xffffffffu, my_pos, i & 31);
+        const bool live = i < cnt && k[u] != invalid && lane_on;
+        x[u] = typename LaneRaw<T, LV>::type{};
+        base[u] = typename LaneRaw<T, LV>::type{};
+        if (live)
+          x[u] = load_raw<T, LV>(upd + (size_t)pos * feature + f0);
+        if (live && ((closed_mask >> i) & 1u))
+          base[u] = load_raw<T, LV>(in + (size_t)k[u] * feature + f0);
+      }
+#pragma unroll
+      for (int u = 0; u < 8; ++u) {
+        const int i = i0 + u;
+        if (i >= cnt)
+          break;
+        if (k[u] == invalid || !lane_on)
+          continue;
+        float xf[LV];
+        unpack_raw<T, LV>(x[u], xf);
+#pragma unroll
+        for (int j = 0; j < LV; ++j)
+          acc[j] += xf[j];
+        if ((end_mask >> i) & 1u) {
+          if ((closed_mask >> i) & 1u) {
+            float bf[LV];
+            unpack_raw<T, LV>(base[u], bf);
+#pragma unroll
+            for (int j = 0; j < LV; ++j)
+              bf[j] += acc[j];
+            store_lane<T, LV>(out + (size_t)k[u] * feature + f0, bf);
+          } else {
+            // first run of the chunk -> slot 0, otherwise (last run) -> slot 1
+            float *dst = (k[u] == first_key ? part0 : part1) + f0;
+#pragma unroll
+            for (int j = 0; j < LV; ++j)
+              dst[j] = acc[j];
+          }
+#pragma unroll
+          for (int j = 0; j < LV; ++j)
+            acc[j] = 0.f;
+        }
+      }
+    }
+  }
+}
+
+// Finishes the runs that cross chunk borders; work list written by the chunk pass.
+// leaders[0] = number of entries, leaders[1] = number of long entries (second
+// list, filled here), leaders[64 + i] = chunk where run i starts,
+// leaders[64 + nchunks + i] = long entries.
+//
+// Short pass: one warp per entry.  The lanes probe the next 32 chunks at once; a
+// run that continues into at most 32 chunks is finished by the warp (partials
+// added in chunk order), a longer one is handed to the long pass.
+template <typename T, int LV>
+__global__ void __launch_bounds__(256)
+    scatter_span_short_kernel(const T *in, T *out, const uint32_t *__restrict__ keys,
+                              const float *__restrict__ part, uint32_t *__restrict__ leaders,
+                              int64_t n, int64_t feature) {
+  const int lane = threadIdx.x & 31;
+  const int64_t nchunks = ceil_div<int64_t>(n, kChunk);
+  const uint32_t nlead = leaders[0];
+  const int64_t warps = (int64_t)gridDim.x * 8;
+  for (int64_t l = (int64_t)blockIdx.x * 8 + (threadIdx.x >> 5); l < nlead; l += warps) {
+    const int64_t chunk = leaders[64 + l];
+    const int64_t e0 = chunk * kChunk;
+    const uint32_t key = keys[min(n, e0 + kChunk) - 1];
+    const int first_slot = keys[e0] == key ? 0 : 1;
+    const int64_t probe = chunk + 1 + lane;
+    const unsigned hits = __ballot_sync(0xffffffffu, probe < nchunks && keys[probe * kChunk] == key);
+    if (hits == 0xffffffffu) { // may go on beyond 32 chunks
+      if (lane == 0)
+        leaders[64 + nchunks + atomicAdd(&leaders[1], 1u)] = (uint32_t)chunk;
+      continue;
+    }
+    const int extra = __popc(hits); // keys are sorted: the hits are the low bits
+    for (int64_t fbase = 0; fbase < feature; fbase += 32 * LV) {
+      const int64_t f0 = fbase + (int64_t)lane * LV;
+      if (f0 >= feature)
+        continue;
+      float base[LV], sum[LV];
+      load_lane<T, LV>(in + (size_t)key * feature + f0, base);
+      const float *p = part + ((size_t)chunk * 2 + first_slot) * feature + f0;
+#pragma unroll
+      for (int j = 0; j < LV; ++j)
+        sum[j] = p[j];
+      for (int c = 1; c <= extra; ++c) {
+        const float *q = part + (size_t)(chunk + c) * 2 * feature + f0;
+#pragma unroll
+        for (int j = 0; j < LV; ++j)
+          sum[j] += q[j];
+      }
+#pragma unroll
+      for (int j = 0; j < LV; ++j)
+        base[j] += sum[j];
+      store_lane<T, LV>(out + (size_t)key * feature + f0, base);
+    }
+  }
+}
+
+// Long pass: blocks of 32 warps walk over the long entries.  The block counts how
+// many following chunks the run continues into, each warp adds the slot-0 partials
+// of a contiguous slice of those chunks, and warp 0 adds the 32 slice sums in
+// order to the run's own partial and the table row.  Which block handles which
+// entry does not affect the result.
+template <typename T, int LV>
+__global__ void __launch_bounds__(1024)
+    scatter_span_long_kernel(const T *in, T *out, const uint32_t *__restrict__ keys,
+                             const float *__restrict__ part, const uint32_t *__restrict__ leaders,
+                             int64_t n, int64_t feature) {
+  __shared__ float sm[32][32 * LV];
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  const int64_t nchunks = ceil_div<int64_t>(n, kChunk);
+  const uint32_t nlead = leaders[1];
+  for (uint32_t l = blockIdx.x; l < nlead; l += gridDim.x) {
+    const int64_t chunk = leaders[64 + nchunks + l];
+    const int64_t e0 = chunk * kChunk;
+    const uint32_t key = keys[min(n, e0 + kChunk) - 1];
+    const int first_slot = keys[e0] == key ? 0 : 1;
+    // number of following chunks that start with this key (keys are sorted, so
+    // the predicate is monotone over the chunks)
+    int64_t extra = 0;
+    for (int64_t c = chunk + 1; c < nchunks; c += 1024) {
+      const int64_t mine = c + threadIdx.x;
+      const int hit = __syncthreads_count(mine < nchunks && keys[mine * kChunk] == key);
+      extra += hit;
+      if (hit < 1024)
+        break;
+    }
+    const int64_t per = ceil_div<int64_t>(extra, 32);
+    const int64_t c0 = chunk + 1 + warp * per;
+    const int64_t c1 = min(chunk + 1 + extra, c0 + per);
+    for (int64_t fbase = 0; fbase < feature; fbase += 32 * LV) {
+      const int64_t f0 = fbase + (int64_t)lane * LV;
+      const bool lane_on = f0 < feature;
+      float total[LV];
+#pragma unroll
+      for (int j = 0; j < LV; ++j)
+        total[j] = 0.f;
+      if (lane_on) {
+        int64_t c = c0;
+        for (; c + 3 < c1; c += 4) {
+          float q[4][LV];
+#pragma unroll
+          for (int u = 0; u < 4; ++u) {
+            const float *p = part + (size_t)(c + u) * 2 * feature + f0;
+#pragma unroll
+            for (int j = 0; j < LV; ++j)
+              q[u][j] = p[j];
+          }
+#pragma unroll
+          for (int u = 0; u < 4; ++u)
+#pragma unroll
+            for (int j = 0; j < LV; ++j)
+              total[j] += q[u][j];
+        }
+        for (; c < c1; ++c) {
+          const float *p = part + (size_t)c * 2 * feature + f0;
+#pragma unroll
+          for (int j = 0; j < LV; ++j)
+            total[j] += p[j];
+        }
+      }
+#pragma unroll
+      for (int j = 0; j < LV; ++j)
+        sm[warp][lane * LV + j] = total[j];
+      __syncthreads();
+      if (warp == 0 && lane_on) {
+        float base[LV], sum[LV];
+        load_lane<T, LV>(in + (size_t)key * feature + f0, base);
+        const float *p = part + ((size_t)chunk * 2 + first_slot) * feature + f0;
+#pragma unroll
+        for (int j = 0; j < LV; ++j)
+          sum[j] = p[j];
+        for (int w = 0; w < 32; ++w)
+#pragma unroll
+          for (int j = 0; j < LV; ++j)
+            sum[j] += sm[w][lane * LV + j];
+#pragma unroll
+        for (int j = 0; j < LV; ++j)
+          base[j] += sum[j];
+        store_lane<T, LV>(out + (size_t)key * feature + f0, base);
+      }
+      __syncthreads();
+    }
+  }
+}
+
+struct ScatterPlan {
+  int64_t nblocks, nchunks;
+  int passes;
+  size_t off_keys[2], off_vals[2], off_hist, off_part, off_leaders, total;
+};
+
+inline size_t align256(size_t v) { return (v + 255) & ~(size_t)255; }
+
+ScatterPlan make_scatter_plan(int64_t rows, int64_t n, int64_t feature) {
+  ScatterPlan p{};
+  p.nblocks = ceil_div<int64_t>(n, kSortTile);
+  p.nchunks = ceil_div<int64_t>(n, kChunk);
+  int bits = 1;
+  while (bits < 32 && ((uint64_t)rows >> bits) != 0)
+    ++bits;
+  p.passes = (bits + kRadixBits - 1) / kRadixBits;
+  size_t off = 0;
+  for (int i = 0; i < 2; ++i) {
+    p.off_keys[i] = off;
+    off += align256((size_t)n * 4);
+    p.off_vals[i] = off;
+    off += align256((size_t)n * 4);
+  }
+  p.off_hist = off;
+  off += align256((size_t)kRadix * p.nblocks * 4);
+  p.off_part = off;
+  off += align256((size_t)p.nchunks * 2 * feature * 4);
+  p.off_leaders = off; // two counters, then two lists of chunk ids (see the span kernels)
+  off += align256((size_t)(64 + 2 * p.nchunks) * 4);
+  p.total = off;
+  return p;
+}
+
+template <typename T, int LV>
+int launch_scatter_tail(const T *in, const T *upd, T *out, const uint32_t *keys, const uint32_t *vals,
+                        float *part, uint32_t *leaders, int64_t n, int64_t rows, int64_t feature,
+                        cudaStream_t stream) {
+  const int64_t nchunks = ceil_div<int64_t>(n, kChunk);
+  scatter_chunk_kernel<T, LV><<<(unsigned)ceil_div<int64_t>(nchunks, 8), 256, 0, stream>>>(
+      in, upd, out, keys, vals, part, leaders, n, rows, feature);
+  if (int rc = check_launch())
+    return rc;
+  const unsigned short_grid = (unsigned)std::min<int64_t>(ceil_div<int64_t>(nchunks, 8), kNumSMs * 8);
+  scatter_span_short_kernel<T, LV><<<short_grid, 256, 0, stream>>>(in, out, keys, part, leaders, n, feature);
+  if (int rc = check_launch())
+    return rc;
+  const unsigned long_grid = (unsigned)std::min<int64_t>(ceil_div<int64_t>(nchunks, 32), kNumSMs);
+  scatter_span_long_kernel<T, LV><<<long_grid, 1024, 0, stream>>>(in, out, keys, part, leaders, n, feature);
+  return check_launch();
+}
+
+// The index sort does not depend on the table copy, so the two run side by side:
+// the sort is forked onto a helper stream and joined before the accumulate pass.
+// One helper stream (and its two events) is kept per (device, caller stream); they
+// are created the first time that caller stream is seen and live until exit.
+struct SideStream {
+  cudaStream_t stream = nullptr;
+  cudaEvent_t fork = nullptr, join = nullptr;
+};
+
+int get_side_stream(cudaStream_t user, SideStream *out) {
+  static std::mutex mu;
+  static std::map<std::pair<int, cudaStream_t>, SideStream> pool;
+  int dev = 0;
+  if (int rc = check_cuda(cudaGetDevice(&dev)))
+    return rc;
+  std::lock_guard<std::mutex> lock(mu);
+  auto it = pool.find({dev, user});
+  if (it == pool.end()) {
+    SideStream s;
+    if (int rc = check_cuda(cudaStreamCreateWithFlags(&s.stream, cudaStreamNonBlocking)))
+      return rc;
+    if (int rc = check_cuda(cudaEventCreateWithFlags(&s.fork, cudaEventDisableTiming)))
+      return rc;
+    if (int rc = check_cuda(cudaEventCreateWithFlags(&s.join, cudaEventDisableTiming)))
+      return rc;
+    it = pool.emplace(std::make_pair(dev, user), s).first;
+  }
+  *out = it->second;
+  return B200_OK;
+}
+
+template <typename T>
+int scatter_add(const T *in, const int64_t *idx, const T *upd, T *out, int64_t rows, int64_t n,
+                int64_t feature, void *ws, size_t ws_bytes, int *status, cudaStream_t user_stream) {
+  const size_t table_bytes = (size_t)rows * feature * sizeof(T);
+  const ScatterPlan p = make_scatter_plan(rows, std::max<int64_t>(n, 1), feature);
+  if (n > 0 && (!ws || ws_bytes < p.total))
+    return B200_ERR_WORKSPACE;
+  // fork: the sort runs on the helper stream while the caller's stream copies the table
+  const bool fork = in != out && n > 0 && table_bytes >= (8u << 20);
+  SideStream side;
+  cudaStream_t stream = user_stream; // stream of the sort
+  if (fork) {
+    if (int rc = get_side_stream(user_stream, &side))
+      return rc;
+    if (int rc = check_cuda(cudaEventRecord(side.fork, user_stream)))
+      return rc;
+    if (int rc = check_cuda(cudaStreamWaitEvent(side.stream, side.fork, 0)))
+      return rc;
+    stream = side.stream;
+  }
+  if (in != out) {
+    cudaStream_t stream = user_stream; // the copy always runs on the caller's stream
+    if (table_bytes % 16 == 0 && aligned16(in) && aligned16(out)) {
+      const int64_t nvec = (int64_t)(table_bytes / 16);
+      copy_table_kernel<<<(unsigned)ceil_div<int64_t>(nvec, 1024), 256, 0, stream>>>(
+          (const uint4 *)in, (uint4 *)out, nvec);
+      if (int rc = check_launch())
+        return rc;
+    } else if (int rc = check_cuda(
+                   cudaMemcpyAsync(out, in, table_bytes, cudaMemcpyDeviceToDevice, stream))) {
+      return rc;
+    }
+  }
+  if (n == 0)
+    return B200_OK;
+  char *w = static_cast<char *>(ws);
+  uint32_t *keys[2] = {(uint32_t *)(w + p.off_keys[0]), (uint32_t *)(w + p.off_keys[1])};
+  uint32_t *vals[2] = {(uint32_t *)(w + p.off_vals[0]), (uint32_t *)(w + p.off_vals[1])};
+  uint32_t *hist = (uint32_t *)(w + p.off_hist);
+  float *part = (float *)(w + p.off_part);
+  uint32_t *leaders = (uint32_t *)(w + p.off_leaders);
+  const int nb = (int)p.nblocks;
+  int cur = 0;
+  for (int pass = 0; pass < p.passes; ++pass) {
+    const int shift = pass * kRadixBits;
+    if (pass == 0)
+      radix_hist_kernel<true><<<nb, 256, 0, stream>>>(idx, nullptr, keys[0], hist, n, rows, shift, nb, status, leaders);
+    else
+      radix_hist_kernel<false><<<nb, 256, 0, stream>>>(nullptr, keys[cur], nullptr, hist, n, rows, shift, nb, nullptr, nullptr);
+    radix_scan_kernel<<<1, 1024, 0, stream>>>(hist, (int64_t)kRadix * nb);
+    if (pass == 0)
+      radix_scatter_kernel<true><<<nb, 256, 0, stream>>>(keys[cur], nullptr, keys[cur ^ 1], vals[cur ^ 1], hist, n, shift, nb);
+    else
+      radix_scatter_kernel<false><<<nb, 256, 0, stream>>>(keys[cur], vals[cur], keys[cur ^ 1], vals[cur ^ 1], hist, n, shift, nb);
+    if (int rc = check_launch())
+      return rc;
+    cur ^= 1;
+  }
+  if (fork) { // join: the accumulate pass needs both the sorted list and the copied table
+    if (int rc = check_cuda(cudaEventRecord(side.join, side.stream)))
+      return rc;
+    if (int rc = check_cuda(cudaStreamWaitEvent(user_stream, side.join, 0)))
+      return rc;
+  }
+  stream = user_stream;
+  // lane vector width: as wide as the row and the pointers allow, but keep 32 lanes busy
+  const uintptr_t mis = reinterpret_cast<uintptr_t>(in) | reinterpret_cast<uintptr_t>(out) |
+                        reinterpret_cast<uintptr_t>(upd) | (uintptr_t)(feature * sizeof(T));
+  int lane_bytes = 16;
+  while (lane_bytes > (int)sizeof(T) && (mis % lane_bytes != 0 || feature * (int64_t)sizeof(T) < 32LL * lane_bytes))
+    lane_bytes >>= 1;
+  const int lv = lane_bytes / (int)sizeof(T);
+  switch (lv) {
+  case 8:
+    if constexpr (sizeof(T) == 2)
+      return launch_scatter_tail<T, 8>(in, upd, out, keys[cur], vals[cur], part, leaders, n, rows, feature, stream);
+    return B200_ERR_UNSUPPORTED;
+  case 4:
+    return launch_scatter_tail<T, 4>(in, upd, out, keys[cur], vals[cur], part, leaders, n, rows, feature, stream);
+  case 2:
+    return launch_scatter_tail<T, 2>(in, upd, out, keys[cur], vals[cur], part, leaders, n, rows, feature, stream);
+  default:
+    return launch_scatter_tail<T, 1>(in, upd, out, keys[cur], vals[cur], part, leaders, n, rows, feature, stream);
+  }
+}
+
+} // namespace
+} // namespace b200
+
+using namespace b200;
+
+extern "C" int b200_index_select_path(int path, int elt_bytes, int idx_bytes, const void *in,
+                                      const void *idx, void *out, int64_t A, int64_t IB, int64_t OB,
+                                      int64_t C, int *status, cudaStream_t stream) {
+  if (elt_bytes <= 0 || (idx_bytes != 4 && idx_bytes != 8) || A < 0 || IB < 0 || OB < 0 || C < 0)
+    return B200_ERR_INVALID_ARG;
+  if (A == 0 || OB == 0 || C == 0)
+    return B200_OK;
+  if (!in || !idx || !out)
+    return B200_ERR_INVALID_ARG;
+  const int64_t row_bytes = C * elt_bytes;
+  if (idx_bytes == 8)
+    return launch_gather<int64_t>(path, in, idx, out, A, IB, OB, row_bytes, status, stream);
+  return launch_gather<uint32_t>(path, in, idx, out, A, IB, OB, row_bytes, status, stream);
+}
+
+extern "C" int b200_index_select(int elt_bytes, int idx_bytes, const void *in, const void *idx,
+                                 void *out, int64_t A, int64_t IB, int64_t OB, int64_t C, int *status,
+                                 cudaStream_t stream) {
+  return b200_index_select_path(0, elt_bytes, idx_bytes, in, idx, out, A, IB, OB, C, status, stream);
+}
+
+extern "C" size_t b200_index_put_workspace_bytes(int dtype, int64_t rows, int64_t index_count,
+                                                 int64_t feature) {
+  (void)dtype;
+  if (rows <= 0 || index_count <= 0 || feature <= 0)
+    return 0;
+  return make_scatter_plan(rows, index_count, feature).total;
+}
+
+extern "C" int b200_index_put_add(int dtype, const void *in, const int64_t *idx, const void *upd,
+                                  void *out, int64_t rows, int64_t index_count, int64_t feature,
+                                  void *workspace, size_t workspace_bytes, int *status,
+                                  cudaStream_t stream) {
+  if (rows < 0 || index_count < 0 || feature < 0 || rows >= 0xffffffffLL ||
+      index_count >= 0xffffffffLL)
+    return B200_ERR_INVALID_ARG;
+  if (rows == 0 || feature == 0)
+    return B200_OK;
+  if (!in || !out || (index_count > 0 && (!idx || !upd)))
+    return B200_ERR_INVALID_ARG;
+  switch (dtype) {
+  case B200_F32:
+    return scatter_add<float>((const float *)in, idx, (const float *)upd, (float *)out, rows,
+                              index_count, feature, workspace, workspace_bytes, status, stream);
+  case B200_F16:
+    return scatter_add<__half>((const __half *)in, idx, (const __half *)upd, (__half *)out, rows,
+                               index_count, feature, workspace, workspace_bytes, status, stream);
+  case B200_BF16:
+    return scatter_add<__nv_bfloat16>((const __nv_bfloat16 *)in, idx, (const __nv_bfloat16 *)upd,
+                                      (__nv_bfloat16 *)out, rows, index_count, feature, workspace,
+                                      workspace_bytes, status, stream);
+  default:
+    return B200_ERR_INVALID_ARG;
+  }
+}

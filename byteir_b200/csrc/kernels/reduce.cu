@@ -1,0 +1,742 @@
+// ReduceSumOp / ReduceMaxOp for sm_100a.
+//
+// The tensor is viewed as A x B x C (row-major) and B is reduced, as the
+// reference does (reduction/reduce_impl.h:28-59).  Both shapes of the problem
+// are bound by HBM bandwidth, so every path is built around 128-bit coalesced
+// streaming loads with several loads in flight per thread:
+//
+//   C == 1  ("rows"):    a group of 1..256 threads owns one row (or one segment
+//                        of a long row); warp shuffles, then shared memory,
+//                        combine the group.  Long rows with few rows in total are
+//                        cut into segments: up to 8 segments are combined inside
+//                        one thread-block cluster through distributed shared
+//                        memory (single launch, no workspace); more segments go
+//                        through f32 partials in the workspace and a second pass.
+//   C  > 1  ("columns"): a warp reads one (or several short) contiguous rows of a
+//                        column slab per step, 8 warps stride over the B rows,
+//                        and B is split over enough blocks to fill 148 SMs
+//                        (split-K); the f32 partials of the splits are combined in
+//                        split order by a second pass, so the result does not
+//                        depend on scheduling.
+//
+// Max semantics (reduction_helper.h:159-180 folded in ascending index order):
+// NaN wins; otherwise the largest value; between +0 and -0, which compare equal,
+// the one at the higher index.  The streaming pass uses the hardware max (which
+// ranks -0 below +0); only a result that is exactly zero triggers a short
+// backward scan for the last zero of the range to fix the sign.
+#include <cooperative_groups.h>
+
+#include "common.cuh"
+
+namespace cg = cooperative_groups;
+
+namespace b200 {
+namespace {
+
+constexpr int kSum = B200_REDUCE_SUM;
+constexpr int kMax = B200_REDUCE_MAX;
+constexpr int kBlock = 256;
+
+__device__ __forceinline__ float max_nan_f32(float a, float b) {
+  float r;
+  asm("max.NaN.f32 %0, %1, %2;" : "=f"(r) : "f"(a), "f"(b));
+  return r;
+}
+
+template <int OP> __device__ __forceinline__ float op_init() {
+  return OP == kSum ? 0.f : -INFINITY;
+}
+// order-insensitive combine of two partial results (zero signs fixed up later)
+template <int OP> __device__ __forceinline__ float op_combine(float a, float b) {
+  return OP == kSum ? a + b : max_nan_f32(a, b);
+}
+// the reference's apply(lhs, rhs) with lhs covering the lower indices
+template <int OP> __device__ __forceinline__ float op_apply_ordered(float lhs, float rhs) {
+  if (OP == kSum)
+    return lhs + rhs;
+  return (isnan(lhs) || lhs > rhs) ? lhs : rhs;
+}
+
+// ---- per-thread accumulators over 16-byte vectors --------------------------
+template <typename T, int OP> struct Acc;
+
+template <> struct Acc<float, kSum> {
+  float a = 0.f, b = 0.f;
+  __device__ __forceinline__ void vec(uint4 v) {
+    a += __uint_as_float(v.x);
+    b += __uint_as_float(v.y);
+    a += __uint_as_float(v.z);
+    b += __uint_as_float(v.w);
+  }
+  __device__ __forceinline__ void one(float v) { a += v; }
+  __device__ __forceinline__ float get() const { return a + b; }
+};
+template <> struct Acc<float, kMax> {
+  float m = -INFINITY;
+  __device__ __forceinline__ void vec(uint4 v) {
+    m = max_nan_f32(m, max_nan_f32(max_nan_f32(__uint_as_float(v.x), __uint_as_float(v.y)),
+                                   max_nan_f32(__uint_as_float(v.z), __uint_as_float(v.w))));
+  }
+  __device__ __forceinline__ void one(float v) { m = max_nan_f32(m, v); }
+  __device__ __forceinline__ float get() const { return m; }
+};
+template <> struct Acc<__half, kSum> {
+  float a = 0.f, b = 0.f;
+  __device__ __forceinline__ void word(uint32_t w) {
+    float2 f = __half22float2(*reinterpret_cast<__half2 *>(&w));
+    a += f.x;
+    b += f.y;
+  }
+  __device__ __forceinline__ void vec(uint4 v) {
+    word(v.x), word(v.y), word(v.z), word(v.w);
+  }
+  __device__ __forceinline__ void one(__half v) { a += __half2float(v); }
+  __device__ __forceinline__ float get() const { return a + b; }
+};
+template <> struct Acc<__nv_bfloat16, kSum> {
+  float a = 0.f, b = 0.f;
+  __device__ __forceinline__ void word(uint32_t w) {
+    a += __uint_as_float(w << 16);
+    b += __uint_as_float(w & 0xffff0000u);
+  }
+  __device__ __forceinline__ void vec(uint4 v) {
+    word(v.x), word(v.y), word(v.z), word(v.w);
+  }
+  __device__ __forceinline__ void one(__nv_bfloat16 v) { a += __bfloat162float(v); }
+  __device__ __forceinline__ float get() const { return a + b; }
+};
+template <> struct Acc<__half, kMax> {
+  __half2 m = __half2half2(__ushort_as_half((unsigned short)0xfc00)); // -inf
+  __device__ __forceinline__ void word(uint32_t w) {
+    m = __hmax2_nan(m, *reinterpret_cast<__half2 *>(&w));
+  }
+  __device__ __forceinline__ void vec(uint4 v) {
+    word(v.x), word(v.y), word(v.z), word(v.w);
+  }
+  __device__ __forceinline__ void one(__half v) { m = __hmax2_nan(m, __half2half2(v)); }
+  __device__ __forceinline__ float get() const {
+    return max_nan_f32(__low2float(m), __high2float(m));
+  }
+};
+template <> struct Acc<__nv_bfloat16, kMax> {
+  __nv_bfloat162 m = __bfloat162bfloat162(__ushort_as_bfloat16((unsigned short)0xff80)); // -inf
+  __device__ __forceinline__ void word(uint32_t w) {
+    m = __hmax2_nan(m, *reinterpret_cast<__nv_bfloat162 *>(&w));
+  }
+  __device__ __forceinline__ void vec(uint4 v) {
+    word(v.x), word(v.y), word(v.z), word(v.w);
+  }
+  __device__ __forceinline__ void one(__nv_bfloat16 v) {
+    m = __hmax2_nan(m, __bfloat162bfloat162(v));
+  }
+  __device__ __forceinline__ float get() const {
+    return max_nan_f32(__low2float(m), __high2float(m));
+  }
+};
+
+template <typename OutT> __device__ __forceinline__ void store_out(OutT *p, float v) {
+  *p = Elt<OutT>::from_f32(v);
+}
+
+// =============================================================================
+// rows: C == 1
+// =============================================================================
+// Grid: one group of `tpr` threads per (row, segment); kBlock / tpr groups per
+// block.  kCluster: the `segs` blocks of a row form one cluster (tpr == kBlock).
+template <typename T, int OP, bool VEC, bool kCluster, typename OutT>
+__global__ void __launch_bounds__(kBlock)
+    reduce_rows_kernel(const T *__restrict__ in, OutT *__restrict__ out,
+                       float *__restrict__ partial, int64_t A, int64_t B, int tpr,
+                       int segs, int64_t seg_len) {
+  constexpr int N = 16 / sizeof(T);
+  __shared__ float warp_part[kBlock / 32];
+  __shared__ float cluster_part;
+  pdl_launch_dependents();
+
+  const int groups_per_block = kBlock / tpr;
+  const int64_t g = (int64_t)blockIdx.x * groups_per_block + threadIdx.x / tpr;
+  const int t = threadIdx.x % tpr;
+  const int64_t a = g / segs;
+  const int s = (int)(g % segs);
+  const bool active = a < A;
+  const int64_t e0 = (int64_t)s * seg_len;
+  const int64_t e1 = active ? min(B, e0 + seg_len) : e0;
+  const T *row = in + (active ? a : 0) * B;
+
+  Acc<T, OP> acc;
+  if (VEC) {
+    const uint4 *vp = reinterpret_cast<const uint4 *>(row + e0);
+    const int64_t nvec = (e1 - e0) / N;
+    int64_t v = t;
+    for (; v + 3 * (int64_t)tpr < nvec; v += 4 * (int64_t)tpr) {
+      uint4 x0 = ld_nc_v4(vp + v);
+      uint4 x1 = ld_nc_v4(vp + v + tpr);
+      uint4 x2 = ld_nc_v4(vp + v + 2 * tpr);
+      uint4 x3 = ld_nc_v4(vp + v + 3 * tpr);
+      acc.vec(x0), acc.vec(x1), acc.vec(x2), acc.vec(x3);
+    }
+    for (; v < nvec; v += tpr)
+      acc.vec(ld_nc_v4(vp + v));
+    for (int64_t e = e0 + nvec * N + t; e < e1; e += tpr)
+      acc.one(row[e]);
+  } else {
+    for (int64_t e = e0 + t; e < e1; e += tpr)
+      acc.one(row[e]);
+  }
+  float r = acc.get();
+
+  // combine the group; every thread of the group ends up with the result
+  const int width = tpr < 32 ? tpr : 32;
+  for (int off = width >> 1; off > 0; off >>= 1)
+    r = op_combine<OP>(r, __shfl_xor_sync(0xffffffffu, r, off));
+  if (tpr > 32) {
+    const int warp = threadIdx.x >> 5;
+    if ((threadIdx.x & 31) == 0)
+      warp_part[warp] = r;
+    __syncthreads();
+    const int w0 = (threadIdx.x / tpr) * (tpr >> 5);
+    r = warp_part[w0];
+    for (int w = 1; w < (tpr >> 5); ++w)
+      r = op_combine<OP>(r, warp_part[w0 + w]);
+  }
+
+  // max == 0: the sign is that of the last zero of the range
+  if (OP == kMax && active && r == 0.f) {
+    const int lanes = width; // the first `width` threads of the group scan backwards
+    const unsigned gmask =
+        tpr >= 32 ? 0xffffffffu : (((1u << tpr) - 1u) << ((threadIdx.x & 31) / tpr * tpr));
+    if (t < lanes) {
+      float found = 0.f;
+      for (int64_t hi = e1; hi > e0; hi -= lanes) {
+        const int64_t e = hi - 1 - t;
+        const float v = e >= e0 ? Elt<T>::to_f32(row[e]) : 1.f;
+        const unsigned hit = __ballot_sync(gmask, v == 0.f);
+        if (hit) {
+          // lowest t = highest index
+          const int src = __ffs(hit) - 1;
+          found = __shfl_sync(gmask, v, src);
+          break;
+        }
+      }
+      r = found; // thread t == 0, which writes the result, is one of the scanners
+    }
+  }
+
+  if (kCluster) {
+    cg::cluster_group cluster = cg::this_cluster();
+    if (threadIdx.x == 0)
+      cluster_part = r;
+    cluster.sync();
+    if (cluster.block_rank() == 0 && threadIdx.x == 0) {
+      float total = r;
+      for (int k = 1; k < segs; ++k)
+        total = op_apply_ordered<OP>(total, *cluster.map_shared_rank(&cluster_part, k));
+      store_out(out + a, total);
+    }
+    cluster.sync(); // keep every block's shared memory alive until rank 0 has read it
+    return;
+  }
+  if (active && t == 0) {
+    if (segs == 1)
+      store_out(out + a, r);
+    else
+      partial[a * segs + s] = r;
+  }
+}
+
+// Short rows (a row is at most VPT 16-byte vectors per thread of its group):
+// persistent blocks walk over the rows, and the loads of the next row are issued
+// before the current one is reduced, so that every thread keeps VPT..2*VPT loads
+// in flight across row boundaries.
+template <typename T, int OP, int VPT, typename OutT>
+__global__ void __launch_bounds__(kBlock)
+    reduce_short_rows_kernel(const T *__restrict__ in, OutT *__restrict__ out, int64_t A, int64_t B,
+                             int tpr) {
+  constexpr int N = 16 / sizeof(T);
+  __shared__ float warp_part[2][kBlock / 32];
+  const int groups_per_block = kBlock / tpr;
+  const int t = threadIdx.x % tpr;
+  const int gib = threadIdx.x / tpr;
+  const int nvec = (int)(B / N);
+  const int64_t block_rows = groups_per_block;
+  const int64_t iters = ceil_div<int64_t>(ceil_div<int64_t>(A, block_rows) - blockIdx.x, (int64_t)gridDim.x);
+  const int width = tpr < 32 ? tpr : 32;
+
+  uint4 cur[VPT], nxt[VPT];
+  auto load_row = [&](int64_t a, uint4(&v)[VPT]) {
+    const uint4 *vp = reinterpret_cast<const uint4 *>(in + a * B);
+#pragma unroll
+    for (int k = 0; k < VPT; ++k) {
+      const int idx = t + k * tpr;
+      if (a < A && idx < nvec)
+        v[k] = ld_nc_v4(vp + idx);
+    }
+  };
+  int64_t a = (int64_t)blockIdx.x * block_rows + gib;
+  load_row(a, cur);
+  for (int64_t it = 0; it < iters; ++it) {
+    const int64_t a_next = a + (int64_t)gridDim.x * block_rows;
+    if (it + 1 < iters)
+      load_row(a_next, nxt);
+    const bool active = a < A;
+    Acc<T, OP> acc;
+#pragma unroll
+    for (int k = 0; k < VPT; ++k)
+      if (active && t + k * tpr < nvec)
+        acc.vec(cur[k]);
+    float r = acc.get();
+    for (int off = width >> 1; off > 0; off >>= 1)
+      r = op_combine<OP>(r, __shfl_xor_sync(0xffffffffu, r, off));
+    if (tpr > 32) {
+      float *wp = warp_part[it & 1];
+      if ((threadIdx.x & 31) == 0)
+        wp[threadIdx.x >> 5] = r;
+      __syncthreads();
+      const int w0 = gib * (tpr >> 5);
+      r = wp[w0];
+      for (int w = 1; w < (tpr >> 5); ++w)
+        r = op_combine<OP>(r, wp[w0 + w]);
+    }
+    if (OP == kMax && active && r == 0.f) { // sign of the last zero of the row
+      const unsigned gmask =
+          tpr >= 32 ? 0xffffffffu : (((1u << tpr) - 1u) << ((threadIdx.x & 31) / tpr * tpr));
+      if (t < width) {
+        const T *row = in + a * B;
+        float found = 0.f;
+        for (int64_t hi = B; hi > 0; hi -= width) {
+          const int64_t e = hi - 1 - t;
+          const float v = e >= 0 ? Elt<T>::to_f32(row[e]) : 1.f;
+          const unsigned hit = __ballot_sync(gmask, v == 0.f);
+          if (hit) {
+            found = __shfl_sync(gmask, v, __ffs(hit) - 1);
+            break;
+          }
+        }
+        r = found;
+      }
+    }
+    if (active && t == 0)
+      store_out(out + a, r);
+#pragma unroll
+    for (int k = 0; k < VPT; ++k)
+      cur[k] = nxt[k];
+    a = a_next;
+  }
+}
+
+// =============================================================================
+// columns: C > 1
+// =============================================================================
+// NV = elements per lane per load (16 / sizeof(T) when 16-byte loads are
+// possible, else 1).  A warp covers `rpw = 32 / lpr` rows of a slab of
+// lpr * NV columns per step; 8 warps stride over the rows of this block's split.
+template <typename T, int OP, int NV, typename OutT>
+__global__ void __launch_bounds__(kBlock)
+    reduce_cols_kernel(const T *__restrict__ in, OutT *__restrict__ out, float *__restrict__ partial,
+                       int64_t A, int64_t B, int64_t C, int lpr, int slabs, int splits,
+                       int64_t rows_per_split) {
+  __shared__ float smem[kBlock / 32][32 * NV];
+  pdl_launch_dependents(); // lets the second pass get scheduled; it waits for this grid's end
+
+  const int64_t bid = blockIdx.x;
+  const int slab = (int)(bid % slabs);
+  const int64_t rest = bid / slabs;
+  const int split = (int)(rest % splits);
+  const int64_t a = rest / splits;
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int rpw = 32 / lpr;
+  const int lane_col = lane % lpr, lane_row = lane / lpr;
+  const int64_t slab_col0 = (int64_t)slab * lpr * NV;
+  const int64_t col0 = slab_col0 + (int64_t)lane_col * NV;
+  const bool col_ok = col0 < C; // C % NV == 0, so a lane is all-in or all-out
+  const int64_t r0 = (int64_t)split * rows_per_split;
+  const int64_t r1 = min(B, r0 + rows_per_split);
+  const T *base = in + a * B * C + col0;
+  const int64_t step = (int64_t)(kBlock / 32) * rpw;
+
+  float acc[NV];
+#pragma unroll
+  for (int j = 0; j < NV; ++j)
+    acc[j] = op_init<OP>();
+
+  auto consume = [&](const uint4 &v) {
+    if constexpr (NV == 1) {
+      // unused
+    } else if constexpr (sizeof(T) == 4) {
+      acc[0] = op_combine<OP>(acc[0], __uint_as_float(v.x));
+      acc[1] = op_combine<OP>(acc[1], __uint_as_float(v.y));
+      acc[2] = op_combine<OP>(acc[2], __uint_as_float(v.z));
+      acc[3] = op_combine<OP>(acc[3], __uint_as_float(v.w));
+    } else {
+      const uint32_t w[4] = {v.x, v.y, v.z, v.w};
+#pragma unroll
+      for (int k = 0; k < 4; ++k) {
+        float lo, hi;
+        if constexpr (std::is_same<T, __half>::value) {
+          float2 f = __half22float2(*reinterpret_cast<const __half2 *>(&w[k]));
+          lo = f.x, hi = f.y;
+        } else {
+          lo = __uint_as_float(w[k] << 16);
+          hi = __uint_as_float(w[k] & 0xffff0000u);
+        }
+        acc[2 * k] = op_combine<OP>(acc[2 * k], lo);
+        acc[2 * k + 1] = op_combine<OP>(acc[2 * k + 1], hi);
+      }
+    }
+  };
+
+  if (col_ok) {
+    int64_t r = r0 + (int64_t)warp * rpw + lane_row;
+    if constexpr (NV > 1) {
+      for (; r + 7 * step < r1; r += 8 * step) {
+        uint4 x[8];
+#pragma unroll
+        for (int u = 0; u < 8; ++u)
+          x[u] = ld_nc_v4(base + (r + u * step) * C);
+#pragma unroll
+        for (int u = 0; u < 8; ++u)
+          consume(x[u]);
+      }
+      for (; r + 3 * step < r1; r += 4 * step) {
+        uint4 x0 = ld_nc_v4(base + r * C);
+        uint4 x1 = ld_nc_v4(base + (r + step) * C);
+        uint4 x2 = ld_nc_v4(base + (r + 2 * step) * C);
+        uint4 x3 = ld_nc_v4(base + (r + 3 * step) * C);
+        consume(x0), consume(x1), consume(x2), consume(x3);
+      }
+      for (; r < r1; r += step)
+        consume(ld_nc_v4(base + r * C));
+    } else {
+      for (; r + 3 * step < r1; r += 4 * step) {
+        float x0 = Elt<T>::to_f32(base[r * C]);
+        float x1 = Elt<T>::to_f32(base[(r + step) * C]);
+        float x2 = Elt<T>::to_f32(base[(r + 2 * step) * C]);
+        float x3 = Elt<T>::to_f32(base[(r + 3 * step) * C]);
+        acc[0] = op_combine<OP>(op_combine<OP>(acc[0], x0), op_combine<OP>(x1, op_combine<OP>(x2, x3)));
+      }
+      for (; r < r1; r += step)
+        acc[0] = op_combine<OP>(acc[0], Elt<T>::to_f32(base[r * C]));
+    }
+  }
+  // rows handled by the same warp step
+  for (int off = lpr; off < 32; off <<= 1) {
+#pragma unroll
+    for (int j = 0; j < NV; ++j)
+      acc[j] = op_combine<OP>(acc[j], __shfl_xor_sync(0xffffffffu, acc[j], off));
+  }
+  if (lane_row == 0) {
+#pragma unroll
+    for (int j = 0; j < NV; ++j)
+      smem[warp][lane_col * NV + j] = acc[j];
+  }
+  __syncthreads();
+  const int ncols = lpr * NV;
+  for (int j = threadIdx.x; j < ncols; j += kBlock) {
+    const int64_t col = slab_col0 + j;
+    if (col >= C)
+      continue;
+    float r = smem[0][j];
+#pragma unroll
+    for (int w = 1; w < kBlock / 32; ++w)
+      r = op_combine<OP>(r, smem[w][j]);
+    if (OP == kMax && r == 0.f) { // sign of the last zero in [r0, r1)
+      const T *colp = in + a * B * C + col;
+      for (int64_t rr = r1 - 1; rr >= r0; --rr) {
+        const float v = Elt<T>::to_f32(colp[rr * C]);
+        if (v == 0.f) {
+          r = v;
+          break;
+        }
+      }
+    }
+    if (splits == 1)
+      store_out(out + a * C + col, r);
+    else
+      partial[((int64_t)split * A + a) * C + col] = r;
+  }
+}
+
+// second pass: out[i] = fold over s of partial[i * stride_i + s * stride_s].
+// 32 outputs per block; 8 warps each fold a contiguous slice of the `count`
+// partials, then warp 0 folds the 8 slice results in order.
+template <int OP, typename OutT>
+__global__ void __launch_bounds__(kBlock)
+    reduce_finalize_kernel(const float *__restrict__ partial, OutT *__restrict__ out,
+                           int64_t n, int count, int64_t stride_i, int64_t stride_s) {
+  __shared__ float sm[kBlock / 32][32];
+  pdl_wait(); // the partials come from the kernel launched just before this one
+  const int lane = threadIdx.x & 31, slice = threadIdx.x >> 5;
+  const int64_t i = (int64_t)blockIdx.x * 32 + lane;
+  const int per = (count + kBlock / 32 - 1) / (kBlock / 32);
+  const int s0 = slice * per, s1 = min(count, s0 + per);
+  float r = 0.f;
+  if (i < n && s0 < s1) {
+    const float *p = partial + i * stride_i;
+    r = p[s0 * stride_s];
+    int s = s0 + 1;
+    for (; s + 3 < s1; s += 4) {
+      const float a = p[s * stride_s], b = p[(s + 1) * stride_s], c = p[(s + 2) * stride_s],
+                  d = p[(s + 3) * stride_s];
+      r = op_apply_ordered<OP>(op_apply_ordered<OP>(op_apply_ordered<OP>(op_apply_ordered<OP>(r, a), b), c), d);
+    }
+    for (; s < s1; ++s)
+      r = op_apply_ordered<OP>(r, p[s * stride_s]);
+  }
+  sm[slice][lane] = r;
+  __syncthreads();
+  if (slice == 0 && i < n) {
+    r = sm[0][lane];
+    for (int w = 1; w < kBlock / 32 && w * per < count; ++w)
+      r = op_apply_ordered<OP>(r, sm[w][lane]);
+    store_out(out + i, r);
+  }
+}
+
+template <typename OutT>
+__global__ void __launch_bounds__(kBlock)
+    cast_from_f32_kernel(const float *__restrict__ in, OutT *__restrict__ out, int64_t n) {
+  const int64_t i = (int64_t)blockIdx.x * kBlock + threadIdx.x;
+  if (i < n)
+    out[i] = Elt<OutT>::from_f32(in[i]);
+}
+
+// ---- launch plan: a pure function of the shape -----------------------------
+struct Plan {
+  bool rows;
+  // rows
+  int tpr, segs;
+  int64_t seg_len;
+  bool cluster;
+  // columns
+  int lpr, slabs, splits;
+  int64_t rows_per_split;
+  size_t ws_bytes;
+};
+
+Plan make_plan(int esize, int64_t A, int64_t B, int64_t C, bool vec_cols) {
+  Plan p{};
+  const int N = 16 / esize;
+  if (C == 1) {
+    p.rows = true;
+    const int64_t row_bytes = B * esize;
+    const int64_t target_groups = 4LL * kNumSMs;
+    p.segs = 1;
+    p.seg_len = B;
+    if (A < 2LL * kNumSMs && row_bytes > 32768) {
+      int64_t segs = std::min<int64_t>(ceil_div<int64_t>(row_bytes, 16384),
+                                       ceil_div<int64_t>(target_groups, A));
+      int64_t seg_len = ceil_div<int64_t>(ceil_div<int64_t>(B, segs), N * 4) * (N * 4);
+      segs = ceil_div<int64_t>(B, seg_len);
+      p.segs = (int)segs;
+      p.seg_len = seg_len;
+    }
+    const int64_t vec_per_seg = ceil_div<int64_t>(p.seg_len, N);
+    p.tpr = (int)std::min<int64_t>(kBlock, pow2_ceil(ceil_div<int64_t>(vec_per_seg, 4)));
+    if (p.segs > 1)
+      p.tpr = kBlock;
+    p.cluster = p.segs > 1 && p.segs <= 8;
+    p.ws_bytes = (p.segs > 1 && !p.cluster) ? (size_t)A * p.segs * sizeof(float) : 0;
+  } else {
+    p.rows = false;
+    const int NV = vec_cols ? N : 1;
+    p.lpr = (int)std::min<int64_t>(32, pow2_ceil(ceil_div<int64_t>(C, NV)));
+    p.slabs = (int)ceil_div<int64_t>(C, (int64_t)p.lpr * NV);
+    const int rpw = 32 / p.lpr;
+    const int64_t rows_per_step = (kBlock / 32) * rpw;
+    const int64_t blocks = A * p.slabs;
+    int64_t splits = std::max<int64_t>(1, ceil_div<int64_t>(4LL * kNumSMs, blocks));
+    splits = std::min<int64_t>(splits, std::max<int64_t>(1, B / (rows_per_step * 4)));
+    p.rows_per_split = ceil_div<int64_t>(B, splits);
+    p.splits = (int)ceil_div<int64_t>(B, p.rows_per_split);
+    p.ws_bytes = p.splits > 1 ? (size_t)p.splits * A * C * sizeof(float) : 0;
+  }
+  return p;
+}
+
+// Whether 16-byte loads are possible for the column kernel is a property of the
+// shape (C a multiple of the vector width); a misaligned base pointer falls back
+// to scalar loads inside the same split plan.
+bool cols_vec_by_shape(int esize, int64_t C) { return C % (16 / esize) == 0; }
+
+template <typename T, int OP, typename OutT>
+int launch(const T *in, OutT *out, int64_t A, int64_t B, int64_t C, void *ws,
+           size_t ws_bytes, cudaStream_t stream) {
+  constexpr int N = 16 / sizeof(T);
+  const Plan p = make_plan(sizeof(T), A, B, C, cols_vec_by_shape(sizeof(T), C));
+  if (p.ws_bytes > 0 && (ws == nullptr || ws_bytes < p.ws_bytes))
+    return B200_ERR_WORKSPACE;
+  float *partial = static_cast<float *>(ws);
+  if (p.rows) {
+    const bool vec = aligned16(in) && (B % N == 0);
+    const int groups_per_block = kBlock / p.tpr;
+    const int64_t groups = A * p.segs;
+    const int64_t grid = ceil_div<int64_t>(groups, groups_per_block);
+    if (grid > 0x7fffffffLL)
+      return B200_ERR_UNSUPPORTED;
+    if (p.cluster) {
+      cudaLaunchConfig_t cfg{};
+      cfg.gridDim = dim3((unsigned)grid);
+      cfg.blockDim = dim3(kBlock);
+      cfg.stream = stream;
+      cudaLaunchAttribute attr[1];
+      attr[0].id = cudaLaunchAttributeClusterDimension;
+      attr[0].val.clusterDim.x = p.segs;
+      attr[0].val.clusterDim.y = 1;
+      attr[0].val.clusterDim.z = 1;
+      cfg.attrs = attr;
+      cfg.numAttrs = 1;
+      cudaError_t e;
+      if (vec)
+        e = cudaLaunchKernelEx(&cfg, reduce_rows_kernel<T, OP, true, true, OutT>, in, out,
+                               partial, A, B, p.tpr, p.segs, p.seg_len);
+      else
+        e = cudaLaunchKernelEx(&cfg, reduce_rows_kernel<T, OP, false, true, OutT>, in, out,
+                               partial, A, B, p.tpr, p.segs, p.seg_len);
+      return check_cuda(e);
+    }
+    const int64_t nvec = B / N;
+    if (vec && p.segs == 1 && nvec <= 4LL * p.tpr) {
+      const int vpt = (int)ceil_div<int64_t>(nvec, p.tpr);
+      const int64_t row_blocks = ceil_div<int64_t>(A, groups_per_block);
+      const unsigned pgrid = (unsigned)std::min<int64_t>(row_blocks, (int64_t)kNumSMs * (2048 / kBlock));
+      if (vpt <= 1)
+        reduce_short_rows_kernel<T, OP, 1, OutT><<<pgrid, kBlock, 0, stream>>>(in, out, A, B, p.tpr);
+      else if (vpt == 2)
+        reduce_short_rows_kernel<T, OP, 2, OutT><<<pgrid, kBlock, 0, stream>>>(in, out, A, B, p.tpr);
+      else
+        reduce_short_rows_kernel<T, OP, 4, OutT><<<pgrid, kBlock, 0, stream>>>(in, out, A, B, p.tpr);
+      return check_launch();
+    }
+    if (vec)
+      reduce_rows_kernel<T, OP, true, false, OutT><<<(unsigned)grid, kBlock, 0, stream>>>(
+          in, out, partial, A, B, p.tpr, p.segs, p.seg_len);
+    else
+      reduce_rows_kernel<T, OP, false, false, OutT><<<(unsigned)grid, kBlock, 0, stream>>>(
+          in, out, partial, A, B, p.tpr, p.segs, p.seg_len);
+    if (int rc = check_launch())
+      return rc;
+    if (p.segs > 1) {
+      return launch_pdl(reduce_finalize_kernel<OP, OutT>, dim3((unsigned)ceil_div<int64_t>(A, 32)),
+                        dim3(kBlock), 0, stream, (const float *)partial, out, A, p.segs,
+                        (int64_t)p.segs, (int64_t)1);
+    }
+    return B200_OK;
+  }
+  const bool vec = cols_vec_by_shape(sizeof(T), C) && aligned16(in);
+  // the split plan is fixed by the shape; only the lane layout follows `vec`
+  Plan q = p;
+  if (!vec && cols_vec_by_shape(sizeof(T), C)) {
+    q.lpr = (int)std::min<int64_t>(32, pow2_ceil(C));
+    q.slabs = (int)ceil_div<int64_t>(C, q.lpr);
+  }
+  const int64_t grid = A * q.slabs * q.splits;
+  if (grid > 0x7fffffffLL)
+    return B200_ERR_UNSUPPORTED;
+  if (vec)
+    reduce_cols_kernel<T, OP, N, OutT><<<(unsigned)grid, kBlock, 0, stream>>>(
+        in, out, partial, A, B, C, q.lpr, q.slabs, q.splits, q.rows_per_split);
+  else
+    reduce_cols_kernel<T, OP, 1, OutT><<<(unsigned)grid, kBlock, 0, stream>>>(
+        in, out, partial, A, B, C, q.lpr, q.slabs, q.splits, q.rows_per_split);
+  if (int rc = check_launch())
+    return rc;
+  if (q.splits > 1) {
+    const int64_t n = A * C;
+    return launch_pdl(reduce_finalize_kernel<OP, OutT>, dim3((unsigned)ceil_div<int64_t>(n, 32)),
+                      dim3(kBlock), 0, stream, (const float *)partial, out, n, q.splits, (int64_t)1, n);
+  }
+  return B200_OK;
+}
+
+template <typename T>
+int dispatch_op(int op, const void *in, void *out, int64_t A, int64_t B, int64_t C, void *ws,
+                size_t ws_bytes, cudaStream_t stream) {
+  if (op == kSum)
+    return launch<T, kSum, T>((const T *)in, (T *)out, A, B, C, ws, ws_bytes, stream);
+  if (op == kMax)
+    return launch<T, kMax, T>((const T *)in, (T *)out, A, B, C, ws, ws_bytes, stream);
+  return B200_ERR_INVALID_ARG;
+}
+
+int esize_of(int dtype) {
+  return dtype == B200_F32 ? 4 : (dtype == B200_F16 || dtype == B200_BF16) ? 2 : 0;
+}
+
+} // namespace
+} // namespace b200
+
+using namespace b200;
+
+extern "C" size_t b200_reduce_workspace_bytes(int op, int dtype, int64_t A, int64_t B, int64_t C) {
+  (void)op;
+  const int es = esize_of(dtype);
+  if (!es || A <= 0 || B <= 0 || C <= 0)
+    return 0;
+  return make_plan(es, A, B, C, cols_vec_by_shape(es, C)).ws_bytes;
+}
+
+extern "C" int b200_reduce(int op, int dtype, const void *in, void *out, int64_t A, int64_t B,
+                           int64_t C, void *workspace, size_t workspace_bytes,
+                           cudaStream_t stream) {
+  const int es = esize_of(dtype);
+  if (!es || A < 0 || B < 0 || C < 0 || (op != kSum && op != kMax))
+    return B200_ERR_INVALID_ARG;
+  if (A == 0 && B == 0) { // nothing to reduce: a copy, as reduce_impl.h:70-73
+    if (C == 0)
+      return B200_OK;
+    if (!in || !out)
+      return B200_ERR_INVALID_ARG;
+    return check_cuda(cudaMemcpyAsync(out, in, (size_t)C * es, cudaMemcpyDeviceToDevice, stream));
+  }
+  if (A == 0 || C == 0)
+    return B200_OK; // empty output
+  if (B == 0 || !in || !out)
+    return B200_ERR_INVALID_ARG;
+  switch (dtype) {
+  case B200_F32:
+    return dispatch_op<float>(op, in, out, A, B, C, workspace, workspace_bytes, stream);
+  case B200_F16:
+    return dispatch_op<__half>(op, in, out, A, B, C, workspace, workspace_bytes, stream);
+  default:
+    return dispatch_op<__nv_bfloat16>(op, in, out, A, B, C, workspace, workspace_bytes, stream);
+  }
+}
+
+extern "C" int b200_reduce_sum_to_f32(int dtype, const void *in, float *out, int64_t A, int64_t B,
+                                      int64_t C, void *workspace, size_t workspace_bytes,
+                                      cudaStream_t stream) {
+  const int es = esize_of(dtype);
+  if (!es || A <= 0 || B <= 0 || C <= 0 || !in || !out)
+    return B200_ERR_INVALID_ARG;
+  switch (dtype) {
+  case B200_F32:
+    return launch<float, kSum, float>((const float *)in, out, A, B, C, workspace, workspace_bytes, stream);
+  case B200_F16:
+    return launch<__half, kSum, float>((const __half *)in, out, A, B, C, workspace, workspace_bytes, stream);
+  default:
+    return launch<__nv_bfloat16, kSum, float>((const __nv_bfloat16 *)in, out, A, B, C, workspace,
+                                              workspace_bytes, stream);
+  }
+}
+
+extern "C" int b200_cast_from_f32(int dtype, const float *in, void *out, int64_t n,
+                                  cudaStream_t stream) {
+  if (n < 0 || !esize_of(dtype))
+    return B200_ERR_INVALID_ARG;
+  if (n == 0)
+    return B200_OK;
+  if (!in || !out)
+    return B200_ERR_INVALID_ARG;
+  const unsigned grid = (unsigned)ceil_div<int64_t>(n, kBlock);
+  switch (dtype) {
+  case B200_F32:
+    cast_from_f32_kernel<float><<<grid, kBlock, 0, stream>>>(in, (float *)out, n);
+    break;
+  case B200_F16:
+    cast_from_f32_kernel<__half><<<grid, kBlock, 0, stream>>>(in, (__half *)out, n);
+    break;
+  default:
+    cast_from_f32_kernel<__nv_bfloat16><<<grid, kBlock, 0, stream>>>(in, (__nv_bfloat16 *)out, n);
+  }
+  return check_launch();
+}

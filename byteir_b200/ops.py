@@ -1,0 +1,189 @@
+"""Host-side mirror of the ByRE compute ops of the default CUDA provider, over
+torch CUDA tensors.  torch supplies device memory and the current stream only;
+every op runs the sm_100a kernels through the C ABI.
+
+Semantics follow the reference op kernels
+(runtime/lib/backends/cuda/providers/default/{reduction,indexing,
+tensor_manipulate}): ReduceSumOp / ReduceMaxOp with a `dimensions` attribute
+(consecutive dims), IndexSelectOp / IndexPutOp with `dim`, TransposeOp with
+`permutation`.
+"""
+import ctypes as C
+
+import torch
+
+from . import _native as N
+
+_DT = {torch.float32: N.F32, torch.float16: N.F16, torch.bfloat16: N.BF16}
+
+
+def _dt(t):
+    try:
+        return _DT[t.dtype]
+    except KeyError:
+        raise TypeError(f"unsupported element type {t.dtype}") from None
+
+
+def _stream():
+    return C.c_void_p(torch.cuda.current_stream().cuda_stream)
+
+
+def _need_cuda(*ts):
+    for t in ts:
+        if not t.is_cuda:
+            raise ValueError("byteir_b200 ops take CUDA tensors; there is no CPU path")
+        if not t.is_contiguous():
+            raise ValueError("tensors must be contiguous (ByRE memrefs are)")
+
+
+def reduce_abc(shape, dimensions):
+    """A x B x C view of reduce_impl.h:28-59."""
+    dims = sorted(d for d in dimensions if shape[d] != 1)
+    if not dims:
+        n = 1
+        for s in shape:
+            n *= s
+        return 0, 0, n
+    for a, b in zip(dims, dims[1:]):
+        if b - a != 1:
+            raise ValueError("Only consecutive dimensions reduction is supported")
+    A = B = Cc = 1
+    for s in shape[:dims[0]]:
+        A *= s
+    for d in dims:
+        B *= shape[d]
+    for s in shape[dims[-1] + 1:]:
+        Cc *= s
+    return A, B, Cc
+
+
+class _NoWorkspace:
+    @staticmethod
+    def data_ptr():
+        return None
+
+    @staticmethod
+    def numel():
+        return 0
+
+
+def _workspace(nbytes, device):
+    if int(nbytes) == 0:
+        return _NoWorkspace
+    return torch.empty(int(nbytes), dtype=torch.uint8, device=device)
+
+
+def _reduce(op, x, dimensions, out=None, workspace=None):
+    _need_cuda(x)
+    A, B, Cc = reduce_abc(tuple(x.shape), list(dimensions))
+    out_shape = [s for i, s in enumerate(x.shape) if i not in set(dimensions)]
+    if out is None:
+        out = torch.empty(out_shape, dtype=x.dtype, device=x.device)
+    need = N.lib().b200_reduce_workspace_bytes(op, _dt(x), A, B, Cc)
+    if workspace is None:
+        workspace = _workspace(need, x.device)
+    rc = N.lib().b200_reduce(op, _dt(x), x.data_ptr(), out.data_ptr(), A, B, Cc,
+                             workspace.data_ptr(), workspace.numel(), _stream())
+    N.check(rc, "b200_reduce")
+    return out
+
+
+def reduce_sum(x, dimensions, out=None, workspace=None):
+    return _reduce(N.REDUCE_SUM, x, dimensions, out, workspace)
+
+
+def reduce_max(x, dimensions, out=None, workspace=None):
+    return _reduce(N.REDUCE_MAX, x, dimensions, out, workspace)
+
+
+def reduce_sum_to_f32(x, dimensions, out=None, workspace=None):
+    """Unrounded f32 partial of a sum (the operand of a later all-reduce)."""
+    _need_cuda(x)
+    A, B, Cc = reduce_abc(tuple(x.shape), list(dimensions))
+    if out is None:
+        out = torch.empty(A * Cc, dtype=torch.float32, device=x.device)
+    need = N.lib().b200_reduce_workspace_bytes(N.REDUCE_SUM, _dt(x), A, B, Cc)
+    if workspace is None:
+        workspace = _workspace(need, x.device)
+    rc = N.lib().b200_reduce_sum_to_f32(_dt(x), x.data_ptr(), out.data_ptr(), A, B, Cc,
+                                        workspace.data_ptr(), workspace.numel(), _stream())
+    N.check(rc, "b200_reduce_sum_to_f32")
+    return out
+
+
+def cast_from_f32(x, dtype, out=None):
+    _need_cuda(x)
+    if out is None:
+        out = torch.empty(x.shape, dtype=dtype, device=x.device)
+    N.check(N.lib().b200_cast_from_f32(_DT[dtype], x.data_ptr(), out.data_ptr(), x.numel(), _stream()),
+            "b200_cast_from_f32")
+    return out
+
+
+def index_select(x, index, dim, out=None, status=None, path=0):
+    _need_cuda(x, index)
+    if index.dtype not in (torch.int64, torch.int32, torch.uint32):
+        raise TypeError("index must be i64 or ui32")
+    shape = tuple(x.shape)
+    A = 1
+    for s in shape[:dim]:
+        A *= s
+    Cc = 1
+    for s in shape[dim + 1:]:
+        Cc *= s
+    IB, OB = shape[dim], index.numel()
+    if out is None:
+        out = torch.empty(shape[:dim] + (OB,) + shape[dim + 1:], dtype=x.dtype, device=x.device)
+    rc = N.lib().b200_index_select_path(path, x.element_size(), index.element_size(), x.data_ptr(),
+                                        index.data_ptr(), out.data_ptr(), A, IB, OB, Cc,
+                                        status.data_ptr() if status is not None else None, _stream())
+    N.check(rc, "b200_index_select")
+    return out
+
+
+def index_put_add(x, index, update, dim=0, out=None, workspace=None, status=None):
+    """out = x; out[index[i], ...] += update[i, ...] (IndexPutOp, accumulate)."""
+    _need_cuda(x, index, update)
+    if index.dtype != torch.int64:
+        raise TypeError("index must be i64")
+    rows = 1
+    for s in x.shape[:dim + 1]:
+        rows *= s
+    feature = 1
+    for s in x.shape[dim + 1:]:
+        feature *= s
+    n = index.numel()
+    if out is None:
+        out = torch.empty_like(x)
+    need = N.lib().b200_index_put_workspace_bytes(_dt(x), rows, n, feature)
+    if workspace is None:
+        workspace = _workspace(need, x.device)
+    rc = N.lib().b200_index_put_add(_dt(x), x.data_ptr(), index.data_ptr(), update.data_ptr(),
+                                    out.data_ptr(), rows, n, feature, workspace.data_ptr(),
+                                    workspace.numel(), status.data_ptr() if status is not None else None,
+                                    _stream())
+    N.check(rc, "b200_index_put_add")
+    return out
+
+
+def transpose(x, permutation, out=None):
+    _need_cuda(x)
+    perm = list(permutation)
+    if out is None:
+        out = torch.empty([x.shape[p] for p in perm], dtype=x.dtype, device=x.device)
+    shape = (C.c_int64 * x.dim())(*x.shape)
+    p = (C.c_int64 * x.dim())(*perm)
+    N.check(N.lib().b200_permute(x.element_size(), x.data_ptr(), out.data_ptr(), x.dim(), shape, p, _stream()),
+            "b200_permute")
+    return out
+
+
+def transpose_batched(x, out=None, path=0):
+    """[batch, rows, cols] -> [batch, cols, rows]"""
+    _need_cuda(x)
+    b, r, c = x.shape
+    if out is None:
+        out = torch.empty((b, c, r), dtype=x.dtype, device=x.device)
+    N.check(N.lib().b200_transpose_batched_path(path, x.element_size(), x.data_ptr(), out.data_ptr(), b, r, c, _stream()),
+            "b200_transpose_batched")
+    return out

@@ -1,0 +1,152 @@
+/* Thin C ABI of the sm_100a kernels behind the ByRE compute ops of ByteIR's
+ * default CUDA provider.  Every entry point only enqueues work on `stream`:
+ * it never synchronises, never allocates device memory and never touches the
+ * host copy of a tensor.  All pointers are device pointers unless said
+ * otherwise; sizes are element counts unless the name says bytes.
+ *
+ * Return value: 0 on success, a negative B200_ERR_* otherwise.  After
+ * B200_ERR_CUDA, b200_last_cuda_error() gives the cudaError_t of the failed
+ * launch (thread-local).
+ *
+ * Each declaration names the reference interface it stands in for, by the
+ * file's path inside bytedance/byteir.
+ */
+#ifndef B200_KERNELS_H_
+#define B200_KERNELS_H_
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#ifndef __DRIVER_TYPES_H__
+typedef struct CUstream_st *cudaStream_t;
+#endif
+
+#define B200_OK 0
+#define B200_ERR_INVALID_ARG (-1)
+#define B200_ERR_UNSUPPORTED (-2)
+#define B200_ERR_WORKSPACE (-3) /* workspace missing or too small */
+#define B200_ERR_CUDA (-4)
+#define B200_ERR_ALIGNMENT (-5)
+
+/* element types (the ByRE key suffixes f32 / f16 / bf16) */
+#define B200_F32 0
+#define B200_F16 1
+#define B200_BF16 2
+
+#define B200_REDUCE_SUM 0
+#define B200_REDUCE_MAX 1
+
+const char *b200_version(void);
+int b200_last_cuda_error(void);
+const char *b200_error_string(int code);
+
+/* ---- ReduceSumOp / ReduceMaxOp -------------------------------------------
+ * Replaces kernel::call_reduce<T, Op> and get_reduce_workspace_in_bytes
+ * (runtime/lib/backends/cuda/providers/default/reduction/kernels/reduction.h,
+ *  reduction.cu:411-434).  Input is viewed as A x B x C, row-major; B is
+ * reduced; output is A x C in the input's element type.  Sum accumulates in
+ * f32 (reduce_impl.h:63-69).  Max follows reduction_helper.h:159-180 folded in
+ * ascending index order: any NaN gives NaN, equal values keep the later one.
+ * Workspace bytes depend only on (op, dtype, A, B, C); the workspace may be
+ * uninitialised.
+ */
+size_t b200_reduce_workspace_bytes(int op, int dtype, int64_t A, int64_t B,
+                                   int64_t C);
+int b200_reduce(int op, int dtype, const void *in, void *out, int64_t A,
+                int64_t B, int64_t C, void *workspace, size_t workspace_bytes,
+                cudaStream_t stream);
+/* Sum only: the same reduction with the A x C result left in f32, unrounded.
+ * This is what a device contributes to nccl.AllReduce when the reduced axis is
+ * itself sharded over devices (runtime/lib/backends/nccl/providers/
+ * all_reduce.cc:44-69); b200_cast_from_f32 then rounds once.  Same workspace
+ * size as b200_reduce. */
+int b200_reduce_sum_to_f32(int dtype, const void *in, float *out_f32, int64_t A,
+                           int64_t B, int64_t C, void *workspace,
+                           size_t workspace_bytes, cudaStream_t stream);
+int b200_cast_from_f32(int dtype, const float *in, void *out, int64_t n,
+                       cudaStream_t stream);
+
+/* ---- IndexSelectOp --------------------------------------------------------
+ * Replaces kernel::index_select<InputTy, IndexTy>
+ * (indexing/kernels/index_select.h; index_select.cu:26-47):
+ *   out[a, ob, c] = in[a, idx[ob], c],  in: A x IB x C, out: A x OB x C.
+ * elt_bytes in {1,2,4,8,16}; idx_bytes 4 (ui32) or 8 (i64).  An index outside
+ * [0, IB) copies nothing for that row, zero-fills it, and sets *status (a
+ * device int, may be NULL) to 1; the reference reads out of bounds there.
+ */
+int b200_index_select(int elt_bytes, int idx_bytes, const void *in,
+                      const void *idx, void *out, int64_t A, int64_t IB,
+                      int64_t OB, int64_t C, int *status, cudaStream_t stream);
+
+/* ---- IndexPutOp (accumulate) ---------------------------------------------
+ * Replaces kernel::index_put<T, true> (indexing/kernels/index_put.h;
+ * index_put.cu:28-55): out = in; out[idx[i], :] += upd[i, :] for every i.
+ * in/out: rows x feature, upd: index_count x feature, idx: int64.
+ * Unlike the reference's atomicAdd, the result does not depend on scheduling:
+ * updates are ordered by (row, i), summed in f32 in a fixed tree, added to the
+ * table value and rounded once.  in == out (in place) is allowed.  Indices
+ * outside [0, rows) are skipped and set *status (device int, may be NULL).
+ */
+size_t b200_index_put_workspace_bytes(int dtype, int64_t rows,
+                                      int64_t index_count, int64_t feature);
+int b200_index_put_add(int dtype, const void *in, const int64_t *idx,
+                       const void *upd, void *out, int64_t rows,
+                       int64_t index_count, int64_t feature, void *workspace,
+                       size_t workspace_bytes, int *status,
+                       cudaStream_t stream);
+
+/* ---- TransposeOp ----------------------------------------------------------
+ * Replaces kernel::transpose_naive_2d (tensor_manipulate/kernels/transpose.h;
+ * transpose.cu:24-41) and the cudnnTransformTensor NCHW<->NHWC path
+ * (tensor_manipulate/transpose.cc:68-123), both of which are a batched 2-D
+ * transpose:  in: batch x rows x cols  ->  out: batch x cols x rows.
+ * elt_bytes in {1,2,4,8}.
+ */
+int b200_transpose_batched(int elt_bytes, const void *in, void *out,
+                           int64_t batch, int64_t rows, int64_t cols,
+                           cudaStream_t stream);
+/* General permutation, rank <= 8: out.shape[k] = shape[perm[k]].  Collapses
+ * to b200_transpose_batched whenever the permutation allows it. */
+int b200_permute(int elt_bytes, const void *in, void *out, int rank,
+                 const int64_t *shape, const int64_t *perm,
+                 cudaStream_t stream);
+
+/* ---- Flash attention ------------------------------------------------------
+ * Typed doors behind the byre.custom entry points run_flash_attn_fwd / _bwd
+ * (external_libs/runtime/flash_attn/lib/flash_api.h:75-82, argument unpacking
+ * flash_api.cu:586-725).  Strides are in elements.  q,k,v,o: [B, S, H, D];
+ * lse: f32 [B, H, Sq].  dtype B200_F16 or B200_BF16.
+ */
+typedef struct {
+  int64_t q_batch_stride, k_batch_stride, v_batch_stride, o_batch_stride;
+  int64_t q_row_stride, k_row_stride, v_row_stride, o_row_stride;
+  int64_t q_head_stride, k_head_stride, v_head_stride, o_head_stride;
+  int64_t b, h, h_k, d, d_rounded;
+  float softmax_scale;
+  int64_t seqlen_q, seqlen_k, seqlen_q_rounded, seqlen_k_rounded;
+  float p_dropout;
+  int64_t window_size_left, window_size_right;
+} b200_flash_attn_params;
+
+int b200_flash_attn_fwd(int dtype, const void *q, const void *k, const void *v,
+                        void *out, float *softmax_lse,
+                        const b200_flash_attn_params *params,
+                        cudaStream_t stream);
+/* d_softmax_sum: f32 [B, H, seqlen_q_rounded]; dq_accum: f32 scratch of
+ * B * seqlen_q_rounded * H * d_rounded elements (both caller-provided, as in
+ * the reference's custom call). */
+int b200_flash_attn_bwd(int dtype, const void *dout, const void *q,
+                        const void *k, const void *v, const void *out,
+                        const float *softmax_lse, void *dq, void *dk, void *dv,
+                        float *d_softmax_sum, float *dq_accum,
+                        const b200_flash_attn_params *params,
+                        cudaStream_t stream);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* B200_KERNELS_H_ */
