@@ -1,0 +1,184 @@
+"""Python door onto the brt host runtime (libbrt_b200.so) through its C API
+(include/brt_c_api.h).  Usage follows the reference's `brt.Session`
+(runtime/python/src/module.cc): create a session for a device, load a ByRE
+module, make a request, bind or fetch argument buffers, run, sync.
+"""
+import ctypes as C
+from pathlib import Path
+
+from ._native import LIB_DIR
+
+# brt::DTypeEnum (include/brt/core/framework/dtype.h)
+DTYPE_NAMES = {1: "f32", 2: "i32", 3: "i64", 4: "ui8", 5: "ui32", 6: "f16", 7: "bf16", 8: "f64", 9: "i1",
+               11: "i8", 12: "i16", 13: "ui16", 14: "ui64"}
+
+_vp, _i64, _int, _sz, _cp = C.c_void_p, C.c_int64, C.c_int, C.c_size_t, C.c_char_p
+
+SIGNATURES = {
+    "brt_last_error": (_cp, []),
+    "brt_register_kernels_from_dynlib": (_int, [_cp]),
+    "brt_session_create": (_vp, []),
+    "brt_session_destroy": (None, [_vp]),
+    "brt_session_add_cpu": (_int, [_vp]),
+    "brt_session_add_cuda": (_int, [_vp, _int]),
+    "brt_session_add_cuda_external": (_int, [_vp, _int, _vp, _vp]),
+    "brt_session_load": (_int, [_vp, _cp]),
+    "brt_session_load_from_memory": (_int, [_vp, _cp]),
+    "brt_session_arg_num": (_i64, [_vp]),
+    "brt_session_arg_offset": (_int, [_vp, _cp]),
+    "brt_session_arg_info": (_int, [_vp, _i64, C.POINTER(_int), C.POINTER(_int), C.POINTER(_i64), _cp, _sz,
+                                    C.POINTER(_int), _cp, _sz]),
+    "brt_request_create": (_vp, [_vp, _vp]),
+    "brt_request_destroy": (None, [_vp]),
+    "brt_request_bind_arg": (_int, [_vp, _i64, _vp]),
+    "brt_request_get_arg": (_vp, [_vp, _i64]),
+    "brt_request_finish_io_binding": (_int, [_vp]),
+    "brt_session_run": (_int, [_vp, _vp]),
+    "brt_request_sync": (_int, [_vp]),
+    "brt_request_enable_op_trace": (_int, [_vp]),
+    "brt_request_op_trace": (_i64, [_vp, _cp, _sz]),
+}
+
+_lib = None
+
+
+def lib():
+    global _lib
+    if _lib is None:
+        path = LIB_DIR / "libbrt_b200.so"
+        if not path.exists():
+            raise ImportError(f"{path} is missing: build it with `python -m byteir_b200.build`")
+        h = C.CDLL(str(path), mode=C.RTLD_GLOBAL)
+        for name, (res, args) in SIGNATURES.items():
+            fn = getattr(h, name)
+            fn.restype, fn.argtypes = res, args
+        _lib = h
+    return _lib
+
+
+class BrtError(RuntimeError):
+    pass
+
+
+def _check(rc):
+    if rc != 0:
+        raise BrtError(lib().brt_last_error().decode(errors="replace"))
+
+
+def register_kernels_from_dynlib(path):
+    _check(lib().brt_register_kernels_from_dynlib(str(path).encode()))
+
+
+class ArgInfo:
+    def __init__(self, offset, name, dtype, shape, space, argtype):
+        self.offset, self.name, self.dtype, self.shape, self.space, self.argtype = offset, name, dtype, shape, space, argtype
+
+    @property
+    def nbytes(self):
+        n = {"f32": 4, "i32": 4, "ui32": 4, "i64": 8, "ui64": 8, "f64": 8, "f16": 2, "bf16": 2, "i16": 2,
+             "ui16": 2, "i8": 1, "ui8": 1, "i1": 1}[self.dtype]
+        for s in self.shape:
+            n *= s
+        return n
+
+    def __repr__(self):
+        return f"ArgInfo({self.offset}, {self.name!r}, {self.dtype}, {self.shape}, {self.space!r}, type={self.argtype})"
+
+
+class Session:
+    """device: "cuda" (default CUDA provider + CUDA allocators) or "cpu"."""
+
+    def __init__(self, device="cuda", device_id=0):
+        self._h = lib().brt_session_create()
+        if not self._h:
+            raise BrtError(lib().brt_last_error().decode())
+        if device == "cuda":
+            _check(lib().brt_session_add_cuda(self._h, device_id))
+        elif device == "cpu":
+            _check(lib().brt_session_add_cpu(self._h))
+        else:
+            raise ValueError(device)
+
+    def close(self):
+        if self._h:
+            lib().brt_session_destroy(self._h)
+            self._h = None
+
+    def __del__(self):
+        try:
+            self.close()
+        except Exception:
+            pass
+
+    def load(self, path):
+        _check(lib().brt_session_load(self._h, str(path).encode()))
+
+    def load_from_memory(self, text):
+        _check(lib().brt_session_load_from_memory(self._h, text.encode()))
+
+    def arg_num(self):
+        return lib().brt_session_arg_num(self._h)
+
+    def arg_offset(self, name):
+        return lib().brt_session_arg_offset(self._h, name.encode())
+
+    def arg_info(self, offset):
+        dt, rank, at = _int(), _int(), _int()
+        shape = (_i64 * 8)()
+        space, name = C.create_string_buffer(32), C.create_string_buffer(128)
+        _check(lib().brt_session_arg_info(self._h, offset, C.byref(dt), C.byref(rank), shape, space, 32,
+                                          C.byref(at), name, 128))
+        return ArgInfo(offset, name.value.decode(), DTYPE_NAMES.get(dt.value, str(dt.value)),
+                       tuple(shape[i] for i in range(rank.value)), space.value.decode(), at.value)
+
+    def args(self):
+        return [self.arg_info(i) for i in range(self.arg_num())]
+
+    def new_request(self, cuda_stream=None):
+        return Request(self, cuda_stream)
+
+
+class Request:
+    def __init__(self, session, cuda_stream=None):
+        self._s = session
+        self._h = lib().brt_request_create(session._h, cuda_stream)
+        if not self._h:
+            raise BrtError(lib().brt_last_error().decode())
+
+    def close(self):
+        if self._h:
+            lib().brt_request_destroy(self._h)
+            self._h = None
+
+    def __del__(self):
+        try:
+            self.close()
+        except Exception:
+            pass
+
+    def bind_arg(self, offset, ptr):
+        _check(lib().brt_request_bind_arg(self._h, offset, ptr))
+
+    def get_arg(self, offset):
+        p = lib().brt_request_get_arg(self._h, offset)
+        if not p:
+            raise BrtError(lib().brt_last_error().decode())
+        return p
+
+    def finish_io_binding(self):
+        _check(lib().brt_request_finish_io_binding(self._h))
+
+    def run(self):
+        _check(lib().brt_session_run(self._s._h, self._h))
+
+    def sync(self):
+        _check(lib().brt_request_sync(self._h))
+
+    def enable_op_trace(self):
+        _check(lib().brt_request_enable_op_trace(self._h))
+
+    def op_trace(self):
+        n = lib().brt_request_op_trace(self._h, None, 0)
+        buf = C.create_string_buffer(n + 1)
+        lib().brt_request_op_trace(self._h, buf, n + 1)
+        return [k for k in buf.value.decode().split(";") if k]

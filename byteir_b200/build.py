@@ -61,8 +61,39 @@ def build_kernels(force=False, verbose_ptxas=False):
     return target
 
 
+CUDA_INC = Path(NVCC).resolve().parent.parent / "include"
+CUDA_LIB = Path(NVCC).resolve().parent.parent / "lib64"
+
+
+def _gxx(srcs, target, extra, deps, force):
+    if not force and not _newer(target, list(srcs) + list(deps)):
+        return target
+    OUT.mkdir(exist_ok=True)
+    _run([HOSTCXX, "-std=c++17", "-O2", "-g", "-fPIC", "-shared", "-Wall", "-Wno-unused-function",
+          "-I", ROOT / "include", "-I", CUDA_INC, *srcs, "-o", target,
+          f"-Wl,-rpath,$ORIGIN", f"-Wl,-rpath,{CUDA_LIB}", *extra])
+    return target
+
+
+def build_flash_attn(force=False):
+    """libflash_attn.so: the byre.custom entry points (run_flash_attn_fwd / _bwd), over libb200_kernels.so"""
+    src = CSRC / "flash_attn" / "flash_api.cc"
+    return _gxx([src], OUT / "libflash_attn.so",
+                ["-L", OUT, "-lb200_kernels", "-L", CUDA_LIB, "-lcudart"],
+                [ROOT / "include" / "b200_kernels.h", OUT / "libb200_kernels.so"], force)
+
+
+def build_brt(force=False):
+    """libbrt_b200.so: the MLIR-free brt host runtime, its CUDA provider and the C API"""
+    srcs = sorted((CSRC / "brt").glob("*.cc"))
+    hdrs = [p for p in (ROOT / "include").rglob("*.h")]
+    return _gxx(srcs, OUT / "libbrt_b200.so",
+                ["-L", OUT, "-lb200_kernels", "-L", CUDA_LIB, "-lcudart", "-ldl", "-lpthread"],
+                hdrs + [OUT / "libb200_kernels.so"], force)
+
+
 def build_all(force=False):
-    libs = [build_kernels(force)]
+    libs = [build_kernels(force), build_flash_attn(force), build_brt(force)]
     return libs
 
 

@@ -1,0 +1,355 @@
+// The default CUDA provider and its op kernels for the ByRE compute ops
+// ReduceSumOp / ReduceMaxOp / IndexSelectOp / IndexPutOp / TransposeOp and the
+// byre.custom bridge.  Each kernel parses its op at construction (shapes and
+// attributes, as the reference's Impl constructors do) and at run time hands raw
+// pointers and the queue's stream to the sm_100a kernels behind b200_kernels.h.
+#include "b200_kernels.h"
+#include "brt/backends/common.h"
+#include "brt/backends/cuda/device/utils/op_kernel_impl_helpers.h"
+#include "brt/backends/cuda/providers/default/cuda_provider.h"
+#include "brt/backends/cuda/providers/default/custom/op_registration.h"
+#include "brt/backends/cuda/providers/default/indexing/op_registration.h"
+#include "brt/backends/cuda/providers/default/reduction/op_registration.h"
+#include "brt/backends/cuda/providers/default/tensor_manipulate/op_registration.h"
+#include "brt/core/common/common.h"
+#include "brt/core/session/session.h"
+
+#include <algorithm>
+#include <cstring>
+#include <dlfcn.h>
+
+namespace brt {
+namespace cuda {
+
+namespace {
+
+common::Status FromRc(int rc, const char *what) {
+  if (rc == B200_OK)
+    return common::Status::OK();
+  std::string msg = std::string(what) + ": " + b200_error_string(rc);
+  if (rc == B200_ERR_CUDA)
+    msg += " (cudaError " + std::to_string(b200_last_cuda_error()) + ")";
+  return common::Status(common::BRT, common::FAIL, msg);
+}
+
+int KernelDType(DTypeEnum dt) {
+  switch (dt) {
+  case DTypeEnum::Float32: return B200_F32;
+  case DTypeEnum::Float16: return B200_F16;
+  case DTypeEnum::BFloat16: return B200_BF16;
+  default: BRT_THROW("element type ", DTypeName(dt), " is not supported by this op");
+  }
+}
+
+// =============================================================================
+// ReduceSumOp / ReduceMaxOp   (reduction/reduce_impl.h:28-107)
+// =============================================================================
+std::vector<int64_t> DeduceReduceShape(const std::vector<int64_t> &shape, std::vector<int64_t> dims) {
+  std::sort(dims.begin(), dims.end());
+  std::vector<int64_t> out;
+  for (size_t i = 0; i < shape.size(); ++i)
+    if (!std::binary_search(dims.begin(), dims.end(), (int64_t)i))
+      out.push_back(shape[i]);
+  return out;
+}
+
+template <int OP> class ReduceImpl {
+public:
+  explicit ReduceImpl(const OpAccessor &accessor) {
+    auto shape = accessor.GetArgShape(0);
+    auto tshape = accessor.GetArgShape(1);
+    std::vector<int64_t> dimensions = accessor.GetAttrAsIntArray("dimensions");
+    for (auto d : dimensions)
+      BRT_ENFORCE(d >= 0 && d < (int64_t)shape.size(), "reduce dimension out of range");
+    BRT_ENFORCE(tshape == DeduceReduceShape(shape, dimensions), "output shape does not match input minus dimensions");
+    BRT_ENFORCE(accessor.GetArgDTypeEnum(0) == accessor.GetArgDTypeEnum(1), "input and output types differ");
+    dtype_ = KernelDType(accessor.GetArgDTypeEnum(0));
+    // dims of size 1 reduce nothing (reduce_impl.h:81-90)
+    dimensions.erase(std::remove_if(dimensions.begin(), dimensions.end(), [&](int64_t d) { return shape[d] == 1; }),
+                     dimensions.end());
+    if (!dimensions.empty()) {
+      std::sort(dimensions.begin(), dimensions.end());
+      for (size_t i = 0; i + 1 < dimensions.size(); ++i)
+        BRT_ENFORCE(dimensions[i + 1] - dimensions[i] == 1,
+                    "Only consecutive dimensions reductino were supported now.");
+      A = B = C = 1;
+      for (int64_t i = 0; i < dimensions.front(); ++i)
+        A *= shape[i];
+      for (auto d : dimensions)
+        B *= shape[d];
+      for (size_t i = dimensions.back() + 1; i < shape.size(); ++i)
+        C *= shape[i];
+    } else {
+      A = B = 0;
+      C = OpAccessor::GetNumElementsOfShape(shape);
+    }
+  }
+
+  common::Status Execute(const void *input, void *output, void *workspace, cudaStream_t stream) {
+    return FromRc(b200_reduce(OP, dtype_, input, output, A, B, C, workspace, GetWorkspaceBytes(), stream),
+                  "b200_reduce");
+  }
+
+  size_t GetWorkspaceSize(const ExecutionContext &) const { return GetWorkspaceBytes(); }
+
+private:
+  size_t GetWorkspaceBytes() const { return (A && B && C) ? b200_reduce_workspace_bytes(OP, dtype_, A, B, C) : 0; }
+  int64_t A, B, C;
+  int dtype_;
+};
+
+template <int OP>
+using Reduce = CudaOpKernelWithWorkspace<ReduceImpl<OP>, TypedOperand<const void *, 0>, TypedOperand<void *, 1>>;
+
+// =============================================================================
+// IndexSelectOp   (indexing/index_select.h:26-51)
+// =============================================================================
+class IndexSelectImpl {
+public:
+  explicit IndexSelectImpl(const OpAccessor &accessor) {
+    auto shape = accessor.GetArgShape(0);
+    const int64_t ndim = (int64_t)shape.size();
+    const int64_t dim = accessor.GetAttrAsInt("dim");
+    BRT_ENFORCE(dim >= 0 && dim < ndim, "dim out of range");
+    BRT_ENFORCE(accessor.GetArgShape(1).size() == 1, "the index must be one-dimensional");
+    A = C = 1;
+    for (int64_t i = 0; i < dim; ++i)
+      A *= shape[i];
+    IB = shape[dim];
+    OB = accessor.GetArgShape(1)[0];
+    for (int64_t i = dim + 1; i < ndim; ++i)
+      C *= shape[i];
+    auto out = accessor.GetArgShape(2);
+    auto want = shape;
+    want[dim] = OB;
+    BRT_ENFORCE(out == want, "output shape does not match");
+    elt_bytes_ = (int)GetDTypeByte(accessor.GetArgDTypeEnum(0));
+    idx_bytes_ = (int)GetDTypeByte(accessor.GetArgDTypeEnum(1));
+    BRT_ENFORCE(idx_bytes_ == 4 || idx_bytes_ == 8, "index must be ui32 or i64");
+  }
+  common::Status Execute(const void *input, const void *index, void *output, cudaStream_t stream) {
+    return FromRc(b200_index_select(elt_bytes_, idx_bytes_, input, index, output, A, IB, OB, C, nullptr, stream),
+                  "b200_index_select");
+  }
+
+private:
+  int64_t A, IB, OB, C;
+  int elt_bytes_, idx_bytes_;
+};
+using IndexSelect = CudaOpKernel<IndexSelectImpl, TypedOperand<const void *, 0>, TypedOperand<const void *, 1>,
+                                 TypedOperand<void *, 2>>;
+
+// =============================================================================
+// IndexPutOp (accumulate)   (indexing/index_put.h:26-66)
+// =============================================================================
+class IndexPutImpl {
+public:
+  explicit IndexPutImpl(const OpAccessor &accessor) {
+    auto shape = accessor.GetArgShape(0);
+    const int64_t ndim = (int64_t)shape.size();
+    const int64_t dim = accessor.GetAttrAsInt("dim");
+    BRT_ENFORCE(dim >= 0 && dim < ndim, "dim out of range");
+    rows_ = 1;
+    for (int64_t i = 0; i <= dim; ++i)
+      rows_ *= shape[i];
+    index_count_ = accessor.GetArgShape(1)[0];
+    feature_ = 1;
+    for (int64_t i = dim + 1; i < ndim; ++i)
+      feature_ *= shape[i];
+    BRT_ENFORCE(accessor.GetArgDTypeEnum(1) == DTypeEnum::Int64, "index must be i64");
+    BRT_ENFORCE(accessor.GetArgShape(3) == shape, "output shape does not match the input");
+    dtype_ = KernelDType(accessor.GetArgDTypeEnum(0));
+  }
+  common::Status Execute(const void *input, const void *index, const void *update, void *output, void *workspace,
+                         cudaStream_t stream) {
+    return FromRc(b200_index_put_add(dtype_, input, static_cast<const int64_t *>(index), update, output, rows_,
+                                     index_count_, feature_, workspace, Bytes(), nullptr, stream),
+                  "b200_index_put_add");
+  }
+  size_t GetWorkspaceSize(const ExecutionContext &) const { return Bytes(); }
+
+private:
+  size_t Bytes() const { return b200_index_put_workspace_bytes(dtype_, rows_, index_count_, feature_); }
+  int64_t rows_, index_count_, feature_;
+  int dtype_;
+};
+using IndexPut = CudaOpKernelWithWorkspace<IndexPutImpl, TypedOperand<const void *, 0>, TypedOperand<const void *, 1>,
+                                           TypedOperand<const void *, 2>, TypedOperand<void *, 3>>;
+
+// =============================================================================
+// TransposeOp   (tensor_manipulate/transpose.{h,cc}): any rank and permutation
+// =============================================================================
+class TransposeImpl {
+public:
+  explicit TransposeImpl(const OpAccessor &accessor) {
+    shape_ = accessor.GetArgShape(0);
+    perm_ = accessor.GetAttrAsIntArray("permutation");
+    BRT_ENFORCE(perm_.size() == shape_.size(), "permutation rank does not match the input");
+    BRT_ENFORCE(shape_.size() >= 1 && shape_.size() <= 8, "unsupported transpose");
+    std::vector<int64_t> want;
+    for (auto p : perm_) {
+      BRT_ENFORCE(p >= 0 && p < (int64_t)shape_.size(), "bad permutation");
+      want.push_back(shape_[p]);
+    }
+    BRT_ENFORCE(accessor.GetArgShape(1) == want, "output shape does not match the permuted input");
+    elt_bytes_ = (int)GetDTypeByte(accessor.GetArgDTypeEnum(0));
+  }
+  common::Status Execute(const void *input, void *output, cudaStream_t stream) {
+    return FromRc(b200_permute(elt_bytes_, input, output, (int)shape_.size(), shape_.data(), perm_.data(), stream),
+                  "b200_permute");
+  }
+
+private:
+  std::vector<int64_t> shape_, perm_;
+  int elt_bytes_;
+};
+using Transpose = CudaOpKernel<TransposeImpl, TypedOperand<const void *, 0>, TypedOperand<void *, 1>>;
+
+// =============================================================================
+// byre.custom bridge   (custom/custom.{h,cc})
+// =============================================================================
+// dlopen(lib_path), dlsym(api_name), call f(void **tensors, void *extra_args, stream).
+// Differences from the reference, on purpose: the packed extra_args blob is built
+// once at construction instead of malloc'd per run; the VERSION symbol is compared
+// as the string it points to and a mismatch only warns; and for the three
+// flash-attention entry points, bf16 operands select the sibling symbol
+// `<api_name>_bf16` when the library exports it (the custom-call ABI itself
+// carries no element type).
+class CustomOpKernel final : public OpKernel {
+public:
+  explicit CustomOpKernel(const OpKernelInfo &info) : OpKernel(info) {
+    OpAccessor accessor(info_);
+    const std::string lib_path = accessor.GetAttrAsString("lib_path");
+    std::string api_name = accessor.GetAttrAsString("api_name");
+    const std::string version = accessor.HasAttr("version") ? accessor.GetAttrAsString("version") : "";
+    handle_ = dlopen(lib_path.c_str(), RTLD_LAZY | RTLD_GLOBAL);
+    BRT_ENFORCE(handle_ != nullptr, "Custom lib ", lib_path, " load failed: ", dlerror());
+    const bool flash = api_name == "run_flash_attn_fwd" || api_name == "run_flash_attn_bwd" ||
+                       api_name == "run_flash_attn_kvcache";
+    if (flash && accessor.GetNumArgs() > 0 && accessor.GetArgDTypeEnum(0) == DTypeEnum::BFloat16) {
+      if (dlsym(handle_, (api_name + "_bf16").c_str()))
+        api_name += "_bf16";
+      else
+        BRT_THROW("custom library ", lib_path, " has no bf16 variant of ", api_name);
+    }
+    run_func_ = reinterpret_cast<RunFn>(dlsym(handle_, api_name.c_str()));
+    BRT_ENFORCE(run_func_ != nullptr, "Couldn't find function: ", api_name);
+    void *sym = dlsym(handle_, "VERSION");
+    BRT_ENFORCE(sym != nullptr, "Version doesn't exist in custom library!");
+    const char *lib_version = *static_cast<const char *const *>(sym);
+    if (!version.empty() && lib_version && version != lib_version)
+      BRT_LOGS_DEFAULT(WARNING) << "custom library " << lib_path << " reports version " << lib_version
+                                << ", the module asks for " << version;
+    last_error_ = reinterpret_cast<LastErrorFn>(dlsym(handle_, "b200_custom_last_error"));
+    if (accessor.HasAttr("extra_args")) {
+      size_t n = 0;
+      void *blob = accessor.GetAttrAsVoidPtr("extra_args", &n);
+      extra_args_.assign(static_cast<char *>(blob), static_cast<char *>(blob) + n);
+      free(blob);
+    }
+    num_args_ = accessor.GetNumArgs();
+  }
+
+  ~CustomOpKernel() override {
+    if (handle_)
+      dlclose(handle_);
+  }
+
+  common::Status RunImpl(const ExecutionContext &ctx) override {
+    OpAccessor accessor(info_, ctx.exec_frame);
+    std::vector<void *> tensors(num_args_);
+    for (size_t i = 0; i < num_args_; ++i)
+      tensors[i] = accessor.GetArgAsyncValueRef(i);
+    cudaStream_t stream = detail::StreamOf(ctx);
+    // the callee may read extra_args only during the call, as in the reference
+    std::vector<char> args = extra_args_;
+    run_func_(tensors.data(), args.data(), stream);
+    if (last_error_) {
+      if (int rc = last_error_())
+        return common::Status(common::BRT, common::FAIL,
+                              "custom call " + info_.GetByREOpName() + " failed with code " + std::to_string(rc));
+    }
+    return BRT_CUDA_CALL(cudaGetLastError());
+  }
+
+private:
+  using RunFn = void (*)(void **, void *, cudaStream_t);
+  using LastErrorFn = int (*)();
+  void *handle_ = nullptr;
+  RunFn run_func_ = nullptr;
+  LastErrorFn last_error_ = nullptr;
+  std::vector<char> extra_args_;
+  size_t num_args_ = 0;
+};
+
+// byre.copy with callee cuda2cuda (copy/copy.cc): a device-to-device copy on the queue's stream
+class Cuda2CudaCopy final : public OpKernel {
+public:
+  explicit Cuda2CudaCopy(const OpKernelInfo &info) : OpKernel(info) {
+    OpAccessor accessor(info_);
+    bytes_ = (size_t)OpAccessor::GetNumElementsOfShape(accessor.GetArgShape(0)) *
+             GetDTypeByte(accessor.GetArgDTypeEnum(0));
+  }
+  common::Status RunImpl(const ExecutionContext &ctx) override {
+    OpAccessor accessor(info_, ctx.exec_frame);
+    cudaStream_t stream = detail::StreamOf(ctx);
+    return BRT_CUDA_CALL(cudaMemcpyAsync(accessor.GetArgAsyncValueRef(1), accessor.GetArgAsyncValueRef(0), bytes_,
+                                         cudaMemcpyDeviceToDevice, stream));
+  }
+
+private:
+  size_t bytes_;
+};
+
+template <typename K> KernelCreateFn Creator() {
+  return [](const OpKernelInfo &info) -> std::shared_ptr<OpKernel> { return std::make_shared<K>(info); };
+}
+
+} // namespace
+
+// keys are <Name>_<operand element types>_<result element types>, as the compiler's
+// getByreKey builds them (compiler/lib/Dialect/Byre/IR/Common.cpp:35-99)
+void RegisterReductionOps(KernelRegistry *registry) {
+  for (const char *t : {"f16_f16", "f32_f32", "bf16_bf16"}) { // reference: f16 and f32 sum, f32 and f16 max
+    registry->Register(std::string("ReduceSumOp_") + t, Creator<Reduce<B200_REDUCE_SUM>>());
+    registry->Register(std::string("ReduceMaxOp_") + t, Creator<Reduce<B200_REDUCE_MAX>>());
+  }
+}
+
+void RegisterIndexingOps(KernelRegistry *registry) {
+  // reference: IndexSelectOp_{f32ui32_f32, f32i64_f32, f16i64_f16}, IndexPutOp_f32i64f32_f32
+  for (const char *t : {"f32", "f16", "bf16"}) {
+    for (const char *i : {"ui32", "i64", "i32"})
+      registry->Register(std::string("IndexSelectOp_") + t + i + "_" + t, Creator<IndexSelect>());
+    registry->Register(std::string("IndexPutOp_") + t + "i64" + t + "_" + t, Creator<IndexPut>());
+  }
+}
+
+void RegisterTensorManipulateOps(KernelRegistry *registry) {
+  for (const char *t : {"f16_f16", "f32_f32", "bf16_bf16", "i32_i32", "i64_i64", "i8_i8", "ui8_ui8", "i16_i16", "f64_f64"})
+    registry->Register(std::string("TransposeOp_") + t, Creator<Transpose>());
+}
+
+void RegisterCustomOps(KernelRegistry *registry) { registry->Register("custom", Creator<CustomOpKernel>()); }
+
+} // namespace cuda
+
+namespace {
+// the provider's own kernels are registered like a plug-in's would be
+BRT_STATIC_KERNEL_REGISTRATION(DeviceKind::CUDA, ProviderType::BRT, [](KernelRegistry *registry) {
+  cuda::RegisterReductionOps(registry);
+  cuda::RegisterIndexingOps(registry);
+  cuda::RegisterTensorManipulateOps(registry);
+  cuda::RegisterCustomOps(registry);
+  registry->Register("cuda2cuda", cuda::Creator<cuda::Cuda2CudaCopy>());
+  RegisterCommonBuiltinOps(registry);
+})
+} // namespace
+
+CUDAExecutionProvider::CUDAExecutionProvider(const std::string &name) : ExecutionProvider(DeviceKind::CUDA, name) {}
+
+common::Status DefaultCUDAExecutionProviderFactory(Session *session) {
+  return session->AddExecutionProvider(std::make_unique<CUDAExecutionProvider>(ProviderType::BRT));
+}
+
+} // namespace brt
