@@ -187,3 +187,38 @@ def transpose_batched(x, out=None, path=0):
     N.check(N.lib().b200_transpose_batched_path(path, x.element_size(), x.data_ptr(), out.data_ptr(), b, r, c, _stream()),
             "b200_transpose_batched")
     return out
+
+
+def _attn_params(q, k, v, o, scale, causal, window):
+    b, sq, h, d = q.shape
+    sk, hk = k.shape[1], k.shape[2]
+    p = N.FlashAttnParams()
+    p.q_batch_stride, p.q_row_stride, p.q_head_stride = q.stride(0), q.stride(1), q.stride(2)
+    p.k_batch_stride, p.k_row_stride, p.k_head_stride = k.stride(0), k.stride(1), k.stride(2)
+    p.v_batch_stride, p.v_row_stride, p.v_head_stride = v.stride(0), v.stride(1), v.stride(2)
+    p.o_batch_stride, p.o_row_stride, p.o_head_stride = o.stride(0), o.stride(1), o.stride(2)
+    p.b, p.h, p.h_k, p.d = b, h, hk, d
+    p.d_rounded = -(-d // 32) * 32
+    p.softmax_scale = scale
+    p.seqlen_q, p.seqlen_k = sq, sk
+    p.seqlen_q_rounded, p.seqlen_k_rounded = -(-sq // 128) * 128, -(-sk // 128) * 128
+    p.p_dropout = 0.0
+    p.window_size_left = window[0]
+    p.window_size_right = 0 if causal else window[1]
+    return p
+
+
+def flash_attn_fwd(q, k, v, softmax_scale, causal=True, window=(-1, -1), out=None, lse=None):
+    """q, k, v: [B, S, H, D] (last dim contiguous), f16 or bf16.  Returns (out, softmax_lse[B, H, Sq])."""
+    for t in (q, k, v):
+        if not t.is_cuda or t.stride(-1) != 1:
+            raise ValueError("q, k, v must be CUDA tensors with a contiguous last dim")
+    if out is None:
+        out = torch.empty_like(q)
+    if lse is None:
+        lse = torch.empty((q.shape[0], q.shape[2], q.shape[1]), dtype=torch.float32, device=q.device)
+    p = _attn_params(q, k, v, out, softmax_scale, causal, window)
+    rc = N.lib().b200_flash_attn_fwd(_dt(q), q.data_ptr(), k.data_ptr(), v.data_ptr(), out.data_ptr(),
+                                     lse.data_ptr(), C.byref(p), _stream())
+    N.check(rc, "b200_flash_attn_fwd")
+    return out, lse
