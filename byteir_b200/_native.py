@@ -46,7 +46,7 @@ SIGNATURES = {
     "b200_transpose_batched": (_int, [_int, _vp, _vp, _i64, _i64, _i64, _vp]),
     "b200_permute": (_int, [_int, _vp, _vp, _int, C.POINTER(_i64), C.POINTER(_i64), _vp]),
     "b200_flash_attn_fwd": (_int, [_int, _vp, _vp, _vp, _vp, _vp, C.POINTER(FlashAttnParams), _vp]),
-    "b200_flash_attn_bwd": (_int, [_int] + [_vp] * 12 + [C.POINTER(FlashAttnParams), _vp]),
+    "b200_flash_attn_bwd": (_int, [_int] + [_vp] * 11 + [C.POINTER(FlashAttnParams), _vp]),
 }
 # tuning doors that pick a code path explicitly (0 = automatic); not in the header
 EXTRA = {

@@ -375,6 +375,451 @@ int make_qkv_map(CUtensorMap *map, bool bf16, const void *base, int64_t d, int64
                          const_cast<void *>(base), dims, strides, box, CU_TENSOR_MAP_SWIZZLE_128B);
 }
 
+
+// =============================================================================
+// backward
+// =============================================================================
+// Three kernels, no atomics, so the result is a function of the inputs alone
+// (the reference adds dQ partials with atomicAdd, flash_bwd_kernel.h:663):
+//   1. bwd_dot_do_o_kernel   D[b,h,i] = sum_d dO * O  (f32)
+//   2. bwd_dkdv_kernel       one block per 128 keys; walks over the query tiles
+//                            that see them; dK, dV accumulate in tensor memory
+//   3. bwd_dq_kernel         one block per 128 queries; walks over the key tiles;
+//                            dQ accumulates in tensor memory
+// Kernels 2 and 3 both recompute P = exp2(S * scale * log2e - LSE * log2e) and
+// dS = P o (dP - D) from the saved LSE, as the reference does
+// (flash_bwd_kernel.h:472-580); P and dS are rounded to the storage type before
+// the following products.  Kernel 2 works on transposed tiles (S^T = K Q^T), so
+// that the thread that owns a key row writes rows of P^T and dS^T, which are the
+// K-major A operands of dV += P^T dO and dK += dS^T Q.
+
+constexpr uint32_t kColDP = 128, kColAcc0 = 256, kColAcc1 = 384;
+
+struct BwdParams {
+  const float *lse;   // [B, H, Sq]
+  const float *dsum;  // [B, H, Sq_rounded]
+  int64_t H, Hk, Sq, Sk, Sq_rounded;
+  float scale, scale_log2;
+  int64_t window_left, window_right;
+};
+
+struct BwdShared {
+  uint64_t bar_resident;          // the block's own tiles (K,V or Q,dO)
+  uint64_t full[2], empty[2];     // streamed tile pairs
+  uint64_t st_full, st_empty;     // S / dP in tensor memory
+  uint64_t pds_full, pds_empty;   // P / dS in shared memory
+  uint32_t tmem_base;
+  int failed;
+};
+struct BwdStats { // row statistics of the streamed query tile (dK/dV kernel only)
+  float lse2[2][128];
+  float dsum[2][128];
+};
+
+// barrier over the four elementwise warps that also ORs a predicate, so that a
+// give-up decision is taken by all 128 threads together
+__device__ __forceinline__ bool named_bar_or(bool pred) {
+  uint32_t out;
+  asm volatile("{\n"
+               ".reg .pred p, q;\n"
+               "setp.ne.u32 q, %1, 0;\n"
+               "bar.red.or.pred p, 1, 128, q;\n"
+               "selp.u32 %0, 1, 0, p;\n"
+               "}\n"
+               : "=r"(out)
+               : "r"((uint32_t)pred)
+               : "memory");
+  return out != 0;
+}
+
+__device__ __forceinline__ bool bwd_wait(uint64_t *bar, uint32_t parity, BwdShared *ss) {
+  if (mbar_wait(bar, parity))
+    return true;
+  ss->failed = 1;
+  return false;
+}
+
+// 16-byte chunk `chunk16` (0..15: 8 columns each) of row `row` of a 128 x 128 16-bit
+// tile stored as [2 column blocks][128 rows][128 B] with the 128-byte swizzle
+__device__ __forceinline__ void store_tile_chunk(unsigned char *tile, int row, int chunk16, uint4 v) {
+  const int blk = chunk16 >> 3, chunk = chunk16 & 7;
+  *reinterpret_cast<uint4 *>(tile + blk * kHalfTile + row * 128 + ((chunk ^ (row & 7)) << 4)) = v;
+}
+
+__global__ void __launch_bounds__(256)
+    bwd_dot_do_o_kernel(const void *__restrict__ dout, const void *__restrict__ out, float *__restrict__ dsum,
+                        int64_t B, int64_t H, int64_t Sq, int64_t Sq_rounded, int64_t o_batch_stride,
+                        int64_t o_row_stride, int64_t o_head_stride, bool bf16) {
+  // 16 threads per (b, h, row): 8 elements each of the 128-wide row
+  const int64_t gid = (int64_t)blockIdx.x * 16 + (threadIdx.x >> 4);
+  const int sub = threadIdx.x & 15;
+  const int64_t total = B * H * Sq;
+  float acc = 0.f;
+  if (gid < total) {
+    const int64_t row = gid % Sq, h = (gid / Sq) % H, b = gid / (Sq * H);
+    const int64_t off = b * o_batch_stride + row * o_row_stride + h * o_head_stride + sub * 8;
+    const uint4 a = ld_nc_v4(static_cast<const uint16_t *>(dout) + off);
+    const uint4 c = ld_nc_v4(static_cast<const uint16_t *>(out) + off);
+    const uint32_t aw[4] = {a.x, a.y, a.z, a.w}, cw[4] = {c.x, c.y, c.z, c.w};
+#pragma unroll
+    for (int k = 0; k < 4; ++k) {
+      float2 x, y;
+      if (bf16) {
+        x = make_float2(__uint_as_float(aw[k] << 16), __uint_as_float(aw[k] & 0xffff0000u));
+        y = make_float2(__uint_as_float(cw[k] << 16), __uint_as_float(cw[k] & 0xffff0000u));
+      } else {
+        x = __half22float2(*reinterpret_cast<const __half2 *>(&aw[k]));
+        y = __half22float2(*reinterpret_cast<const __half2 *>(&cw[k]));
+      }
+      acc = fmaf(x.x, y.x, acc);
+      acc = fmaf(x.y, y.y, acc);
+    }
+  }
+  for (int off = 8; off > 0; off >>= 1)
+    acc += __shfl_xor_sync(0xffffffffu, acc, off);
+  if (gid < total && sub == 0) {
+    const int64_t row = gid % Sq, bh = gid / Sq;
+    dsum[bh * Sq_rounded + row] = acc;
+  }
+}
+
+// kDKDV = true : block owns keys [kv0, kv0+128) (rows of the transposed tiles), streams (Q, dO) tiles
+// kDKDV = false: block owns queries [q0, q0+128), streams (K, V) tiles
+template <bool kBF16, bool kDKDV>
+__global__ void __launch_bounds__(kThreads, 1)
+    flash_bwd_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_constant__ CUtensorMap k_map,
+                     const __grid_constant__ CUtensorMap v_map, const __grid_constant__ CUtensorMap do_map,
+                     const __grid_constant__ CUtensorMap out0_map, // dK (kDKDV) or dQ
+                     const __grid_constant__ CUtensorMap out1_map, // dV (kDKDV), unused otherwise
+                     const BwdParams p) {
+  extern __shared__ __align__(1024) unsigned char smem_raw[];
+  unsigned char *smem =
+      reinterpret_cast<unsigned char *>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
+  // resident pair, streamed pairs, then the dS tile (and the P tile for dK/dV).
+  // Shared memory holds 7 tiles: the dK/dV kernel needs P and dS, so it streams
+  // through a single stage; the dQ kernel needs only dS and double-buffers.
+  constexpr int kBwdStages = kDKDV ? 1 : 2;
+  unsigned char *sRes0 = smem;                       // K (kDKDV) / Q
+  unsigned char *sRes1 = sRes0 + kTileBytes;         // V (kDKDV) / dO
+  unsigned char *sStr = sRes1 + kTileBytes;          // [stage][2 tiles]: (Q, dO) or (K, V)
+  unsigned char *sDS = sStr + kBwdStages * 2 * kTileBytes;
+  unsigned char *sP = sDS + kTileBytes;              // kDKDV only
+  BwdShared *ss = reinterpret_cast<BwdShared *>(sDS + (kDKDV ? 2 : 1) * kTileBytes);
+  BwdStats *stats = reinterpret_cast<BwdStats *>(ss + 1); // present only if kDKDV
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int b = blockIdx.z;
+  const int64_t shift = p.Sk - p.Sq;
+  const bool right_bounded = p.window_right >= 0;
+  const bool left_bounded = p.window_left >= 0;
+  const int group = (int)(p.H / p.Hk);
+  const int n_q_tiles = (int)((p.Sq + kBM - 1) / kBM);
+  const int n_k_tiles = (int)((p.Sk + kBN - 1) / kBN);
+
+  // the tile this block owns, and the range of streamed tiles [t_begin, t_end)
+  int own_tile, head, t_begin, t_end, heads_in_loop;
+  if (kDKDV) {
+    own_tile = blockIdx.x;
+    head = blockIdx.y; // key/value head
+    heads_in_loop = group;
+    t_begin = 0;
+    t_end = n_q_tiles;
+    if (right_bounded) { // queries that can see key kv0: q >= kv0 - shift - window_right
+      const int64_t first_q = (int64_t)own_tile * kBN - shift - p.window_right;
+      t_begin = first_q <= 0 ? 0 : (int)min((int64_t)n_q_tiles, first_q / kBM);
+    }
+  } else {
+    own_tile = n_q_tiles - 1 - (int)blockIdx.x;
+    head = blockIdx.y; // query head
+    heads_in_loop = 1;
+    t_begin = 0;
+    t_end = n_k_tiles;
+    if (right_bounded) {
+      const int64_t last_visible = (int64_t)own_tile * kBM + kBM - 1 + shift + p.window_right;
+      t_end = last_visible < 0 ? 0 : (int)min((int64_t)n_k_tiles, last_visible / kBN + 1);
+    }
+  }
+  const int tiles_per_head = max(0, t_end - t_begin);
+  const int T = tiles_per_head * heads_in_loop;
+  const int64_t own0 = (int64_t)own_tile * 128;
+
+  if (threadIdx.x == 0) {
+    mbar_init(&ss->bar_resident, 1);
+    for (int s = 0; s < 2; ++s) {
+      mbar_init(&ss->full[s], 1);
+      mbar_init(&ss->empty[s], 1);
+    }
+    mbar_init(&ss->st_full, 1);
+    mbar_init(&ss->st_empty, 4);
+    mbar_init(&ss->pds_full, 4);
+    mbar_init(&ss->pds_empty, 1);
+    ss->failed = 0;
+    mbar_fence_init();
+  }
+  if (warp == 1) {
+    tmem_alloc(&ss->tmem_base, kTmemCols);
+    tmem_relinquish();
+  }
+  tc_fence_before_sync();
+  __syncthreads();
+  tc_fence_after_sync();
+  const uint32_t tmem = ss->tmem_base;
+
+  // streamed iteration -> (query head, streamed tile index)
+  auto iter_head = [&](int it) { return kDKDV ? head * group + it / tiles_per_head : head; };
+  auto iter_tile = [&](int it) { return t_begin + (kDKDV ? it % tiles_per_head : it); };
+  const int kv_head = kDKDV ? head : head / group;
+
+  if (warp == 0) {
+    // ------------------------------------------------------------- producer
+    if (lane == 0 && T > 0) {
+      mbar_arrive_expect_tx(&ss->bar_resident, 2 * kTileBytes);
+      if (kDKDV) {
+        tma_load_4d(sRes0, &k_map, 0, kv_head, (int)own0, b, &ss->bar_resident);
+        tma_load_4d(sRes0 + kHalfTile, &k_map, 64, kv_head, (int)own0, b, &ss->bar_resident);
+        tma_load_4d(sRes1, &v_map, 0, kv_head, (int)own0, b, &ss->bar_resident);
+        tma_load_4d(sRes1 + kHalfTile, &v_map, 64, kv_head, (int)own0, b, &ss->bar_resident);
+      } else {
+        tma_load_4d(sRes0, &q_map, 0, head, (int)own0, b, &ss->bar_resident);
+        tma_load_4d(sRes0 + kHalfTile, &q_map, 64, head, (int)own0, b, &ss->bar_resident);
+        tma_load_4d(sRes1, &do_map, 0, head, (int)own0, b, &ss->bar_resident);
+        tma_load_4d(sRes1 + kHalfTile, &do_map, 64, head, (int)own0, b, &ss->bar_resident);
+      }
+      for (int it = 0; it < T; ++it) {
+        const int st = it % kBwdStages;
+        if (!bwd_wait(&ss->empty[st], (uint32_t)(((it / kBwdStages) & 1) ^ 1), ss))
+          break;
+        mbar_arrive_expect_tx(&ss->full[st], 2 * kTileBytes);
+        unsigned char *t0 = sStr + st * 2 * kTileBytes, *t1 = t0 + kTileBytes;
+        const int row0 = iter_tile(it) * 128;
+        const CUtensorMap *m0 = kDKDV ? &q_map : &k_map, *m1 = kDKDV ? &do_map : &v_map;
+        const int hh = kDKDV ? iter_head(it) : kv_head;
+        tma_load_4d(t0, m0, 0, hh, row0, b, &ss->full[st]);
+        tma_load_4d(t0 + kHalfTile, m0, 64, hh, row0, b, &ss->full[st]);
+        tma_load_4d(t1, m1, 0, hh, row0, b, &ss->full[st]);
+        tma_load_4d(t1 + kHalfTile, m1, 64, hh, row0, b, &ss->full[st]);
+      }
+    }
+  } else if (warp == 1) {
+    // ------------------------------------------------------------- MMA issuer
+    if (lane == 0 && T > 0) {
+      constexpr uint32_t idesc_nt = umma_idesc_f16(kBF16, 128, 128, false, false); // A, B both K-major
+      constexpr uint32_t idesc_nn = umma_idesc_f16(kBF16, 128, 128, false, true);  // B rows = K index
+      const uint32_t res0 = smem_addr(sRes0), res1 = smem_addr(sRes1), str = smem_addr(sStr);
+      const uint32_t p_addr = smem_addr(sP), ds_addr = smem_addr(sDS);
+      bool ok = bwd_wait(&ss->bar_resident, 0, ss);
+      for (int it = 0; ok && it < T; ++it) {
+        const int st = it % kBwdStages;
+        const uint32_t t0 = str + st * 2 * kTileBytes, t1 = t0 + kTileBytes;
+        ok = bwd_wait(&ss->full[st], (uint32_t)((it / kBwdStages) & 1), ss) &&
+             bwd_wait(&ss->st_empty, (uint32_t)((it & 1) ^ 1), ss);
+        if (!ok)
+          break;
+        tc_fence_after_sync();
+        // kDKDV: S^T = K Q^T, dP^T = V dO^T ; else: S = Q K^T, dP = dO V^T  (contraction over head dim)
+#pragma unroll
+        for (int kb = 0; kb < 2; ++kb)
+#pragma unroll
+          for (int ks = 0; ks < 4; ++ks) {
+            const uint32_t off = kb * kHalfTile + ks * 32;
+            umma_ss(tmem + kColS0, umma_smem_desc(res0 + off, 16, 1024), umma_smem_desc(t0 + off, 16, 1024),
+                    idesc_nt, (kb | ks) != 0);
+          }
+#pragma unroll
+        for (int kb = 0; kb < 2; ++kb)
+#pragma unroll
+          for (int ks = 0; ks < 4; ++ks) {
+            const uint32_t off = kb * kHalfTile + ks * 32;
+            umma_ss(tmem + kColDP, umma_smem_desc(res1 + off, 16, 1024), umma_smem_desc(t1 + off, 16, 1024),
+                    idesc_nt, (kb | ks) != 0);
+          }
+        umma_commit(&ss->st_full);
+        ok = bwd_wait(&ss->pds_full, (uint32_t)(it & 1), ss);
+        if (!ok)
+          break;
+        tc_fence_after_sync();
+        // contraction over the 128 streamed (kDKDV: query) or owned-side columns of P / dS
+#pragma unroll
+        for (int kb = 0; kb < 2; ++kb)
+#pragma unroll
+          for (int ks = 0; ks < 4; ++ks) {
+            const uint32_t a_off = kb * kHalfTile + ks * 32;
+            const uint32_t b_off = (kb * 64 + ks * 16) * 128;
+            if (kDKDV) {
+              // dV += P^T dO ; dK += dS^T Q   (B = streamed tiles, rows = queries)
+              umma_ss(tmem + kColAcc0, umma_smem_desc(p_addr + a_off, 16, 1024),
+                      umma_smem_desc(t1 + b_off, kHalfTile, 1024), idesc_nn, (it | kb | ks) != 0);
+              umma_ss(tmem + kColAcc1, umma_smem_desc(ds_addr + a_off, 16, 1024),
+                      umma_smem_desc(t0 + b_off, kHalfTile, 1024), idesc_nn, (it | kb | ks) != 0);
+            } else {
+              // dQ += dS K   (B = streamed K tile, rows = keys)
+              umma_ss(tmem + kColAcc0, umma_smem_desc(ds_addr + a_off, 16, 1024),
+                      umma_smem_desc(t0 + b_off, kHalfTile, 1024), idesc_nn, (it | kb | ks) != 0);
+            }
+          }
+        umma_commit(&ss->pds_empty);
+        umma_commit(&ss->empty[st]);
+      }
+    }
+  } else {
+    // ------------------------------------------------------------- elementwise warps
+    const int quarter = warp & 3;
+    const int row = quarter * 32 + lane;       // owned-side row: a key (kDKDV) or a query
+    const int64_t own_idx = own0 + row;
+    const uint32_t lane_base = (uint32_t)(quarter * 32) << 16;
+    const int tid128 = (warp - 2) * 32 + lane; // 0..127 among the four warps
+    const float kLog2e = 1.4426950408889634f;
+    float my_lse2 = 0.f, my_dsum = 0.f;
+    if (!kDKDV && own_idx < p.Sq) {
+      my_lse2 = p.lse[((int64_t)b * p.H + head) * p.Sq + own_idx] * kLog2e;
+      my_dsum = p.dsum[((int64_t)b * p.H + head) * p.Sq_rounded + own_idx];
+    }
+    bool ok = T > 0;
+    for (int it = 0; ok && it < T; ++it) {
+      const int64_t str0 = (int64_t)iter_tile(it) * 128;
+      if (kDKDV) { // statistics of the streamed query tile, one element per thread
+        const int64_t qi = str0 + tid128;
+        const int qh = iter_head(it);
+        float l2 = INFINITY, dd = 0.f; // rows past the end: P = exp2(-inf) = 0
+        if (qi < p.Sq) {
+          l2 = p.lse[((int64_t)b * p.H + qh) * p.Sq + qi] * kLog2e;
+          dd = p.dsum[((int64_t)b * p.H + qh) * p.Sq_rounded + qi];
+        }
+        stats->lse2[it & 1][tid128] = l2;
+        stats->dsum[it & 1][tid128] = dd;
+      }
+      const bool waited = bwd_wait(&ss->st_full, (uint32_t)(it & 1), ss) &&
+                          (it == 0 || bwd_wait(&ss->pds_empty, (uint32_t)((it - 1) & 1), ss));
+      // one barrier per tile: publishes the statistics above and makes giving up unanimous
+      if (named_bar_or(!waited)) {
+        ok = false;
+        break;
+      }
+      tc_fence_after_sync();
+      // visibility of (query, key): key <= query + shift + wr, key >= query + shift - wl, both in range
+      const int64_t q_base = kDKDV ? str0 : own_idx; // + column if kDKDV
+      const int64_t k_base = kDKDV ? own_idx : str0; // + column if !kDKDV
+#pragma unroll
+      for (int c = 0; c < 4; ++c) {
+        uint32_t sr[32], dr[32];
+        tmem_ld32(tmem + lane_base + kColS0 + c * 32, sr);
+        tmem_ld32(tmem + lane_base + kColDP + c * 32, dr);
+        tmem_wait_ld();
+        if (c == 3) { // all of S / dP has been read: the tensor core may overwrite them
+          tc_fence_before_sync();
+          __syncwarp();
+          if (lane == 0)
+            mbar_arrive(&ss->st_empty);
+        }
+        uint32_t pp[16], dd[16];
+#pragma unroll
+        for (int i = 0; i < 32; i += 2) {
+          float pv[2], dv[2];
+#pragma unroll
+          for (int e = 0; e < 2; ++e) {
+            const int col = c * 32 + i + e;
+            const int64_t qi = kDKDV ? q_base + col : q_base;
+            const int64_t ki = kDKDV ? k_base : k_base + col;
+            const float l2 = kDKDV ? stats->lse2[it & 1][col] : my_lse2;
+            const float ds_ = kDKDV ? stats->dsum[it & 1][col] : my_dsum;
+            bool vis = qi < p.Sq && ki < p.Sk;
+            if (right_bounded)
+              vis = vis && ki <= qi + shift + p.window_right;
+            if (left_bounded)
+              vis = vis && ki >= qi + shift - p.window_left;
+            const float pr = vis ? fast_exp2(fmaf(__uint_as_float(sr[i + e]), p.scale_log2, -l2)) : 0.f;
+            pv[e] = pr;
+            dv[e] = pr * (__uint_as_float(dr[i + e]) - ds_);
+          }
+          pp[i / 2] = pack2(pv[0], pv[1], kBF16);
+          dd[i / 2] = pack2(dv[0], dv[1], kBF16);
+        }
+#pragma unroll
+        for (int g = 0; g < 4; ++g) {
+          if (kDKDV)
+            store_tile_chunk(sP, row, c * 4 + g, make_uint4(pp[g * 4], pp[g * 4 + 1], pp[g * 4 + 2], pp[g * 4 + 3]));
+          store_tile_chunk(sDS, row, c * 4 + g, make_uint4(dd[g * 4], dd[g * 4 + 1], dd[g * 4 + 2], dd[g * 4 + 3]));
+        }
+      }
+      fence_proxy_async_smem();
+      tc_fence_before_sync();
+      __syncwarp();
+      if (lane == 0)
+        mbar_arrive(&ss->pds_full);
+    }
+
+    // ---- epilogue: accumulators -> 16 bit -> shared -> TMA store
+    if (ok && T > 0)
+      ok = bwd_wait(&ss->pds_empty, (uint32_t)((T - 1) & 1), ss);
+    tc_fence_after_sync();
+    const bool have = ok && T > 0;
+    const int n_acc = kDKDV ? 2 : 1;
+    for (int a = 0; a < n_acc; ++a) {
+      // kDKDV: acc0 = dV (unscaled) -> sP, acc1 = dK (* scale) -> sDS ; else acc0 = dQ (* scale) -> sDS
+      const uint32_t col0 = a == 0 ? kColAcc0 : kColAcc1;
+      unsigned char *stage = (kDKDV && a == 0) ? sP : sDS;
+      const float mul = (kDKDV && a == 0) ? 1.f : p.scale;
+#pragma unroll
+      for (int c = 0; c < 4; ++c) {
+        uint32_t r[32];
+        if (have) {
+          tmem_ld32(tmem + lane_base + col0 + c * 32, r);
+          tmem_wait_ld();
+        } else {
+#pragma unroll
+          for (int i = 0; i < 32; ++i)
+            r[i] = 0u;
+        }
+#pragma unroll
+        for (int g = 0; g < 4; ++g) {
+          uint4 v;
+          v.x = pack2(__uint_as_float(r[g * 8 + 0]) * mul, __uint_as_float(r[g * 8 + 1]) * mul, kBF16);
+          v.y = pack2(__uint_as_float(r[g * 8 + 2]) * mul, __uint_as_float(r[g * 8 + 3]) * mul, kBF16);
+          v.z = pack2(__uint_as_float(r[g * 8 + 4]) * mul, __uint_as_float(r[g * 8 + 5]) * mul, kBF16);
+          v.w = pack2(__uint_as_float(r[g * 8 + 6]) * mul, __uint_as_float(r[g * 8 + 7]) * mul, kBF16);
+          store_tile_chunk(stage, row, c * 4 + g, v);
+        }
+      }
+    }
+    fence_proxy_async_smem();
+    asm volatile("bar.sync 1, 128;" ::: "memory");
+    if (warp == 2 && lane == 0 && ss->failed == 0) {
+      if (kDKDV) {
+        tma_store_4d(&out1_map, sP, 0, head, (int)own0, b);
+        tma_store_4d(&out1_map, sP + kHalfTile, 64, head, (int)own0, b);
+      }
+      tma_store_4d(&out0_map, sDS, 0, head, (int)own0, b);
+      tma_store_4d(&out0_map, sDS + kHalfTile, 64, head, (int)own0, b);
+      bulk_commit();
+      bulk_wait_all<0>();
+    }
+  }
+
+  tc_fence_before_sync();
+  __syncthreads();
+  if (warp == 1) {
+    tc_fence_after_sync();
+    tmem_dealloc(tmem, kTmemCols);
+  }
+}
+
+template <bool kBF16, bool kDKDV>
+int launch_bwd(const CUtensorMap &q_map, const CUtensorMap &k_map, const CUtensorMap &v_map,
+               const CUtensorMap &do_map, const CUtensorMap &out0, const CUtensorMap &out1,
+               const BwdParams &p, dim3 grid, cudaStream_t stream) {
+  const size_t smem = kDKDV ? (size_t)6 * kTileBytes + sizeof(BwdShared) + sizeof(BwdStats) + 1024
+                            : (size_t)7 * kTileBytes + sizeof(BwdShared) + 1024;
+  static bool attr_set = false;
+  if (!attr_set) {
+    if (int rc = check_cuda(cudaFuncSetAttribute(flash_bwd_kernel<kBF16, kDKDV>,
+                                                 cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem)))
+      return rc;
+    attr_set = true;
+  }
+  flash_bwd_kernel<kBF16, kDKDV><<<grid, kThreads, smem, stream>>>(q_map, k_map, v_map, do_map, out0, out1, p);
+  return check_launch();
+}
+
 } // namespace
 } // namespace b200
 
@@ -435,8 +880,73 @@ extern "C" int b200_flash_attn_fwd(int dtype, const void *q, const void *k, cons
   return check_launch();
 }
 
-extern "C" int b200_flash_attn_bwd(int, const void *, const void *, const void *, const void *, const void *,
-                                   const float *, void *, void *, void *, float *, float *,
-                                   const b200_flash_attn_params *, cudaStream_t) {
-  return B200_ERR_UNSUPPORTED;
+extern "C" int b200_flash_attn_bwd(int dtype, const void *dout, const void *q, const void *k, const void *v,
+                                   const void *out, const float *softmax_lse, void *dq, void *dk, void *dv,
+                                   float *d_softmax_sum, float *dq_accum, const b200_flash_attn_params *pp,
+                                   cudaStream_t stream) {
+  (void)dq_accum; // the reference's f32 dQ accumulator: not needed, dQ has its own pass
+  if (!pp || !dout || !q || !k || !v || !out || !softmax_lse || !dq || !dk || !dv || !d_softmax_sum)
+    return B200_ERR_INVALID_ARG;
+  const b200_flash_attn_params &a = *pp;
+  if (dtype != B200_F16 && dtype != B200_BF16)
+    return B200_ERR_UNSUPPORTED;
+  if (a.d != kD || a.p_dropout != 0.f || a.h_k <= 0 || a.h % a.h_k != 0 || a.b <= 0 || a.seqlen_q <= 0 ||
+      a.seqlen_k <= 0 || a.seqlen_q_rounded < a.seqlen_q)
+    return B200_ERR_UNSUPPORTED;
+  const int64_t strides[] = {a.q_batch_stride, a.k_batch_stride, a.v_batch_stride, a.o_batch_stride,
+                             a.q_row_stride,   a.k_row_stride,   a.v_row_stride,   a.o_row_stride,
+                             a.q_head_stride,  a.k_head_stride,  a.v_head_stride,  a.o_head_stride};
+  for (int64_t s : strides)
+    if (s <= 0 || s % 8 != 0)
+      return B200_ERR_ALIGNMENT;
+  const void *ptrs[] = {dout, q, k, v, out, dq, dk, dv};
+  for (const void *ptr : ptrs)
+    if (!aligned16(ptr))
+      return B200_ERR_ALIGNMENT;
+  const bool bf16 = dtype == B200_BF16;
+  // dq / dk / dv use the strides of q / k / v and dout those of out, as in the
+  // reference's custom call (flash_api.cu:370-381)
+  CUtensorMap q_map, k_map, v_map, do_map, dq_map, dk_map, dv_map;
+  struct {
+    CUtensorMap *m;
+    const void *base;
+    int64_t heads, seq, hs, rs, bs;
+  } maps[] = {{&q_map, q, a.h, a.seqlen_q, a.q_head_stride, a.q_row_stride, a.q_batch_stride},
+              {&k_map, k, a.h_k, a.seqlen_k, a.k_head_stride, a.k_row_stride, a.k_batch_stride},
+              {&v_map, v, a.h_k, a.seqlen_k, a.v_head_stride, a.v_row_stride, a.v_batch_stride},
+              {&do_map, dout, a.h, a.seqlen_q, a.o_head_stride, a.o_row_stride, a.o_batch_stride},
+              {&dq_map, dq, a.h, a.seqlen_q, a.q_head_stride, a.q_row_stride, a.q_batch_stride},
+              {&dk_map, dk, a.h_k, a.seqlen_k, a.k_head_stride, a.k_row_stride, a.k_batch_stride},
+              {&dv_map, dv, a.h_k, a.seqlen_k, a.v_head_stride, a.v_row_stride, a.v_batch_stride}};
+  for (auto &m : maps)
+    if (int rc = make_qkv_map(m.m, bf16, m.base, a.d, m.heads, m.seq, a.b, m.hs, m.rs, m.bs))
+      return rc;
+
+  const int64_t rows = a.b * a.h * a.seqlen_q;
+  bwd_dot_do_o_kernel<<<(unsigned)ceil_div<int64_t>(rows, 16), 256, 0, stream>>>(
+      dout, out, d_softmax_sum, a.b, a.h, a.seqlen_q, a.seqlen_q_rounded, a.o_batch_stride, a.o_row_stride,
+      a.o_head_stride, bf16);
+  if (int rc = check_launch())
+    return rc;
+
+  BwdParams p;
+  p.lse = softmax_lse;
+  p.dsum = d_softmax_sum;
+  p.H = a.h;
+  p.Hk = a.h_k;
+  p.Sq = a.seqlen_q;
+  p.Sk = a.seqlen_k;
+  p.Sq_rounded = a.seqlen_q_rounded;
+  p.scale = a.softmax_scale;
+  p.scale_log2 = a.softmax_scale * 1.4426950408889634f;
+  p.window_left = a.window_size_left;
+  p.window_right = a.window_size_right;
+  const dim3 grid_kv((unsigned)((a.seqlen_k + kBN - 1) / kBN), (unsigned)a.h_k, (unsigned)a.b);
+  const dim3 grid_q((unsigned)((a.seqlen_q + kBM - 1) / kBM), (unsigned)a.h, (unsigned)a.b);
+  int rc = bf16 ? launch_bwd<true, true>(q_map, k_map, v_map, do_map, dk_map, dv_map, p, grid_kv, stream)
+                : launch_bwd<false, true>(q_map, k_map, v_map, do_map, dk_map, dv_map, p, grid_kv, stream);
+  if (rc)
+    return rc;
+  return bf16 ? launch_bwd<true, false>(q_map, k_map, v_map, do_map, dq_map, dq_map, p, grid_q, stream)
+              : launch_bwd<false, false>(q_map, k_map, v_map, do_map, dq_map, dq_map, p, grid_q, stream);
 }

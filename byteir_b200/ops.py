@@ -222,3 +222,25 @@ def flash_attn_fwd(q, k, v, softmax_scale, causal=True, window=(-1, -1), out=Non
                                      lse.data_ptr(), C.byref(p), _stream())
     N.check(rc, "b200_flash_attn_fwd")
     return out, lse
+
+
+def flash_attn_bwd(dout, q, k, v, out, lse, softmax_scale, causal=True, window=(-1, -1),
+                   dq=None, dk=None, dv=None, d_softmax_sum=None):
+    """Gradients of flash_attn_fwd.  Returns (dq, dk, dv); dq/dk/dv share the strides of q/k/v."""
+    for t in (dout, q, k, v, out):
+        if not t.is_cuda or t.stride(-1) != 1:
+            raise ValueError("tensors must be CUDA tensors with a contiguous last dim")
+    if dout.stride() != out.stride():
+        raise ValueError("dout must share out's strides")
+    dq = torch.empty_like(q) if dq is None else dq
+    dk = torch.empty_like(k) if dk is None else dk
+    dv = torch.empty_like(v) if dv is None else dv
+    p = _attn_params(q, k, v, out, softmax_scale, causal, window)
+    if d_softmax_sum is None:
+        d_softmax_sum = torch.empty((q.shape[0], q.shape[2], p.seqlen_q_rounded), dtype=torch.float32,
+                                    device=q.device)
+    rc = N.lib().b200_flash_attn_bwd(_dt(q), dout.data_ptr(), q.data_ptr(), k.data_ptr(), v.data_ptr(),
+                                     out.data_ptr(), lse.data_ptr(), dq.data_ptr(), dk.data_ptr(),
+                                     dv.data_ptr(), d_softmax_sum.data_ptr(), None, C.byref(p), _stream())
+    N.check(rc, "b200_flash_attn_bwd")
+    return dq, dk, dv
