@@ -396,9 +396,102 @@ class TransposeC4(Workload):
         assert np.array_equal(outs[1].view(self.torch.int16).cpu().numpy().view(np.uint16), np.ascontiguousarray(b.T))
 
 
-WORKLOADS = {"reduce_c2": ReduceC2, "reduce_c1": ReduceC1, "gather": GatherC3, "scatter": ScatterC3,
+
+class AttnC5(Workload):
+    """FlashAttn fwd+bwd: bf16 Q,K,V,dO [B=8, S=4096, H=32, D=128] N(0,1), causal, scale 1/sqrt(128)"""
+    name = "flash_attn_fwd_bwd_bf16_b8_s4096_h32_d128_causal"
+    unit = "TFLOP/s"
+    dtype = "bf16 (f32 accumulate)"
+    bound = "tensor"
+    B, S, H, D = 8, 4096, 32, 128
+    FWD_FLOPS = 4 * 8 * 32 * 4096 * 4096 * 128 // 2
+    BWD_FLOPS = FWD_FLOPS * 5 // 2
+
+    def __init__(self, rank, world):
+        self.rank, self.world = rank, world
+
+    def _gen(self, rng, shape):
+        return rng.standard_normal(shape, dtype=np.float32)
+
+    def host_inputs(self, n):
+        import oracle_lib as O
+        rng = np.random.default_rng(1234 + 5 + 1000 * self.rank)
+        shape = (self.B, self.S, self.H, self.D)
+        out = []
+        for _ in range(min(n, 1)):  # 1 GiB of host data per set: one set, reused
+            out.append(tuple(O.f32_to_bf16(self._gen(rng, shape)) for _ in range(4)))
+        return out * n
+
+    def work_per_step(self):
+        return self.FWD_FLOPS + self.BWD_FLOPS
+
+    def launches_per_step(self):
+        return 4  # fwd, dot(dO,O), dK/dV, dQ
+
+    def dominant(self):
+        return "flash_fwd_kernel<bf16>", self.FWD_FLOPS
+
+    def to_dev(self, torch, x):
+        return tuple(torch.from_numpy(a.view(np.int16)).cuda().view(torch.bfloat16) for a in x)
+
+    def setup_gpu(self, torch, ops, xs):
+        self.ops, self.torch = ops, torch
+        q = xs[0][0]
+        self.o = torch.empty_like(q)
+        self.lse = torch.empty((self.B, self.H, self.S), dtype=torch.float32, device="cuda")
+        self.dq, self.dk, self.dv = (torch.empty_like(q) for _ in range(3))
+        self.dsum = torch.empty((self.B, self.H, self.S), dtype=torch.float32, device="cuda")
+        self.scale = 1.0 / float(np.sqrt(self.D))
+
+    def step_gpu(self, x, dist=None):
+        q, k, v, do = x
+        self.ops.flash_attn_fwd(q, k, v, self.scale, True, out=self.o, lse=self.lse)
+        self.ops.flash_attn_bwd(do, q, k, v, self.o, self.lse, self.scale, True, dq=self.dq, dk=self.dk,
+                                dv=self.dv, d_softmax_sum=self.dsum)
+        return self.o, self.dq, self.dk, self.dv
+
+    def dominant_gpu(self, x):
+        q, k, v, do = x
+        self.ops.flash_attn_fwd(q, k, v, self.scale, True, out=self.o, lse=self.lse)
+
+    def result_bytes(self):
+        return 4 * self.B * self.S * self.H * self.D * 2
+
+    # CPU: a bounded sample (one batch entry, 8 heads, 1024 positions) of the same op
+    CPU_SAMPLE = (1, 1024, 8, 128)
+
+    def cpu_sample_flops(self):
+        b, s, h, d = self.CPU_SAMPLE
+        return (4 * b * h * s * s * d // 2) * 7 // 2
+
+    def step_cpu(self, O, x):
+        b, s, h, d = self.CPU_SAMPLE
+        q, k, v, do = (a[:b, :s, :h, :] for a in x)
+        o, lse = O.flash_attn_fwd(q, k, v, self.scale, True)
+        O.flash_attn_bwd(do, q, k, v, o, lse, self.scale, True)
+
+    def check(self, O, x, outs):
+        # one (batch, head) slice of the full-size result against the oracle, first 512 positions
+        # (causal: the first rows depend only on the first keys)
+        q, k, v, do = (np.ascontiguousarray(a[:1, :512, :2, :]) for a in x)
+        o, lse = O.flash_attn_fwd(q, k, v, self.scale, True)
+        got = outs[0][:1, :512, :2, :].contiguous().view(self.torch.int16).cpu().numpy().view(np.uint16)
+        np.testing.assert_allclose(O.bf16_to_f32(got), O.bf16_to_f32(o), rtol=2e-2, atol=1e-2)
+
+
+WORKLOADS = {"attn": AttnC5, "reduce_c2": ReduceC2, "reduce_c1": ReduceC1, "gather": GatherC3, "scatter": ScatterC3,
              "transpose": TransposeC4}
 METRIC = "HBM GB/s (algorithmic bytes / time) of the ByRE compute op"
+METRIC_TENSOR = "flash-attn fwd+bwd TFLOP/s (algorithmic FLOPs / time)"
+
+
+def metric_of(wl):
+    return METRIC_TENSOR if wl.bound == "tensor" else METRIC
+
+
+def rate(wl, work, seconds):
+    """GB/s for byte work, TFLOP/s for FLOP work"""
+    return work / seconds / (1e12 if wl.bound == "tensor" else 1e9)
 
 
 def to_dev_default(torch, x):
@@ -421,14 +514,17 @@ def run_reference(args, rank, world):
     for i in range(args.steps):
         wl.step_cpu(O, xs[i % 2])
     dt = (time.perf_counter() - t0) / args.steps
-    val = wl.work_per_step() / dt / 1e9
+    cpu_work = wl.cpu_sample_flops() if hasattr(wl, "cpu_sample_flops") else wl.work_per_step()
+    val = rate(wl, cpu_work, dt)
     print(json.dumps({
-        "impl": "reference", "metric": METRIC, "value": val, "unit": wl.unit, "n_gpus": args.gpus, "steps": args.steps,
+        "impl": "reference", "metric": metric_of(wl), "value": val, "unit": wl.unit, "n_gpus": args.gpus, "steps": args.steps,
         "warmup": args.warmup, "ms_per_step": dt * 1e3, "higher_is_better": True, "scaling": "weak",
         "vs_baseline": None, "dtype": wl.dtype, "data": "synthetic (seeded)",
-        "config": {"workload": wl.name, "note": "CPU port of the reference op semantics; one full batch per step"},
+        "config": {"workload": wl.name, "note": "CPU port of the reference op semantics; " + (
+            f"each step a bounded sample {wl.CPU_SAMPLE} [B,S,H,D] of the workload" if hasattr(wl, "CPU_SAMPLE")
+            else "one full batch per step")},
         "cpu_baseline": {"value": val, "unit": wl.unit, "cores": cores, "kind": "port",
-                         "sample": f"{args.steps} full steps on the host"},
+                         "sample": f"{args.steps} steps on the host"},
         "e2e": {"value": val, "unit": wl.unit, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
     }))
 
@@ -470,7 +566,9 @@ def main():
     # rotate over enough distinct inputs that together they exceed L2
     first = xs_host[0]
     per_buf = sum(a.nbytes for a in (first if isinstance(first, tuple) else (first,)))
-    n_buf = max(2, -(-2 * L2_BYTES // per_buf)) if args.workload not in ("scatter", "transpose") else 2
+    n_buf = max(2, -(-2 * L2_BYTES // per_buf)) if args.workload not in ("scatter", "transpose", "attn") else 2
+    if args.workload == "attn":
+        n_buf = 1  # one input set is 1 GiB, far beyond L2
     n_buf = min(n_buf, 8)
     xs_host = wl.host_inputs(n_buf)
     to_dev = getattr(wl, "to_dev", to_dev_default)
@@ -534,7 +632,7 @@ def main():
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
     ms = float(t.item())
     ms_per_step = ms / args.steps
-    value = wl.work_per_step() * world / (ms_per_step * 1e-3) / 1e9
+    value = rate(wl, wl.work_per_step() * world, ms_per_step * 1e-3)
 
     # dominant kernel alone: `reps` back-to-back launches over rotating inputs,
     # CUDA events around the batch (graph replay, so launch gaps are the device's own)
@@ -577,7 +675,7 @@ def main():
         return tuple(vals) if isinstance(like, tuple) else vals[0]
 
     def e2e_step(i):
-        k = i % 2
+        k = i % len(pinned_in)
         for src, dst in zip(pinned_in[k], dev_in[k]):
             dst.copy_(src, non_blocking=True)
         o = wl.step_gpu(as_input(dev_in[k], xs[0]), dist)
@@ -597,7 +695,7 @@ def main():
     if dist is not None:
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
     e2e_ms = float(t.item()) / e2e_steps
-    e2e_val = wl.work_per_step() * world / (e2e_ms * 1e-3) / 1e9
+    e2e_val = rate(wl, wl.work_per_step() * world, e2e_ms * 1e-3)
     h2d = sum(p.numel() * p.element_size() for p in pinned_in[0])
     d2h = sum(p.numel() * p.element_size() for p in pinned_out)
 
@@ -607,9 +705,10 @@ def main():
         return
 
     peaks = measured_peaks()
-    achieved = dom_work / (dom_ms * 1e-3) / 1e9
-    roofline = {"bound": "hbm", "kernel": dom_name, "achieved": achieved, "peak": peaks["hbm_gbs"], "unit": "GB/s",
-                "frac": achieved / peaks["hbm_gbs"], "peak_source": peaks["source"], "us_per_launch": dom_ms * 1e3,
+    achieved = rate(wl, dom_work, dom_ms * 1e-3)
+    peak = peaks["bf16_tflops"] if wl.bound == "tensor" else peaks["hbm_gbs"]
+    roofline = {"bound": wl.bound, "kernel": dom_name, "achieved": achieved, "peak": peak, "unit": wl.unit,
+                "frac": achieved / peak, "peak_source": peaks["source"], "us_per_launch": dom_ms * 1e3,
                 "traffic": NCU_TRAFFIC.get(args.workload)}
 
     cpu = None
@@ -625,11 +724,14 @@ def main():
             if time.perf_counter() - t0 > 10.0 or n >= 50:
                 break
         dt = (time.perf_counter() - t0) / n
-        cpu = {"value": wl.work_per_step() / dt / 1e9, "unit": wl.unit, "cores": cores, "kind": "port",
-               "sample": f"{n} full steps of the same workload (about 10 s)", "ms_per_step": dt * 1e3}
+        cpu_work = wl.cpu_sample_flops() if hasattr(wl, "cpu_sample_flops") else wl.work_per_step()
+        sample = (f"{n} steps on a {wl.CPU_SAMPLE} [B,S,H,D] slice of the workload" if hasattr(wl, "CPU_SAMPLE")
+                  else f"{n} full steps of the same workload (about 10 s)")
+        cpu = {"value": rate(wl, cpu_work, dt), "unit": wl.unit, "cores": cores, "kind": "port",
+               "sample": sample, "ms_per_step": dt * 1e3}
 
     line = {
-        "metric": METRIC, "value": value, "unit": wl.unit, "n_gpus": world, "steps": args.steps, "warmup": args.warmup,
+        "metric": metric_of(wl), "value": value, "unit": wl.unit, "n_gpus": world, "steps": args.steps, "warmup": args.warmup,
         "ms_per_step": ms_per_step, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
         "dtype": wl.dtype, "data": "synthetic (seeded numpy Generator)",
         "config": {"workload": wl.name, "per_gpu_batch": wl.__doc__.strip(),
