@@ -26,6 +26,8 @@
 // backward scan for the last zero of the range to fix the sign.
 #include <cooperative_groups.h>
 
+#include <mutex>
+
 #include "common.cuh"
 
 namespace cg = cooperative_groups;
@@ -739,4 +741,48 @@ extern "C" int b200_cast_from_f32(int dtype, const float *in, void *out, int64_t
     cast_from_f32_kernel<__nv_bfloat16><<<grid, kBlock, 0, stream>>>(in, (__nv_bfloat16 *)out, n);
   }
   return check_launch();
+}
+
+// ---- reduction without a caller-provided workspace ----------------------------
+// Scratch for b200_reduce_no_alloc: one fixed block of device memory per GPU that
+// loads this library, held until the process exits.
+namespace {
+constexpr size_t kStaticScratchBytes = 1u << 20;
+static __device__ __align__(256) unsigned char g_reduce_static_scratch[kStaticScratchBytes];
+
+// `g_reduce_static_scratch` names a host-side handle here, not device memory: the
+// device address has to be asked for, once per device, with that device current.
+int static_scratch_for_current_device(void **ptr) {
+  constexpr int kMaxDevices = 64;
+  static std::mutex mu;
+  static void *addr[kMaxDevices] = {};
+  int dev = 0;
+  if (int rc = check_cuda(cudaGetDevice(&dev)))
+    return rc;
+  if (dev < 0 || dev >= kMaxDevices)
+    return B200_ERR_UNSUPPORTED;
+  std::lock_guard<std::mutex> lock(mu);
+  if (!addr[dev]) {
+    void *p = nullptr;
+    if (int rc = check_cuda(cudaGetSymbolAddress(&p, g_reduce_static_scratch)))
+      return rc;
+    addr[dev] = p;
+  }
+  *ptr = addr[dev];
+  return B200_OK;
+}
+} // namespace
+
+extern "C" size_t b200_reduce_no_alloc_max_bytes(void) { return kStaticScratchBytes; }
+
+extern "C" int b200_reduce_no_alloc(int op, int dtype, const void *in, void *out, int64_t A, int64_t B,
+                                    int64_t C, cudaStream_t stream) {
+  const size_t need = b200_reduce_workspace_bytes(op, dtype, A, B, C);
+  if (need > kStaticScratchBytes)
+    return B200_ERR_WORKSPACE; // this shape needs more scratch than the fixed block holds
+  void *scratch = nullptr;
+  if (need > 0)
+    if (int rc = static_scratch_for_current_device(&scratch))
+      return rc;
+  return b200_reduce(op, dtype, in, out, A, B, C, scratch, need ? kStaticScratchBytes : 0, stream);
 }

@@ -70,6 +70,31 @@ int b200_reduce_sum_to_f32(int dtype, const void *in, float *out_f32, int64_t A,
 int b200_cast_from_f32(int dtype, const float *in, void *out, int64_t n,
                        cudaStream_t stream);
 
+/* Same reduction as b200_reduce, for callers that have no way to hand in scratch
+ * memory.  (No counterpart in the reference: its reduce kernels always get their
+ * workspace from the session's allocator.)  A kernel reached through the
+ * byre.custom call, for instance, receives only tensor pointers, a packed
+ * attribute blob and a stream: it sees no allocator and no workspace operand, and
+ * a cudaMalloc in the middle of an enqueue-only op would synchronise the whole
+ * device.  Here the partial sums go to a
+ * fixed block of b200_reduce_no_alloc_max_bytes() (1 MiB) of device memory that is
+ * part of the library image; every GPU that loads the library holds that block
+ * until the process exits.  The call allocates and frees nothing.
+ *  - A shape whose b200_reduce_workspace_bytes() exceeds the block is refused with
+ *    B200_ERR_WORKSPACE; nothing is launched.
+ *  - The first call made with a given device current looks up the block's device
+ *    address (a host-side query, no device work).  Make that first call before any
+ *    stream capture begins.
+ *  - All calls on a device share the one block.  It keeps whatever the last call
+ *    left in it, which is harmless: every partial is written before it is read, so
+ *    nothing has to be cleared.  But two calls whose kernels overlap on the GPU
+ *    (different streams, no ordering between them) would overwrite each other's
+ *    partials: order such calls yourself.
+ */
+size_t b200_reduce_no_alloc_max_bytes(void);
+int b200_reduce_no_alloc(int op, int dtype, const void *in, void *out, int64_t A,
+                         int64_t B, int64_t C, cudaStream_t stream);
+
 /* ---- IndexSelectOp --------------------------------------------------------
  * Replaces kernel::index_select<InputTy, IndexTy>
  * (indexing/kernels/index_select.h; index_select.cu:26-47):
