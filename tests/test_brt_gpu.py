@@ -119,3 +119,52 @@ module attributes {byre.container_module} {
     assert cudart.cudaMemcpy(y.ctypes.data, yout, y.nbytes, 2) == 0
     assert np.array_equal(y, x.max(axis=1))
     assert s.arg_info(0).name == "X"
+
+
+FLASH = """
+module attributes {byre.container_module} {
+  func.func @attn(%arg0 : memref<%QSHAPE, "cuda"> {byre.argname = "d_Out", byre.argtype = 1: i32},
+                 %arg1 : memref<%QSHAPE, "cuda"> {byre.argname = "Q", byre.argtype = 1: i32},
+                 %arg2 : memref<%QSHAPE, "cuda"> {byre.argname = "K", byre.argtype = 1: i32},
+                 %arg3 : memref<%QSHAPE, "cuda"> {byre.argname = "V", byre.argtype = 1: i32},
+                 %arg4 : memref<%QSHAPE, "cuda"> {byre.argname = "Out", byre.argtype = 2: i32},
+                 %arg5 : memref<%LSHAPE, "cuda"> {byre.argname = "SoftmaxLse", byre.argtype = 2: i32},
+                 %arg6 : memref<%QSHAPE, "cuda"> {byre.argname = "d_Q", byre.argtype = 2: i32},
+                 %arg7 : memref<%QSHAPE, "cuda"> {byre.argname = "d_K", byre.argtype = 2: i32},
+                 %arg8 : memref<%QSHAPE, "cuda"> {byre.argname = "d_V", byre.argtype = 2: i32},
+                 %arg9 : memref<2xi64, "cuda"> {byre.argname = "RngState", byre.argtype = 2: i32},
+                 %arg10 : memref<%LSHAPE, "cuda"> {byre.argname = "d_SoftmaxLse", byre.argtype = 2: i32},
+                 %arg11 : memref<%ASHAPE, "cuda"> {byre.argname = "d_Q_accum", byre.argtype = 2: i32},
+                 %arg12 : memref<1xf32, "cuda"> {byre.argname = "SoftmaxPtr", byre.argtype = 2: i32}) attributes {byre.entry_point} {
+    "byre.custom"(%arg1, %arg2, %arg3, %arg9, %arg4, %arg5, %arg12) {callee = "custom", lib_path = "%LIB", api_name = "run_flash_attn_fwd", version = "2.5.3", extra_args = %EXTRA} : (memref<%QSHAPE, "cuda">, memref<%QSHAPE, "cuda">, memref<%QSHAPE, "cuda">, memref<2xi64, "cuda">, memref<%QSHAPE, "cuda">, memref<%LSHAPE, "cuda">, memref<1xf32, "cuda">) -> ()
+    "byre.custom"(%arg0, %arg1, %arg2, %arg3, %arg4, %arg5, %arg9, %arg6, %arg7, %arg8, %arg10, %arg11) {callee = "custom", lib_path = "%LIB", api_name = "run_flash_attn_bwd", version = "2.5.3", extra_args = %EXTRA} : (memref<%QSHAPE, "cuda">, memref<%QSHAPE, "cuda">, memref<%QSHAPE, "cuda">, memref<%QSHAPE, "cuda">, memref<%QSHAPE, "cuda">, memref<%LSHAPE, "cuda">, memref<2xi64, "cuda">, memref<%QSHAPE, "cuda">, memref<%QSHAPE, "cuda">, memref<%QSHAPE, "cuda">, memref<%LSHAPE, "cuda">, memref<%ASHAPE, "cuda">) -> ()
+    return
+  }
+}
+"""
+
+
+@pytest.mark.parametrize("t", ["f16", "bf16"])
+def test_flash_attn_fwd_bwd_custom_call_through_session(t):
+    """the module of runtime/test/test_files/flash_attn_bwd.mlir, at head dim 128: forward then backward
+    through byre.custom -> libflash_attn.so; bf16 memrefs select the bf16 entry points"""
+    from pathlib import Path
+    b, s, h, d = 1, 256, 3, 128
+    lib = str(Path(__file__).resolve().parent.parent / "byteir_b200" / "_lib" / "libflash_attn.so")
+    extra = [s * h * d] * 4 + [h * d] * 4 + [d] * 4 + [b, h, h, d, d]
+    extra_s = "[" + ", ".join(f"{v} : i64" for v in extra) + f", {0.08838834764831845} : f32, " + \
+        ", ".join(f"{v} : i64" for v in (s, s, s, s)) + ", 0.0 : f32, -1 : i64, 0 : i64]"
+    text = (FLASH.replace("%QSHAPE", f"{b}x{s}x{h}x{d}x{t}").replace("%LSHAPE", f"{b}x{h}x{s}xf32")
+            .replace("%ASHAPE", f"{b}x{h}x{s}x{d}xf32").replace("%LIB", lib).replace("%EXTRA", extra_s))
+    rng = np.random.default_rng(21)
+    mk = lambda: (rng.standard_normal((b, s, h, d), dtype=np.float32).astype(np.float16) if t == "f16"
+                  else O.f32_to_bf16(rng.standard_normal((b, s, h, d), dtype=np.float32)))
+    q, k, v, do = mk(), mk(), mk(), mk()
+    out = _run(text, {"Q": q, "K": k, "V": v, "d_Out": do})
+    scale = 0.08838834764831845
+    wo, wl = O.flash_attn_fwd(q, k, v, scale, True)
+    np.testing.assert_allclose(out["SoftmaxLse"], wl, rtol=1e-3, atol=1e-3)
+    np.testing.assert_allclose(O.to_f32(out["Out"]), O.to_f32(wo), rtol=2e-2, atol=1e-2)
+    wq, wk, wv = O.flash_attn_bwd(do, q, k, v, out["Out"], out["SoftmaxLse"], scale, True)
+    for name, want in (("d_Q", wq), ("d_K", wk), ("d_V", wv)):
+        np.testing.assert_allclose(O.to_f32(out[name]), O.to_f32(want), rtol=2e-2, atol=1e-2, err_msg=name)
