@@ -19,6 +19,30 @@
 #include "indexing/kernels/index_put.h"
 #include "tensor_manipulate/kernels/transpose.h"
 
+#include "brt/backends/cuda/device/common/cuda_call.h"
+
+#include <cstdio>
+#include <stdexcept>
+
+// The reference kernels check launches with BRT_CUDA_CHECK, whose implementation
+// (runtime/lib/backends/cuda/device/common/cuda_call.cc) drags in cuBLAS, cuDNN,
+// CUTLASS and NCCL headers.  The one instantiation the four kernel files use is
+// supplied here with the same contract: throw on a CUDA error.
+namespace brt {
+namespace cuda {
+template <>
+void CudaCall<cudaError, true>(cudaError retCode, const char *exprString, const char *libName,
+                               cudaError successCode, const char *msg) {
+  if (retCode != successCode) {
+    char buf[512];
+    std::snprintf(buf, sizeof(buf), "%s failure %d: %s ; expr=%s ; %s", libName, (int)retCode,
+                  cudaGetErrorString(retCode), exprString, msg);
+    throw std::runtime_error(buf);
+  }
+}
+} // namespace cuda
+} // namespace brt
+
 using namespace brt::cuda::kernel;
 
 extern "C" {
