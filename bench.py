@@ -167,13 +167,16 @@ class ReduceC2(Workload):
     def step_gpu(self, x, dist=None):
         ops = self.ops
         if self.world > 1:
-            # the reduced axis (dim 0 of the global [64 * world, 512, 1024] tensor) is sharded
+            # the reduced axis (dim 0 of the global [64 * world, 512, 1024] tensor) is sharded: the
+            # all-reduce of the 4 KiB of f32 partials runs beside the (independent) max reduction
             ops.reduce_sum_to_f32(x, [0, 1], out=self.part, workspace=self.ws)
-            dist.all_reduce(self.part)
+            work = dist.all_reduce(self.part, async_op=True)
+            ops.reduce_max(x, [2], out=self.out_max)
+            work.wait()
             ops.cast_from_f32(self.part, self.torch.float16, out=self.out_sum)
         else:
             ops.reduce_sum(x, [0, 1], out=self.out_sum, workspace=self.ws)
-        ops.reduce_max(x, [2], out=self.out_max)
+            ops.reduce_max(x, [2], out=self.out_max)
         return self.out_sum, self.out_max
 
     def dominant_gpu(self, x):
@@ -538,8 +541,15 @@ def main():
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-graph", action="store_true", help="time eager launches instead of a CUDA-graph replay")
+    ap.add_argument("--attn-shape", default="", help="B,S,H override of the attention workload (profiling a small case)")
+    ap.add_argument("--watchdog", type=int, default=1500,
+                    help="dump every thread's Python stack and exit if the run takes longer than this many seconds")
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3) if args.impl == "ours" else args.warmup
+
+    if args.watchdog > 0:
+        import faulthandler
+        faulthandler.dump_traceback_later(args.watchdog, exit=True)
 
     rank = int(os.environ.get("RANK", "0"))
     world = int(os.environ.get("WORLD_SIZE", "1"))
@@ -561,6 +571,11 @@ def main():
         dist.init_process_group("nccl", device_id=torch.device("cuda", local_rank))
 
     wl = WORKLOADS[args.workload](rank, world)
+    if args.workload == "attn" and args.attn_shape:
+        wl.B, wl.S, wl.H = (int(v) for v in args.attn_shape.split(","))
+        wl.FWD_FLOPS = 4 * wl.B * wl.H * wl.S * wl.S * wl.D // 2
+        wl.BWD_FLOPS = wl.FWD_FLOPS * 5 // 2
+        wl.name = f"flash_attn_fwd_bwd_bf16_b{wl.B}_s{wl.S}_h{wl.H}_d128_causal"
     per_buf = None
     xs_host = wl.host_inputs(1)
     # rotate over enough distinct inputs that together they exceed L2
@@ -699,9 +714,22 @@ def main():
     h2d = sum(p.numel() * p.element_size() for p in pinned_in[0])
     d2h = sum(p.numel() * p.element_size() for p in pinned_out)
 
-    if rank != 0:
+    def finish():
+        # Tearing the NCCL group down while CUDA graphs that captured its collectives exist has
+        # blocked; the graphs are dropped, the ranks meet once more, and the processes leave
+        # without the group destructor.
+        nonlocal step_graph, dom_graph
+        step_graph = dom_graph = None
+        torch.cuda.synchronize()
         if dist is not None:
-            dist.destroy_process_group()
+            dist.barrier()
+            torch.cuda.synchronize()
+            sys.stdout.flush()
+            sys.stderr.flush()
+            os._exit(0)
+
+    if rank != 0:
+        finish()
         return
 
     peaks = measured_peaks()
@@ -745,8 +773,7 @@ def main():
         "clocks": clocks,
     }
     print(json.dumps(line))
-    if dist is not None:
-        dist.destroy_process_group()
+    finish()
 
 
 if __name__ == "__main__":
