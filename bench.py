@@ -150,7 +150,7 @@ class ReduceC2(Workload):
         return self.SUM_BYTES + self.MAX_BYTES
 
     def launches_per_step(self):
-        return 3 + (1 if self.world > 1 else 0)  # column pass, finalize, row max (+ cast after all-reduce)
+        return 3 + (1 if self.world > 1 else 0)  # column pass, finalize, row max (+ exchange/cast kernel)
 
     def dominant(self):
         return "reduce_cols_kernel+reduce_finalize_kernel (ReduceSum dims {0,1})", self.SUM_BYTES
@@ -163,6 +163,36 @@ class ReduceC2(Workload):
         from byteir_b200 import _native as N
         need = N.lib().b200_reduce_workspace_bytes(0, N.F16, 1, 64 * 512, 1024)
         self.ws = torch.empty(max(need, 1), dtype=torch.uint8, device="cuda")
+        self.exchange = "none"
+        self.sharded = None
+        if self.world > 1:
+            self.exchange = "nccl all-reduce + cast"
+            if os.environ.get("B200_EXCHANGE", "peer") == "peer":
+                try:
+                    self._setup_peer_exchange(torch, ops, N)
+                    self.exchange = "b200_sharded_sum_finish (one kernel over NVLink peer memory)"
+                except Exception as e:  # symmetric memory unavailable: keep NCCL
+                    print(f"peer-memory exchange unavailable ({type(e).__name__}: {e}); using NCCL", file=sys.stderr)
+
+    def _setup_peer_exchange(self, torch, ops, N):
+        import torch.distributed as dist
+        import torch.distributed._symmetric_memory as symm_mem
+        n = 1024
+        inbox_bytes = N.lib().b200_sharded_sum_inbox_bytes(self.world, n)
+        flag_off = (inbox_bytes + 255) // 256 * 256
+        total = flag_off + 256
+        buf = symm_mem.empty(total // 4, dtype=torch.float32, device=torch.device("cuda", torch.cuda.current_device()))
+        buf.zero_()
+        hdl = symm_mem.rendezvous(buf, dist.group.WORLD)
+        ptrs = [int(p) for p in hdl.buffer_ptrs]
+        torch.cuda.synchronize()
+        dist.barrier()  # every inbox and flag word is zero before anyone publishes
+        self._symm = (buf, hdl)
+        self.counter = torch.zeros(1, dtype=torch.int32, device="cuda")
+        self.status = torch.zeros(1, dtype=torch.int32, device="cuda")
+        self.sharded = ops.ShardedSum(self.rank, self.world, n, ptrs, [p + flag_off for p in ptrs],
+                                      self.counter, self.status)
+        self.side = torch.cuda.Stream()
 
     def step_gpu(self, x, dist=None):
         ops = self.ops
@@ -170,10 +200,19 @@ class ReduceC2(Workload):
             # the reduced axis (dim 0 of the global [64 * world, 512, 1024] tensor) is sharded: the
             # all-reduce of the 4 KiB of f32 partials runs beside the (independent) max reduction
             ops.reduce_sum_to_f32(x, [0, 1], out=self.part, workspace=self.ws)
-            work = dist.all_reduce(self.part, async_op=True)
-            ops.reduce_max(x, [2], out=self.out_max)
-            work.wait()
-            ops.cast_from_f32(self.part, self.torch.float16, out=self.out_sum)
+            if self.sharded is not None:
+                # exchange (one block, NVLink latency) beside the max reduction (whole GPU, HBM-bound)
+                cur = self.torch.cuda.current_stream()
+                self.side.wait_stream(cur)
+                with self.torch.cuda.stream(self.side):
+                    self.sharded(self.part, self.out_sum)
+                ops.reduce_max(x, [2], out=self.out_max)
+                cur.wait_stream(self.side)
+            else:
+                work = dist.all_reduce(self.part, async_op=True)
+                ops.reduce_max(x, [2], out=self.out_max)
+                work.wait()
+                ops.cast_from_f32(self.part, self.torch.float16, out=self.out_sum)
         else:
             ops.reduce_sum(x, [0, 1], out=self.out_sum, workspace=self.ws)
             ops.reduce_max(x, [2], out=self.out_max)
@@ -194,6 +233,14 @@ class ReduceC2(Workload):
         if self.world == 1:
             want = O.reduce("sum", x, 1, 64 * 512, 1024)
             np.testing.assert_allclose(s.astype(np.float64), want.astype(np.float64), rtol=2e-2, atol=1e-2)
+        else:
+            # the global tensor is [64 * world, 512, 1024]: rebuild every rank's first shard on this host
+            total = O.reduce_sum_f64(x, 1, 64 * 512, 1024)
+            for r in range(1, self.world):
+                total = total + O.reduce_sum_f64(ReduceC2(r, self.world).host_inputs(1)[0], 1, 64 * 512, 1024)
+            np.testing.assert_allclose(s.astype(np.float64), total, rtol=2e-2, atol=2e-2)
+            if getattr(self, "status", None) is not None:
+                assert int(self.status.item()) == 0, "the peer exchange timed out"
         wm = O.reduce("max", x, 64 * 512, 1024, 1)
         assert np.array_equal(m.reshape(-1).view(np.uint16), wm.view(np.uint16)), "ReduceMax not bit-exact"
 
@@ -501,7 +548,7 @@ def to_dev_default(torch, x):
     return torch.from_numpy(x).cuda()
 
 
-def run_reference(args, rank, world):
+def run_reference(args, rank, world, json_out):
     """The reference arm: the CPU restatement of the reference's op semantics on all
     host cores (the reference's own CPU pipeline needs LLVM/MLIR, which this
     image does not have)."""
@@ -519,7 +566,7 @@ def run_reference(args, rank, world):
     dt = (time.perf_counter() - t0) / args.steps
     cpu_work = wl.cpu_sample_flops() if hasattr(wl, "cpu_sample_flops") else wl.work_per_step()
     val = rate(wl, cpu_work, dt)
-    print(json.dumps({
+    json_out.write(json.dumps({
         "impl": "reference", "metric": metric_of(wl), "value": val, "unit": wl.unit, "n_gpus": args.gpus, "steps": args.steps,
         "warmup": args.warmup, "ms_per_step": dt * 1e3, "higher_is_better": True, "scaling": "weak",
         "vs_baseline": None, "dtype": wl.dtype, "data": "synthetic (seeded)",
@@ -529,7 +576,8 @@ def run_reference(args, rank, world):
         "cpu_baseline": {"value": val, "unit": wl.unit, "cores": cores, "kind": "port",
                          "sample": f"{args.steps} steps on the host"},
         "e2e": {"value": val, "unit": wl.unit, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
-    }))
+    }) + "\n")
+    json_out.flush()
 
 
 def main():
@@ -555,8 +603,14 @@ def main():
     world = int(os.environ.get("WORLD_SIZE", "1"))
     local_rank = int(os.environ.get("LOCAL_RANK", "0"))
 
+    # stdout carries exactly one JSON line: anything a library prints to file descriptor 1
+    # (NCCL's version banner, for one) is sent to stderr instead
+    sys.stdout.flush()
+    json_out = os.fdopen(os.dup(1), "w")
+    os.dup2(2, 1)
+
     if args.impl == "reference":
-        run_reference(args, rank, world)
+        run_reference(args, rank, world, json_out)
         return
 
     import torch
@@ -633,6 +687,11 @@ def main():
     if rank == 0:
         sampler.start()
     ev0, ev1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    if step_graph is not None and world > 1:
+        # Ranks leave the host barrier hundreds of microseconds apart, which is comparable to the whole
+        # timed region.  One more untimed replay is queued right before the timed one: its last
+        # exchange aligns the GPUs to within microseconds, and the timed K steps start from there.
+        step_graph.replay()
     ev0.record()
     if step_graph is not None:
         step_graph.replay()
@@ -765,6 +824,7 @@ def main():
         "config": {"workload": wl.name, "per_gpu_batch": wl.__doc__.strip(),
                    "l2_policy": f"inputs rotate over {n_buf} distinct buffers ({n_buf * per_buf / 2**20:.0f} MiB, L2 is 126 MiB)",
                    "launch": "CUDA graph replay of the K steps" if use_graph else "eager launches",
+                   "exchange": getattr(wl, "exchange", "none"),
                    "parallelism": f"dp{world}"},
         "roofline": roofline, "cpu_baseline": cpu,
         "e2e": {"value": e2e_val, "unit": wl.unit, "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h,
@@ -772,7 +832,8 @@ def main():
         "gpu_launches": wl.launches_per_step() * args.steps,
         "clocks": clocks,
     }
-    print(json.dumps(line))
+    json_out.write(json.dumps(line) + "\n")
+    json_out.flush()
     finish()
 
 

@@ -5,10 +5,12 @@
 //   warp 0      TMA producer: Q once, then K and V tiles into 2-stage rings
 //   warp 1      MMA issuer (one lane): S = Q K^T and O += P V with tcgen05.mma,
 //               accumulators in tensor memory (S double-buffered, O resident)
-//   warps 2..5  softmax: thread t owns query row t; it reads its row of S from
-//               tensor memory, keeps the running max / sum, writes P (16-bit) to
-//               shared memory as the A operand of P V, rescales O in tensor
-//               memory when the running max moved, and writes O / LSE at the end
+//   warps 2..9  softmax: two threads per query row, 64 key columns each; a thread
+//               reads its part of the row of S from tensor memory, keeps the
+//               running max (agreed with its partner) and its part of the row sum,
+//               writes P (16-bit) to shared memory as the A operand of P V,
+//               rescales its half of O in tensor memory when the running max
+//               moved, and writes O / LSE at the end
 // While the softmax warps work on tile j the tensor core already computes
 // S for tile j + 1.
 //
@@ -34,10 +36,12 @@ constexpr int kD = 128;         // head dim
 constexpr int kStages = 2;      // K / V ring depth
 constexpr uint32_t kTileBytes = kBN * kD * 2;  // 32 KiB: two 64-column blocks of 128 x 128 B
 constexpr uint32_t kHalfTile = kTileBytes / 2; // one 64-column block
-constexpr int kThreads = 192;
+constexpr int kThreads = 320;    // forward: producer, MMA issuer, eight softmax warps
+constexpr int kBwdThreads = 192; // backward: producer, MMA issuer, one elementwise group
 constexpr uint32_t kTmemCols = 512;
 constexpr uint32_t kColS0 = 0, kColS1 = 128, kColO = 256;
 constexpr float kRescaleThreshold = 8.0f; // log2 units
+constexpr int kPolyEvery = 4; // forward softmax: one exponential in 4 is a polynomial (0 = none)
 
 struct FwdParams {
   float *lse;
@@ -47,6 +51,38 @@ struct FwdParams {
   int64_t window_left, window_right; // < 0: unbounded
 };
 
+// 2^x for x <= 0 on the FMA/ALU pipes (the MUFU unit, 16 results per clock per SM, is the
+// softmax bottleneck).  Round x to the nearest integer n with the 1.5 * 2^23 trick, evaluate
+// 2^(x - n) on [-0.5, 0.5] with a degree-4 polynomial (relative error 4e-5, well below the
+// 16-bit rounding P gets anyway) and add n to the exponent field.  Below 2^-125: exactly 0.
+__device__ __forceinline__ float exp2_poly(float x) {
+  const float xc = fmaxf(x, -125.f);
+  const float r = xc + 12582912.f;
+  const float f = xc - (r - 12582912.f);
+  float y = fmaf(f, 0.009618129f, 0.05550411f);
+  y = fmaf(y, f, 0.2402265f);
+  y = fmaf(y, f, 0.6931472f);
+  y = fmaf(y, f, 1.0f);
+  const float v = __uint_as_float(__float_as_uint(y) + (__float_as_uint(r) << 23));
+  return x < -125.f ? 0.f : v;
+}
+
+// Named barrier 1 over the N worker threads of a block that also ORs a predicate, so that a
+// decision to give up is taken by all of them together (nobody is left waiting at a barrier).
+template <int N> __device__ __forceinline__ bool named_bar_or_n(bool pred) {
+  uint32_t out;
+  asm volatile("{\n"
+               ".reg .pred p, q;\n"
+               "setp.ne.u32 q, %1, 0;\n"
+               "bar.red.or.pred p, 1, %2, q;\n"
+               "selp.u32 %0, 1, 0, p;\n"
+               "}\n"
+               : "=r"(out)
+               : "r"((uint32_t)pred), "n"(N)
+               : "memory");
+  return out != 0;
+}
+
 struct SharedStorage {
   uint64_t bar_q;
   uint64_t k_full[kStages], k_empty[kStages], v_full[kStages], v_empty[kStages];
@@ -54,6 +90,7 @@ struct SharedStorage {
   uint64_t p_full, o_done;
   uint32_t tmem_base;
   int failed;
+  float xch[2][2][128]; // per-row values the two column halves of the softmax exchange
 };
 
 __device__ __forceinline__ bool wait_or_flag(uint64_t *bar, uint32_t parity, SharedStorage *ss) {
@@ -113,9 +150,9 @@ __global__ void __launch_bounds__(kThreads, 1)
     }
     for (int s = 0; s < 2; ++s) {
       mbar_init(&ss->s_full[s], 1);
-      mbar_init(&ss->s_empty[s], 4);
+      mbar_init(&ss->s_empty[s], 8);
     }
-    mbar_init(&ss->p_full, 4);
+    mbar_init(&ss->p_full, 8);
     mbar_init(&ss->o_done, 1);
     ss->failed = 0;
     mbar_fence_init();
@@ -210,57 +247,70 @@ __global__ void __launch_bounds__(kThreads, 1)
     }
   } else {
     // ------------------------------------------------------------- softmax
-    const int quarter = warp & 3;            // tensor-memory lanes 32 * quarter .. + 31
-    const int row = quarter * 32 + lane;     // query row inside the tile
-    const int64_t qrow = q0 + row;           // global query row
+    // Eight warps: warps 2..5 take key columns 0..63 of the tile, warps 6..9 columns 64..127;
+    // inside each half, thread t owns query row t.  The two threads of a row agree on the row
+    // maximum through shared memory once per tile; their row sums only meet in the epilogue.
+    const int half = (warp - 2) >> 2;          // which 64 key columns (and, for O, which 64 dims)
+    const int quarter = warp & 3;              // tensor-memory lanes 32 * quarter .. + 31
+    const int row = quarter * 32 + lane;       // query row inside the tile
+    const int64_t qrow = q0 + row;             // global query row
     const uint32_t lane_base = (uint32_t)(quarter * 32) << 16;
+    constexpr int kHC = kBN / 2;               // columns per thread
     float m_used = -INFINITY, l = 0.f;
-    bool ok = n > 0;
+    bool ok = n > 0, waits_ok = true;
     for (int j = 0; ok && j < n; ++j) {
-      if (!wait_or_flag(&ss->s_full[j & 1], (uint32_t)((j / 2) & 1), ss)) {
-        ok = false;
-        break;
-      }
+      waits_ok = waits_ok && wait_or_flag(&ss->s_full[j & 1], (uint32_t)((j / 2) & 1), ss);
       tc_fence_after_sync();
-      float s[kBN];
+      // this thread's 64 columns of S into registers; S may then be overwritten by the
+      // Q K^T after next
+      uint32_t s[kHC];
       {
-        const uint32_t base = tmem + lane_base + ((j & 1) ? kColS1 : kColS0);
-#pragma unroll
-        for (int c = 0; c < 4; ++c) {
-          uint32_t r[32];
-          tmem_ld32(base + c * 32, r);
-          tmem_wait_ld();
-#pragma unroll
-          for (int i = 0; i < 32; ++i)
-            s[c * 32 + i] = __uint_as_float(r[i]);
-        }
+        const uint32_t base = tmem + lane_base + ((j & 1) ? kColS1 : kColS0) + half * kHC;
+        tmem_ld32(base, *reinterpret_cast<uint32_t(*)[32]>(&s[0]));
+        tmem_ld32(base + 32, *reinterpret_cast<uint32_t(*)[32]>(&s[32]));
+        tmem_wait_ld();
       }
       tc_fence_before_sync();
       __syncwarp();
       if (lane == 0)
         mbar_arrive(&ss->s_empty[j & 1]);
 
-      const int64_t kv0 = (int64_t)j * kBN;
-      const bool need_mask = (right_bounded && kv0 + kBN - 1 > q0 + shift + p.window_right) ||
-                             (kv0 + kBN > p.Sk) || left_bounded;
-      if (need_mask) {
-        const int64_t hi = right_bounded ? min(p.Sk - 1, qrow + shift + p.window_right) : p.Sk - 1;
-        const int64_t lo = left_bounded ? qrow + shift - p.window_left : 0;
+      const int64_t kv0 = (int64_t)j * kBN + half * kHC; // first key column of this thread
+      const bool need_mask = (right_bounded && (int64_t)j * kBN + kBN - 1 > q0 + shift + p.window_right) ||
+                             ((int64_t)j * kBN + kBN > p.Sk) || left_bounded;
+      if (need_mask) { // visible columns for this row among this thread's 64: [lo, hi]
+        const int64_t hi64 = (right_bounded ? min(p.Sk - 1, qrow + shift + p.window_right) : p.Sk - 1) - kv0;
+        const int64_t lo64 = (left_bounded ? qrow + shift - p.window_left : 0) - kv0;
+        const int hi = (int)max((int64_t)-1, min((int64_t)kHC - 1, hi64));
+        const int lo = (int)max((int64_t)0, min((int64_t)kHC, lo64));
 #pragma unroll
-        for (int c = 0; c < kBN; ++c) {
-          const int64_t kv = kv0 + c;
-          if (kv > hi || kv < lo)
-            s[c] = -INFINITY;
-        }
+        for (int c = 0; c < kHC; ++c)
+          if (c > hi || c < lo)
+            s[c] = 0xff800000u; // -inf
       }
-      float mx = s[0];
+      float mx8[8];
 #pragma unroll
-      for (int c = 1; c < kBN; ++c)
-        mx = fmaxf(mx, s[c]);
+      for (int e = 0; e < 8; ++e)
+        mx8[e] = fmaxf(__uint_as_float(s[2 * e]), __uint_as_float(s[2 * e + 1]));
+#pragma unroll
+      for (int c = 16; c < kHC; c += 16) {
+#pragma unroll
+        for (int e = 0; e < 8; ++e)
+          mx8[e] = fmaxf(mx8[e], fmaxf(__uint_as_float(s[c + 2 * e]), __uint_as_float(s[c + 2 * e + 1])));
+      }
+      float mx = fmaxf(fmaxf(fmaxf(mx8[0], mx8[1]), fmaxf(mx8[2], mx8[3])),
+                       fmaxf(fmaxf(mx8[4], mx8[5]), fmaxf(mx8[6], mx8[7])));
+      // the other half's maximum of the same row (buffers alternate with the tile's parity)
+      ss->xch[j & 1][half][row] = mx;
+      if (named_bar_or_n<256>(!waits_ok)) { // a wait ran out somewhere: all 256 leave together
+        ok = false;
+        break;
+      }
+      mx = fmaxf(mx, ss->xch[j & 1][half ^ 1][row]);
       const float m_new = fmaxf(m_used, mx * p.scale_log2);
       float alpha = 1.f;
       const bool grew = m_new - m_used > kRescaleThreshold; // also true for -inf -> finite
-      const bool rescale = j > 0 && __any_sync(0xffffffffu, grew);
+      const bool rescale = j > 0 && __any_sync(0xffffffffu, grew); // same verdict in both halves
       if (j == 0) {
         m_used = m_new;
       } else if (rescale) {
@@ -269,35 +319,36 @@ __global__ void __launch_bounds__(kThreads, 1)
         l *= alpha;
       }
       const float m_safe = (m_used == -INFINITY) ? 0.f : m_used;
-      float sum = 0.f;
-      uint32_t packed[kBN / 2];
+      // probabilities (one in kPolyEvery on the FMA pipes, the rest on the MUFU unit), four
+      // independent partial sums; the packed 16-bit P reuses the front of the registers
+      float sum4[4] = {0.f, 0.f, 0.f, 0.f};
 #pragma unroll
-      for (int c = 0; c < kBN; c += 2) {
-        const float p0 = fast_exp2(fmaf(s[c], p.scale_log2, -m_safe));
-        const float p1 = fast_exp2(fmaf(s[c + 1], p.scale_log2, -m_safe));
-        sum += p0 + p1;
-        packed[c / 2] = pack2(p0, p1, kBF16);
+      for (int c = 0; c < kHC; c += 2) {
+        const float x0 = fmaf(__uint_as_float(s[c]), p.scale_log2, -m_safe);
+        const float x1 = fmaf(__uint_as_float(s[c + 1]), p.scale_log2, -m_safe);
+        const float p0 = fast_exp2(x0);
+        const float p1 = (kPolyEvery > 0 && (c + 1) % kPolyEvery == kPolyEvery - 1) ? exp2_poly(x1) : fast_exp2(x1);
+        sum4[(c >> 1) & 3] += p0 + p1;
+        s[c >> 1] = pack2(p0, p1, kBF16);
       }
-      l += sum;
+      l += (sum4[0] + sum4[1]) + (sum4[2] + sum4[3]);
 
-      // P's buffer and O are busy until P V of the previous tile has finished
-      if (j > 0 && !wait_or_flag(&ss->o_done, (uint32_t)((j - 1) & 1), ss)) {
-        ok = false;
-        break;
-      }
+      // P's buffer and O are busy until P V of the previous tile has finished (a wait that runs
+      // out is reported at the next barrier)
+      if (j > 0)
+        waits_ok = waits_ok && wait_or_flag(&ss->o_done, (uint32_t)((j - 1) & 1), ss);
       tc_fence_after_sync();
-      // P row -> shared memory, K-major 128-byte swizzled: [2 key blocks][128 rows][128 B]
+      // P row -> shared memory, K-major 128-byte swizzled: [2 key blocks][128 rows][128 B];
+      // this thread's 64 columns are exactly key block `half`
 #pragma unroll
-      for (int ch = 0; ch < 16; ++ch) {
-        const int kb = ch >> 3, chunk = ch & 7;
-        uint4 v = make_uint4(packed[ch * 4], packed[ch * 4 + 1], packed[ch * 4 + 2], packed[ch * 4 + 3]);
-        *reinterpret_cast<uint4 *>(sP + kb * kHalfTile + row * 128 + ((chunk ^ (row & 7)) << 4)) = v;
-      }
+      for (int chunk = 0; chunk < 8; ++chunk)
+        *reinterpret_cast<uint4 *>(sP + half * kHalfTile + row * 128 + ((chunk ^ (row & 7)) << 4)) =
+            make_uint4(s[chunk * 4], s[chunk * 4 + 1], s[chunk * 4 + 2], s[chunk * 4 + 3]);
       fence_proxy_async_smem();
-      if (rescale) {
-        const uint32_t base = tmem + lane_base + kColO;
+      if (rescale) { // this thread's 64 of the row's 128 head dims
+        const uint32_t base = tmem + lane_base + kColO + half * kHC;
 #pragma unroll
-        for (int c = 0; c < 4; ++c) {
+        for (int c = 0; c < 2; ++c) {
           uint32_t r[32];
           tmem_ld32(base + c * 32, r);
           tmem_wait_ld();
@@ -316,15 +367,19 @@ __global__ void __launch_bounds__(kThreads, 1)
 
     // ---- epilogue: O / l -> 16 bit -> shared -> TMA store; LSE
     if (ok && n > 0)
-      ok = wait_or_flag(&ss->o_done, (uint32_t)((n - 1) & 1), ss);
+      waits_ok = waits_ok && wait_or_flag(&ss->o_done, (uint32_t)((n - 1) & 1), ss);
     tc_fence_after_sync();
+    ss->xch[n & 1][half][row] = l; // the row sum is the sum of the two halves' sums
+    if (named_bar_or_n<256>(!waits_ok))
+      ok = false;
+    l += ss->xch[n & 1][half ^ 1][row];
     const float inv_l = (l > 0.f) ? 1.f / l : 0.f;
     const bool have_o = ok && n > 0;
 #pragma unroll
-    for (int c = 0; c < 4; ++c) {
+    for (int c = 0; c < 2; ++c) {
       uint32_t r[32];
       if (have_o) {
-        tmem_ld32(tmem + lane_base + kColO + c * 32, r);
+        tmem_ld32(tmem + lane_base + kColO + half * kHC + c * 32, r);
         tmem_wait_ld();
       } else {
 #pragma unroll
@@ -332,22 +387,21 @@ __global__ void __launch_bounds__(kThreads, 1)
           r[i] = 0u;
       }
 #pragma unroll
-      for (int g = 0; g < 4; ++g) { // 8 columns = one 16-byte chunk
+      for (int g = 0; g < 4; ++g) { // 8 columns = one 16-byte chunk of head-dim block `half`
         uint4 v;
         v.x = pack2(__uint_as_float(r[g * 8 + 0]) * inv_l, __uint_as_float(r[g * 8 + 1]) * inv_l, kBF16);
         v.y = pack2(__uint_as_float(r[g * 8 + 2]) * inv_l, __uint_as_float(r[g * 8 + 3]) * inv_l, kBF16);
         v.z = pack2(__uint_as_float(r[g * 8 + 4]) * inv_l, __uint_as_float(r[g * 8 + 5]) * inv_l, kBF16);
         v.w = pack2(__uint_as_float(r[g * 8 + 6]) * inv_l, __uint_as_float(r[g * 8 + 7]) * inv_l, kBF16);
-        const int col = c * 32 + g * 8; // head-dim column of this chunk
-        const int db = col >> 6, chunk = (col & 63) >> 3;
-        *reinterpret_cast<uint4 *>(sP + db * kHalfTile + row * 128 + ((chunk ^ (row & 7)) << 4)) = v;
+        const int chunk = c * 4 + g;
+        *reinterpret_cast<uint4 *>(sP + half * kHalfTile + row * 128 + ((chunk ^ (row & 7)) << 4)) = v;
       }
     }
     fence_proxy_async_smem();
-    if (qrow < p.Sq)
+    if (half == 0 && qrow < p.Sq)
       p.lse[((int64_t)b * p.H + h) * p.Sq + qrow] =
           (l > 0.f) ? (m_used + log2f(l)) * 0.6931471805599453f : INFINITY;
-    asm volatile("bar.sync 1, 128;" ::: "memory"); // the four softmax warps
+    asm volatile("bar.sync 1, 256;" ::: "memory"); // the eight softmax warps
     if (warp == 2 && lane == 0 && ss->failed == 0) {
       tma_store_4d(&o_map, sP, 0, h, (int)q0, b);
       tma_store_4d(&o_map, sP + kHalfTile, 64, h, (int)q0, b);
@@ -416,21 +470,7 @@ struct BwdStats { // row statistics of the streamed query tile (dK/dV kernel onl
   float dsum[2][128];
 };
 
-// barrier over the four elementwise warps that also ORs a predicate, so that a
-// give-up decision is taken by all 128 threads together
-__device__ __forceinline__ bool named_bar_or(bool pred) {
-  uint32_t out;
-  asm volatile("{\n"
-               ".reg .pred p, q;\n"
-               "setp.ne.u32 q, %1, 0;\n"
-               "bar.red.or.pred p, 1, 128, q;\n"
-               "selp.u32 %0, 1, 0, p;\n"
-               "}\n"
-               : "=r"(out)
-               : "r"((uint32_t)pred)
-               : "memory");
-  return out != 0;
-}
+__device__ __forceinline__ bool named_bar_or(bool pred) { return named_bar_or_n<128>(pred); }
 
 __device__ __forceinline__ bool bwd_wait(uint64_t *bar, uint32_t parity, BwdShared *ss) {
   if (mbar_wait(bar, parity))
@@ -486,7 +526,7 @@ __global__ void __launch_bounds__(256)
 // kDKDV = true : block owns keys [kv0, kv0+128) (rows of the transposed tiles), streams (Q, dO) tiles
 // kDKDV = false: block owns queries [q0, q0+128), streams (K, V) tiles
 template <bool kBF16, bool kDKDV>
-__global__ void __launch_bounds__(kThreads, 1)
+__global__ void __launch_bounds__(kBwdThreads, 1)
     flash_bwd_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_constant__ CUtensorMap k_map,
                      const __grid_constant__ CUtensorMap v_map, const __grid_constant__ CUtensorMap do_map,
                      const __grid_constant__ CUtensorMap out0_map, // dK (kDKDV) or dQ
@@ -816,7 +856,7 @@ int launch_bwd(const CUtensorMap &q_map, const CUtensorMap &k_map, const CUtenso
       return rc;
     attr_set = true;
   }
-  flash_bwd_kernel<kBF16, kDKDV><<<grid, kThreads, smem, stream>>>(q_map, k_map, v_map, do_map, out0, out1, p);
+  flash_bwd_kernel<kBF16, kDKDV><<<grid, kBwdThreads, smem, stream>>>(q_map, k_map, v_map, do_map, out0, out1, p);
   return check_launch();
 }
 

@@ -153,6 +153,7 @@ __global__ void __launch_bounds__(kBlock)
   constexpr int N = 16 / sizeof(T);
   __shared__ float warp_part[kBlock / 32];
   __shared__ float cluster_part;
+  pdl_wait();
   pdl_launch_dependents();
 
   const int groups_per_block = kBlock / tpr;
@@ -256,6 +257,8 @@ __global__ void __launch_bounds__(kBlock)
                              int tpr) {
   constexpr int N = 16 / sizeof(T);
   __shared__ float warp_part[2][kBlock / 32];
+  pdl_wait();
+  pdl_launch_dependents();
   const int groups_per_block = kBlock / tpr;
   const int t = threadIdx.x % tpr;
   const int gib = threadIdx.x / tpr;
@@ -333,28 +336,29 @@ __global__ void __launch_bounds__(kBlock)
 // possible, else 1).  A warp covers `rpw = 32 / lpr` rows of a slab of
 // lpr * NV columns per step; 8 warps stride over the rows of this block's split.
 template <typename T, int OP, int NV, typename OutT>
-__global__ void __launch_bounds__(kBlock)
+__global__ void __launch_bounds__(kBlock, 4)
     reduce_cols_kernel(const T *__restrict__ in, OutT *__restrict__ out, float *__restrict__ partial,
                        int64_t A, int64_t B, int64_t C, int lpr, int slabs, int splits,
                        int64_t rows_per_split) {
-  __shared__ float smem[kBlock / 32][32 * NV];
-  pdl_launch_dependents(); // lets the second pass get scheduled; it waits for this grid's end
+  __shared__ float smem[kBlock * NV]; // [row lane][column of the slab]
+  pdl_wait();              // inputs may come from the kernel launched just before this one
+  pdl_launch_dependents(); // lets the next kernel (the second pass) be scheduled while this one runs
 
   const int64_t bid = blockIdx.x;
   const int slab = (int)(bid % slabs);
   const int64_t rest = bid / slabs;
   const int split = (int)(rest % splits);
   const int64_t a = rest / splits;
-  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const int rpw = 32 / lpr;
-  const int lane_col = lane % lpr, lane_row = lane / lpr;
+  // `lpr` threads cover one row of the slab (16 bytes each); kBlock / lpr rows per step
+  const int row_lanes = kBlock / lpr;
+  const int lane_col = threadIdx.x % lpr, lane_row = threadIdx.x / lpr;
   const int64_t slab_col0 = (int64_t)slab * lpr * NV;
   const int64_t col0 = slab_col0 + (int64_t)lane_col * NV;
-  const bool col_ok = col0 < C; // C % NV == 0, so a lane is all-in or all-out
+  const bool col_ok = col0 < C; // C % NV == 0, so a thread is all-in or all-out
   const int64_t r0 = (int64_t)split * rows_per_split;
   const int64_t r1 = min(B, r0 + rows_per_split);
   const T *base = in + a * B * C + col0;
-  const int64_t step = (int64_t)(kBlock / 32) * rpw;
+  const int64_t step = row_lanes;
 
   float acc[NV];
 #pragma unroll
@@ -388,26 +392,21 @@ __global__ void __launch_bounds__(kBlock)
   };
 
   if (col_ok) {
-    int64_t r = r0 + (int64_t)warp * rpw + lane_row;
+    int64_t r = r0 + lane_row;
     if constexpr (NV > 1) {
-      for (; r + 7 * step < r1; r += 8 * step) {
+      // 8 loads in flight per thread; the last, partial batch is predicated rather than
+      // handled load by load, so the tail does not pay one memory latency per row
+      for (; r < r1; r += 8 * step) {
         uint4 x[8];
 #pragma unroll
         for (int u = 0; u < 8; ++u)
-          x[u] = ld_nc_v4(base + (r + u * step) * C);
+          if (r + u * step < r1)
+            x[u] = ld_nc_v4(base + (r + u * step) * C);
 #pragma unroll
         for (int u = 0; u < 8; ++u)
-          consume(x[u]);
+          if (r + u * step < r1)
+            consume(x[u]);
       }
-      for (; r + 3 * step < r1; r += 4 * step) {
-        uint4 x0 = ld_nc_v4(base + r * C);
-        uint4 x1 = ld_nc_v4(base + (r + step) * C);
-        uint4 x2 = ld_nc_v4(base + (r + 2 * step) * C);
-        uint4 x3 = ld_nc_v4(base + (r + 3 * step) * C);
-        consume(x0), consume(x1), consume(x2), consume(x3);
-      }
-      for (; r < r1; r += step)
-        consume(ld_nc_v4(base + r * C));
     } else {
       for (; r + 3 * step < r1; r += 4 * step) {
         float x0 = Elt<T>::to_f32(base[r * C]);
@@ -420,27 +419,18 @@ __global__ void __launch_bounds__(kBlock)
         acc[0] = op_combine<OP>(acc[0], Elt<T>::to_f32(base[r * C]));
     }
   }
-  // rows handled by the same warp step
-  for (int off = lpr; off < 32; off <<= 1) {
 #pragma unroll
-    for (int j = 0; j < NV; ++j)
-      acc[j] = op_combine<OP>(acc[j], __shfl_xor_sync(0xffffffffu, acc[j], off));
-  }
-  if (lane_row == 0) {
-#pragma unroll
-    for (int j = 0; j < NV; ++j)
-      smem[warp][lane_col * NV + j] = acc[j];
-  }
+  for (int j = 0; j < NV; ++j)
+    smem[(lane_row * lpr + lane_col) * NV + j] = acc[j];
   __syncthreads();
   const int ncols = lpr * NV;
   for (int j = threadIdx.x; j < ncols; j += kBlock) {
     const int64_t col = slab_col0 + j;
     if (col >= C)
       continue;
-    float r = smem[0][j];
-#pragma unroll
-    for (int w = 1; w < kBlock / 32; ++w)
-      r = op_combine<OP>(r, smem[w][j]);
+    float r = smem[j];
+    for (int w = 1; w < row_lanes; ++w)
+      r = op_combine<OP>(r, smem[w * ncols + j]);
     if (OP == kMax && r == 0.f) { // sign of the last zero in [r0, r1)
       const T *colp = in + a * B * C + col;
       for (int64_t rr = r1 - 1; rr >= r0; --rr) {
@@ -467,6 +457,7 @@ __global__ void __launch_bounds__(kBlock)
                            int64_t n, int count, int64_t stride_i, int64_t stride_s) {
   __shared__ float sm[kBlock / 32][32];
   pdl_wait(); // the partials come from the kernel launched just before this one
+  pdl_launch_dependents();
   const int lane = threadIdx.x & 31, slice = threadIdx.x >> 5;
   const int64_t i = (int64_t)blockIdx.x * 32 + lane;
   const int per = (count + kBlock / 32 - 1) / (kBlock / 32);
@@ -501,6 +492,10 @@ __global__ void __launch_bounds__(kBlock)
   if (i < n)
     out[i] = Elt<OutT>::from_f32(in[i]);
 }
+
+// plan constants of the column path (threads that cover one row of a slab; blocks per SM aimed at)
+int g_cols_threads_per_row = 32;
+int g_cols_blocks_per_sm = 4;
 
 // ---- launch plan: a pure function of the shape -----------------------------
 struct Plan {
@@ -541,12 +536,11 @@ Plan make_plan(int esize, int64_t A, int64_t B, int64_t C, bool vec_cols) {
   } else {
     p.rows = false;
     const int NV = vec_cols ? N : 1;
-    p.lpr = (int)std::min<int64_t>(32, pow2_ceil(ceil_div<int64_t>(C, NV)));
+    p.lpr = (int)std::min<int64_t>(g_cols_threads_per_row, pow2_ceil(ceil_div<int64_t>(C, NV)));
     p.slabs = (int)ceil_div<int64_t>(C, (int64_t)p.lpr * NV);
-    const int rpw = 32 / p.lpr;
-    const int64_t rows_per_step = (kBlock / 32) * rpw;
+    const int64_t rows_per_step = kBlock / p.lpr;
     const int64_t blocks = A * p.slabs;
-    int64_t splits = std::max<int64_t>(1, ceil_div<int64_t>(4LL * kNumSMs, blocks));
+    int64_t splits = std::max<int64_t>(1, ceil_div<int64_t>((int64_t)g_cols_blocks_per_sm * kNumSMs, blocks));
     splits = std::min<int64_t>(splits, std::max<int64_t>(1, B / (rows_per_step * 4)));
     p.rows_per_split = ceil_div<int64_t>(B, splits);
     p.splits = (int)ceil_div<int64_t>(B, p.rows_per_split);
@@ -602,12 +596,11 @@ int launch(const T *in, OutT *out, int64_t A, int64_t B, int64_t C, void *ws,
       const int64_t row_blocks = ceil_div<int64_t>(A, groups_per_block);
       const unsigned pgrid = (unsigned)std::min<int64_t>(row_blocks, (int64_t)kNumSMs * (2048 / kBlock));
       if (vpt <= 1)
-        reduce_short_rows_kernel<T, OP, 1, OutT><<<pgrid, kBlock, 0, stream>>>(in, out, A, B, p.tpr);
+        return launch_pdl(reduce_short_rows_kernel<T, OP, 1, OutT>, dim3(pgrid), dim3(kBlock), 0, stream, in, out, A, B, p.tpr);
       else if (vpt == 2)
-        reduce_short_rows_kernel<T, OP, 2, OutT><<<pgrid, kBlock, 0, stream>>>(in, out, A, B, p.tpr);
+        return launch_pdl(reduce_short_rows_kernel<T, OP, 2, OutT>, dim3(pgrid), dim3(kBlock), 0, stream, in, out, A, B, p.tpr);
       else
-        reduce_short_rows_kernel<T, OP, 4, OutT><<<pgrid, kBlock, 0, stream>>>(in, out, A, B, p.tpr);
-      return check_launch();
+        return launch_pdl(reduce_short_rows_kernel<T, OP, 4, OutT>, dim3(pgrid), dim3(kBlock), 0, stream, in, out, A, B, p.tpr);
     }
     if (vec)
       reduce_rows_kernel<T, OP, true, false, OutT><<<(unsigned)grid, kBlock, 0, stream>>>(
@@ -628,19 +621,20 @@ int launch(const T *in, OutT *out, int64_t A, int64_t B, int64_t C, void *ws,
   // the split plan is fixed by the shape; only the lane layout follows `vec`
   Plan q = p;
   if (!vec && cols_vec_by_shape(sizeof(T), C)) {
-    q.lpr = (int)std::min<int64_t>(32, pow2_ceil(C));
+    q.lpr = (int)std::min<int64_t>(g_cols_threads_per_row, pow2_ceil(C));
     q.slabs = (int)ceil_div<int64_t>(C, q.lpr);
   }
   const int64_t grid = A * q.slabs * q.splits;
   if (grid > 0x7fffffffLL)
     return B200_ERR_UNSUPPORTED;
+  int rc;
   if (vec)
-    reduce_cols_kernel<T, OP, N, OutT><<<(unsigned)grid, kBlock, 0, stream>>>(
-        in, out, partial, A, B, C, q.lpr, q.slabs, q.splits, q.rows_per_split);
+    rc = launch_pdl(reduce_cols_kernel<T, OP, N, OutT>, dim3((unsigned)grid), dim3(kBlock), 0, stream, in, out,
+                    partial, A, B, C, q.lpr, q.slabs, q.splits, q.rows_per_split);
   else
-    reduce_cols_kernel<T, OP, 1, OutT><<<(unsigned)grid, kBlock, 0, stream>>>(
-        in, out, partial, A, B, C, q.lpr, q.slabs, q.splits, q.rows_per_split);
-  if (int rc = check_launch())
+    rc = launch_pdl(reduce_cols_kernel<T, OP, 1, OutT>, dim3((unsigned)grid), dim3(kBlock), 0, stream, in, out,
+                    partial, A, B, C, q.lpr, q.slabs, q.splits, q.rows_per_split);
+  if (rc)
     return rc;
   if (q.splits > 1) {
     const int64_t n = A * C;
@@ -785,4 +779,13 @@ extern "C" int b200_reduce_no_alloc(int op, int dtype, const void *in, void *out
     if (int rc = static_scratch_for_current_device(&scratch))
       return rc;
   return b200_reduce(op, dtype, in, out, A, B, C, scratch, need ? kStaticScratchBytes : 0, stream);
+}
+
+// tuning door used by the measurement scripts (not part of the ABI): changes the plan of the column
+// path for subsequent calls; workspace sizes change with it
+extern "C" void b200_reduce_tune(int threads_per_row, int blocks_per_sm) {
+  if (threads_per_row >= 1 && threads_per_row <= kBlock && (threads_per_row & (threads_per_row - 1)) == 0)
+    g_cols_threads_per_row = threads_per_row;
+  if (blocks_per_sm >= 1 && blocks_per_sm <= 16)
+    g_cols_blocks_per_sm = blocks_per_sm;
 }

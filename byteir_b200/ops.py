@@ -244,3 +244,23 @@ def flash_attn_bwd(dout, q, k, v, out, lse, softmax_scale, causal=True, window=(
                                      dv.data_ptr(), d_softmax_sum.data_ptr(), None, C.byref(p), _stream())
     N.check(rc, "b200_flash_attn_bwd")
     return dq, dk, dv
+
+
+class ShardedSum:
+    """Exchange step of a sum whose reduced axis is sharded over ranks (one kernel over NVLink peer
+    memory instead of all-reduce + cast).  `peer_inbox` / `peer_flags`: device addresses per rank of
+    memory all ranks can write (e.g. from torch symmetric memory), `counter`: a zeroed device uint32."""
+
+    def __init__(self, rank, world, n, peer_inbox, peer_flags, counter, status=None):
+        self.rank, self.world, self.n = rank, world, n
+        self._inbox = (C.c_void_p * world)(*peer_inbox)
+        self._flags = (C.c_void_p * world)(*peer_flags)
+        self._counter, self._status = counter, status
+
+    def __call__(self, partial, out):
+        rc = N.lib().b200_sharded_sum_finish(
+            _dt(out), partial.data_ptr(), self._inbox, self._flags, self.rank, self.world, self.n,
+            self._counter.data_ptr(), out.data_ptr(),
+            self._status.data_ptr() if self._status is not None else None, _stream())
+        N.check(rc, "b200_sharded_sum_finish")
+        return out

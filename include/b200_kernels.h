@@ -70,6 +70,30 @@ int b200_reduce_sum_to_f32(int dtype, const void *in, float *out_f32, int64_t A,
 int b200_cast_from_f32(int dtype, const float *in, void *out, int64_t n,
                        cudaStream_t stream);
 
+/* The exchange step of a sum whose reduced axis is sharded over `world` GPUs:
+ * stands in for nccl.AllReduce(sum) on the f32 partials followed by the cast to the
+ * storage type (runtime/lib/backends/nccl/providers/all_reduce.cc:44-69;
+ * DistributedBackendNCCL::all_reduce, distributed_backend_nccl.cc:175-194), as ONE
+ * kernel over NVLink peer memory.  Every rank calls it once per step, in the same
+ * order, with:
+ *   partial       this rank's n unrounded f32 partial sums (b200_reduce_sum_to_f32)
+ *   peer_inbox[p] rank p's inbox, b200_sharded_sum_inbox_bytes(world, n) bytes,
+ *   peer_flags[p] rank p's flag words, world * 4 bytes, zeroed once before first use;
+ *                 both must be memory every rank can write (symmetric / IPC-mapped;
+ *                 host arrays of device pointers, indexed by rank, own rank included)
+ *   epoch_counter a device uint32 of this rank, zeroed once, owned by this call chain
+ *   out           n elements of `dtype`, identical on every rank afterwards
+ * The wait for the peers is bounded (2 s); on expiry *status (device int, may be
+ * NULL) is set to 3 and the kernel ends.  Ranks must not run ahead of each other by
+ * more than this call enforces itself (a rank needs every peer's epoch to finish
+ * one), so no other synchronisation is needed between steps.
+ */
+size_t b200_sharded_sum_inbox_bytes(int world, int64_t n);
+int b200_sharded_sum_finish(int dtype, const float *partial, void *const *peer_inbox,
+                            void *const *peer_flags, int rank, int world, int64_t n,
+                            uint32_t *epoch_counter, void *out, int *status,
+                            cudaStream_t stream);
+
 /* Same reduction as b200_reduce, for callers that have no way to hand in scratch
  * memory.  (No counterpart in the reference: its reduce kernels always get their
  * workspace from the session's allocator.)  A kernel reached through the

@@ -26,7 +26,7 @@ enum StatusCode {
   EP_FAIL = 11
 };
 
-class [[nodiscard]] Status {
+class Status {
 public:
   Status() noexcept = default;
   Status(StatusCategory category, int code, const std::string &msg)

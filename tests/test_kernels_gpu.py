@@ -306,3 +306,43 @@ def test_transpose_config4_shapes(ops):
     y = O.f32_to_bf16(rng.uniform(-1, 1, (8192, 8192)).astype(np.float32))
     got = _to_host(ops.transpose(_to_dev(y), (1, 0)))
     assert np.array_equal(got, np.ascontiguousarray(y.T))
+
+
+def test_sharded_sum_finish_single_rank_protocol(ops):
+    """world = 1: the rank pushes to its own inbox, waits for its own flag, folds, rounds; repeated
+    calls alternate inbox slots and advance the epoch."""
+    from byteir_b200 import _native as N
+    n = 1024
+    inbox = torch.zeros(N.lib().b200_sharded_sum_inbox_bytes(1, n) // 4, dtype=torch.float32, device="cuda")
+    flags = torch.zeros(64, dtype=torch.int32, device="cuda")
+    counter = torch.zeros(1, dtype=torch.int32, device="cuda")
+    status = torch.zeros(1, dtype=torch.int32, device="cuda")
+    ss = ops.ShardedSum(0, 1, n, [inbox.data_ptr()], [flags.data_ptr()], counter, status)
+    out = torch.empty(n, dtype=torch.float16, device="cuda")
+    for step in range(5):
+        part = torch.randn(n, device="cuda") * 100
+        ss(part, out)
+        torch.cuda.synchronize()
+        assert torch.equal(out, part.to(torch.float16))
+        assert int(counter.item()) == step + 1 and int(flags[0].item()) == step + 1
+    assert int(status.item()) == 0
+
+
+def test_sharded_sum_finish_times_out_instead_of_hanging(ops):
+    """a peer that never publishes: the bounded wait expires, the status word says so, the context
+    stays usable (world = 2 with the second rank's memory emulated locally and left silent)"""
+    from byteir_b200 import _native as N
+    n = 256
+    nb = N.lib().b200_sharded_sum_inbox_bytes(2, n) // 4
+    inbox0, inbox1 = (torch.zeros(nb, dtype=torch.float32, device="cuda") for _ in range(2))
+    flags0, flags1 = (torch.zeros(64, dtype=torch.int32, device="cuda") for _ in range(2))
+    counter = torch.zeros(1, dtype=torch.int32, device="cuda")
+    status = torch.zeros(1, dtype=torch.int32, device="cuda")
+    ss = ops.ShardedSum(0, 2, n, [inbox0.data_ptr(), inbox1.data_ptr()], [flags0.data_ptr(), flags1.data_ptr()],
+                        counter, status)
+    out = torch.empty(n, dtype=torch.float32, device="cuda")
+    ss(torch.ones(n, device="cuda"), out)
+    torch.cuda.synchronize()  # returns after the 2 s limit
+    assert int(status.item()) == 3
+    assert int(flags1[0].item()) == 1  # rank 0 did publish to its peer
+    assert float(torch.ones(4, device="cuda").sum().item()) == 4.0
