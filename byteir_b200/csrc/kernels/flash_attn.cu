@@ -1,26 +1,31 @@
 // Flash-attention forward for sm_100a (head dim 128, f16 / bf16, f32 accumulate).
 //
 // One block owns 128 query rows of one (batch, head) and walks over the key/value
-// tiles of 128 rows that the mask lets it see.  Warp roles:
-//   warp 0      TMA producer: Q once, then K and V tiles into 2-stage rings
-//   warp 1      MMA issuer (one lane): S = Q K^T and O += P V with tcgen05.mma,
-//               accumulators in tensor memory (S double-buffered, O resident)
-//   warps 2..9  softmax: two threads per query row, 64 key columns each; a thread
-//               reads its part of the row of S from tensor memory, keeps the
-//               running max (agreed with its partner) and its part of the row sum,
-//               writes P (16-bit) to shared memory as the A operand of P V,
-//               rescales its half of O in tensor memory when the running max
-//               moved, and writes O / LSE at the end
-// While the softmax warps work on tile j the tensor core already computes
-// S for tile j + 1.
+// tiles of 128 rows that the mask lets it see.  Warp roles (three warpgroups):
+//   warp 0        TMA producer of Q (once) and of the K tiles (2-stage ring)
+//   warp 2        TMA producer of the V tiles (2-stage ring)
+//   warp 1        MMA issuer (one lane): S = Q K^T and O += P V with tcgen05.mma,
+//                 accumulators in tensor memory
+//   warps 4..7    softmax group 0: key tiles 0, 2, 4, ...
+//   warps 8..11   softmax group 1: key tiles 1, 3, 5, ...
+// Each group has its own S tile and its own O accumulator in tensor memory, its own
+// P buffer in shared memory and its own running (max, sum) per row, so a group has two
+// MMA periods for the softmax of one tile and the tensor core always has the other
+// group's products to run.  Inside a group thread t owns query row t: it reads its
+// row of S, keeps the running max / sum, writes P (16-bit) to shared memory as the A
+// operand of P V and rescales its O when the running max moved.  At the end the two
+// partial results of a row are merged like two splits of the key axis:
+//   O = (O0 2^(m0-m) + O1 2^(m1-m)) / (l0 2^(m0-m) + l1 2^(m1-m)),  m = max(m0, m1).
+// The control warps give most of their registers to the softmax warps (setmaxnreg).
 //
 // Numerics follow the reference kernel (external_libs/runtime/flash_attn/lib/
 // softmax.h:129-178, flash_fwd_kernel.h:276-453): exp2 domain with the scale
 // folded in, row sum from the unrounded f32 probabilities, P rounded to the
 // storage type before P V, LSE = max * scale + ln(sum), +inf for a fully masked
-// row.  One deviation that does not change the result: O is only rescaled when
+// row.  Deviations that stay inside the rounding of P: O is only rescaled when
 // the running max grew by more than 2^8 (the stale max is used consistently for
-// P, the row sum and the LSE).
+// P, the row sum and the LSE), and one exponential in four is evaluated by a
+// polynomial on the FMA pipes.
 #include <cuda.h>
 
 #include "common.cuh"
@@ -36,10 +41,16 @@ constexpr int kD = 128;         // head dim
 constexpr int kStages = 2;      // K / V ring depth
 constexpr uint32_t kTileBytes = kBN * kD * 2;  // 32 KiB: two 64-column blocks of 128 x 128 B
 constexpr uint32_t kHalfTile = kTileBytes / 2; // one 64-column block
-constexpr int kThreads = 320;    // forward: producer, MMA issuer, eight softmax warps
+constexpr int kThreads = 384;    // forward: four control warps, two softmax groups of four warps
 constexpr int kBwdThreads = 192; // backward: producer, MMA issuer, one elementwise group
 constexpr uint32_t kTmemCols = 512;
-constexpr uint32_t kColS0 = 0, kColS1 = 128, kColO = 256;
+// forward: key tiles of 64 rows, so that two S tiles, two P tiles, Q and two O accumulators
+// share the 512 columns of tensor memory
+constexpr int kFwdBN = 64;
+constexpr int kFwdStages = 4;                        // K / V ring depth of the forward kernel
+constexpr uint32_t kKVTileBytes = kFwdBN * kD * 2;   // 16 KiB: two 64-column blocks of 64 x 128 B
+constexpr uint32_t kKVHalf = kKVTileBytes / 2;
+constexpr uint32_t kColS0 = 0, kColS1 = 64, kColP0 = 128, kColP1 = 160, kColQ = 192, kColO0 = 256, kColO1 = 384;
 constexpr float kRescaleThreshold = 8.0f; // log2 units
 constexpr int kPolyEvery = 4; // forward softmax: one exponential in 4 is a polynomial (0 = none)
 
@@ -84,13 +95,13 @@ template <int N> __device__ __forceinline__ bool named_bar_or_n(bool pred) {
 }
 
 struct SharedStorage {
-  uint64_t bar_q;
-  uint64_t k_full[kStages], k_empty[kStages], v_full[kStages], v_empty[kStages];
-  uint64_t s_full[2], s_empty[2];
-  uint64_t p_full, o_done;
+  uint64_t bar_q, q_ready;
+  uint64_t k_full[kFwdStages], k_empty[kFwdStages], v_full[kFwdStages], v_empty[kFwdStages];
+  uint64_t s_full[2], s_empty[2]; // per softmax group
+  uint64_t p_full[2], o_done[2];  // per softmax group
   uint32_t tmem_base;
   int failed;
-  float xch[2][2][128]; // per-row values the two column halves of the softmax exchange
+  float2 xch[2][kBM]; // (running max, row sum) of each group, for the final merge
 };
 
 __device__ __forceinline__ bool wait_or_flag(uint64_t *bar, uint32_t parity, SharedStorage *ss) {
@@ -98,6 +109,28 @@ __device__ __forceinline__ bool wait_or_flag(uint64_t *bar, uint32_t parity, Sha
     return true;
   ss->failed = 1; // some arrival never came: every role gives up at its next wait
   return false;
+}
+
+// The MMA-issuing warp runs its loop with all 32 lanes (waits included) and only the
+// tcgen05 instructions themselves are executed by one elected lane: descriptors and
+// addresses then live in uniform registers, which is what the instruction takes, and
+// an issue costs ~10 cycles instead of ~55 from inside a single-lane branch.
+__device__ __forceinline__ bool elect_one() {
+  uint32_t pred;
+  asm volatile("{\n"
+               ".reg .pred P;\n"
+               "elect.sync _|P, 0xffffffff;\n"
+               "selp.u32 %0, 1, 0, P;\n"
+               "}\n"
+               : "=r"(pred));
+  return pred != 0;
+}
+// all 32 lanes wait; the verdict is the same in every lane
+__device__ __forceinline__ bool warp_wait_or_flag(uint64_t *bar, uint32_t parity, SharedStorage *ss) {
+  const bool ok = __all_sync(0xffffffffu, mbar_wait(bar, parity));
+  if (!ok)
+    ss->failed = 1;
+  return ok;
 }
 
 __device__ __forceinline__ uint32_t pack2(float lo, float hi, bool bf16) {
@@ -117,13 +150,12 @@ __global__ void __launch_bounds__(kThreads, 1)
   extern __shared__ __align__(1024) unsigned char smem_raw[];
   unsigned char *smem =
       reinterpret_cast<unsigned char *>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
-  unsigned char *sQ = smem;
+  unsigned char *sQ = smem; // Q on its way to tensor memory; the finished O tile at the end
   unsigned char *sK = sQ + kTileBytes;
-  unsigned char *sV = sK + kStages * kTileBytes;
-  unsigned char *sP = sV + kStages * kTileBytes;
-  SharedStorage *ss = reinterpret_cast<SharedStorage *>(sP + kTileBytes);
+  unsigned char *sV = sK + kFwdStages * kKVTileBytes;
+  SharedStorage *ss = reinterpret_cast<SharedStorage *>(sV + kFwdStages * kKVTileBytes);
 
-  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int warp = __shfl_sync(0xffffffffu, threadIdx.x >> 5, 0), lane = threadIdx.x & 31; // warp: known uniform
   const int n_q_tiles = (int)((p.Sq + kBM - 1) / kBM);
   const int q_tile = n_q_tiles - 1 - (int)blockIdx.x; // longest rows first
   const int h = blockIdx.y, b = blockIdx.z;
@@ -133,27 +165,28 @@ __global__ void __launch_bounds__(kThreads, 1)
   const bool right_bounded = p.window_right >= 0;
   const bool left_bounded = p.window_left >= 0;
 
-  // key tiles this block visits: [0, n)
-  int n = (int)((p.Sk + kBN - 1) / kBN);
+  // key tiles (64 keys each) this block visits: [0, n)
+  int n = (int)((p.Sk + kFwdBN - 1) / kFwdBN);
   if (right_bounded) {
     const int64_t last_visible = q0 + kBM - 1 + shift + p.window_right;
-    n = last_visible < 0 ? 0 : (int)min((int64_t)n, last_visible / kBN + 1);
+    n = last_visible < 0 ? 0 : (int)min((int64_t)n, last_visible / kFwdBN + 1);
   }
 
   if (threadIdx.x == 0) {
     mbar_init(&ss->bar_q, 1);
-    for (int s = 0; s < kStages; ++s) {
+    mbar_init(&ss->q_ready, 4);
+    for (int s = 0; s < kFwdStages; ++s) {
       mbar_init(&ss->k_full[s], 1);
       mbar_init(&ss->k_empty[s], 1);
       mbar_init(&ss->v_full[s], 1);
       mbar_init(&ss->v_empty[s], 1);
     }
-    for (int s = 0; s < 2; ++s) {
-      mbar_init(&ss->s_full[s], 1);
-      mbar_init(&ss->s_empty[s], 8);
+    for (int g = 0; g < 2; ++g) {
+      mbar_init(&ss->s_full[g], 1);
+      mbar_init(&ss->s_empty[g], 4);
+      mbar_init(&ss->p_full[g], 4);
+      mbar_init(&ss->o_done[g], 1);
     }
-    mbar_init(&ss->p_full, 8);
-    mbar_init(&ss->o_done, 1);
     ss->failed = 0;
     mbar_fence_init();
   }
@@ -167,105 +200,145 @@ __global__ void __launch_bounds__(kThreads, 1)
   const uint32_t tmem = ss->tmem_base;
 
   if (warp == 0) {
-    // ------------------------------------------------------------- producer
+    // ----------------------------------------------------------- producer of Q and K
     if (lane == 0 && n > 0) {
       prefetch_tensormap(&q_map);
       prefetch_tensormap(&k_map);
-      prefetch_tensormap(&v_map);
       mbar_arrive_expect_tx(&ss->bar_q, kTileBytes);
       tma_load_4d(sQ, &q_map, 0, h, (int)q0, b, &ss->bar_q);
       tma_load_4d(sQ + kHalfTile, &q_map, 64, h, (int)q0, b, &ss->bar_q);
       for (int j = 0; j < n; ++j) {
-        const int st = j % kStages;
-        const uint32_t ph = (uint32_t)((j / kStages) & 1);
-        if (!wait_or_flag(&ss->k_empty[st], ph ^ 1, ss))
+        const int st = j % kFwdStages;
+        if (!wait_or_flag(&ss->k_empty[st], (uint32_t)(((j / kFwdStages) & 1) ^ 1), ss))
           break;
-        mbar_arrive_expect_tx(&ss->k_full[st], kTileBytes);
-        tma_load_4d(sK + st * kTileBytes, &k_map, 0, hk, j * kBN, b, &ss->k_full[st]);
-        tma_load_4d(sK + st * kTileBytes + kHalfTile, &k_map, 64, hk, j * kBN, b, &ss->k_full[st]);
-        if (!wait_or_flag(&ss->v_empty[st], ph ^ 1, ss))
+        mbar_arrive_expect_tx(&ss->k_full[st], kKVTileBytes);
+        tma_load_4d(sK + st * kKVTileBytes, &k_map, 0, hk, j * kFwdBN, b, &ss->k_full[st]);
+        tma_load_4d(sK + st * kKVTileBytes + kKVHalf, &k_map, 64, hk, j * kFwdBN, b, &ss->k_full[st]);
+      }
+    }
+  } else if (warp == 2) {
+    // ----------------------------------------------------------- producer of V
+    if (lane == 0 && n > 0) {
+      prefetch_tensormap(&v_map);
+      for (int j = 0; j < n; ++j) {
+        const int st = j % kFwdStages;
+        if (!wait_or_flag(&ss->v_empty[st], (uint32_t)(((j / kFwdStages) & 1) ^ 1), ss))
           break;
-        mbar_arrive_expect_tx(&ss->v_full[st], kTileBytes);
-        tma_load_4d(sV + st * kTileBytes, &v_map, 0, hk, j * kBN, b, &ss->v_full[st]);
-        tma_load_4d(sV + st * kTileBytes + kHalfTile, &v_map, 64, hk, j * kBN, b, &ss->v_full[st]);
+        mbar_arrive_expect_tx(&ss->v_full[st], kKVTileBytes);
+        tma_load_4d(sV + st * kKVTileBytes, &v_map, 0, hk, j * kFwdBN, b, &ss->v_full[st]);
+        tma_load_4d(sV + st * kKVTileBytes + kKVHalf, &v_map, 64, hk, j * kFwdBN, b, &ss->v_full[st]);
       }
     }
   } else if (warp == 1) {
-    // ------------------------------------------------------------- MMA issuer
-    if (lane == 0 && n > 0) {
-      constexpr uint32_t idesc_qk = umma_idesc_f16(kBF16, kBM, kBN, false, false);
+    // ----------------------------------------------------------- MMA issuer
+    // Both products take their A operand from tensor memory (Q, copied there once; P, written
+    // there by the softmax warps), so shared memory only feeds the B operands K and V.
+    if (n > 0) {
+      constexpr uint32_t idesc_qk = umma_idesc_f16(kBF16, kBM, kFwdBN, false, false);
       constexpr uint32_t idesc_pv = umma_idesc_f16(kBF16, kBM, kD, false, true);
-      const uint32_t q_addr = smem_addr(sQ), k_addr = smem_addr(sK), v_addr = smem_addr(sV), p_addr = smem_addr(sP);
-      auto issue_qk = [&](int j) { // S[j & 1] = Q K_j^T
-        const int st = j % kStages;
-        const uint32_t d_tmem = tmem + ((j & 1) ? kColS1 : kColS0);
+      const uint32_t tm = __shfl_sync(0xffffffffu, tmem, 0);
+      const uint32_t k_addr = smem_addr(sK), v_addr = smem_addr(sV);
+      auto issue_qk = [&](int j) { // S[j & 1] = Q K_j^T: 8 steps of 16 head dims
+        const int st = j % kFwdStages;
+        const uint32_t d_tmem = tm + ((j & 1) ? kColS1 : kColS0);
 #pragma unroll
-        for (int kb = 0; kb < 2; ++kb)
-#pragma unroll
-          for (int ks = 0; ks < 4; ++ks) {
-            const uint32_t off = kb * kHalfTile + ks * 32;
-            umma_ss(d_tmem, umma_smem_desc(q_addr + off, 16, 1024),
-                    umma_smem_desc(k_addr + st * kTileBytes + off, 16, 1024), idesc_qk, (kb | ks) != 0);
-          }
-        umma_commit(&ss->s_full[j & 1]);
-        umma_commit(&ss->k_empty[st]);
+        for (int kk = 0; kk < 8; ++kk) {
+          const uint64_t bdesc =
+              umma_smem_desc(k_addr + st * kKVTileBytes + (kk >> 2) * kKVHalf + (kk & 3) * 32, 16, 1024);
+          if (elect_one())
+            umma_ts(d_tmem, tm + kColQ + kk * 8, bdesc, idesc_qk, kk != 0);
+        }
+        if (elect_one()) {
+          umma_commit(&ss->s_full[j & 1]);
+          umma_commit(&ss->k_empty[st]);
+        }
       };
-      bool ok = wait_or_flag(&ss->bar_q, 0, ss) && wait_or_flag(&ss->k_full[0], 0, ss);
-      if (ok) {
-        tc_fence_after_sync();
-        issue_qk(0);
+      bool ok = warp_wait_or_flag(&ss->q_ready, 0, ss);
+      for (int j = 0; ok && j < 2 && j < n; ++j) {
+        ok = warp_wait_or_flag(&ss->k_full[j % kFwdStages], 0, ss);
+        if (ok) {
+          tc_fence_after_sync();
+          issue_qk(j);
+        }
       }
       for (int j = 0; ok && j < n; ++j) {
-        if (j + 1 < n) {
-          const int st = (j + 1) % kStages;
-          ok = wait_or_flag(&ss->k_full[st], (uint32_t)(((j + 1) / kStages) & 1), ss) &&
-               wait_or_flag(&ss->s_empty[(j + 1) & 1], (uint32_t)((((j + 1) / 2) & 1) ^ 1), ss);
+        const int g = j & 1, i = j >> 1; // tile j is the i-th tile of softmax group g
+        if (j + 2 < n) {
+          // S of group g is free again once the group has its i-th tile in registers
+          const int st = (j + 2) % kFwdStages;
+          ok = warp_wait_or_flag(&ss->k_full[st], (uint32_t)(((j + 2) / kFwdStages) & 1), ss) &&
+               warp_wait_or_flag(&ss->s_empty[g], (uint32_t)(i & 1), ss);
           if (!ok)
             break;
           tc_fence_after_sync();
-          issue_qk(j + 1);
+          issue_qk(j + 2);
         }
-        const int st = j % kStages;
-        ok = wait_or_flag(&ss->p_full, (uint32_t)(j & 1), ss) &&
-             wait_or_flag(&ss->v_full[st], (uint32_t)((j / kStages) & 1), ss);
+        const int st = j % kFwdStages;
+        ok = warp_wait_or_flag(&ss->p_full[g], (uint32_t)(i & 1), ss) &&
+             warp_wait_or_flag(&ss->v_full[st], (uint32_t)((j / kFwdStages) & 1), ss);
         if (!ok)
           break;
         tc_fence_after_sync();
 #pragma unroll
-        for (int kb = 0; kb < 2; ++kb)
-#pragma unroll
-          for (int ks = 0; ks < 4; ++ks) {
-            // A: P[:, 16 keys] (K-major); B: V[16 keys, 128 dims] (dims contiguous = MN-major)
-            const uint64_t adesc = umma_smem_desc(p_addr + kb * kHalfTile + ks * 32, 16, 1024);
-            const uint64_t bdesc =
-                umma_smem_desc(v_addr + st * kTileBytes + (kb * 64 + ks * 16) * 128, kHalfTile, 1024);
-            umma_ss(tmem + kColO, adesc, bdesc, idesc_pv, (j | kb | ks) != 0);
-          }
-        umma_commit(&ss->o_done);
-        umma_commit(&ss->v_empty[st]);
+        for (int ks = 0; ks < 4; ++ks) {
+          // A: P[:, 16 keys] in tensor memory; B: V[16 keys, 128 dims] (dims contiguous = MN-major)
+          const uint64_t bdesc = umma_smem_desc(v_addr + st * kKVTileBytes + ks * 16 * 128, kKVHalf, 1024);
+          if (elect_one())
+            umma_ts(tm + (g ? kColO1 : kColO0), tm + (g ? kColP1 : kColP0) + ks * 8, bdesc, idesc_pv,
+                    (i | ks) != 0);
+        }
+        if (elect_one()) {
+          umma_commit(&ss->o_done[g]);
+          umma_commit(&ss->v_empty[st]);
+        }
       }
     }
-  } else {
+  } else if (warp >= 4) {
     // ------------------------------------------------------------- softmax
-    // Eight warps: warps 2..5 take key columns 0..63 of the tile, warps 6..9 columns 64..127;
-    // inside each half, thread t owns query row t.  The two threads of a row agree on the row
-    // maximum through shared memory once per tile; their row sums only meet in the epilogue.
-    const int half = (warp - 2) >> 2;          // which 64 key columns (and, for O, which 64 dims)
-    const int quarter = warp & 3;              // tensor-memory lanes 32 * quarter .. + 31
-    const int row = quarter * 32 + lane;       // query row inside the tile
-    const int64_t qrow = q0 + row;             // global query row
+    const int g = (warp - 4) >> 2;           // group: key tiles g, g + 2, g + 4, ...
+    const int quarter = warp & 3;            // tensor-memory lanes 32 * quarter .. + 31
+    const int row = quarter * 32 + lane;     // query row inside the tile
+    const int64_t qrow = q0 + row;           // global query row
     const uint32_t lane_base = (uint32_t)(quarter * 32) << 16;
-    constexpr int kHC = kBN / 2;               // columns per thread
+    const uint32_t col_s = g ? kColS1 : kColS0, col_o = g ? kColO1 : kColO0, col_p = g ? kColP1 : kColP0;
+    const int n_mine = (n + 1 - g) >> 1;
     float m_used = -INFINITY, l = 0.f;
-    bool ok = n > 0, waits_ok = true;
-    for (int j = 0; ok && j < n; ++j) {
-      waits_ok = waits_ok && wait_or_flag(&ss->s_full[j & 1], (uint32_t)((j / 2) & 1), ss);
+    bool ok = true;
+
+    if (g == 0 && n > 0) {
+      // Q row -> tensor memory (two 16-bit head dims per 32-bit column), as the A operand of Q K^T
+      ok = wait_or_flag(&ss->bar_q, 0, ss);
+#pragma unroll
+      for (int db = 0; db < 2; ++db) {
+        uint32_t r[32];
+#pragma unroll
+        for (int c = 0; c < 8; ++c) {
+          const uint4 v = *reinterpret_cast<const uint4 *>(sQ + db * kHalfTile + row * 128 + ((c ^ (row & 7)) << 4));
+          r[c * 4 + 0] = v.x;
+          r[c * 4 + 1] = v.y;
+          r[c * 4 + 2] = v.z;
+          r[c * 4 + 3] = v.w;
+        }
+        tmem_st32(tmem + lane_base + kColQ + db * 32, r);
+      }
+      tmem_wait_st();
+      tc_fence_before_sync();
+      __syncwarp();
+      if (lane == 0 && ok)
+        mbar_arrive(&ss->q_ready);
+    }
+
+    for (int i = 0; ok && i < n_mine; ++i) {
+      const int j = 2 * i + g;
+      if (!wait_or_flag(&ss->s_full[g], (uint32_t)(i & 1), ss)) {
+        ok = false;
+        break;
+      }
       tc_fence_after_sync();
-      // this thread's 64 columns of S into registers; S may then be overwritten by the
-      // Q K^T after next
-      uint32_t s[kHC];
+      // the whole row of S into registers; S may then be overwritten by the group's next Q K^T
+      uint32_t s[kFwdBN];
       {
-        const uint32_t base = tmem + lane_base + ((j & 1) ? kColS1 : kColS0) + half * kHC;
+        const uint32_t base = tmem + lane_base + col_s;
         tmem_ld32(base, *reinterpret_cast<uint32_t(*)[32]>(&s[0]));
         tmem_ld32(base + 32, *reinterpret_cast<uint32_t(*)[32]>(&s[32]));
         tmem_wait_ld();
@@ -273,45 +346,39 @@ __global__ void __launch_bounds__(kThreads, 1)
       tc_fence_before_sync();
       __syncwarp();
       if (lane == 0)
-        mbar_arrive(&ss->s_empty[j & 1]);
+        mbar_arrive(&ss->s_empty[g]);
 
-      const int64_t kv0 = (int64_t)j * kBN + half * kHC; // first key column of this thread
-      const bool need_mask = (right_bounded && (int64_t)j * kBN + kBN - 1 > q0 + shift + p.window_right) ||
-                             ((int64_t)j * kBN + kBN > p.Sk) || left_bounded;
-      if (need_mask) { // visible columns for this row among this thread's 64: [lo, hi]
+      const int64_t kv0 = (int64_t)j * kFwdBN;
+      const bool need_mask = (right_bounded && kv0 + kFwdBN - 1 > q0 + shift + p.window_right) ||
+                             (kv0 + kFwdBN > p.Sk) || left_bounded;
+      if (need_mask) { // visible columns of this tile for this row: [lo, hi]
         const int64_t hi64 = (right_bounded ? min(p.Sk - 1, qrow + shift + p.window_right) : p.Sk - 1) - kv0;
         const int64_t lo64 = (left_bounded ? qrow + shift - p.window_left : 0) - kv0;
-        const int hi = (int)max((int64_t)-1, min((int64_t)kHC - 1, hi64));
-        const int lo = (int)max((int64_t)0, min((int64_t)kHC, lo64));
+        const int hi = (int)max((int64_t)-1, min((int64_t)kFwdBN - 1, hi64));
+        const int lo = (int)max((int64_t)0, min((int64_t)kFwdBN, lo64));
 #pragma unroll
-        for (int c = 0; c < kHC; ++c)
+        for (int c = 0; c < kFwdBN; ++c)
           if (c > hi || c < lo)
             s[c] = 0xff800000u; // -inf
       }
+      // row maximum: eight independent chains
       float mx8[8];
 #pragma unroll
       for (int e = 0; e < 8; ++e)
         mx8[e] = fmaxf(__uint_as_float(s[2 * e]), __uint_as_float(s[2 * e + 1]));
 #pragma unroll
-      for (int c = 16; c < kHC; c += 16) {
+      for (int c = 16; c < kFwdBN; c += 16) {
 #pragma unroll
         for (int e = 0; e < 8; ++e)
           mx8[e] = fmaxf(mx8[e], fmaxf(__uint_as_float(s[c + 2 * e]), __uint_as_float(s[c + 2 * e + 1])));
       }
-      float mx = fmaxf(fmaxf(fmaxf(mx8[0], mx8[1]), fmaxf(mx8[2], mx8[3])),
-                       fmaxf(fmaxf(mx8[4], mx8[5]), fmaxf(mx8[6], mx8[7])));
-      // the other half's maximum of the same row (buffers alternate with the tile's parity)
-      ss->xch[j & 1][half][row] = mx;
-      if (named_bar_or_n<256>(!waits_ok)) { // a wait ran out somewhere: all 256 leave together
-        ok = false;
-        break;
-      }
-      mx = fmaxf(mx, ss->xch[j & 1][half ^ 1][row]);
+      const float mx = fmaxf(fmaxf(fmaxf(mx8[0], mx8[1]), fmaxf(mx8[2], mx8[3])),
+                             fmaxf(fmaxf(mx8[4], mx8[5]), fmaxf(mx8[6], mx8[7])));
       const float m_new = fmaxf(m_used, mx * p.scale_log2);
       float alpha = 1.f;
       const bool grew = m_new - m_used > kRescaleThreshold; // also true for -inf -> finite
-      const bool rescale = j > 0 && __any_sync(0xffffffffu, grew); // same verdict in both halves
-      if (j == 0) {
+      const bool rescale = i > 0 && __any_sync(0xffffffffu, grew);
+      if (i == 0) {
         m_used = m_new;
       } else if (rescale) {
         alpha = (m_new == -INFINITY) ? 1.f : fast_exp2(m_used - m_new);
@@ -320,91 +387,100 @@ __global__ void __launch_bounds__(kThreads, 1)
       }
       const float m_safe = (m_used == -INFINITY) ? 0.f : m_used;
       // probabilities (one in kPolyEvery on the FMA pipes, the rest on the MUFU unit), four
-      // independent partial sums; the packed 16-bit P reuses the front of the registers
+      // independent partial sums; the packed 16-bit P reuses the front of the row's registers
       float sum4[4] = {0.f, 0.f, 0.f, 0.f};
+      uint32_t(&packed)[kFwdBN] = s;
 #pragma unroll
-      for (int c = 0; c < kHC; c += 2) {
+      for (int c = 0; c < kFwdBN; c += 2) {
         const float x0 = fmaf(__uint_as_float(s[c]), p.scale_log2, -m_safe);
         const float x1 = fmaf(__uint_as_float(s[c + 1]), p.scale_log2, -m_safe);
         const float p0 = fast_exp2(x0);
         const float p1 = (kPolyEvery > 0 && (c + 1) % kPolyEvery == kPolyEvery - 1) ? exp2_poly(x1) : fast_exp2(x1);
         sum4[(c >> 1) & 3] += p0 + p1;
-        s[c >> 1] = pack2(p0, p1, kBF16);
+        packed[c >> 1] = pack2(p0, p1, kBF16);
       }
       l += (sum4[0] + sum4[1]) + (sum4[2] + sum4[3]);
 
-      // P's buffer and O are busy until P V of the previous tile has finished (a wait that runs
-      // out is reported at the next barrier)
-      if (j > 0)
-        waits_ok = waits_ok && wait_or_flag(&ss->o_done, (uint32_t)((j - 1) & 1), ss);
+      // the group's P columns and O are busy until P V of its previous tile has finished
+      if (i > 0 && !wait_or_flag(&ss->o_done[g], (uint32_t)((i - 1) & 1), ss)) {
+        ok = false;
+        break;
+      }
       tc_fence_after_sync();
-      // P row -> shared memory, K-major 128-byte swizzled: [2 key blocks][128 rows][128 B];
-      // this thread's 64 columns are exactly key block `half`
+      // P row -> tensor memory: 64 keys = 32 columns of two 16-bit values
+      tmem_st32(tmem + lane_base + col_p, *reinterpret_cast<uint32_t(*)[32]>(&packed[0]));
+      if (rescale) {
+        const uint32_t base = tmem + lane_base + col_o;
 #pragma unroll
-      for (int chunk = 0; chunk < 8; ++chunk)
-        *reinterpret_cast<uint4 *>(sP + half * kHalfTile + row * 128 + ((chunk ^ (row & 7)) << 4)) =
-            make_uint4(s[chunk * 4], s[chunk * 4 + 1], s[chunk * 4 + 2], s[chunk * 4 + 3]);
-      fence_proxy_async_smem();
-      if (rescale) { // this thread's 64 of the row's 128 head dims
-        const uint32_t base = tmem + lane_base + kColO + half * kHC;
-#pragma unroll
-        for (int c = 0; c < 2; ++c) {
+        for (int c = 0; c < 4; ++c) {
           uint32_t r[32];
           tmem_ld32(base + c * 32, r);
           tmem_wait_ld();
 #pragma unroll
-          for (int i = 0; i < 32; ++i)
-            r[i] = __float_as_uint(__uint_as_float(r[i]) * alpha);
+          for (int q = 0; q < 32; ++q)
+            r[q] = __float_as_uint(__uint_as_float(r[q]) * alpha);
           tmem_st32(base + c * 32, r);
         }
-        tmem_wait_st();
       }
+      tmem_wait_st();
       tc_fence_before_sync();
       __syncwarp();
       if (lane == 0)
-        mbar_arrive(&ss->p_full);
+        mbar_arrive(&ss->p_full[g]);
     }
 
-    // ---- epilogue: O / l -> 16 bit -> shared -> TMA store; LSE
-    if (ok && n > 0)
-      waits_ok = waits_ok && wait_or_flag(&ss->o_done, (uint32_t)((n - 1) & 1), ss);
+    // ---- epilogue: merge the two groups' partial results, O / l -> 16 bit -> shared -> TMA store; LSE
+    if (ok && n_mine > 0)
+      ok = wait_or_flag(&ss->o_done[g], (uint32_t)((n_mine - 1) & 1), ss);
+    ss->xch[g][row] = make_float2(m_used, l);
+    tc_fence_before_sync();
+    const bool give_up = named_bar_or_n<256>(!ok); // both groups; every product and load is complete
     tc_fence_after_sync();
-    ss->xch[n & 1][half][row] = l; // the row sum is the sum of the two halves' sums
-    if (named_bar_or_n<256>(!waits_ok))
-      ok = false;
-    l += ss->xch[n & 1][half ^ 1][row];
-    const float inv_l = (l > 0.f) ? 1.f / l : 0.f;
-    const bool have_o = ok && n > 0;
+    const float2 other = ss->xch[g ^ 1][row];
+    const float m_tot = fmaxf(m_used, other.x);
+    const float a_mine = (m_used == -INFINITY) ? 0.f : fast_exp2(m_used - m_tot);
+    const float a_other = (other.x == -INFINITY) ? 0.f : fast_exp2(other.x - m_tot);
+    const float l_tot = l * a_mine + other.y * a_other;
+    const float inv_l = (l_tot > 0.f) ? 1.f / l_tot : 0.f;
+    const float w0 = (g == 0 ? a_mine : a_other) * inv_l; // weight of group 0's accumulator
+    const float w1 = (g == 0 ? a_other : a_mine) * inv_l;
+    const bool have0 = !give_up && n > 0, have1 = !give_up && n > 1;
+    // this thread finishes head-dim columns [64 g, 64 g + 64) of its row; staging in Q's tile
 #pragma unroll
     for (int c = 0; c < 2; ++c) {
-      uint32_t r[32];
-      if (have_o) {
-        tmem_ld32(tmem + lane_base + kColO + half * kHC + c * 32, r);
-        tmem_wait_ld();
-      } else {
+      uint32_t r0[32], r1[32];
+      if (have0)
+        tmem_ld32(tmem + lane_base + kColO0 + g * 64 + c * 32, r0);
+      if (have1)
+        tmem_ld32(tmem + lane_base + kColO1 + g * 64 + c * 32, r1);
+      tmem_wait_ld();
+      float o[32];
 #pragma unroll
-        for (int i = 0; i < 32; ++i)
-          r[i] = 0u;
+      for (int q = 0; q < 32; ++q) {
+        float acc = have0 ? __uint_as_float(r0[q]) * w0 : 0.f;
+        if (have1)
+          acc = fmaf(__uint_as_float(r1[q]), w1, acc);
+        o[q] = acc;
       }
 #pragma unroll
-      for (int g = 0; g < 4; ++g) { // 8 columns = one 16-byte chunk of head-dim block `half`
+      for (int q = 0; q < 4; ++q) { // 8 columns = one 16-byte chunk
         uint4 v;
-        v.x = pack2(__uint_as_float(r[g * 8 + 0]) * inv_l, __uint_as_float(r[g * 8 + 1]) * inv_l, kBF16);
-        v.y = pack2(__uint_as_float(r[g * 8 + 2]) * inv_l, __uint_as_float(r[g * 8 + 3]) * inv_l, kBF16);
-        v.z = pack2(__uint_as_float(r[g * 8 + 4]) * inv_l, __uint_as_float(r[g * 8 + 5]) * inv_l, kBF16);
-        v.w = pack2(__uint_as_float(r[g * 8 + 6]) * inv_l, __uint_as_float(r[g * 8 + 7]) * inv_l, kBF16);
-        const int chunk = c * 4 + g;
-        *reinterpret_cast<uint4 *>(sP + half * kHalfTile + row * 128 + ((chunk ^ (row & 7)) << 4)) = v;
+        v.x = pack2(o[q * 8 + 0], o[q * 8 + 1], kBF16);
+        v.y = pack2(o[q * 8 + 2], o[q * 8 + 3], kBF16);
+        v.z = pack2(o[q * 8 + 4], o[q * 8 + 5], kBF16);
+        v.w = pack2(o[q * 8 + 6], o[q * 8 + 7], kBF16);
+        const int chunk = c * 4 + q;
+        *reinterpret_cast<uint4 *>(sQ + g * kHalfTile + row * 128 + ((chunk ^ (row & 7)) << 4)) = v;
       }
     }
     fence_proxy_async_smem();
-    if (half == 0 && qrow < p.Sq)
+    if (g == 0 && qrow < p.Sq)
       p.lse[((int64_t)b * p.H + h) * p.Sq + qrow] =
-          (l > 0.f) ? (m_used + log2f(l)) * 0.6931471805599453f : INFINITY;
-    asm volatile("bar.sync 1, 256;" ::: "memory"); // the eight softmax warps
-    if (warp == 2 && lane == 0 && ss->failed == 0) {
-      tma_store_4d(&o_map, sP, 0, h, (int)q0, b);
-      tma_store_4d(&o_map, sP + kHalfTile, 64, h, (int)q0, b);
+          (l_tot > 0.f) ? (m_tot + log2f(l_tot)) * 0.6931471805599453f : INFINITY;
+    asm volatile("bar.sync 2, 256;" ::: "memory"); // both softmax groups
+    if (warp == 4 && lane == 0 && ss->failed == 0) {
+      tma_store_4d(&o_map, sQ, 0, h, (int)q0, b);
+      tma_store_4d(&o_map, sQ + kHalfTile, 64, h, (int)q0, b);
       bulk_commit();
       bulk_wait_all<0>();
     }
@@ -421,10 +497,11 @@ __global__ void __launch_bounds__(kThreads, 1)
 }
 
 int make_qkv_map(CUtensorMap *map, bool bf16, const void *base, int64_t d, int64_t heads, int64_t seq,
-                 int64_t batch, int64_t head_stride, int64_t row_stride, int64_t batch_stride) {
+                 int64_t batch, int64_t head_stride, int64_t row_stride, int64_t batch_stride,
+                 uint32_t box_rows = 128) {
   const uint64_t dims[4] = {(uint64_t)d, (uint64_t)heads, (uint64_t)seq, (uint64_t)batch};
   const uint64_t strides[3] = {(uint64_t)head_stride * 2, (uint64_t)row_stride * 2, (uint64_t)batch_stride * 2};
-  const uint32_t box[4] = {64, 1, 128, 1};
+  const uint32_t box[4] = {64, 1, box_rows, 1};
   return make_tensor_map(map, bf16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 4,
                          const_cast<void *>(base), dims, strides, box, CU_TENSOR_MAP_SWIZZLE_128B);
 }
@@ -887,9 +964,9 @@ extern "C" int b200_flash_attn_fwd(int dtype, const void *q, const void *k, cons
   CUtensorMap q_map, k_map, v_map, o_map;
   if (int rc = make_qkv_map(&q_map, bf16, q, a.d, a.h, a.seqlen_q, a.b, a.q_head_stride, a.q_row_stride, a.q_batch_stride))
     return rc;
-  if (int rc = make_qkv_map(&k_map, bf16, k, a.d, a.h_k, a.seqlen_k, a.b, a.k_head_stride, a.k_row_stride, a.k_batch_stride))
+  if (int rc = make_qkv_map(&k_map, bf16, k, a.d, a.h_k, a.seqlen_k, a.b, a.k_head_stride, a.k_row_stride, a.k_batch_stride, kFwdBN))
     return rc;
-  if (int rc = make_qkv_map(&v_map, bf16, v, a.d, a.h_k, a.seqlen_k, a.b, a.v_head_stride, a.v_row_stride, a.v_batch_stride))
+  if (int rc = make_qkv_map(&v_map, bf16, v, a.d, a.h_k, a.seqlen_k, a.b, a.v_head_stride, a.v_row_stride, a.v_batch_stride, kFwdBN))
     return rc;
   if (int rc = make_qkv_map(&o_map, bf16, out, a.d, a.h, a.seqlen_q, a.b, a.o_head_stride, a.o_row_stride, a.o_batch_stride))
     return rc;
@@ -903,7 +980,7 @@ extern "C" int b200_flash_attn_fwd(int dtype, const void *q, const void *k, cons
   p.scale_log2 = a.softmax_scale * 1.4426950408889634f;
   p.window_left = a.window_size_left;
   p.window_right = a.window_size_right;
-  const size_t smem = (size_t)(1 + 2 * kStages + 1) * kTileBytes + sizeof(SharedStorage) + 1024;
+  const size_t smem = (size_t)kTileBytes + 2 * kFwdStages * kKVTileBytes + sizeof(SharedStorage) + 1024;
   static bool attr_set[2] = {false, false};
   if (!attr_set[bf16]) {
     cudaError_t e = bf16 ? cudaFuncSetAttribute(flash_fwd_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem)
