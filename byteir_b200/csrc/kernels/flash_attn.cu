@@ -38,7 +38,6 @@ namespace {
 constexpr int kBM = 128;        // query rows per block
 constexpr int kBN = 128;        // key rows per tile
 constexpr int kD = 128;         // head dim
-constexpr int kStages = 2;      // K / V ring depth
 constexpr uint32_t kTileBytes = kBN * kD * 2;  // 32 KiB: two 64-column blocks of 128 x 128 B
 constexpr uint32_t kHalfTile = kTileBytes / 2; // one 64-column block
 constexpr int kThreads = 384;    // forward: four control warps, two softmax groups of four warps
@@ -131,6 +130,22 @@ __device__ __forceinline__ bool warp_wait_or_flag(uint64_t *bar, uint32_t parity
   if (!ok)
     ss->failed = 1;
   return ok;
+}
+
+// two barriers at once: the polls overlap instead of following each other
+__device__ __forceinline__ bool warp_wait2_or_flag(uint64_t *bar_a, uint32_t parity_a, uint64_t *bar_b,
+                                                   uint32_t parity_b, SharedStorage *ss) {
+  bool done_a = false, done_b = false;
+  for (uint32_t it = 0; it < 4000000u; ++it) {
+    const bool a = done_a || mbar_try_wait(bar_a, parity_a);
+    const bool b = done_b || mbar_try_wait(bar_b, parity_b);
+    done_a = a;
+    done_b = b;
+    if (__all_sync(0xffffffffu, a && b))
+      return true;
+  }
+  ss->failed = 1;
+  return false;
 }
 
 __device__ __forceinline__ uint32_t pack2(float lo, float hi, bool bf16) {
@@ -230,52 +245,49 @@ __global__ void __launch_bounds__(kThreads, 1)
       }
     }
   } else if (warp == 1) {
-    // ----------------------------------------------------------- MMA issuer
+    // ----------------------------------------------------------- issuer of S = Q K^T
     // Both products take their A operand from tensor memory (Q, copied there once; P, written
-    // there by the softmax warps), so shared memory only feeds the B operands K and V.
+    // there by the softmax warps), so shared memory only feeds the B operands K and V.  The two
+    // products have their own issuing warps: each loop is two waits and a handful of
+    // instructions per tile, and neither product ever queues behind a wait of the other.
     if (n > 0) {
       constexpr uint32_t idesc_qk = umma_idesc_f16(kBF16, kBM, kFwdBN, false, false);
-      constexpr uint32_t idesc_pv = umma_idesc_f16(kBF16, kBM, kD, false, true);
       const uint32_t tm = __shfl_sync(0xffffffffu, tmem, 0);
-      const uint32_t k_addr = smem_addr(sK), v_addr = smem_addr(sV);
-      auto issue_qk = [&](int j) { // S[j & 1] = Q K_j^T: 8 steps of 16 head dims
-        const int st = j % kFwdStages;
-        const uint32_t d_tmem = tm + ((j & 1) ? kColS1 : kColS0);
+      const uint32_t k_addr = smem_addr(sK);
+      bool ok = warp_wait_or_flag(&ss->q_ready, 0, ss);
+      for (int j = 0; ok && j < n; ++j) {
+        const int g = j & 1, i = j >> 1, st = j % kFwdStages; // tile j is the i-th tile of softmax group g
+        // S of group g is free once the group has its previous tile in registers
+        ok = warp_wait2_or_flag(&ss->k_full[st], (uint32_t)((j / kFwdStages) & 1), &ss->s_empty[g],
+                                (uint32_t)((i & 1) ^ 1), ss);
+        if (!ok)
+          break;
+        tc_fence_after_sync();
+        const uint32_t d_tmem = tm + (g ? kColS1 : kColS0);
 #pragma unroll
-        for (int kk = 0; kk < 8; ++kk) {
+        for (int kk = 0; kk < 8; ++kk) { // 8 steps of 16 head dims
           const uint64_t bdesc =
               umma_smem_desc(k_addr + st * kKVTileBytes + (kk >> 2) * kKVHalf + (kk & 3) * 32, 16, 1024);
           if (elect_one())
             umma_ts(d_tmem, tm + kColQ + kk * 8, bdesc, idesc_qk, kk != 0);
         }
         if (elect_one()) {
-          umma_commit(&ss->s_full[j & 1]);
+          umma_commit(&ss->s_full[g]);
           umma_commit(&ss->k_empty[st]);
         }
-      };
-      bool ok = warp_wait_or_flag(&ss->q_ready, 0, ss);
-      for (int j = 0; ok && j < 2 && j < n; ++j) {
-        ok = warp_wait_or_flag(&ss->k_full[j % kFwdStages], 0, ss);
-        if (ok) {
-          tc_fence_after_sync();
-          issue_qk(j);
-        }
       }
+    }
+  } else if (warp == 3) {
+    // ----------------------------------------------------------- issuer of O += P V
+    if (n > 0) {
+      constexpr uint32_t idesc_pv = umma_idesc_f16(kBF16, kBM, kD, false, true);
+      const uint32_t tm = __shfl_sync(0xffffffffu, tmem, 0);
+      const uint32_t v_addr = smem_addr(sV);
+      bool ok = true;
       for (int j = 0; ok && j < n; ++j) {
-        const int g = j & 1, i = j >> 1; // tile j is the i-th tile of softmax group g
-        if (j + 2 < n) {
-          // S of group g is free again once the group has its i-th tile in registers
-          const int st = (j + 2) % kFwdStages;
-          ok = warp_wait_or_flag(&ss->k_full[st], (uint32_t)(((j + 2) / kFwdStages) & 1), ss) &&
-               warp_wait_or_flag(&ss->s_empty[g], (uint32_t)(i & 1), ss);
-          if (!ok)
-            break;
-          tc_fence_after_sync();
-          issue_qk(j + 2);
-        }
-        const int st = j % kFwdStages;
-        ok = warp_wait_or_flag(&ss->p_full[g], (uint32_t)(i & 1), ss) &&
-             warp_wait_or_flag(&ss->v_full[st], (uint32_t)((j / kFwdStages) & 1), ss);
+        const int g = j & 1, i = j >> 1, st = j % kFwdStages;
+        ok = warp_wait2_or_flag(&ss->v_full[st], (uint32_t)((j / kFwdStages) & 1), &ss->p_full[g],
+                                (uint32_t)(i & 1), ss);
         if (!ok)
           break;
         tc_fence_after_sync();
@@ -556,6 +568,13 @@ __device__ __forceinline__ bool bwd_wait(uint64_t *bar, uint32_t parity, BwdShar
   return false;
 }
 
+__device__ __forceinline__ bool bwd_warp_wait(uint64_t *bar, uint32_t parity, BwdShared *ss) {
+  const bool ok = __all_sync(0xffffffffu, mbar_wait(bar, parity));
+  if (!ok)
+    ss->failed = 1;
+  return ok;
+}
+
 // 16-byte chunk `chunk16` (0..15: 8 columns each) of row `row` of a 128 x 128 16-bit
 // tile stored as [2 column blocks][128 rows][128 B] with the 128-byte swizzle
 __device__ __forceinline__ void store_tile_chunk(unsigned char *tile, int row, int chunk16, uint4 v) {
@@ -624,7 +643,7 @@ __global__ void __launch_bounds__(kBwdThreads, 1)
   BwdShared *ss = reinterpret_cast<BwdShared *>(sDS + (kDKDV ? 2 : 1) * kTileBytes);
   BwdStats *stats = reinterpret_cast<BwdStats *>(ss + 1); // present only if kDKDV
 
-  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int warp = __shfl_sync(0xffffffffu, threadIdx.x >> 5, 0), lane = threadIdx.x & 31; // warp: known uniform
   const int b = blockIdx.z;
   const int64_t shift = p.Sk - p.Sq;
   const bool right_bounded = p.window_right >= 0;
@@ -719,63 +738,67 @@ __global__ void __launch_bounds__(kBwdThreads, 1)
     }
   } else if (warp == 1) {
     // ------------------------------------------------------------- MMA issuer
-    if (lane == 0 && T > 0) {
+    // all 32 lanes run the loop and the waits; one elected lane executes the tcgen05 instructions
+    if (T > 0) {
       constexpr uint32_t idesc_nt = umma_idesc_f16(kBF16, 128, 128, false, false); // A, B both K-major
       constexpr uint32_t idesc_nn = umma_idesc_f16(kBF16, 128, 128, false, true);  // B rows = K index
+      const uint32_t tm = __shfl_sync(0xffffffffu, tmem, 0);
       const uint32_t res0 = smem_addr(sRes0), res1 = smem_addr(sRes1), str = smem_addr(sStr);
       const uint32_t p_addr = smem_addr(sP), ds_addr = smem_addr(sDS);
-      bool ok = bwd_wait(&ss->bar_resident, 0, ss);
+      bool ok = bwd_warp_wait(&ss->bar_resident, 0, ss);
       for (int it = 0; ok && it < T; ++it) {
         const int st = it % kBwdStages;
         const uint32_t t0 = str + st * 2 * kTileBytes, t1 = t0 + kTileBytes;
-        ok = bwd_wait(&ss->full[st], (uint32_t)((it / kBwdStages) & 1), ss) &&
-             bwd_wait(&ss->st_empty, (uint32_t)((it & 1) ^ 1), ss);
+        ok = bwd_warp_wait(&ss->full[st], (uint32_t)((it / kBwdStages) & 1), ss) &&
+             bwd_warp_wait(&ss->st_empty, (uint32_t)((it & 1) ^ 1), ss);
         if (!ok)
           break;
         tc_fence_after_sync();
         // kDKDV: S^T = K Q^T, dP^T = V dO^T ; else: S = Q K^T, dP = dO V^T  (contraction over head dim)
 #pragma unroll
-        for (int kb = 0; kb < 2; ++kb)
+        for (int kk = 0; kk < 8; ++kk) {
+          const uint32_t off = (kk >> 2) * kHalfTile + (kk & 3) * 32;
+          const uint64_t adesc = umma_smem_desc(res0 + off, 16, 1024), bdesc = umma_smem_desc(t0 + off, 16, 1024);
+          if (elect_one())
+            umma_ss(tm + kColS0, adesc, bdesc, idesc_nt, kk != 0);
+        }
 #pragma unroll
-          for (int ks = 0; ks < 4; ++ks) {
-            const uint32_t off = kb * kHalfTile + ks * 32;
-            umma_ss(tmem + kColS0, umma_smem_desc(res0 + off, 16, 1024), umma_smem_desc(t0 + off, 16, 1024),
-                    idesc_nt, (kb | ks) != 0);
-          }
-#pragma unroll
-        for (int kb = 0; kb < 2; ++kb)
-#pragma unroll
-          for (int ks = 0; ks < 4; ++ks) {
-            const uint32_t off = kb * kHalfTile + ks * 32;
-            umma_ss(tmem + kColDP, umma_smem_desc(res1 + off, 16, 1024), umma_smem_desc(t1 + off, 16, 1024),
-                    idesc_nt, (kb | ks) != 0);
-          }
-        umma_commit(&ss->st_full);
-        ok = bwd_wait(&ss->pds_full, (uint32_t)(it & 1), ss);
+        for (int kk = 0; kk < 8; ++kk) {
+          const uint32_t off = (kk >> 2) * kHalfTile + (kk & 3) * 32;
+          const uint64_t adesc = umma_smem_desc(res1 + off, 16, 1024), bdesc = umma_smem_desc(t1 + off, 16, 1024);
+          if (elect_one())
+            umma_ss(tm + kColDP, adesc, bdesc, idesc_nt, kk != 0);
+        }
+        if (elect_one())
+          umma_commit(&ss->st_full);
+        ok = bwd_warp_wait(&ss->pds_full, (uint32_t)(it & 1), ss);
         if (!ok)
           break;
         tc_fence_after_sync();
         // contraction over the 128 streamed (kDKDV: query) or owned-side columns of P / dS
 #pragma unroll
-        for (int kb = 0; kb < 2; ++kb)
-#pragma unroll
-          for (int ks = 0; ks < 4; ++ks) {
-            const uint32_t a_off = kb * kHalfTile + ks * 32;
-            const uint32_t b_off = (kb * 64 + ks * 16) * 128;
-            if (kDKDV) {
-              // dV += P^T dO ; dK += dS^T Q   (B = streamed tiles, rows = queries)
-              umma_ss(tmem + kColAcc0, umma_smem_desc(p_addr + a_off, 16, 1024),
-                      umma_smem_desc(t1 + b_off, kHalfTile, 1024), idesc_nn, (it | kb | ks) != 0);
-              umma_ss(tmem + kColAcc1, umma_smem_desc(ds_addr + a_off, 16, 1024),
-                      umma_smem_desc(t0 + b_off, kHalfTile, 1024), idesc_nn, (it | kb | ks) != 0);
-            } else {
-              // dQ += dS K   (B = streamed K tile, rows = keys)
-              umma_ss(tmem + kColAcc0, umma_smem_desc(ds_addr + a_off, 16, 1024),
-                      umma_smem_desc(t0 + b_off, kHalfTile, 1024), idesc_nn, (it | kb | ks) != 0);
+        for (int kk = 0; kk < 8; ++kk) {
+          const uint32_t a_off = (kk >> 2) * kHalfTile + (kk & 3) * 32;
+          const uint32_t b_off = ((kk >> 2) * 64 + (kk & 3) * 16) * 128;
+          if (kDKDV) {
+            // dV += P^T dO ; dK += dS^T Q   (B = streamed tiles, rows = queries)
+            const uint64_t a0 = umma_smem_desc(p_addr + a_off, 16, 1024), b0 = umma_smem_desc(t1 + b_off, kHalfTile, 1024);
+            const uint64_t a1 = umma_smem_desc(ds_addr + a_off, 16, 1024), b1 = umma_smem_desc(t0 + b_off, kHalfTile, 1024);
+            if (elect_one()) {
+              umma_ss(tm + kColAcc0, a0, b0, idesc_nn, (it | kk) != 0);
+              umma_ss(tm + kColAcc1, a1, b1, idesc_nn, (it | kk) != 0);
             }
+          } else {
+            // dQ += dS K   (B = streamed K tile, rows = keys)
+            const uint64_t a0 = umma_smem_desc(ds_addr + a_off, 16, 1024), b0 = umma_smem_desc(t0 + b_off, kHalfTile, 1024);
+            if (elect_one())
+              umma_ss(tm + kColAcc0, a0, b0, idesc_nn, (it | kk) != 0);
           }
-        umma_commit(&ss->pds_empty);
-        umma_commit(&ss->empty[st]);
+        }
+        if (elect_one()) {
+          umma_commit(&ss->pds_empty);
+          umma_commit(&ss->empty[st]);
+        }
       }
     }
   } else {
@@ -813,9 +836,27 @@ __global__ void __launch_bounds__(kBwdThreads, 1)
         break;
       }
       tc_fence_after_sync();
-      // visibility of (query, key): key <= query + shift + wr, key >= query + shift - wl, both in range
-      const int64_t q_base = kDKDV ? str0 : own_idx; // + column if kDKDV
-      const int64_t k_base = kDKDV ? own_idx : str0; // + column if !kDKDV
+      // visibility of (query, key): key <= query + shift + wr, key >= query + shift - wl, both in
+      // range.  For this thread's row that is a column interval [lo, hi] of the tile; most tiles
+      // are fully visible and skip the masking altogether.
+      int lo, hi;
+      {
+        int64_t lo64, hi64;
+        if (kDKDV) { // row = key own_idx, columns = queries str0 + c
+          hi64 = (left_bounded ? min(p.Sq - 1, own_idx - shift + p.window_left) : p.Sq - 1) - str0;
+          lo64 = (right_bounded ? own_idx - shift - p.window_right : 0) - str0;
+          if (own_idx >= p.Sk)
+            hi64 = -1;
+        } else { // row = query own_idx, columns = keys str0 + c
+          hi64 = (right_bounded ? min(p.Sk - 1, own_idx + shift + p.window_right) : p.Sk - 1) - str0;
+          lo64 = (left_bounded ? own_idx + shift - p.window_left : 0) - str0;
+          if (own_idx >= p.Sq)
+            hi64 = -1;
+        }
+        hi = (int)max((int64_t)-1, min((int64_t)127, hi64));
+        lo = (int)max((int64_t)0, min((int64_t)128, lo64));
+      }
+      const bool need_mask = __any_sync(0xffffffffu, lo > 0 || hi < 127);
 #pragma unroll
       for (int c = 0; c < 4; ++c) {
         uint32_t sr[32], dr[32];
@@ -828,6 +869,12 @@ __global__ void __launch_bounds__(kBwdThreads, 1)
           if (lane == 0)
             mbar_arrive(&ss->st_empty);
         }
+        if (need_mask) {
+#pragma unroll
+          for (int i = 0; i < 32; ++i)
+            if (c * 32 + i > hi || c * 32 + i < lo)
+              sr[i] = 0xff800000u; // -inf: P = 0, dS = 0
+        }
         uint32_t pp[16], dd[16];
 #pragma unroll
         for (int i = 0; i < 32; i += 2) {
@@ -835,16 +882,9 @@ __global__ void __launch_bounds__(kBwdThreads, 1)
 #pragma unroll
           for (int e = 0; e < 2; ++e) {
             const int col = c * 32 + i + e;
-            const int64_t qi = kDKDV ? q_base + col : q_base;
-            const int64_t ki = kDKDV ? k_base : k_base + col;
             const float l2 = kDKDV ? stats->lse2[it & 1][col] : my_lse2;
             const float ds_ = kDKDV ? stats->dsum[it & 1][col] : my_dsum;
-            bool vis = qi < p.Sq && ki < p.Sk;
-            if (right_bounded)
-              vis = vis && ki <= qi + shift + p.window_right;
-            if (left_bounded)
-              vis = vis && ki >= qi + shift - p.window_left;
-            const float pr = vis ? fast_exp2(fmaf(__uint_as_float(sr[i + e]), p.scale_log2, -l2)) : 0.f;
+            const float pr = fast_exp2(fmaf(__uint_as_float(sr[i + e]), p.scale_log2, -l2));
             pv[e] = pr;
             dv[e] = pr * (__uint_as_float(dr[i + e]) - ds_);
           }
