@@ -1,22 +1,25 @@
 // Flash-attention forward for sm_100a (head dim 128, f16 / bf16, f32 accumulate).
 //
 // One block owns 128 query rows of one (batch, head) and walks over the key/value
-// tiles of 128 rows that the mask lets it see.  Warp roles (three warpgroups):
-//   warp 0        TMA producer of Q (once) and of the K tiles (2-stage ring)
-//   warp 2        TMA producer of the V tiles (2-stage ring)
-//   warp 1        MMA issuer (one lane): S = Q K^T and O += P V with tcgen05.mma,
-//                 accumulators in tensor memory
+// tiles of 64 rows that the mask lets it see.  Warp roles (three warpgroups):
+//   warp 0        TMA producer of Q (once) and of the K tiles (4-stage ring)
+//   warp 2        TMA producer of the V tiles (4-stage ring)
+//   warp 1        issuer of S = Q K^T   (tcgen05.mma; all lanes run the loop, one elected lane issues)
+//   warp 3        issuer of O += P V
 //   warps 4..7    softmax group 0: key tiles 0, 2, 4, ...
 //   warps 8..11   softmax group 1: key tiles 1, 3, 5, ...
-// Each group has its own S tile and its own O accumulator in tensor memory, its own
-// P buffer in shared memory and its own running (max, sum) per row, so a group has two
-// MMA periods for the softmax of one tile and the tensor core always has the other
-// group's products to run.  Inside a group thread t owns query row t: it reads its
-// row of S, keeps the running max / sum, writes P (16-bit) to shared memory as the A
-// operand of P V and rescales its O when the running max moved.  At the end the two
-// partial results of a row are merged like two splits of the key axis:
+// Both products read their A operand from tensor memory: Q is copied there once per
+// block, P is written there by the softmax warps, so shared memory only feeds the B
+// operands K and V (the bandwidth of shared memory, 128 B per clock, is what bounds a
+// product with both operands there).  Each group has its own S tile, P tile and O
+// accumulator in tensor memory and its own running (max, sum) per row, so a group has
+// two MMA periods for the softmax of one tile and the tensor core always has the other
+// group's products to run.  Tensor-memory columns: S 0,64 | P 128,160 | Q 192 | O 256,384.
+// Inside a group thread t owns query row t: it reads its row of S, keeps the running
+// max / sum, writes P (16-bit) back to tensor memory and rescales its O when the running
+// max moved.  At the end the two partial results of a row are merged like two splits of
+// the key axis:
 //   O = (O0 2^(m0-m) + O1 2^(m1-m)) / (l0 2^(m0-m) + l1 2^(m1-m)),  m = max(m0, m1).
-// The control warps give most of their registers to the softmax warps (setmaxnreg).
 //
 // Numerics follow the reference kernel (external_libs/runtime/flash_attn/lib/
 // softmax.h:129-178, flash_fwd_kernel.h:276-453): exp2 domain with the scale
@@ -40,8 +43,7 @@ constexpr int kBN = 128;        // key rows per tile
 constexpr int kD = 128;         // head dim
 constexpr uint32_t kTileBytes = kBN * kD * 2;  // 32 KiB: two 64-column blocks of 128 x 128 B
 constexpr uint32_t kHalfTile = kTileBytes / 2; // one 64-column block
-constexpr int kThreads = 384;    // forward: four control warps, two softmax groups of four warps
-constexpr int kBwdThreads = 192; // backward: producer, MMA issuer, one elementwise group
+constexpr int kThreads = 384;    // four control warps, two groups of four softmax / elementwise warps
 constexpr uint32_t kTmemCols = 512;
 // forward: key tiles of 64 rows, so that two S tiles, two P tiles, Q and two O accumulators
 // share the 512 columns of tensor memory
@@ -89,6 +91,21 @@ template <int N> __device__ __forceinline__ bool named_bar_or_n(bool pred) {
                "}\n"
                : "=r"(out)
                : "r"((uint32_t)pred), "n"(N)
+               : "memory");
+  return out != 0;
+}
+
+// the same over 128 threads with the barrier number chosen at run time
+__device__ __forceinline__ bool named_bar_or_id(int id, bool pred) {
+  uint32_t out;
+  asm volatile("{\n"
+               ".reg .pred p, q;\n"
+               "setp.ne.u32 q, %1, 0;\n"
+               "bar.red.or.pred p, %2, 128, q;\n"
+               "selp.u32 %0, 1, 0, p;\n"
+               "}\n"
+               : "=r"(out)
+               : "r"((uint32_t)pred), "r"(id)
                : "memory");
   return out != 0;
 }
@@ -536,7 +553,15 @@ int make_qkv_map(CUtensorMap *map, bool bf16, const void *base, int64_t d, int64
 // that the thread that owns a key row writes rows of P^T and dS^T, which are the
 // K-major A operands of dV += P^T dO and dK += dS^T Q.
 
-constexpr uint32_t kColDP = 128, kColAcc0 = 256, kColAcc1 = 384;
+// Tensor-memory columns.  S / dP tiles are 128 x 64 (64 streamed rows per step) and
+// double-buffered, one buffer per elementwise group; P and dS (16 bit) overwrite the
+// front of the S / dP buffer they were computed from.
+//   dK/dV kernel: S^T 0,64 | dP^T 128,192 | dV 256 | dK 384
+//   dQ kernel:    Q 0 | dO 64 (A operands) | S 128,192 | dP 256,320 | dQ 384
+constexpr int kBwdBN = 64;       // streamed rows per step
+constexpr int kBwdStages = 4;    // ring depth of the streamed (row tile, row tile) pairs
+constexpr uint32_t kStrTileBytes = kBwdBN * kD * 2; // 16 KiB: [2 column blocks][64 rows][128 B]
+constexpr uint32_t kStrHalf = kStrTileBytes / 2;
 
 struct BwdParams {
   const float *lse;   // [B, H, Sq]
@@ -547,19 +572,16 @@ struct BwdParams {
 };
 
 struct BwdShared {
-  uint64_t bar_resident;          // the block's own tiles (K,V or Q,dO)
-  uint64_t full[2], empty[2];     // streamed tile pairs
-  uint64_t st_full, st_empty;     // S / dP in tensor memory
-  uint64_t pds_full, pds_empty;   // P / dS in shared memory
+  uint64_t bar_resident;                          // the block's own tiles (K,V or Q,dO) in shared memory
+  uint64_t res_ready;                             // ... and, dQ kernel, copied to tensor memory
+  uint64_t full[kBwdStages], empty[kBwdStages];   // streamed tile pairs
+  uint64_t sdp_full[2];                           // S / dP of a group's tile are in tensor memory
+  uint64_t pds_full[2];                           // the group has written P / dS
+  uint64_t all_done;                              // every MMA of the block has completed
   uint32_t tmem_base;
   int failed;
+  float2 stats[2][2][kBwdBN]; // dK/dV kernel: (lse * log2e, dsum) of the streamed queries [group][parity][row]
 };
-struct BwdStats { // row statistics of the streamed query tile (dK/dV kernel only)
-  float lse2[2][128];
-  float dsum[2][128];
-};
-
-__device__ __forceinline__ bool named_bar_or(bool pred) { return named_bar_or_n<128>(pred); }
 
 __device__ __forceinline__ bool bwd_wait(uint64_t *bar, uint32_t parity, BwdShared *ss) {
   if (mbar_wait(bar, parity))
@@ -567,7 +589,6 @@ __device__ __forceinline__ bool bwd_wait(uint64_t *bar, uint32_t parity, BwdShar
   ss->failed = 1;
   return false;
 }
-
 __device__ __forceinline__ bool bwd_warp_wait(uint64_t *bar, uint32_t parity, BwdShared *ss) {
   const bool ok = __all_sync(0xffffffffu, mbar_wait(bar, parity));
   if (!ok)
@@ -580,6 +601,10 @@ __device__ __forceinline__ bool bwd_warp_wait(uint64_t *bar, uint32_t parity, Bw
 __device__ __forceinline__ void store_tile_chunk(unsigned char *tile, int row, int chunk16, uint4 v) {
   const int blk = chunk16 >> 3, chunk = chunk16 & 7;
   *reinterpret_cast<uint4 *>(tile + blk * kHalfTile + row * 128 + ((chunk ^ (row & 7)) << 4)) = v;
+}
+__device__ __forceinline__ uint4 load_tile_chunk(const unsigned char *tile, int row, int chunk16) {
+  const int blk = chunk16 >> 3, chunk = chunk16 & 7;
+  return *reinterpret_cast<const uint4 *>(tile + blk * kHalfTile + row * 128 + ((chunk ^ (row & 7)) << 4));
 }
 
 __global__ void __launch_bounds__(256)
@@ -619,29 +644,36 @@ __global__ void __launch_bounds__(256)
   }
 }
 
-// kDKDV = true : block owns keys [kv0, kv0+128) (rows of the transposed tiles), streams (Q, dO) tiles
-// kDKDV = false: block owns queries [q0, q0+128), streams (K, V) tiles
+// kDKDV = true : block owns keys [own0, own0+128) (rows of the transposed tiles) and streams
+//                (Q, dO) tiles of 64 queries:  S^T = K Q^T, dP^T = V dO^T, dV += P^T dO, dK += dS^T Q
+// kDKDV = false: block owns queries [own0, own0+128) and streams (K, V) tiles of 64 keys:
+//                S = Q K^T, dP = dO V^T, dQ += dS K
+// Warp roles: 0 TMA producer, 1 MMA issuer (all lanes run the loop, one elected lane issues),
+// 4..7 and 8..11 two elementwise groups that take the streamed tiles alternately, so that the
+// tensor core works on one group's products while the other group computes P and dS.
+// P^T / dS^T (dS) go back to tensor memory and are the A operands of the accumulating
+// products; in the dQ kernel Q and dO are A operands from tensor memory as well.
 template <bool kBF16, bool kDKDV>
-__global__ void __launch_bounds__(kBwdThreads, 1)
-    flash_bwd_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_constant__ CUtensorMap k_map,
-                     const __grid_constant__ CUtensorMap v_map, const __grid_constant__ CUtensorMap do_map,
+__global__ void __launch_bounds__(kThreads, 1)
+    flash_bwd_kernel(const __grid_constant__ CUtensorMap res0_map, // K (kDKDV) or Q, 128-row boxes
+                     const __grid_constant__ CUtensorMap res1_map, // V (kDKDV) or dO
+                     const __grid_constant__ CUtensorMap str0_map, // Q (kDKDV) or K, 64-row boxes
+                     const __grid_constant__ CUtensorMap str1_map, // dO (kDKDV) or V
                      const __grid_constant__ CUtensorMap out0_map, // dK (kDKDV) or dQ
                      const __grid_constant__ CUtensorMap out1_map, // dV (kDKDV), unused otherwise
                      const BwdParams p) {
   extern __shared__ __align__(1024) unsigned char smem_raw[];
   unsigned char *smem =
       reinterpret_cast<unsigned char *>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
-  // resident pair, streamed pairs, then the dS tile (and the P tile for dK/dV).
-  // Shared memory holds 7 tiles: the dK/dV kernel needs P and dS, so it streams
-  // through a single stage; the dQ kernel needs only dS and double-buffers.
-  constexpr int kBwdStages = kDKDV ? 1 : 2;
-  unsigned char *sRes0 = smem;                       // K (kDKDV) / Q
-  unsigned char *sRes1 = sRes0 + kTileBytes;         // V (kDKDV) / dO
-  unsigned char *sStr = sRes1 + kTileBytes;          // [stage][2 tiles]: (Q, dO) or (K, V)
-  unsigned char *sDS = sStr + kBwdStages * 2 * kTileBytes;
-  unsigned char *sP = sDS + kTileBytes;              // kDKDV only
-  BwdShared *ss = reinterpret_cast<BwdShared *>(sDS + (kDKDV ? 2 : 1) * kTileBytes);
-  BwdStats *stats = reinterpret_cast<BwdStats *>(ss + 1); // present only if kDKDV
+  unsigned char *sRes0 = smem;                     // K (kDKDV) / Q; at the end dK / dQ on its way out
+  unsigned char *sRes1 = sRes0 + kTileBytes;       // V (kDKDV) / dO; at the end dV
+  unsigned char *sStr = sRes1 + kTileBytes;        // [stage][2 tiles of 64 rows]
+  BwdShared *ss = reinterpret_cast<BwdShared *>(sStr + kBwdStages * 2 * kStrTileBytes);
+
+  constexpr uint32_t kColA0 = 0, kColA1 = 64;                    // dQ kernel: Q, dO
+  constexpr uint32_t kColS = kDKDV ? 0 : 128;                    // + 64 * group
+  constexpr uint32_t kColDP = kDKDV ? 128 : 256;                 // + 64 * group
+  constexpr uint32_t kColAcc0 = kDKDV ? 256 : 384, kColAcc1 = 384; // dV | dK, or dQ
 
   const int warp = __shfl_sync(0xffffffffu, threadIdx.x >> 5, 0), lane = threadIdx.x & 31; // warp: known uniform
   const int b = blockIdx.z;
@@ -650,29 +682,28 @@ __global__ void __launch_bounds__(kBwdThreads, 1)
   const bool left_bounded = p.window_left >= 0;
   const int group = (int)(p.H / p.Hk);
   const int n_q_tiles = (int)((p.Sq + kBM - 1) / kBM);
-  const int n_k_tiles = (int)((p.Sk + kBN - 1) / kBN);
 
-  // the tile this block owns, and the range of streamed tiles [t_begin, t_end)
+  // the tile this block owns, and the range of streamed 64-row tiles [t_begin, t_end)
   int own_tile, head, t_begin, t_end, heads_in_loop;
   if (kDKDV) {
     own_tile = blockIdx.x;
     head = blockIdx.y; // key/value head
     heads_in_loop = group;
     t_begin = 0;
-    t_end = n_q_tiles;
-    if (right_bounded) { // queries that can see key kv0: q >= kv0 - shift - window_right
-      const int64_t first_q = (int64_t)own_tile * kBN - shift - p.window_right;
-      t_begin = first_q <= 0 ? 0 : (int)min((int64_t)n_q_tiles, first_q / kBM);
+    t_end = (int)((p.Sq + kBwdBN - 1) / kBwdBN);
+    if (right_bounded) { // queries that can see key own0: q >= own0 - shift - window_right
+      const int64_t first_q = (int64_t)own_tile * 128 - shift - p.window_right;
+      t_begin = first_q <= 0 ? 0 : (int)min((int64_t)t_end, first_q / kBwdBN);
     }
   } else {
     own_tile = n_q_tiles - 1 - (int)blockIdx.x;
     head = blockIdx.y; // query head
     heads_in_loop = 1;
     t_begin = 0;
-    t_end = n_k_tiles;
+    t_end = (int)((p.Sk + kBwdBN - 1) / kBwdBN);
     if (right_bounded) {
       const int64_t last_visible = (int64_t)own_tile * kBM + kBM - 1 + shift + p.window_right;
-      t_end = last_visible < 0 ? 0 : (int)min((int64_t)n_k_tiles, last_visible / kBN + 1);
+      t_end = last_visible < 0 ? 0 : (int)min((int64_t)t_end, last_visible / kBwdBN + 1);
     }
   }
   const int tiles_per_head = max(0, t_end - t_begin);
@@ -681,14 +712,16 @@ __global__ void __launch_bounds__(kBwdThreads, 1)
 
   if (threadIdx.x == 0) {
     mbar_init(&ss->bar_resident, 1);
-    for (int s = 0; s < 2; ++s) {
+    mbar_init(&ss->res_ready, 8);
+    for (int s = 0; s < kBwdStages; ++s) {
       mbar_init(&ss->full[s], 1);
       mbar_init(&ss->empty[s], 1);
     }
-    mbar_init(&ss->st_full, 1);
-    mbar_init(&ss->st_empty, 4);
-    mbar_init(&ss->pds_full, 4);
-    mbar_init(&ss->pds_empty, 1);
+    for (int g = 0; g < 2; ++g) {
+      mbar_init(&ss->sdp_full[g], 1);
+      mbar_init(&ss->pds_full[g], 4);
+    }
+    mbar_init(&ss->all_done, 1);
     ss->failed = 0;
     mbar_fence_init();
   }
@@ -709,105 +742,115 @@ __global__ void __launch_bounds__(kBwdThreads, 1)
   if (warp == 0) {
     // ------------------------------------------------------------- producer
     if (lane == 0 && T > 0) {
+      prefetch_tensormap(&res0_map);
+      prefetch_tensormap(&res1_map);
+      prefetch_tensormap(&str0_map);
+      prefetch_tensormap(&str1_map);
+      const int res_head = kDKDV ? kv_head : head;
       mbar_arrive_expect_tx(&ss->bar_resident, 2 * kTileBytes);
-      if (kDKDV) {
-        tma_load_4d(sRes0, &k_map, 0, kv_head, (int)own0, b, &ss->bar_resident);
-        tma_load_4d(sRes0 + kHalfTile, &k_map, 64, kv_head, (int)own0, b, &ss->bar_resident);
-        tma_load_4d(sRes1, &v_map, 0, kv_head, (int)own0, b, &ss->bar_resident);
-        tma_load_4d(sRes1 + kHalfTile, &v_map, 64, kv_head, (int)own0, b, &ss->bar_resident);
-      } else {
-        tma_load_4d(sRes0, &q_map, 0, head, (int)own0, b, &ss->bar_resident);
-        tma_load_4d(sRes0 + kHalfTile, &q_map, 64, head, (int)own0, b, &ss->bar_resident);
-        tma_load_4d(sRes1, &do_map, 0, head, (int)own0, b, &ss->bar_resident);
-        tma_load_4d(sRes1 + kHalfTile, &do_map, 64, head, (int)own0, b, &ss->bar_resident);
-      }
+      tma_load_4d(sRes0, &res0_map, 0, res_head, (int)own0, b, &ss->bar_resident);
+      tma_load_4d(sRes0 + kHalfTile, &res0_map, 64, res_head, (int)own0, b, &ss->bar_resident);
+      tma_load_4d(sRes1, &res1_map, 0, res_head, (int)own0, b, &ss->bar_resident);
+      tma_load_4d(sRes1 + kHalfTile, &res1_map, 64, res_head, (int)own0, b, &ss->bar_resident);
       for (int it = 0; it < T; ++it) {
         const int st = it % kBwdStages;
         if (!bwd_wait(&ss->empty[st], (uint32_t)(((it / kBwdStages) & 1) ^ 1), ss))
           break;
-        mbar_arrive_expect_tx(&ss->full[st], 2 * kTileBytes);
-        unsigned char *t0 = sStr + st * 2 * kTileBytes, *t1 = t0 + kTileBytes;
-        const int row0 = iter_tile(it) * 128;
-        const CUtensorMap *m0 = kDKDV ? &q_map : &k_map, *m1 = kDKDV ? &do_map : &v_map;
+        mbar_arrive_expect_tx(&ss->full[st], 2 * kStrTileBytes);
+        unsigned char *t0 = sStr + st * 2 * kStrTileBytes, *t1 = t0 + kStrTileBytes;
+        const int row0 = iter_tile(it) * kBwdBN;
         const int hh = kDKDV ? iter_head(it) : kv_head;
-        tma_load_4d(t0, m0, 0, hh, row0, b, &ss->full[st]);
-        tma_load_4d(t0 + kHalfTile, m0, 64, hh, row0, b, &ss->full[st]);
-        tma_load_4d(t1, m1, 0, hh, row0, b, &ss->full[st]);
-        tma_load_4d(t1 + kHalfTile, m1, 64, hh, row0, b, &ss->full[st]);
+        tma_load_4d(t0, &str0_map, 0, hh, row0, b, &ss->full[st]);
+        tma_load_4d(t0 + kStrHalf, &str0_map, 64, hh, row0, b, &ss->full[st]);
+        tma_load_4d(t1, &str1_map, 0, hh, row0, b, &ss->full[st]);
+        tma_load_4d(t1 + kStrHalf, &str1_map, 64, hh, row0, b, &ss->full[st]);
       }
     }
   } else if (warp == 1) {
     // ------------------------------------------------------------- MMA issuer
-    // all 32 lanes run the loop and the waits; one elected lane executes the tcgen05 instructions
     if (T > 0) {
-      constexpr uint32_t idesc_nt = umma_idesc_f16(kBF16, 128, 128, false, false); // A, B both K-major
-      constexpr uint32_t idesc_nn = umma_idesc_f16(kBF16, 128, 128, false, true);  // B rows = K index
+      constexpr uint32_t idesc_sdp = umma_idesc_f16(kBF16, 128, kBwdBN, false, false); // B K-major, N = 64
+      constexpr uint32_t idesc_acc = umma_idesc_f16(kBF16, 128, 128, false, true);     // B rows = K index
       const uint32_t tm = __shfl_sync(0xffffffffu, tmem, 0);
       const uint32_t res0 = smem_addr(sRes0), res1 = smem_addr(sRes1), str = smem_addr(sStr);
-      const uint32_t p_addr = smem_addr(sP), ds_addr = smem_addr(sDS);
-      bool ok = bwd_warp_wait(&ss->bar_resident, 0, ss);
-      for (int it = 0; ok && it < T; ++it) {
-        const int st = it % kBwdStages;
-        const uint32_t t0 = str + st * 2 * kTileBytes, t1 = t0 + kTileBytes;
-        ok = bwd_warp_wait(&ss->full[st], (uint32_t)((it / kBwdStages) & 1), ss) &&
-             bwd_warp_wait(&ss->st_empty, (uint32_t)((it & 1) ^ 1), ss);
-        if (!ok)
-          break;
-        tc_fence_after_sync();
-        // kDKDV: S^T = K Q^T, dP^T = V dO^T ; else: S = Q K^T, dP = dO V^T  (contraction over head dim)
-#pragma unroll
-        for (int kk = 0; kk < 8; ++kk) {
-          const uint32_t off = (kk >> 2) * kHalfTile + (kk & 3) * 32;
-          const uint64_t adesc = umma_smem_desc(res0 + off, 16, 1024), bdesc = umma_smem_desc(t0 + off, 16, 1024);
-          if (elect_one())
-            umma_ss(tm + kColS0, adesc, bdesc, idesc_nt, kk != 0);
-        }
-#pragma unroll
-        for (int kk = 0; kk < 8; ++kk) {
-          const uint32_t off = (kk >> 2) * kHalfTile + (kk & 3) * 32;
-          const uint64_t adesc = umma_smem_desc(res1 + off, 16, 1024), bdesc = umma_smem_desc(t1 + off, 16, 1024);
-          if (elect_one())
-            umma_ss(tm + kColDP, adesc, bdesc, idesc_nt, kk != 0);
-        }
-        if (elect_one())
-          umma_commit(&ss->st_full);
-        ok = bwd_warp_wait(&ss->pds_full, (uint32_t)(it & 1), ss);
-        if (!ok)
-          break;
-        tc_fence_after_sync();
-        // contraction over the 128 streamed (kDKDV: query) or owned-side columns of P / dS
+      // S (S^T) and dP (dP^T) of streamed tile `it` into the buffers of group it & 1:
+      // contraction over the 128 head dims, 8 steps of 16
+      auto issue_sdp = [&](int it) {
+        const int st = it % kBwdStages, g = it & 1;
+        const uint32_t t0 = str + st * 2 * kStrTileBytes, t1 = t0 + kStrTileBytes;
 #pragma unroll
         for (int kk = 0; kk < 8; ++kk) {
           const uint32_t a_off = (kk >> 2) * kHalfTile + (kk & 3) * 32;
-          const uint32_t b_off = ((kk >> 2) * 64 + (kk & 3) * 16) * 128;
+          const uint32_t b_off = (kk >> 2) * kStrHalf + (kk & 3) * 32;
+          const uint64_t b0 = umma_smem_desc(t0 + b_off, 16, 1024), b1 = umma_smem_desc(t1 + b_off, 16, 1024);
           if (kDKDV) {
-            // dV += P^T dO ; dK += dS^T Q   (B = streamed tiles, rows = queries)
-            const uint64_t a0 = umma_smem_desc(p_addr + a_off, 16, 1024), b0 = umma_smem_desc(t1 + b_off, kHalfTile, 1024);
-            const uint64_t a1 = umma_smem_desc(ds_addr + a_off, 16, 1024), b1 = umma_smem_desc(t0 + b_off, kHalfTile, 1024);
+            const uint64_t a0 = umma_smem_desc(res0 + a_off, 16, 1024), a1 = umma_smem_desc(res1 + a_off, 16, 1024);
             if (elect_one()) {
-              umma_ss(tm + kColAcc0, a0, b0, idesc_nn, (it | kk) != 0);
-              umma_ss(tm + kColAcc1, a1, b1, idesc_nn, (it | kk) != 0);
+              umma_ss(tm + kColS + g * 64, a0, b0, idesc_sdp, kk != 0);
+              umma_ss(tm + kColDP + g * 64, a1, b1, idesc_sdp, kk != 0);
             }
-          } else {
-            // dQ += dS K   (B = streamed K tile, rows = keys)
-            const uint64_t a0 = umma_smem_desc(ds_addr + a_off, 16, 1024), b0 = umma_smem_desc(t0 + b_off, kHalfTile, 1024);
-            if (elect_one())
-              umma_ss(tm + kColAcc0, a0, b0, idesc_nn, (it | kk) != 0);
+          } else if (elect_one()) {
+            umma_ts(tm + kColS + g * 64, tm + kColA0 + kk * 8, b0, idesc_sdp, kk != 0);
+            umma_ts(tm + kColDP + g * 64, tm + kColA1 + kk * 8, b1, idesc_sdp, kk != 0);
           }
         }
-        if (elect_one()) {
-          umma_commit(&ss->pds_empty);
-          umma_commit(&ss->empty[st]);
+        if (elect_one())
+          umma_commit(&ss->sdp_full[g]);
+      };
+      bool ok = kDKDV ? bwd_warp_wait(&ss->bar_resident, 0, ss) : bwd_warp_wait(&ss->res_ready, 0, ss);
+      for (int it = 0; ok && it < 2 && it < T; ++it) {
+        ok = bwd_warp_wait(&ss->full[it % kBwdStages], 0, ss);
+        if (ok) {
+          tc_fence_after_sync();
+          issue_sdp(it);
         }
       }
+      for (int it = 0; ok && it < T; ++it) {
+        const int st = it % kBwdStages, g = it & 1;
+        const uint32_t t0 = str + st * 2 * kStrTileBytes, t1 = t0 + kStrTileBytes;
+        ok = bwd_warp_wait(&ss->pds_full[g], (uint32_t)((it >> 1) & 1), ss);
+        if (!ok)
+          break;
+        tc_fence_after_sync();
+        // contraction over the 64 streamed rows: 4 steps of 16; B = streamed tile, rows = K index
+#pragma unroll
+        for (int ks = 0; ks < 4; ++ks) {
+          const uint64_t b0 = umma_smem_desc(t0 + ks * 16 * 128, kStrHalf, 1024);
+          const uint64_t b1 = umma_smem_desc(t1 + ks * 16 * 128, kStrHalf, 1024);
+          if (elect_one()) {
+            if (kDKDV) {
+              // dV += P^T dO ; dK += dS^T Q
+              umma_ts(tm + kColAcc0, tm + kColS + g * 64 + ks * 8, b1, idesc_acc, (it | ks) != 0);
+              umma_ts(tm + kColAcc1, tm + kColDP + g * 64 + ks * 8, b0, idesc_acc, (it | ks) != 0);
+            } else {
+              // dQ += dS K
+              umma_ts(tm + kColAcc0, tm + kColDP + g * 64 + ks * 8, b0, idesc_acc, (it | ks) != 0);
+            }
+          }
+        }
+        if (elect_one())
+          umma_commit(&ss->empty[st]);
+        // the group's buffers are free for its next tile as soon as the products above have
+        // read P / dS: the tensor core runs what this lane issues in order
+        if (it + 2 < T) {
+          ok = bwd_warp_wait(&ss->full[(it + 2) % kBwdStages], (uint32_t)(((it + 2) / kBwdStages) & 1), ss);
+          if (!ok)
+            break;
+          tc_fence_after_sync();
+          issue_sdp(it + 2);
+        }
+      }
+      if (ok && elect_one())
+        umma_commit(&ss->all_done);
     }
-  } else {
-    // ------------------------------------------------------------- elementwise warps
+  } else if (warp >= 4) {
+    // ------------------------------------------------------------- elementwise groups
+    const int g = (warp - 4) >> 2;
     const int quarter = warp & 3;
     const int row = quarter * 32 + lane;       // owned-side row: a key (kDKDV) or a query
     const int64_t own_idx = own0 + row;
     const uint32_t lane_base = (uint32_t)(quarter * 32) << 16;
-    const int tid128 = (warp - 2) * 32 + lane; // 0..127 among the four warps
+    const uint32_t col_s = kColS + g * 64, col_dp = kColDP + g * 64;
     const float kLog2e = 1.4426950408889634f;
     float my_lse2 = 0.f, my_dsum = 0.f;
     if (!kDKDV && own_idx < p.Sq) {
@@ -815,23 +858,49 @@ __global__ void __launch_bounds__(kBwdThreads, 1)
       my_dsum = p.dsum[((int64_t)b * p.H + head) * p.Sq_rounded + own_idx];
     }
     bool ok = T > 0;
-    for (int it = 0; ok && it < T; ++it) {
-      const int64_t str0 = (int64_t)iter_tile(it) * 128;
-      if (kDKDV) { // statistics of the streamed query tile, one element per thread
-        const int64_t qi = str0 + tid128;
-        const int qh = iter_head(it);
-        float l2 = INFINITY, dd = 0.f; // rows past the end: P = exp2(-inf) = 0
-        if (qi < p.Sq) {
-          l2 = p.lse[((int64_t)b * p.H + qh) * p.Sq + qi] * kLog2e;
-          dd = p.dsum[((int64_t)b * p.H + qh) * p.Sq_rounded + qi];
+    if (!kDKDV && T > 0) {
+      // own Q (group 0) / dO (group 1) row -> tensor memory, the A operands of S and dP
+      ok = bwd_wait(&ss->bar_resident, 0, ss);
+      const unsigned char *src = g == 0 ? sRes0 : sRes1;
+#pragma unroll
+      for (int db = 0; db < 2; ++db) {
+        uint32_t r[32];
+#pragma unroll
+        for (int c = 0; c < 8; ++c) {
+          const uint4 v = load_tile_chunk(src, row, db * 8 + c);
+          r[c * 4 + 0] = v.x;
+          r[c * 4 + 1] = v.y;
+          r[c * 4 + 2] = v.z;
+          r[c * 4 + 3] = v.w;
         }
-        stats->lse2[it & 1][tid128] = l2;
-        stats->dsum[it & 1][tid128] = dd;
+        tmem_st32(tmem + lane_base + (g == 0 ? kColA0 : kColA1) + db * 32, r);
       }
-      const bool waited = bwd_wait(&ss->st_full, (uint32_t)(it & 1), ss) &&
-                          (it == 0 || bwd_wait(&ss->pds_empty, (uint32_t)((it - 1) & 1), ss));
-      // one barrier per tile: publishes the statistics above and makes giving up unanimous
-      if (named_bar_or(!waited)) {
+      tmem_wait_st();
+      tc_fence_before_sync();
+      __syncwarp();
+      if (lane == 0 && ok)
+        mbar_arrive(&ss->res_ready);
+    }
+    const int n_mine = (T + 1 - g) >> 1;
+    for (int i = 0; ok && i < n_mine; ++i) {
+      const int it = 2 * i + g;
+      const int64_t str0 = (int64_t)iter_tile(it) * kBwdBN;
+      if (kDKDV) { // statistics of the 64 streamed queries, one per thread of the first two warps
+        const int t = (warp & 3) * 32 + lane;
+        if (t < kBwdBN) {
+          const int64_t qi = str0 + t;
+          const int qh = iter_head(it);
+          float l2 = INFINITY, dd = 0.f; // rows past the end: P = exp2(-inf) = 0
+          if (qi < p.Sq) {
+            l2 = p.lse[((int64_t)b * p.H + qh) * p.Sq + qi] * kLog2e;
+            dd = p.dsum[((int64_t)b * p.H + qh) * p.Sq_rounded + qi];
+          }
+          ss->stats[g][i & 1][t] = make_float2(l2, dd);
+        }
+      }
+      const bool waited = bwd_wait(&ss->sdp_full[g], (uint32_t)(i & 1), ss);
+      // one barrier per tile and group: publishes the statistics and makes giving up unanimous
+      if (named_bar_or_id(1 + g, !waited)) {
         ok = false;
         break;
       }
@@ -853,100 +922,95 @@ __global__ void __launch_bounds__(kBwdThreads, 1)
           if (own_idx >= p.Sq)
             hi64 = -1;
         }
-        hi = (int)max((int64_t)-1, min((int64_t)127, hi64));
-        lo = (int)max((int64_t)0, min((int64_t)128, lo64));
+        hi = (int)max((int64_t)-1, min((int64_t)kBwdBN - 1, hi64));
+        lo = (int)max((int64_t)0, min((int64_t)kBwdBN, lo64));
       }
-      const bool need_mask = __any_sync(0xffffffffu, lo > 0 || hi < 127);
+      const bool need_mask = __any_sync(0xffffffffu, lo > 0 || hi < kBwdBN - 1);
+      uint32_t pp[32], dd[32]; // the row's 64 values of P and dS, 16 bit
 #pragma unroll
-      for (int c = 0; c < 4; ++c) {
+      for (int c = 0; c < 2; ++c) {
         uint32_t sr[32], dr[32];
-        tmem_ld32(tmem + lane_base + kColS0 + c * 32, sr);
-        tmem_ld32(tmem + lane_base + kColDP + c * 32, dr);
+        tmem_ld32(tmem + lane_base + col_s + c * 32, sr);
+        tmem_ld32(tmem + lane_base + col_dp + c * 32, dr);
         tmem_wait_ld();
-        if (c == 3) { // all of S / dP has been read: the tensor core may overwrite them
-          tc_fence_before_sync();
-          __syncwarp();
-          if (lane == 0)
-            mbar_arrive(&ss->st_empty);
-        }
         if (need_mask) {
 #pragma unroll
-          for (int i = 0; i < 32; ++i)
-            if (c * 32 + i > hi || c * 32 + i < lo)
-              sr[i] = 0xff800000u; // -inf: P = 0, dS = 0
+          for (int q = 0; q < 32; ++q)
+            if (c * 32 + q > hi || c * 32 + q < lo)
+              sr[q] = 0xff800000u; // -inf: P = 0, dS = 0
         }
-        uint32_t pp[16], dd[16];
 #pragma unroll
-        for (int i = 0; i < 32; i += 2) {
+        for (int q = 0; q < 32; q += 2) {
           float pv[2], dv[2];
 #pragma unroll
           for (int e = 0; e < 2; ++e) {
-            const int col = c * 32 + i + e;
-            const float l2 = kDKDV ? stats->lse2[it & 1][col] : my_lse2;
-            const float ds_ = kDKDV ? stats->dsum[it & 1][col] : my_dsum;
-            const float pr = fast_exp2(fmaf(__uint_as_float(sr[i + e]), p.scale_log2, -l2));
+            const int col = c * 32 + q + e;
+            float l2 = my_lse2, ds_ = my_dsum;
+            if (kDKDV) {
+              const float2 st = ss->stats[g][i & 1][col];
+              l2 = st.x;
+              ds_ = st.y;
+            }
+            const float pr = fast_exp2(fmaf(__uint_as_float(sr[q + e]), p.scale_log2, -l2));
             pv[e] = pr;
-            dv[e] = pr * (__uint_as_float(dr[i + e]) - ds_);
+            dv[e] = pr * (__uint_as_float(dr[q + e]) - ds_);
           }
-          pp[i / 2] = pack2(pv[0], pv[1], kBF16);
-          dd[i / 2] = pack2(dv[0], dv[1], kBF16);
-        }
-#pragma unroll
-        for (int g = 0; g < 4; ++g) {
-          if (kDKDV)
-            store_tile_chunk(sP, row, c * 4 + g, make_uint4(pp[g * 4], pp[g * 4 + 1], pp[g * 4 + 2], pp[g * 4 + 3]));
-          store_tile_chunk(sDS, row, c * 4 + g, make_uint4(dd[g * 4], dd[g * 4 + 1], dd[g * 4 + 2], dd[g * 4 + 3]));
+          pp[c * 16 + q / 2] = pack2(pv[0], pv[1], kBF16);
+          dd[c * 16 + q / 2] = pack2(dv[0], dv[1], kBF16);
         }
       }
-      fence_proxy_async_smem();
+      // both tiles are in registers: P^T / dS^T (dS) take the place of the values they came from
+      if (kDKDV)
+        tmem_st32(tmem + lane_base + col_s, pp);
+      tmem_st32(tmem + lane_base + col_dp, dd);
+      tmem_wait_st();
       tc_fence_before_sync();
       __syncwarp();
       if (lane == 0)
-        mbar_arrive(&ss->pds_full);
+        mbar_arrive(&ss->pds_full[g]);
     }
 
     // ---- epilogue: accumulators -> 16 bit -> shared -> TMA store
     if (ok && T > 0)
-      ok = bwd_wait(&ss->pds_empty, (uint32_t)((T - 1) & 1), ss);
+      ok = bwd_wait(&ss->all_done, 0, ss);
     tc_fence_after_sync();
     const bool have = ok && T > 0;
-    const int n_acc = kDKDV ? 2 : 1;
-    for (int a = 0; a < n_acc; ++a) {
-      // kDKDV: acc0 = dV (unscaled) -> sP, acc1 = dK (* scale) -> sDS ; else acc0 = dQ (* scale) -> sDS
-      const uint32_t col0 = a == 0 ? kColAcc0 : kColAcc1;
-      unsigned char *stage = (kDKDV && a == 0) ? sP : sDS;
-      const float mul = (kDKDV && a == 0) ? 1.f : p.scale;
+    // kDKDV: group 0 takes dV (unscaled) -> V's tile, group 1 dK (* scale) -> K's tile;
+    // else both groups take half of dQ's columns each (* scale) -> Q's tile
+    const uint32_t col0 = kDKDV ? (g == 0 ? kColAcc0 : kColAcc1) : kColAcc0 + g * 64;
+    unsigned char *stage = (kDKDV && g == 0) ? sRes1 : sRes0;
+    const float mul = (kDKDV && g == 0) ? 1.f : p.scale;
+    constexpr int kChunks = kDKDV ? 4 : 2;
 #pragma unroll
-      for (int c = 0; c < 4; ++c) {
-        uint32_t r[32];
-        if (have) {
-          tmem_ld32(tmem + lane_base + col0 + c * 32, r);
-          tmem_wait_ld();
-        } else {
+    for (int c = 0; c < kChunks; ++c) {
+      uint32_t r[32];
+      if (have) {
+        tmem_ld32(tmem + lane_base + col0 + c * 32, r);
+        tmem_wait_ld();
+      } else {
 #pragma unroll
-          for (int i = 0; i < 32; ++i)
-            r[i] = 0u;
-        }
+        for (int q = 0; q < 32; ++q)
+          r[q] = 0u;
+      }
 #pragma unroll
-        for (int g = 0; g < 4; ++g) {
-          uint4 v;
-          v.x = pack2(__uint_as_float(r[g * 8 + 0]) * mul, __uint_as_float(r[g * 8 + 1]) * mul, kBF16);
-          v.y = pack2(__uint_as_float(r[g * 8 + 2]) * mul, __uint_as_float(r[g * 8 + 3]) * mul, kBF16);
-          v.z = pack2(__uint_as_float(r[g * 8 + 4]) * mul, __uint_as_float(r[g * 8 + 5]) * mul, kBF16);
-          v.w = pack2(__uint_as_float(r[g * 8 + 6]) * mul, __uint_as_float(r[g * 8 + 7]) * mul, kBF16);
-          store_tile_chunk(stage, row, c * 4 + g, v);
-        }
+      for (int q = 0; q < 4; ++q) {
+        uint4 v;
+        v.x = pack2(__uint_as_float(r[q * 8 + 0]) * mul, __uint_as_float(r[q * 8 + 1]) * mul, kBF16);
+        v.y = pack2(__uint_as_float(r[q * 8 + 2]) * mul, __uint_as_float(r[q * 8 + 3]) * mul, kBF16);
+        v.z = pack2(__uint_as_float(r[q * 8 + 4]) * mul, __uint_as_float(r[q * 8 + 5]) * mul, kBF16);
+        v.w = pack2(__uint_as_float(r[q * 8 + 6]) * mul, __uint_as_float(r[q * 8 + 7]) * mul, kBF16);
+        store_tile_chunk(stage, row, (kDKDV ? 0 : g * 8) + c * 4 + q, v);
       }
     }
     fence_proxy_async_smem();
-    asm volatile("bar.sync 1, 128;" ::: "memory");
-    if (warp == 2 && lane == 0 && ss->failed == 0) {
+    asm volatile("bar.sync 3, 256;" ::: "memory"); // both groups
+    if (warp == 4 && lane == 0 && ss->failed == 0) {
       if (kDKDV) {
-        tma_store_4d(&out1_map, sP, 0, head, (int)own0, b);
-        tma_store_4d(&out1_map, sP + kHalfTile, 64, head, (int)own0, b);
+        tma_store_4d(&out1_map, sRes1, 0, head, (int)own0, b);
+        tma_store_4d(&out1_map, sRes1 + kHalfTile, 64, head, (int)own0, b);
       }
-      tma_store_4d(&out0_map, sDS, 0, head, (int)own0, b);
-      tma_store_4d(&out0_map, sDS + kHalfTile, 64, head, (int)own0, b);
+      tma_store_4d(&out0_map, sRes0, 0, head, (int)own0, b);
+      tma_store_4d(&out0_map, sRes0 + kHalfTile, 64, head, (int)own0, b);
       bulk_commit();
       bulk_wait_all<0>();
     }
@@ -961,11 +1025,10 @@ __global__ void __launch_bounds__(kBwdThreads, 1)
 }
 
 template <bool kBF16, bool kDKDV>
-int launch_bwd(const CUtensorMap &q_map, const CUtensorMap &k_map, const CUtensorMap &v_map,
-               const CUtensorMap &do_map, const CUtensorMap &out0, const CUtensorMap &out1,
-               const BwdParams &p, dim3 grid, cudaStream_t stream) {
-  const size_t smem = kDKDV ? (size_t)6 * kTileBytes + sizeof(BwdShared) + sizeof(BwdStats) + 1024
-                            : (size_t)7 * kTileBytes + sizeof(BwdShared) + 1024;
+int launch_bwd(const CUtensorMap &res0, const CUtensorMap &res1, const CUtensorMap &str0, const CUtensorMap &str1,
+               const CUtensorMap &out0, const CUtensorMap &out1, const BwdParams &p, dim3 grid,
+               cudaStream_t stream) {
+  const size_t smem = (size_t)2 * kTileBytes + (size_t)kBwdStages * 2 * kStrTileBytes + sizeof(BwdShared) + 1024;
   static bool attr_set = false;
   if (!attr_set) {
     if (int rc = check_cuda(cudaFuncSetAttribute(flash_bwd_kernel<kBF16, kDKDV>,
@@ -973,7 +1036,7 @@ int launch_bwd(const CUtensorMap &q_map, const CUtensorMap &k_map, const CUtenso
       return rc;
     attr_set = true;
   }
-  flash_bwd_kernel<kBF16, kDKDV><<<grid, kBwdThreads, smem, stream>>>(q_map, k_map, v_map, do_map, out0, out1, p);
+  flash_bwd_kernel<kBF16, kDKDV><<<grid, kThreads, smem, stream>>>(res0, res1, str0, str1, out0, out1, p);
   return check_launch();
 }
 
@@ -1063,20 +1126,26 @@ extern "C" int b200_flash_attn_bwd(int dtype, const void *dout, const void *q, c
   const bool bf16 = dtype == B200_BF16;
   // dq / dk / dv use the strides of q / k / v and dout those of out, as in the
   // reference's custom call (flash_api.cu:370-381)
-  CUtensorMap q_map, k_map, v_map, do_map, dq_map, dk_map, dv_map;
+  // q / k / v / dout are read both as a block's own 128-row tile and as streamed 64-row tiles
+  CUtensorMap q_map, k_map, v_map, do_map, q64_map, k64_map, v64_map, do64_map, dq_map, dk_map, dv_map;
   struct {
     CUtensorMap *m;
     const void *base;
     int64_t heads, seq, hs, rs, bs;
-  } maps[] = {{&q_map, q, a.h, a.seqlen_q, a.q_head_stride, a.q_row_stride, a.q_batch_stride},
-              {&k_map, k, a.h_k, a.seqlen_k, a.k_head_stride, a.k_row_stride, a.k_batch_stride},
-              {&v_map, v, a.h_k, a.seqlen_k, a.v_head_stride, a.v_row_stride, a.v_batch_stride},
-              {&do_map, dout, a.h, a.seqlen_q, a.o_head_stride, a.o_row_stride, a.o_batch_stride},
-              {&dq_map, dq, a.h, a.seqlen_q, a.q_head_stride, a.q_row_stride, a.q_batch_stride},
-              {&dk_map, dk, a.h_k, a.seqlen_k, a.k_head_stride, a.k_row_stride, a.k_batch_stride},
-              {&dv_map, dv, a.h_k, a.seqlen_k, a.v_head_stride, a.v_row_stride, a.v_batch_stride}};
+    uint32_t box_rows;
+  } maps[] = {{&q_map, q, a.h, a.seqlen_q, a.q_head_stride, a.q_row_stride, a.q_batch_stride, 128},
+              {&k_map, k, a.h_k, a.seqlen_k, a.k_head_stride, a.k_row_stride, a.k_batch_stride, 128},
+              {&v_map, v, a.h_k, a.seqlen_k, a.v_head_stride, a.v_row_stride, a.v_batch_stride, 128},
+              {&do_map, dout, a.h, a.seqlen_q, a.o_head_stride, a.o_row_stride, a.o_batch_stride, 128},
+              {&q64_map, q, a.h, a.seqlen_q, a.q_head_stride, a.q_row_stride, a.q_batch_stride, kBwdBN},
+              {&k64_map, k, a.h_k, a.seqlen_k, a.k_head_stride, a.k_row_stride, a.k_batch_stride, kBwdBN},
+              {&v64_map, v, a.h_k, a.seqlen_k, a.v_head_stride, a.v_row_stride, a.v_batch_stride, kBwdBN},
+              {&do64_map, dout, a.h, a.seqlen_q, a.o_head_stride, a.o_row_stride, a.o_batch_stride, kBwdBN},
+              {&dq_map, dq, a.h, a.seqlen_q, a.q_head_stride, a.q_row_stride, a.q_batch_stride, 128},
+              {&dk_map, dk, a.h_k, a.seqlen_k, a.k_head_stride, a.k_row_stride, a.k_batch_stride, 128},
+              {&dv_map, dv, a.h_k, a.seqlen_k, a.v_head_stride, a.v_row_stride, a.v_batch_stride, 128}};
   for (auto &m : maps)
-    if (int rc = make_qkv_map(m.m, bf16, m.base, a.d, m.heads, m.seq, a.b, m.hs, m.rs, m.bs))
+    if (int rc = make_qkv_map(m.m, bf16, m.base, a.d, m.heads, m.seq, a.b, m.hs, m.rs, m.bs, m.box_rows))
       return rc;
 
   const int64_t rows = a.b * a.h * a.seqlen_q;
@@ -1098,12 +1167,12 @@ extern "C" int b200_flash_attn_bwd(int dtype, const void *dout, const void *q, c
   p.scale_log2 = a.softmax_scale * 1.4426950408889634f;
   p.window_left = a.window_size_left;
   p.window_right = a.window_size_right;
-  const dim3 grid_kv((unsigned)((a.seqlen_k + kBN - 1) / kBN), (unsigned)a.h_k, (unsigned)a.b);
+  const dim3 grid_kv((unsigned)((a.seqlen_k + 127) / 128), (unsigned)a.h_k, (unsigned)a.b);
   const dim3 grid_q((unsigned)((a.seqlen_q + kBM - 1) / kBM), (unsigned)a.h, (unsigned)a.b);
-  int rc = bf16 ? launch_bwd<true, true>(q_map, k_map, v_map, do_map, dk_map, dv_map, p, grid_kv, stream)
-                : launch_bwd<false, true>(q_map, k_map, v_map, do_map, dk_map, dv_map, p, grid_kv, stream);
+  int rc = bf16 ? launch_bwd<true, true>(k_map, v_map, q64_map, do64_map, dk_map, dv_map, p, grid_kv, stream)
+                : launch_bwd<false, true>(k_map, v_map, q64_map, do64_map, dk_map, dv_map, p, grid_kv, stream);
   if (rc)
     return rc;
-  return bf16 ? launch_bwd<true, false>(q_map, k_map, v_map, do_map, dq_map, dq_map, p, grid_q, stream)
-              : launch_bwd<false, false>(q_map, k_map, v_map, do_map, dq_map, dq_map, p, grid_q, stream);
+  return bf16 ? launch_bwd<true, false>(q_map, do_map, k64_map, v64_map, dq_map, dq_map, p, grid_q, stream)
+              : launch_bwd<false, false>(q_map, do_map, k64_map, v64_map, dq_map, dq_map, p, grid_q, stream);
 }
