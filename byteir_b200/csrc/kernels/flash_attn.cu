@@ -25,10 +25,9 @@
 // softmax.h:129-178, flash_fwd_kernel.h:276-453): exp2 domain with the scale
 // folded in, row sum from the unrounded f32 probabilities, P rounded to the
 // storage type before P V, LSE = max * scale + ln(sum), +inf for a fully masked
-// row.  Deviations that stay inside the rounding of P: O is only rescaled when
+// row.  One deviation that stays inside the rounding of P: O is only rescaled when
 // the running max grew by more than 2^8 (the stale max is used consistently for
-// P, the row sum and the LSE), and one exponential in four is evaluated by a
-// polynomial on the FMA pipes.
+// P, the row sum and the LSE).
 #include <cuda.h>
 
 #include "common.cuh"
@@ -53,7 +52,6 @@ constexpr uint32_t kKVTileBytes = kFwdBN * kD * 2;   // 16 KiB: two 64-column bl
 constexpr uint32_t kKVHalf = kKVTileBytes / 2;
 constexpr uint32_t kColS0 = 0, kColS1 = 64, kColP0 = 128, kColP1 = 160, kColQ = 192, kColO0 = 256, kColO1 = 384;
 constexpr float kRescaleThreshold = 8.0f; // log2 units
-constexpr int kPolyEvery = 4; // forward softmax: one exponential in 4 is a polynomial (0 = none)
 
 struct FwdParams {
   float *lse;
@@ -63,20 +61,30 @@ struct FwdParams {
   int64_t window_left, window_right; // < 0: unbounded
 };
 
-// 2^x for x <= 0 on the FMA/ALU pipes (the MUFU unit, 16 results per clock per SM, is the
-// softmax bottleneck).  Round x to the nearest integer n with the 1.5 * 2^23 trick, evaluate
-// 2^(x - n) on [-0.5, 0.5] with a degree-4 polynomial (relative error 4e-5, well below the
-// 16-bit rounding P gets anyway) and add n to the exponent field.  Below 2^-125: exactly 0.
-__device__ __forceinline__ float exp2_poly(float x) {
-  const float xc = fmaxf(x, -125.f);
-  const float r = xc + 12582912.f;
-  const float f = xc - (r - 12582912.f);
-  float y = fmaf(f, 0.009618129f, 0.05550411f);
-  y = fmaf(y, f, 0.2402265f);
-  y = fmaf(y, f, 0.6931472f);
-  y = fmaf(y, f, 1.0f);
-  const float v = __uint_as_float(__float_as_uint(y) + (__float_as_uint(r) << 23));
-  return x < -125.f ? 0.f : v;
+// Two f32 in one 64-bit register for the packed FMA / ADD of sm_100 (one issue slot for two
+// results); the softmax loop is bound by instruction issue, not by any one pipe.
+__device__ __forceinline__ uint64_t f2_pack(float lo, float hi) {
+  uint64_t r;
+  asm("mov.b64 %0, {%1, %2};" : "=l"(r) : "f"(lo), "f"(hi));
+  return r;
+}
+__device__ __forceinline__ void f2_unpack(uint64_t v, float &lo, float &hi) {
+  asm("mov.b64 {%0, %1}, %2;" : "=f"(lo), "=f"(hi) : "l"(v));
+}
+__device__ __forceinline__ uint64_t f2_fma(uint64_t a, uint64_t b, uint64_t c) {
+  uint64_t r;
+  asm("fma.rn.f32x2 %0, %1, %2, %3;" : "=l"(r) : "l"(a), "l"(b), "l"(c));
+  return r;
+}
+__device__ __forceinline__ uint64_t f2_add(uint64_t a, uint64_t b) {
+  uint64_t r;
+  asm("add.rn.f32x2 %0, %1, %2;" : "=l"(r) : "l"(a), "l"(b));
+  return r;
+}
+__device__ __forceinline__ float fmax3(float a, float b, float c) {
+  float r;
+  asm("max.f32 %0, %1, %2, %3;" : "=f"(r) : "f"(a), "f"(b), "f"(c));
+  return r;
 }
 
 // Named barrier 1 over the N worker threads of a block that also ORs a predicate, so that a
@@ -390,19 +398,18 @@ __global__ void __launch_bounds__(kThreads, 1)
           if (c > hi || c < lo)
             s[c] = 0xff800000u; // -inf
       }
-      // row maximum: eight independent chains
-      float mx8[8];
+      // row maximum: four independent chains of 3-input max
+      float mx4[4];
 #pragma unroll
-      for (int e = 0; e < 8; ++e)
-        mx8[e] = fmaxf(__uint_as_float(s[2 * e]), __uint_as_float(s[2 * e + 1]));
+      for (int e = 0; e < 4; ++e)
+        mx4[e] = fmaxf(__uint_as_float(s[2 * e]), __uint_as_float(s[2 * e + 1]));
 #pragma unroll
-      for (int c = 16; c < kFwdBN; c += 16) {
+      for (int c = 8; c < kFwdBN; c += 8) {
 #pragma unroll
-        for (int e = 0; e < 8; ++e)
-          mx8[e] = fmaxf(mx8[e], fmaxf(__uint_as_float(s[c + 2 * e]), __uint_as_float(s[c + 2 * e + 1])));
+        for (int e = 0; e < 4; ++e)
+          mx4[e] = fmax3(mx4[e], __uint_as_float(s[c + 2 * e]), __uint_as_float(s[c + 2 * e + 1]));
       }
-      const float mx = fmaxf(fmaxf(fmaxf(mx8[0], mx8[1]), fmaxf(mx8[2], mx8[3])),
-                             fmaxf(fmaxf(mx8[4], mx8[5]), fmaxf(mx8[6], mx8[7])));
+      const float mx = fmaxf(fmax3(mx4[0], mx4[1], mx4[2]), mx4[3]);
       const float m_new = fmaxf(m_used, mx * p.scale_log2);
       float alpha = 1.f;
       const bool grew = m_new - m_used > kRescaleThreshold; // also true for -inf -> finite
@@ -415,20 +422,26 @@ __global__ void __launch_bounds__(kThreads, 1)
         l *= alpha;
       }
       const float m_safe = (m_used == -INFINITY) ? 0.f : m_used;
-      // probabilities (one in kPolyEvery on the FMA pipes, the rest on the MUFU unit), four
-      // independent partial sums; the packed 16-bit P reuses the front of the row's registers
-      float sum4[4] = {0.f, 0.f, 0.f, 0.f};
+      // probabilities: x = s * scale - m for two columns per packed FMA, 2^x on the MUFU unit,
+      // four independent packed partial sums; the 16-bit P reuses the front of the row's registers
+      const uint64_t scale2 = f2_pack(p.scale_log2, p.scale_log2), negm2 = f2_pack(-m_safe, -m_safe);
+      uint64_t sum2[4] = {0ull, 0ull, 0ull, 0ull};
       uint32_t(&packed)[kFwdBN] = s;
 #pragma unroll
       for (int c = 0; c < kFwdBN; c += 2) {
-        const float x0 = fmaf(__uint_as_float(s[c]), p.scale_log2, -m_safe);
-        const float x1 = fmaf(__uint_as_float(s[c + 1]), p.scale_log2, -m_safe);
-        const float p0 = fast_exp2(x0);
-        const float p1 = (kPolyEvery > 0 && (c + 1) % kPolyEvery == kPolyEvery - 1) ? exp2_poly(x1) : fast_exp2(x1);
-        sum4[(c >> 1) & 3] += p0 + p1;
+        const uint64_t x2 = f2_fma(f2_pack(__uint_as_float(s[c]), __uint_as_float(s[c + 1])), scale2, negm2);
+        float x0, x1;
+        f2_unpack(x2, x0, x1);
+        const float p0 = fast_exp2(x0), p1 = fast_exp2(x1);
+        sum2[(c >> 1) & 3] = f2_add(sum2[(c >> 1) & 3], f2_pack(p0, p1));
         packed[c >> 1] = pack2(p0, p1, kBF16);
       }
-      l += (sum4[0] + sum4[1]) + (sum4[2] + sum4[3]);
+      {
+        float a0, a1, b0, b1;
+        f2_unpack(f2_add(sum2[0], sum2[1]), a0, a1);
+        f2_unpack(f2_add(sum2[2], sum2[3]), b0, b1);
+        l += (a0 + a1) + (b0 + b1);
+      }
 
       // the group's P columns and O are busy until P V of its previous tile has finished
       if (i > 0 && !wait_or_flag(&ss->o_done[g], (uint32_t)((i - 1) & 1), ss)) {
@@ -511,7 +524,7 @@ __global__ void __launch_bounds__(kThreads, 1)
       tma_store_4d(&o_map, sQ, 0, h, (int)q0, b);
       tma_store_4d(&o_map, sQ + kHalfTile, 64, h, (int)q0, b);
       bulk_commit();
-      bulk_wait_all<0>();
+      bulk_wait_read<0>(); // shared memory must outlive the store's reads, not its completion
     }
   }
 

@@ -30,24 +30,26 @@ __device__ __forceinline__ void mbar_arrive(uint64_t *bar) {
   asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_addr(bar)) : "memory");
 }
 
+// One poll of the barrier.  The time hint lets the hardware park the thread until the phase
+// completes (or the hint expires), so a waiting warp does not burn issue slots in a spin loop.
 __device__ __forceinline__ bool mbar_try_wait(uint64_t *bar, uint32_t parity) {
   uint32_t ok;
   asm volatile("{\n"
                ".reg .pred p;\n"
-               "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n"
+               "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2, %3;\n"
                "selp.u32 %0, 1, 0, p;\n"
                "}\n"
                : "=r"(ok)
-               : "r"(smem_addr(bar)), "r"(parity)
+               : "r"(smem_addr(bar)), "r"(parity), "r"(20000u)
                : "memory");
   return ok != 0;
 }
 
 // Bounded wait: gives up after `limit` polls and returns false, so that a
-// protocol error can never hang the GPU.  try_wait itself suspends the thread
-// for a hardware-defined time slice, so the limit is far beyond any real wait.
+// protocol error can never hang the GPU.  A poll parks the thread for up to 20 us,
+// so the limit (2 s) is far beyond any real wait.
 __device__ __forceinline__ bool mbar_wait(uint64_t *bar, uint32_t parity,
-                                          uint32_t limit = 4000000u) {
+                                          uint32_t limit = 100000u) {
   for (uint32_t i = 0; i < limit; ++i)
     if (mbar_try_wait(bar, parity))
       return true;
