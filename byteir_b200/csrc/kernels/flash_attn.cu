@@ -1,25 +1,24 @@
 // Flash-attention forward for sm_100a (head dim 128, f16 / bf16, f32 accumulate).
 //
 // One block owns 128 query rows of one (batch, head) and walks over the key/value
-// tiles of 64 rows that the mask lets it see.  Warp roles (three warpgroups):
-//   warp 0        TMA producer of Q (once) and of the K tiles (4-stage ring)
-//   warp 2        TMA producer of the V tiles (4-stage ring)
-//   warp 1        issuer of S = Q K^T   (tcgen05.mma; all lanes run the loop, one elected lane issues)
-//   warp 3        issuer of O += P V
+// tiles of 128 rows that the mask lets it see.  Warp roles (three warpgroups):
+//   warp 0        TMA producer of Q (once) and of the K tiles (3-stage ring)
+//   warp 2        TMA producer of the V tiles (2-stage ring)
+//   warp 1        MMA issuer: S = Q K^T and O += P V with tcgen05.mma; all lanes run the
+//                 loop and the waits, one elected lane executes the tcgen05 instructions
 //   warps 4..7    softmax group 0: key tiles 0, 2, 4, ...
 //   warps 8..11   softmax group 1: key tiles 1, 3, 5, ...
-// Both products read their A operand from tensor memory: Q is copied there once per
-// block, P is written there by the softmax warps, so shared memory only feeds the B
-// operands K and V (the bandwidth of shared memory, 128 B per clock, is what bounds a
-// product with both operands there).  Each group has its own S tile, P tile and O
-// accumulator in tensor memory and its own running (max, sum) per row, so a group has
-// two MMA periods for the softmax of one tile and the tensor core always has the other
-// group's products to run.  Tensor-memory columns: S 0,64 | P 128,160 | Q 192 | O 256,384.
-// Inside a group thread t owns query row t: it reads its row of S, keeps the running
-// max / sum, writes P (16-bit) back to tensor memory and rescales its O when the running
-// max moved.  At the end the two partial results of a row are merged like two splits of
-// the key axis:
+// Each group has its own S tile and its own O accumulator in tensor memory (columns
+// S 0,128 | O 256,384: all 512) and its own running (max, sum) per row.  Inside a group
+// thread t owns query row t: it reads its row of S, keeps the running max / sum, writes
+// P (16-bit) back to tensor memory over the front half of the row's S, where it is the A
+// operand of P V, and rescales its O when the running max moved.  For a group the tensor
+// core runs  P V (tile j),  Q K^T (tile j + 2)  back to back while the other group does
+// its softmax, so the two groups alternate between the tensor core and the MUFU / FMA
+// pipes.  At the end the two partial results of a row are merged like two splits of the
+// key axis:
 //   O = (O0 2^(m0-m) + O1 2^(m1-m)) / (l0 2^(m0-m) + l1 2^(m1-m)),  m = max(m0, m1).
+// The control warps give most of their registers to the softmax warps (setmaxnreg).
 //
 // Numerics follow the reference kernel (external_libs/runtime/flash_attn/lib/
 // softmax.h:129-178, flash_fwd_kernel.h:276-453): exp2 domain with the scale
@@ -44,13 +43,11 @@ constexpr uint32_t kTileBytes = kBN * kD * 2;  // 32 KiB: two 64-column blocks o
 constexpr uint32_t kHalfTile = kTileBytes / 2; // one 64-column block
 constexpr int kThreads = 384;    // four control warps, two groups of four softmax / elementwise warps
 constexpr uint32_t kTmemCols = 512;
-// forward: key tiles of 64 rows, so that two S tiles, two P tiles, Q and two O accumulators
-// share the 512 columns of tensor memory
-constexpr int kFwdBN = 64;
-constexpr int kFwdStages = 4;                        // K / V ring depth of the forward kernel
-constexpr uint32_t kKVTileBytes = kFwdBN * kD * 2;   // 16 KiB: two 64-column blocks of 64 x 128 B
-constexpr uint32_t kKVHalf = kKVTileBytes / 2;
-constexpr uint32_t kColS0 = 0, kColS1 = 64, kColP0 = 128, kColP1 = 160, kColQ = 192, kColO0 = 256, kColO1 = 384;
+// forward: two S tiles (P overlays their front halves) and two O accumulators fill the 512
+// columns of tensor memory
+constexpr int kFwdKStages = 3, kFwdVStages = 2; // K / V ring depths of the forward kernel
+constexpr uint32_t kColS0 = 0, kColS1 = 128, kColO0 = 256, kColO1 = 384;
+constexpr int kCtrlRegs = 56, kSoftmaxRegs = 224; // 128 * 56 + 256 * 224 <= 64 Ki registers
 constexpr float kRescaleThreshold = 8.0f; // log2 units
 
 struct FwdParams {
@@ -118,11 +115,21 @@ __device__ __forceinline__ bool named_bar_or_id(int id, bool pred) {
   return out != 0;
 }
 
+// Registers move from the control warps to the softmax warps at run time (all four warps
+// of a warpgroup execute the instruction).
+template <int N> __device__ __forceinline__ void reg_dec() {
+  asm volatile("setmaxnreg.dec.sync.aligned.u32 %0;" ::"n"(N));
+}
+template <int N> __device__ __forceinline__ void reg_inc() {
+  asm volatile("setmaxnreg.inc.sync.aligned.u32 %0;" ::"n"(N));
+}
+
 struct SharedStorage {
-  uint64_t bar_q, q_ready;
-  uint64_t k_full[kFwdStages], k_empty[kFwdStages], v_full[kFwdStages], v_empty[kFwdStages];
-  uint64_t s_full[2], s_empty[2]; // per softmax group
-  uint64_t p_full[2], o_done[2];  // per softmax group
+  uint64_t bar_q;
+  uint64_t k_full[kFwdKStages], k_empty[kFwdKStages], v_full[kFwdVStages], v_empty[kFwdVStages];
+  uint64_t s_full[2];  // per softmax group: S of its tile is in tensor memory
+  uint64_t p_full[2];  // per softmax group: P of its tile is in tensor memory
+  uint64_t o_done[2];  // per softmax group: its last P V has completed
   uint32_t tmem_base;
   int failed;
   float2 xch[2][kBM]; // (running max, row sum) of each group, for the final merge
@@ -157,22 +164,6 @@ __device__ __forceinline__ bool warp_wait_or_flag(uint64_t *bar, uint32_t parity
   return ok;
 }
 
-// two barriers at once: the polls overlap instead of following each other
-__device__ __forceinline__ bool warp_wait2_or_flag(uint64_t *bar_a, uint32_t parity_a, uint64_t *bar_b,
-                                                   uint32_t parity_b, SharedStorage *ss) {
-  bool done_a = false, done_b = false;
-  for (uint32_t it = 0; it < 4000000u; ++it) {
-    const bool a = done_a || mbar_try_wait(bar_a, parity_a);
-    const bool b = done_b || mbar_try_wait(bar_b, parity_b);
-    done_a = a;
-    done_b = b;
-    if (__all_sync(0xffffffffu, a && b))
-      return true;
-  }
-  ss->failed = 1;
-  return false;
-}
-
 __device__ __forceinline__ uint32_t pack2(float lo, float hi, bool bf16) {
   if (bf16) {
     __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);
@@ -190,10 +181,10 @@ __global__ void __launch_bounds__(kThreads, 1)
   extern __shared__ __align__(1024) unsigned char smem_raw[];
   unsigned char *smem =
       reinterpret_cast<unsigned char *>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
-  unsigned char *sQ = smem; // Q on its way to tensor memory; the finished O tile at the end
+  unsigned char *sQ = smem; // Q; the finished O tile at the end
   unsigned char *sK = sQ + kTileBytes;
-  unsigned char *sV = sK + kFwdStages * kKVTileBytes;
-  SharedStorage *ss = reinterpret_cast<SharedStorage *>(sV + kFwdStages * kKVTileBytes);
+  unsigned char *sV = sK + kFwdKStages * kTileBytes;
+  SharedStorage *ss = reinterpret_cast<SharedStorage *>(sV + kFwdVStages * kTileBytes);
 
   const int warp = __shfl_sync(0xffffffffu, threadIdx.x >> 5, 0), lane = threadIdx.x & 31; // warp: known uniform
   const int n_q_tiles = (int)((p.Sq + kBM - 1) / kBM);
@@ -205,25 +196,25 @@ __global__ void __launch_bounds__(kThreads, 1)
   const bool right_bounded = p.window_right >= 0;
   const bool left_bounded = p.window_left >= 0;
 
-  // key tiles (64 keys each) this block visits: [0, n)
-  int n = (int)((p.Sk + kFwdBN - 1) / kFwdBN);
+  // key tiles (128 keys each) this block visits: [0, n)
+  int n = (int)((p.Sk + kBN - 1) / kBN);
   if (right_bounded) {
     const int64_t last_visible = q0 + kBM - 1 + shift + p.window_right;
-    n = last_visible < 0 ? 0 : (int)min((int64_t)n, last_visible / kFwdBN + 1);
+    n = last_visible < 0 ? 0 : (int)min((int64_t)n, last_visible / kBN + 1);
   }
 
   if (threadIdx.x == 0) {
     mbar_init(&ss->bar_q, 1);
-    mbar_init(&ss->q_ready, 4);
-    for (int s = 0; s < kFwdStages; ++s) {
+    for (int s = 0; s < kFwdKStages; ++s) {
       mbar_init(&ss->k_full[s], 1);
       mbar_init(&ss->k_empty[s], 1);
+    }
+    for (int s = 0; s < kFwdVStages; ++s) {
       mbar_init(&ss->v_full[s], 1);
       mbar_init(&ss->v_empty[s], 1);
     }
     for (int g = 0; g < 2; ++g) {
       mbar_init(&ss->s_full[g], 1);
-      mbar_init(&ss->s_empty[g], 4);
       mbar_init(&ss->p_full[g], 4);
       mbar_init(&ss->o_done[g], 1);
     }
@@ -239,6 +230,8 @@ __global__ void __launch_bounds__(kThreads, 1)
   tc_fence_after_sync();
   const uint32_t tmem = ss->tmem_base;
 
+  if (warp < 4)
+    reg_dec<kCtrlRegs>(); // the four control warps hand registers to the softmax warps
   if (warp == 0) {
     // ----------------------------------------------------------- producer of Q and K
     if (lane == 0 && n > 0) {
@@ -248,12 +241,12 @@ __global__ void __launch_bounds__(kThreads, 1)
       tma_load_4d(sQ, &q_map, 0, h, (int)q0, b, &ss->bar_q);
       tma_load_4d(sQ + kHalfTile, &q_map, 64, h, (int)q0, b, &ss->bar_q);
       for (int j = 0; j < n; ++j) {
-        const int st = j % kFwdStages;
-        if (!wait_or_flag(&ss->k_empty[st], (uint32_t)(((j / kFwdStages) & 1) ^ 1), ss))
+        const int st = j % kFwdKStages;
+        if (!wait_or_flag(&ss->k_empty[st], (uint32_t)(((j / kFwdKStages) & 1) ^ 1), ss))
           break;
-        mbar_arrive_expect_tx(&ss->k_full[st], kKVTileBytes);
-        tma_load_4d(sK + st * kKVTileBytes, &k_map, 0, hk, j * kFwdBN, b, &ss->k_full[st]);
-        tma_load_4d(sK + st * kKVTileBytes + kKVHalf, &k_map, 64, hk, j * kFwdBN, b, &ss->k_full[st]);
+        mbar_arrive_expect_tx(&ss->k_full[st], kTileBytes);
+        tma_load_4d(sK + st * kTileBytes, &k_map, 0, hk, j * kBN, b, &ss->k_full[st]);
+        tma_load_4d(sK + st * kTileBytes + kHalfTile, &k_map, 64, hk, j * kBN, b, &ss->k_full[st]);
       }
     }
   } else if (warp == 2) {
@@ -261,109 +254,89 @@ __global__ void __launch_bounds__(kThreads, 1)
     if (lane == 0 && n > 0) {
       prefetch_tensormap(&v_map);
       for (int j = 0; j < n; ++j) {
-        const int st = j % kFwdStages;
-        if (!wait_or_flag(&ss->v_empty[st], (uint32_t)(((j / kFwdStages) & 1) ^ 1), ss))
+        const int st = j % kFwdVStages;
+        if (!wait_or_flag(&ss->v_empty[st], (uint32_t)(((j / kFwdVStages) & 1) ^ 1), ss))
           break;
-        mbar_arrive_expect_tx(&ss->v_full[st], kKVTileBytes);
-        tma_load_4d(sV + st * kKVTileBytes, &v_map, 0, hk, j * kFwdBN, b, &ss->v_full[st]);
-        tma_load_4d(sV + st * kKVTileBytes + kKVHalf, &v_map, 64, hk, j * kFwdBN, b, &ss->v_full[st]);
+        mbar_arrive_expect_tx(&ss->v_full[st], kTileBytes);
+        tma_load_4d(sV + st * kTileBytes, &v_map, 0, hk, j * kBN, b, &ss->v_full[st]);
+        tma_load_4d(sV + st * kTileBytes + kHalfTile, &v_map, 64, hk, j * kBN, b, &ss->v_full[st]);
       }
     }
   } else if (warp == 1) {
-    // ----------------------------------------------------------- issuer of S = Q K^T
-    // Both products take their A operand from tensor memory (Q, copied there once; P, written
-    // there by the softmax warps), so shared memory only feeds the B operands K and V.  The two
-    // products have their own issuing warps: each loop is two waits and a handful of
-    // instructions per tile, and neither product ever queues behind a wait of the other.
+    // ----------------------------------------------------------- MMA issuer
+    // For a group's tile j the order is  O_g += P_g V_j ,  S_g = Q K_{j+2}^T : the tensor core runs
+    // what this warp issues in order, so the product that reads P_g from the columns of S_g is
+    // done with them before the next S_g is written there.
     if (n > 0) {
-      constexpr uint32_t idesc_qk = umma_idesc_f16(kBF16, kBM, kFwdBN, false, false);
-      const uint32_t tm = __shfl_sync(0xffffffffu, tmem, 0);
-      const uint32_t k_addr = smem_addr(sK);
-      bool ok = warp_wait_or_flag(&ss->q_ready, 0, ss);
-      for (int j = 0; ok && j < n; ++j) {
-        const int g = j & 1, i = j >> 1, st = j % kFwdStages; // tile j is the i-th tile of softmax group g
-        // S of group g is free once the group has its previous tile in registers
-        ok = warp_wait2_or_flag(&ss->k_full[st], (uint32_t)((j / kFwdStages) & 1), &ss->s_empty[g],
-                                (uint32_t)((i & 1) ^ 1), ss);
-        if (!ok)
-          break;
-        tc_fence_after_sync();
-        const uint32_t d_tmem = tm + (g ? kColS1 : kColS0);
-#pragma unroll
-        for (int kk = 0; kk < 8; ++kk) { // 8 steps of 16 head dims
-          const uint64_t bdesc =
-              umma_smem_desc(k_addr + st * kKVTileBytes + (kk >> 2) * kKVHalf + (kk & 3) * 32, 16, 1024);
-          if (elect_one())
-            umma_ts(d_tmem, tm + kColQ + kk * 8, bdesc, idesc_qk, kk != 0);
-        }
-        if (elect_one()) {
-          umma_commit(&ss->s_full[g]);
-          umma_commit(&ss->k_empty[st]);
-        }
-      }
-    }
-  } else if (warp == 3) {
-    // ----------------------------------------------------------- issuer of O += P V
-    if (n > 0) {
+      constexpr uint32_t idesc_qk = umma_idesc_f16(kBF16, kBM, kBN, false, false);
       constexpr uint32_t idesc_pv = umma_idesc_f16(kBF16, kBM, kD, false, true);
       const uint32_t tm = __shfl_sync(0xffffffffu, tmem, 0);
-      const uint32_t v_addr = smem_addr(sV);
-      bool ok = true;
+      const uint32_t q_addr = smem_addr(sQ), k_addr = smem_addr(sK), v_addr = smem_addr(sV);
+      auto issue_qk = [&](int j) { // S[j & 1] = Q K_j^T: 8 steps of 16 head dims
+        const int st = j % kFwdKStages;
+        const uint32_t d_tmem = tm + ((j & 1) ? kColS1 : kColS0);
+#pragma unroll
+        for (int kk = 0; kk < 8; ++kk) {
+          const uint32_t off = (kk >> 2) * kHalfTile + (kk & 3) * 32;
+          const uint64_t adesc = umma_smem_desc(q_addr + off, 16, 1024);
+          const uint64_t bdesc = umma_smem_desc(k_addr + st * kTileBytes + off, 16, 1024);
+          if (elect_one())
+            umma_ss(d_tmem, adesc, bdesc, idesc_qk, kk != 0);
+        }
+        if (elect_one()) {
+          umma_commit(&ss->s_full[j & 1]);
+          umma_commit(&ss->k_empty[st]);
+        }
+      };
+      bool ok = warp_wait_or_flag(&ss->bar_q, 0, ss);
+      for (int j = 0; ok && j < 2 && j < n; ++j) {
+        ok = warp_wait_or_flag(&ss->k_full[j % kFwdKStages], 0, ss);
+        if (ok) {
+          tc_fence_after_sync();
+          issue_qk(j);
+        }
+      }
       for (int j = 0; ok && j < n; ++j) {
-        const int g = j & 1, i = j >> 1, st = j % kFwdStages;
-        ok = warp_wait2_or_flag(&ss->v_full[st], (uint32_t)((j / kFwdStages) & 1), &ss->p_full[g],
-                                (uint32_t)(i & 1), ss);
+        const int g = j & 1, i = j >> 1, st = j % kFwdVStages; // tile j is the i-th tile of softmax group g
+        ok = warp_wait_or_flag(&ss->v_full[st], (uint32_t)((j / kFwdVStages) & 1), ss) &&
+             warp_wait_or_flag(&ss->p_full[g], (uint32_t)(i & 1), ss);
         if (!ok)
           break;
         tc_fence_after_sync();
 #pragma unroll
-        for (int ks = 0; ks < 4; ++ks) {
+        for (int kk = 0; kk < 8; ++kk) { // 8 steps of 16 keys
           // A: P[:, 16 keys] in tensor memory; B: V[16 keys, 128 dims] (dims contiguous = MN-major)
-          const uint64_t bdesc = umma_smem_desc(v_addr + st * kKVTileBytes + ks * 16 * 128, kKVHalf, 1024);
+          const uint64_t bdesc = umma_smem_desc(v_addr + st * kTileBytes + kk * 16 * 128, kHalfTile, 1024);
           if (elect_one())
-            umma_ts(tm + (g ? kColO1 : kColO0), tm + (g ? kColP1 : kColP0) + ks * 8, bdesc, idesc_pv,
-                    (i | ks) != 0);
+            umma_ts(tm + (g ? kColO1 : kColO0), tm + (g ? kColS1 : kColS0) + kk * 8, bdesc, idesc_pv,
+                    (i | kk) != 0);
         }
         if (elect_one()) {
-          umma_commit(&ss->o_done[g]);
           umma_commit(&ss->v_empty[st]);
+          if (j + 2 >= n)
+            umma_commit(&ss->o_done[g]); // the group's last tile
+        }
+        if (j + 2 < n) {
+          ok = warp_wait_or_flag(&ss->k_full[(j + 2) % kFwdKStages], (uint32_t)(((j + 2) / kFwdKStages) & 1), ss);
+          if (!ok)
+            break;
+          tc_fence_after_sync();
+          issue_qk(j + 2);
         }
       }
     }
   } else if (warp >= 4) {
     // ------------------------------------------------------------- softmax
+    reg_inc<kSoftmaxRegs>();
     const int g = (warp - 4) >> 2;           // group: key tiles g, g + 2, g + 4, ...
     const int quarter = warp & 3;            // tensor-memory lanes 32 * quarter .. + 31
     const int row = quarter * 32 + lane;     // query row inside the tile
     const int64_t qrow = q0 + row;           // global query row
     const uint32_t lane_base = (uint32_t)(quarter * 32) << 16;
-    const uint32_t col_s = g ? kColS1 : kColS0, col_o = g ? kColO1 : kColO0, col_p = g ? kColP1 : kColP0;
+    const uint32_t col_s = g ? kColS1 : kColS0, col_o = g ? kColO1 : kColO0;
     const int n_mine = (n + 1 - g) >> 1;
     float m_used = -INFINITY, l = 0.f;
     bool ok = true;
-
-    if (g == 0 && n > 0) {
-      // Q row -> tensor memory (two 16-bit head dims per 32-bit column), as the A operand of Q K^T
-      ok = wait_or_flag(&ss->bar_q, 0, ss);
-#pragma unroll
-      for (int db = 0; db < 2; ++db) {
-        uint32_t r[32];
-#pragma unroll
-        for (int c = 0; c < 8; ++c) {
-          const uint4 v = *reinterpret_cast<const uint4 *>(sQ + db * kHalfTile + row * 128 + ((c ^ (row & 7)) << 4));
-          r[c * 4 + 0] = v.x;
-          r[c * 4 + 1] = v.y;
-          r[c * 4 + 2] = v.z;
-          r[c * 4 + 3] = v.w;
-        }
-        tmem_st32(tmem + lane_base + kColQ + db * 32, r);
-      }
-      tmem_wait_st();
-      tc_fence_before_sync();
-      __syncwarp();
-      if (lane == 0 && ok)
-        mbar_arrive(&ss->q_ready);
-    }
 
     for (int i = 0; ok && i < n_mine; ++i) {
       const int j = 2 * i + g;
@@ -372,44 +345,43 @@ __global__ void __launch_bounds__(kThreads, 1)
         break;
       }
       tc_fence_after_sync();
-      // the whole row of S into registers; S may then be overwritten by the group's next Q K^T
-      uint32_t s[kFwdBN];
+      // The whole row of S into registers.  S of this tile being there means that the group's
+      // previous P V has completed as well (products complete in issue order), so both the P
+      // columns, which overlay S, and O may be written below without another wait.
+      uint32_t s[kBN];
       {
         const uint32_t base = tmem + lane_base + col_s;
-        tmem_ld32(base, *reinterpret_cast<uint32_t(*)[32]>(&s[0]));
-        tmem_ld32(base + 32, *reinterpret_cast<uint32_t(*)[32]>(&s[32]));
+#pragma unroll
+        for (int c = 0; c < 4; ++c)
+          tmem_ld32(base + c * 32, *reinterpret_cast<uint32_t(*)[32]>(&s[c * 32]));
         tmem_wait_ld();
       }
-      tc_fence_before_sync();
-      __syncwarp();
-      if (lane == 0)
-        mbar_arrive(&ss->s_empty[g]);
 
-      const int64_t kv0 = (int64_t)j * kFwdBN;
-      const bool need_mask = (right_bounded && kv0 + kFwdBN - 1 > q0 + shift + p.window_right) ||
-                             (kv0 + kFwdBN > p.Sk) || left_bounded;
+      const int64_t kv0 = (int64_t)j * kBN;
+      const bool need_mask = (right_bounded && kv0 + kBN - 1 > q0 + shift + p.window_right) ||
+                             (kv0 + kBN > p.Sk) || left_bounded;
       if (need_mask) { // visible columns of this tile for this row: [lo, hi]
         const int64_t hi64 = (right_bounded ? min(p.Sk - 1, qrow + shift + p.window_right) : p.Sk - 1) - kv0;
         const int64_t lo64 = (left_bounded ? qrow + shift - p.window_left : 0) - kv0;
-        const int hi = (int)max((int64_t)-1, min((int64_t)kFwdBN - 1, hi64));
-        const int lo = (int)max((int64_t)0, min((int64_t)kFwdBN, lo64));
+        const int hi = (int)max((int64_t)-1, min((int64_t)kBN - 1, hi64));
+        const int lo = (int)max((int64_t)0, min((int64_t)kBN, lo64));
 #pragma unroll
-        for (int c = 0; c < kFwdBN; ++c)
+        for (int c = 0; c < kBN; ++c)
           if (c > hi || c < lo)
             s[c] = 0xff800000u; // -inf
       }
-      // row maximum: four independent chains of 3-input max
-      float mx4[4];
+      // row maximum: eight independent chains of 3-input max
+      float mx8[8];
 #pragma unroll
-      for (int e = 0; e < 4; ++e)
-        mx4[e] = fmaxf(__uint_as_float(s[2 * e]), __uint_as_float(s[2 * e + 1]));
+      for (int e = 0; e < 8; ++e)
+        mx8[e] = fmaxf(__uint_as_float(s[2 * e]), __uint_as_float(s[2 * e + 1]));
 #pragma unroll
-      for (int c = 8; c < kFwdBN; c += 8) {
+      for (int c = 16; c < kBN; c += 16) {
 #pragma unroll
-        for (int e = 0; e < 4; ++e)
-          mx4[e] = fmax3(mx4[e], __uint_as_float(s[c + 2 * e]), __uint_as_float(s[c + 2 * e + 1]));
+        for (int e = 0; e < 8; ++e)
+          mx8[e] = fmax3(mx8[e], __uint_as_float(s[c + 2 * e]), __uint_as_float(s[c + 2 * e + 1]));
       }
-      const float mx = fmaxf(fmax3(mx4[0], mx4[1], mx4[2]), mx4[3]);
+      const float mx = fmax3(fmax3(mx8[0], mx8[1], mx8[2]), fmax3(mx8[3], mx8[4], mx8[5]), fmaxf(mx8[6], mx8[7]));
       const float m_new = fmaxf(m_used, mx * p.scale_log2);
       float alpha = 1.f;
       const bool grew = m_new - m_used > kRescaleThreshold; // also true for -inf -> finite
@@ -426,9 +398,9 @@ __global__ void __launch_bounds__(kThreads, 1)
       // four independent packed partial sums; the 16-bit P reuses the front of the row's registers
       const uint64_t scale2 = f2_pack(p.scale_log2, p.scale_log2), negm2 = f2_pack(-m_safe, -m_safe);
       uint64_t sum2[4] = {0ull, 0ull, 0ull, 0ull};
-      uint32_t(&packed)[kFwdBN] = s;
+      uint32_t(&packed)[kBN] = s;
 #pragma unroll
-      for (int c = 0; c < kFwdBN; c += 2) {
+      for (int c = 0; c < kBN; c += 2) {
         const uint64_t x2 = f2_fma(f2_pack(__uint_as_float(s[c]), __uint_as_float(s[c + 1])), scale2, negm2);
         float x0, x1;
         f2_unpack(x2, x0, x1);
@@ -443,14 +415,10 @@ __global__ void __launch_bounds__(kThreads, 1)
         l += (a0 + a1) + (b0 + b1);
       }
 
-      // the group's P columns and O are busy until P V of its previous tile has finished
-      if (i > 0 && !wait_or_flag(&ss->o_done[g], (uint32_t)((i - 1) & 1), ss)) {
-        ok = false;
-        break;
-      }
-      tc_fence_after_sync();
-      // P row -> tensor memory: 64 keys = 32 columns of two 16-bit values
-      tmem_st32(tmem + lane_base + col_p, *reinterpret_cast<uint32_t(*)[32]>(&packed[0]));
+      // P row -> tensor memory, over the front half of the row's S: 128 keys = 64 columns of two
+      // 16-bit values
+      tmem_st32(tmem + lane_base + col_s, *reinterpret_cast<uint32_t(*)[32]>(&packed[0]));
+      tmem_st32(tmem + lane_base + col_s + 32, *reinterpret_cast<uint32_t(*)[32]>(&packed[32]));
       if (rescale) {
         const uint32_t base = tmem + lane_base + col_o;
 #pragma unroll
@@ -473,7 +441,7 @@ __global__ void __launch_bounds__(kThreads, 1)
 
     // ---- epilogue: merge the two groups' partial results, O / l -> 16 bit -> shared -> TMA store; LSE
     if (ok && n_mine > 0)
-      ok = wait_or_flag(&ss->o_done[g], (uint32_t)((n_mine - 1) & 1), ss);
+      ok = wait_or_flag(&ss->o_done[g], 0, ss);
     ss->xch[g][row] = make_float2(m_used, l);
     tc_fence_before_sync();
     const bool give_up = named_bar_or_n<256>(!ok); // both groups; every product and load is complete
@@ -1080,9 +1048,9 @@ extern "C" int b200_flash_attn_fwd(int dtype, const void *q, const void *k, cons
   CUtensorMap q_map, k_map, v_map, o_map;
   if (int rc = make_qkv_map(&q_map, bf16, q, a.d, a.h, a.seqlen_q, a.b, a.q_head_stride, a.q_row_stride, a.q_batch_stride))
     return rc;
-  if (int rc = make_qkv_map(&k_map, bf16, k, a.d, a.h_k, a.seqlen_k, a.b, a.k_head_stride, a.k_row_stride, a.k_batch_stride, kFwdBN))
+  if (int rc = make_qkv_map(&k_map, bf16, k, a.d, a.h_k, a.seqlen_k, a.b, a.k_head_stride, a.k_row_stride, a.k_batch_stride))
     return rc;
-  if (int rc = make_qkv_map(&v_map, bf16, v, a.d, a.h_k, a.seqlen_k, a.b, a.v_head_stride, a.v_row_stride, a.v_batch_stride, kFwdBN))
+  if (int rc = make_qkv_map(&v_map, bf16, v, a.d, a.h_k, a.seqlen_k, a.b, a.v_head_stride, a.v_row_stride, a.v_batch_stride))
     return rc;
   if (int rc = make_qkv_map(&o_map, bf16, out, a.d, a.h, a.seqlen_q, a.b, a.o_head_stride, a.o_row_stride, a.o_batch_stride))
     return rc;
@@ -1096,7 +1064,7 @@ extern "C" int b200_flash_attn_fwd(int dtype, const void *q, const void *k, cons
   p.scale_log2 = a.softmax_scale * 1.4426950408889634f;
   p.window_left = a.window_size_left;
   p.window_right = a.window_size_right;
-  const size_t smem = (size_t)kTileBytes + 2 * kFwdStages * kKVTileBytes + sizeof(SharedStorage) + 1024;
+  const size_t smem = (size_t)(1 + kFwdKStages + kFwdVStages) * kTileBytes + sizeof(SharedStorage) + 1024;
   static bool attr_set[2] = {false, false};
   if (!attr_set[bf16]) {
     cudaError_t e = bf16 ? cudaFuncSetAttribute(flash_fwd_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem)
