@@ -135,6 +135,9 @@ class Workload:
     def work_per_step(self):  # algorithmic bytes (or FLOPs) of one step on one GPU
         raise NotImplementedError
 
+    def end_batch(self):  # joins whatever a batch of pipelined steps left running beside the stream
+        pass
+
     def dominant(self):  # (kernel name, algorithmic work per launch)
         raise NotImplementedError
 
@@ -201,30 +204,49 @@ class ReduceC2(Workload):
         self.sharded = ops.ShardedSum(self.rank, self.world, n, ptrs, [p + flag_off for p in ptrs],
                                       self.counter, self.status)
         self.side = torch.cuda.Stream()
+        self.parts = [self.part, torch.empty_like(self.part)]
+        self.xdone = [torch.cuda.Event(), torch.cuda.Event()]
+        self.kstep = 0
 
-    def step_gpu(self, x, dist=None):
+    def step_gpu(self, x, dist=None, pipelined=False):
         ops = self.ops
-        if self.world > 1:
-            # the reduced axis (dim 0 of the global [64 * world, 512, 1024] tensor) is sharded: the
-            # all-reduce of the 4 KiB of f32 partials runs beside the (independent) max reduction
+        if self.world > 1 and self.sharded is not None:
+            # The reduced axis (dim 0 of the global [64 * world, 512, 1024] tensor) is sharded.  The
+            # exchange of the 4 KiB of f32 partials (one block, NVLink latency) runs on a side stream
+            # beside the max reduction (whole GPU, HBM-bound).  Inside a batch of back-to-back steps
+            # (pipelined) the step does not wait for its exchange: it overlaps the next step as well,
+            # the partials alternate between two buffers, and end_batch() joins the side stream.
+            torch = self.torch
+            cur = torch.cuda.current_stream()
+            k = self.kstep
+            part = self.parts[k & 1]
+            if k >= 2:
+                cur.wait_event(self.xdone[k & 1])  # the exchange two steps back has read this buffer
+            ops.reduce_sum_to_f32(x, [0, 1], out=part, workspace=self.ws)
+            self.side.wait_stream(cur)
+            with torch.cuda.stream(self.side):
+                self.sharded(part, self.out_sum)
+                self.xdone[k & 1].record(self.side)
+            ops.reduce_max(x, [2], out=self.out_max)
+            self.kstep = k + 1
+            if not pipelined:
+                self.end_batch()
+        elif self.world > 1:
+            # comparison path: NCCL all-reduce of the partials beside the max reduction, then the cast
             ops.reduce_sum_to_f32(x, [0, 1], out=self.part, workspace=self.ws)
-            if self.sharded is not None:
-                # exchange (one block, NVLink latency) beside the max reduction (whole GPU, HBM-bound)
-                cur = self.torch.cuda.current_stream()
-                self.side.wait_stream(cur)
-                with self.torch.cuda.stream(self.side):
-                    self.sharded(self.part, self.out_sum)
-                ops.reduce_max(x, [2], out=self.out_max)
-                cur.wait_stream(self.side)
-            else:
-                work = dist.all_reduce(self.part, async_op=True)
-                ops.reduce_max(x, [2], out=self.out_max)
-                work.wait()
-                ops.cast_from_f32(self.part, self.torch.float16, out=self.out_sum)
+            work = dist.all_reduce(self.part, async_op=True)
+            ops.reduce_max(x, [2], out=self.out_max)
+            work.wait()
+            ops.cast_from_f32(self.part, self.torch.float16, out=self.out_sum)
         else:
             ops.reduce_sum(x, [0, 1], out=self.out_sum, workspace=self.ws)
             ops.reduce_max(x, [2], out=self.out_max)
         return self.out_sum, self.out_max
+
+    def end_batch(self):
+        if self.world > 1 and self.sharded is not None:
+            self.torch.cuda.current_stream().wait_stream(self.side)
+            self.kstep = 0
 
     def dominant_gpu(self, x):
         self.ops.reduce_sum(x, [0, 1], out=self.out_sum, workspace=self.ws)
@@ -680,11 +702,23 @@ def main():
                 fn(i)
         return g
 
+    # a batch of K back-to-back steps: a workload with an exchange step may let it overlap the
+    # next step (ReduceC2 at N > 1); the last call of the batch joins it
+    pipelined = isinstance(wl, ReduceC2) and world > 1
+
+    def batch_step(i):
+        if pipelined:
+            wl.step_gpu(xs[i % n_buf], dist, pipelined=True)
+            if i == args.steps - 1:
+                wl.end_batch()
+        else:
+            wl.step_gpu(xs[i % n_buf], dist)
+
     use_graph = not args.no_graph
     step_graph = None
     if use_graph:
         try:
-            step_graph = capture(lambda i: wl.step_gpu(xs[i % n_buf], dist), args.steps)
+            step_graph = capture(batch_step, args.steps)
             step_graph.replay()  # untimed: first replay uploads the graph
         except Exception as e:  # pragma: no cover - depends on the NCCL / driver combination
             print(f"graph capture failed ({e}); timing eager launches", file=sys.stderr)
@@ -705,7 +739,7 @@ def main():
         step_graph.replay()
     else:
         for i in range(args.steps):
-            wl.step_gpu(xs[i % n_buf], dist)
+            batch_step(i)
     ev1.record()
     sync_all()
     ms = ev0.elapsed_time(ev1)
