@@ -78,6 +78,11 @@ __device__ __forceinline__ uint64_t f2_add(uint64_t a, uint64_t b) {
   asm("add.rn.f32x2 %0, %1, %2;" : "=l"(r) : "l"(a), "l"(b));
   return r;
 }
+__device__ __forceinline__ uint64_t f2_mul(uint64_t a, uint64_t b) {
+  uint64_t r;
+  asm("mul.rn.f32x2 %0, %1, %2;" : "=l"(r) : "l"(a), "l"(b));
+  return r;
+}
 __device__ __forceinline__ float fmax3(float a, float b, float c) {
   float r;
   asm("max.f32 %0, %1, %2, %3;" : "=f"(r) : "f"(a), "f"(b), "f"(c));
@@ -561,7 +566,10 @@ struct BwdShared {
   uint64_t all_done;                              // every MMA of the block has completed
   uint32_t tmem_base;
   int failed;
-  float2 stats[2][2][kBwdBN]; // dK/dV kernel: (lse * log2e, dsum) of the streamed queries [group][parity][row]
+  // dK/dV kernel: -lse * log2e and -dsum of the streamed queries [group][parity][row], negated
+  // so that pairs of them are addends of packed FMAs / ADDs
+  float neg_lse2[2][2][kBwdBN];
+  float neg_dsum[2][2][kBwdBN];
 };
 
 __device__ __forceinline__ bool bwd_wait(uint64_t *bar, uint32_t parity, BwdShared *ss) {
@@ -863,21 +871,34 @@ __global__ void __launch_bounds__(kThreads, 1)
         mbar_arrive(&ss->res_ready);
     }
     const int n_mine = (T + 1 - g) >> 1;
+    // dK/dV: statistics of the 64 streamed queries of a tile, one query per thread of the group's
+    // first two warps.  They are fetched one tile ahead, so that the two dependent global loads
+    // are not on the path between two tiles.
+    const int stat_t = (warp & 3) * 32 + lane;
+    auto load_stats = [&](int i, float &l2, float &dd) {
+      l2 = INFINITY, dd = 0.f; // rows past the end: P = exp2(-inf) = 0
+      if (kDKDV && stat_t < kBwdBN && i < n_mine) {
+        const int it = 2 * i + g;
+        const int64_t qi = (int64_t)iter_tile(it) * kBwdBN + stat_t;
+        const int qh = iter_head(it);
+        if (qi < p.Sq) {
+          l2 = p.lse[((int64_t)b * p.H + qh) * p.Sq + qi] * kLog2e;
+          dd = p.dsum[((int64_t)b * p.H + qh) * p.Sq_rounded + qi];
+        }
+      }
+    };
+    float next_l2, next_dd;
+    load_stats(0, next_l2, next_dd);
+    const uint64_t scale2 = f2_pack(p.scale_log2, p.scale_log2);
     for (int i = 0; ok && i < n_mine; ++i) {
       const int it = 2 * i + g;
       const int64_t str0 = (int64_t)iter_tile(it) * kBwdBN;
-      if (kDKDV) { // statistics of the 64 streamed queries, one per thread of the first two warps
-        const int t = (warp & 3) * 32 + lane;
-        if (t < kBwdBN) {
-          const int64_t qi = str0 + t;
-          const int qh = iter_head(it);
-          float l2 = INFINITY, dd = 0.f; // rows past the end: P = exp2(-inf) = 0
-          if (qi < p.Sq) {
-            l2 = p.lse[((int64_t)b * p.H + qh) * p.Sq + qi] * kLog2e;
-            dd = p.dsum[((int64_t)b * p.H + qh) * p.Sq_rounded + qi];
-          }
-          ss->stats[g][i & 1][t] = make_float2(l2, dd);
+      if (kDKDV) {
+        if (stat_t < kBwdBN) {
+          ss->neg_lse2[g][i & 1][stat_t] = -next_l2;
+          ss->neg_dsum[g][i & 1][stat_t] = -next_dd;
         }
+        load_stats(i + 1, next_l2, next_dd); // in flight during this tile
       }
       const bool waited = bwd_wait(&ss->sdp_full[g], (uint32_t)(i & 1), ss);
       // one barrier per tile and group: publishes the statistics and makes giving up unanimous
@@ -920,24 +941,32 @@ __global__ void __launch_bounds__(kThreads, 1)
             if (c * 32 + q > hi || c * 32 + q < lo)
               sr[q] = 0xff800000u; // -inf: P = 0, dS = 0
         }
+        // P = 2^(S * scale - lse), dS = P * (dP - dsum): four columns per step, two per packed op
 #pragma unroll
-        for (int q = 0; q < 32; q += 2) {
-          float pv[2], dv[2];
+        for (int q = 0; q < 32; q += 4) {
+          uint64_t nl[2], nd[2];
+          if (kDKDV) {
+            const float4 l4 = *reinterpret_cast<const float4 *>(&ss->neg_lse2[g][i & 1][c * 32 + q]);
+            const float4 d4 = *reinterpret_cast<const float4 *>(&ss->neg_dsum[g][i & 1][c * 32 + q]);
+            nl[0] = f2_pack(l4.x, l4.y), nl[1] = f2_pack(l4.z, l4.w);
+            nd[0] = f2_pack(d4.x, d4.y), nd[1] = f2_pack(d4.z, d4.w);
+          } else {
+            nl[0] = nl[1] = f2_pack(-my_lse2, -my_lse2);
+            nd[0] = nd[1] = f2_pack(-my_dsum, -my_dsum);
+          }
 #pragma unroll
           for (int e = 0; e < 2; ++e) {
-            const int col = c * 32 + q + e;
-            float l2 = my_lse2, ds_ = my_dsum;
-            if (kDKDV) {
-              const float2 st = ss->stats[g][i & 1][col];
-              l2 = st.x;
-              ds_ = st.y;
-            }
-            const float pr = fast_exp2(fmaf(__uint_as_float(sr[q + e]), p.scale_log2, -l2));
-            pv[e] = pr;
-            dv[e] = pr * (__uint_as_float(dr[q + e]) - ds_);
+            const int k = q + 2 * e;
+            const uint64_t x2 = f2_fma(f2_pack(__uint_as_float(sr[k]), __uint_as_float(sr[k + 1])), scale2, nl[e]);
+            float x0, x1;
+            f2_unpack(x2, x0, x1);
+            const float p0 = fast_exp2(x0), p1 = fast_exp2(x1);
+            const uint64_t t2 = f2_add(f2_pack(__uint_as_float(dr[k]), __uint_as_float(dr[k + 1])), nd[e]);
+            float d0, d1;
+            f2_unpack(f2_mul(f2_pack(p0, p1), t2), d0, d1);
+            pp[c * 16 + k / 2] = pack2(p0, p1, kBF16);
+            dd[c * 16 + k / 2] = pack2(d0, d1, kBF16);
           }
-          pp[c * 16 + q / 2] = pack2(pv[0], pv[1], kBF16);
-          dd[c * 16 + q / 2] = pack2(dv[0], dv[1], kBF16);
         }
       }
       // both tiles are in registers: P^T / dS^T (dS) take the place of the values they came from
