@@ -4,29 +4,38 @@
 // tiles of 128 rows that the mask lets it see.  Warp roles (three warpgroups):
 //   warp 0        TMA producer of Q (once) and of the K tiles (3-stage ring)
 //   warp 2        TMA producer of the V tiles (2-stage ring)
-//   warp 1        MMA issuer: S = Q K^T and O += P V with tcgen05.mma; all lanes run the
-//                 loop and the waits, one elected lane executes the tcgen05 instructions
+//   warp 1        issuer of S = Q K^T  (tcgen05.mma; all lanes run the loop and the waits,
+//   warp 3        issuer of O += P V    one elected lane executes the tcgen05 instructions)
 //   warps 4..7    softmax group 0: key tiles 0, 2, 4, ...
 //   warps 8..11   softmax group 1: key tiles 1, 3, 5, ...
-// Each group has its own S tile and its own O accumulator in tensor memory (columns
-// S 0,128 | O 256,384: all 512) and its own running (max, sum) per row.  Inside a group
-// thread t owns query row t: it reads its row of S, keeps the running max / sum, writes
-// P (16-bit) back to tensor memory over the front half of the row's S, where it is the A
-// operand of P V, and rescales its O when the running max moved.  For a group the tensor
-// core runs  P V (tile j),  Q K^T (tile j + 2)  back to back while the other group does
-// its softmax, so the two groups alternate between the tensor core and the MUFU / FMA
-// pipes.  At the end the two partial results of a row are merged like two splits of the
-// key axis:
-//   O = (O0 2^(m0-m) + O1 2^(m1-m)) / (l0 2^(m0-m) + l1 2^(m1-m)),  m = max(m0, m1).
+// Tensor memory (all 512 columns): S 0,128 | P 256,320 | O 384.  Each group has its own S
+// tile and its own P tile, so the next S of a group is computed while the group still works
+// on its current tile and nothing waits for a buffer; the one O accumulator takes P V of all
+// tiles in order.  Inside a group thread t owns query row t: it reads its row of S, finds
+// the row maximum, writes P (16-bit) to tensor memory, where it is the A operand of P V
+// (tcgen05.mma with A in tensor memory), and keeps a partial row sum.
+//
+// One accumulator for two groups needs one reference maximum per row that both threads of the
+// row agree on.  It is the running maximum of the sequential algorithm: every thread replays
+// the same steps over ALL key tiles (ref_step), its own tiles from its own maxima, the other
+// group's tiles from the maxima that group publishes in shared memory right after finding
+// them (long before they are needed, so the wait is a formality).  The step of tile j belongs
+// to the group of tile j: if the reference moved, that thread multiplies the row of O by
+// 2^(old - new) after P V of tile j - 1 has completed and before it hands over P of tile j;
+// the P V issuer takes the tiles in order, so no product ever sees a half-rescaled row.  Both
+// threads scale their partial sums by every step's factor.  The reference only moves when a
+// row of the warp grew by more than 2^8, so rescaling is rare after the first tiles.
+// At the end the two partial sums are added (the thread that is one step behind scales
+// its sum by the last factor), each thread finishes 64 head-dim columns of its row.
 // The control warps give most of their registers to the softmax warps (setmaxnreg).
 //
 // Numerics follow the reference kernel (external_libs/runtime/flash_attn/lib/
 // softmax.h:129-178, flash_fwd_kernel.h:276-453): exp2 domain with the scale
 // folded in, row sum from the unrounded f32 probabilities, P rounded to the
 // storage type before P V, LSE = max * scale + ln(sum), +inf for a fully masked
-// row.  One deviation that stays inside the rounding of P: O is only rescaled when
-// the running max grew by more than 2^8 (the stale max is used consistently for
-// P, the row sum and the LSE).
+// row.  One deviation that stays inside the rounding of P: the stale reference
+// (at most 2^8 below the true running maximum) is used consistently for P, the
+// row sum and the LSE.
 #include <cuda.h>
 
 #include "common.cuh"
@@ -43,10 +52,9 @@ constexpr uint32_t kTileBytes = kBN * kD * 2;  // 32 KiB: two 64-column blocks o
 constexpr uint32_t kHalfTile = kTileBytes / 2; // one 64-column block
 constexpr int kThreads = 384;    // four control warps, two groups of four softmax / elementwise warps
 constexpr uint32_t kTmemCols = 512;
-// forward: two S tiles (P overlays their front halves) and two O accumulators fill the 512
-// columns of tensor memory
+// forward: two S tiles, two P tiles and one O accumulator fill the 512 columns of tensor memory
 constexpr int kFwdKStages = 3, kFwdVStages = 2; // K / V ring depths of the forward kernel
-constexpr uint32_t kColS0 = 0, kColS1 = 128, kColO0 = 256, kColO1 = 384;
+constexpr uint32_t kColS0 = 0, kColS1 = 128, kColP0 = 256, kColP1 = 320, kColO = 384;
 constexpr int kCtrlRegs = 56, kSoftmaxRegs = 224; // 128 * 56 + 256 * 224 <= 64 Ki registers
 constexpr float kRescaleThreshold = 8.0f; // log2 units
 
@@ -132,12 +140,14 @@ template <int N> __device__ __forceinline__ void reg_inc() {
 struct SharedStorage {
   uint64_t bar_q;
   uint64_t k_full[kFwdKStages], k_empty[kFwdKStages], v_full[kFwdVStages], v_empty[kFwdVStages];
-  uint64_t s_full[2];  // per softmax group: S of its tile is in tensor memory
-  uint64_t p_full[2];  // per softmax group: P of its tile is in tensor memory
-  uint64_t o_done[2];  // per softmax group: its last P V has completed
+  uint64_t s_full[2], s_empty[2]; // per softmax group: S of its tile is in tensor memory / in registers
+  uint64_t p_full[2];             // per softmax group: P of its tile is in tensor memory, O is rescaled
+  uint64_t pv_done[2];            // per softmax group: the P V of its tile has completed
+  uint64_t mx_ready[2];           // per softmax group: the row maxima of its tile are in `rowmax`
   uint32_t tmem_base;
   int failed;
-  float2 xch[2][kBM]; // (running max, row sum) of each group, for the final merge
+  float rowmax[2][2][kBM]; // [group][tile parity][row]: scaled row maximum of the group's tile
+  float2 xch[2][kBM];      // (reference max, row sum) of each group, for the final merge
 };
 
 __device__ __forceinline__ bool wait_or_flag(uint64_t *bar, uint32_t parity, SharedStorage *ss) {
@@ -147,7 +157,7 @@ __device__ __forceinline__ bool wait_or_flag(uint64_t *bar, uint32_t parity, Sha
   return false;
 }
 
-// The MMA-issuing warp runs its loop with all 32 lanes (waits included) and only the
+// The MMA-issuing warps run their loops with all 32 lanes (waits included) and only the
 // tcgen05 instructions themselves are executed by one elected lane: descriptors and
 // addresses then live in uniform registers, which is what the instruction takes, and
 // an issue costs ~10 cycles instead of ~55 from inside a single-lane branch.
@@ -176,6 +186,24 @@ __device__ __forceinline__ uint32_t pack2(float lo, float hi, bool bf16) {
   }
   __half2 v = __floats2half2_rn(lo, hi);
   return *reinterpret_cast<uint32_t *>(&v);
+}
+
+// One step of the running reference maximum of the rows of a warp: `m` are the rows' (scaled)
+// maxima of key tile `tile`.  The reference only moves when some row of the warp grew by more
+// than 2^8 (then every row of the warp takes its new maximum), so that O is rescaled rarely.
+// Returns whether it moved; alpha = 2^(old - new) is the factor for everything accumulated so far.
+__device__ __forceinline__ bool ref_step(int tile, float m, float &ref, float &alpha) {
+  const float m_new = fmaxf(ref, m);
+  const bool grew = m_new - ref > kRescaleThreshold; // also true for -inf -> finite
+  const bool moved = tile > 0 && __any_sync(0xffffffffu, grew);
+  alpha = 1.f;
+  if (tile == 0) {
+    ref = m_new;
+  } else if (moved) {
+    alpha = (m_new == -INFINITY) ? 1.f : fast_exp2(ref - m_new);
+    ref = m_new;
+  }
+  return moved;
 }
 
 template <bool kBF16>
@@ -220,8 +248,10 @@ __global__ void __launch_bounds__(kThreads, 1)
     }
     for (int g = 0; g < 2; ++g) {
       mbar_init(&ss->s_full[g], 1);
+      mbar_init(&ss->s_empty[g], 4);
       mbar_init(&ss->p_full[g], 4);
-      mbar_init(&ss->o_done[g], 1);
+      mbar_init(&ss->pv_done[g], 1);
+      mbar_init(&ss->mx_ready[g], 4);
     }
     ss->failed = 0;
     mbar_fence_init();
@@ -268,20 +298,24 @@ __global__ void __launch_bounds__(kThreads, 1)
       }
     }
   } else if (warp == 1) {
-    // ----------------------------------------------------------- MMA issuer
-    // For a group's tile j the order is  O_g += P_g V_j ,  S_g = Q K_{j+2}^T : the tensor core runs
-    // what this warp issues in order, so the product that reads P_g from the columns of S_g is
-    // done with them before the next S_g is written there.
+    // ----------------------------------------------------------- issuer of S = Q K^T
+    // S of a group is free as soon as the group has its previous tile in registers, so the
+    // next S is normally ready before the group asks for it.
     if (n > 0) {
       constexpr uint32_t idesc_qk = umma_idesc_f16(kBF16, kBM, kBN, false, false);
-      constexpr uint32_t idesc_pv = umma_idesc_f16(kBF16, kBM, kD, false, true);
       const uint32_t tm = __shfl_sync(0xffffffffu, tmem, 0);
-      const uint32_t q_addr = smem_addr(sQ), k_addr = smem_addr(sK), v_addr = smem_addr(sV);
-      auto issue_qk = [&](int j) { // S[j & 1] = Q K_j^T: 8 steps of 16 head dims
-        const int st = j % kFwdKStages;
-        const uint32_t d_tmem = tm + ((j & 1) ? kColS1 : kColS0);
+      const uint32_t q_addr = smem_addr(sQ), k_addr = smem_addr(sK);
+      bool ok = warp_wait_or_flag(&ss->bar_q, 0, ss);
+      for (int j = 0; ok && j < n; ++j) {
+        const int g = j & 1, i = j >> 1, st = j % kFwdKStages; // tile j is the i-th tile of softmax group g
+        ok = warp_wait_or_flag(&ss->k_full[st], (uint32_t)((j / kFwdKStages) & 1), ss) &&
+             warp_wait_or_flag(&ss->s_empty[g], (uint32_t)((i & 1) ^ 1), ss);
+        if (!ok)
+          break;
+        tc_fence_after_sync();
+        const uint32_t d_tmem = tm + (g ? kColS1 : kColS0);
 #pragma unroll
-        for (int kk = 0; kk < 8; ++kk) {
+        for (int kk = 0; kk < 8; ++kk) { // 8 steps of 16 head dims
           const uint32_t off = (kk >> 2) * kHalfTile + (kk & 3) * 32;
           const uint64_t adesc = umma_smem_desc(q_addr + off, 16, 1024);
           const uint64_t bdesc = umma_smem_desc(k_addr + st * kTileBytes + off, 16, 1024);
@@ -289,20 +323,20 @@ __global__ void __launch_bounds__(kThreads, 1)
             umma_ss(d_tmem, adesc, bdesc, idesc_qk, kk != 0);
         }
         if (elect_one()) {
-          umma_commit(&ss->s_full[j & 1]);
+          umma_commit(&ss->s_full[g]);
           umma_commit(&ss->k_empty[st]);
         }
-      };
-      bool ok = warp_wait_or_flag(&ss->bar_q, 0, ss);
-      for (int j = 0; ok && j < 2 && j < n; ++j) {
-        ok = warp_wait_or_flag(&ss->k_full[j % kFwdKStages], 0, ss);
-        if (ok) {
-          tc_fence_after_sync();
-          issue_qk(j);
-        }
       }
+    }
+  } else if (warp == 3) {
+    // ----------------------------------------------------------- issuer of O += P V
+    if (n > 0) {
+      constexpr uint32_t idesc_pv = umma_idesc_f16(kBF16, kBM, kD, false, true);
+      const uint32_t tm = __shfl_sync(0xffffffffu, tmem, 0);
+      const uint32_t v_addr = smem_addr(sV);
+      bool ok = true;
       for (int j = 0; ok && j < n; ++j) {
-        const int g = j & 1, i = j >> 1, st = j % kFwdVStages; // tile j is the i-th tile of softmax group g
+        const int g = j & 1, i = j >> 1, st = j % kFwdVStages;
         ok = warp_wait_or_flag(&ss->v_full[st], (uint32_t)((j / kFwdVStages) & 1), ss) &&
              warp_wait_or_flag(&ss->p_full[g], (uint32_t)(i & 1), ss);
         if (!ok)
@@ -313,20 +347,11 @@ __global__ void __launch_bounds__(kThreads, 1)
           // A: P[:, 16 keys] in tensor memory; B: V[16 keys, 128 dims] (dims contiguous = MN-major)
           const uint64_t bdesc = umma_smem_desc(v_addr + st * kTileBytes + kk * 16 * 128, kHalfTile, 1024);
           if (elect_one())
-            umma_ts(tm + (g ? kColO1 : kColO0), tm + (g ? kColS1 : kColS0) + kk * 8, bdesc, idesc_pv,
-                    (i | kk) != 0);
+            umma_ts(tm + kColO, tm + (g ? kColP1 : kColP0) + kk * 8, bdesc, idesc_pv, (j | kk) != 0);
         }
         if (elect_one()) {
+          umma_commit(&ss->pv_done[g]);
           umma_commit(&ss->v_empty[st]);
-          if (j + 2 >= n)
-            umma_commit(&ss->o_done[g]); // the group's last tile
-        }
-        if (j + 2 < n) {
-          ok = warp_wait_or_flag(&ss->k_full[(j + 2) % kFwdKStages], (uint32_t)(((j + 2) / kFwdKStages) & 1), ss);
-          if (!ok)
-            break;
-          tc_fence_after_sync();
-          issue_qk(j + 2);
         }
       }
     }
@@ -338,9 +363,12 @@ __global__ void __launch_bounds__(kThreads, 1)
     const int row = quarter * 32 + lane;     // query row inside the tile
     const int64_t qrow = q0 + row;           // global query row
     const uint32_t lane_base = (uint32_t)(quarter * 32) << 16;
-    const uint32_t col_s = g ? kColS1 : kColS0, col_o = g ? kColO1 : kColO0;
+    const uint32_t col_s = g ? kColS1 : kColS0, col_p = g ? kColP1 : kColP0;
     const int n_mine = (n + 1 - g) >> 1;
-    float m_used = -INFINITY, l = 0.f;
+    // `ref` is the reference maximum of the row after the last tile this thread knows about:
+    // both threads of a row replay the same sequence of steps (ref_step) over all key tiles,
+    // the other group's tiles from the maxima it publishes.
+    float ref = -INFINITY, l = 0.f;
     bool ok = true;
 
     for (int i = 0; ok && i < n_mine; ++i) {
@@ -350,9 +378,7 @@ __global__ void __launch_bounds__(kThreads, 1)
         break;
       }
       tc_fence_after_sync();
-      // The whole row of S into registers.  S of this tile being there means that the group's
-      // previous P V has completed as well (products complete in issue order), so both the P
-      // columns, which overlay S, and O may be written below without another wait.
+      // the whole row of S into registers; S may then be overwritten by the group's next Q K^T
       uint32_t s[kBN];
       {
         const uint32_t base = tmem + lane_base + col_s;
@@ -361,6 +387,10 @@ __global__ void __launch_bounds__(kThreads, 1)
           tmem_ld32(base + c * 32, *reinterpret_cast<uint32_t(*)[32]>(&s[c * 32]));
         tmem_wait_ld();
       }
+      tc_fence_before_sync();
+      __syncwarp();
+      if (lane == 0)
+        mbar_arrive(&ss->s_empty[g]);
 
       const int64_t kv0 = (int64_t)j * kBN;
       const bool need_mask = (right_bounded && kv0 + kBN - 1 > q0 + shift + p.window_right) ||
@@ -386,19 +416,30 @@ __global__ void __launch_bounds__(kThreads, 1)
         for (int e = 0; e < 8; ++e)
           mx8[e] = fmax3(mx8[e], __uint_as_float(s[c + 2 * e]), __uint_as_float(s[c + 2 * e + 1]));
       }
-      const float mx = fmax3(fmax3(mx8[0], mx8[1], mx8[2]), fmax3(mx8[3], mx8[4], mx8[5]), fmaxf(mx8[6], mx8[7]));
-      const float m_new = fmaxf(m_used, mx * p.scale_log2);
-      float alpha = 1.f;
-      const bool grew = m_new - m_used > kRescaleThreshold; // also true for -inf -> finite
-      const bool rescale = i > 0 && __any_sync(0xffffffffu, grew);
-      if (i == 0) {
-        m_used = m_new;
-      } else if (rescale) {
-        alpha = (m_new == -INFINITY) ? 1.f : fast_exp2(m_used - m_new);
-        m_used = m_new;
-        l *= alpha;
+      const float m_mine =
+          fmax3(fmax3(mx8[0], mx8[1], mx8[2]), fmax3(mx8[3], mx8[4], mx8[5]), fmaxf(mx8[6], mx8[7])) * p.scale_log2;
+      // publish this tile's maxima for the other group, then take its maxima of the tile before
+      ss->rowmax[g][i & 1][row] = m_mine;
+      __syncwarp();
+      if (lane == 0)
+        mbar_arrive(&ss->mx_ready[g]);
+      float alpha, a_step;
+      bool rescale = false;
+      alpha = 1.f;
+      if (j > 0) {
+        const int io = (j - 1) >> 1; // tile j - 1 is the io-th tile of the other group
+        if (!wait_or_flag(&ss->mx_ready[g ^ 1], (uint32_t)(io & 1), ss)) {
+          ok = false;
+          break;
+        }
+        const float m_other = ss->rowmax[g ^ 1][io & 1][row];
+        ref_step(j - 1, m_other, ref, a_step); // the other group rescaled O for this step
+        alpha = a_step;
       }
-      const float m_safe = (m_used == -INFINITY) ? 0.f : m_used;
+      rescale = ref_step(j, m_mine, ref, a_step); // this thread rescales O for this step
+      alpha *= a_step;
+      l *= alpha; // this group's partial row sum follows every move of the reference
+      const float m_safe = (ref == -INFINITY) ? 0.f : ref;
       // probabilities: x = s * scale - m for two columns per packed FMA, 2^x on the MUFU unit,
       // four independent packed partial sums; the 16-bit P reuses the front of the row's registers
       const uint64_t scale2 = f2_pack(p.scale_log2, p.scale_log2), negm2 = f2_pack(-m_safe, -m_safe);
@@ -420,12 +461,18 @@ __global__ void __launch_bounds__(kThreads, 1)
         l += (a0 + a1) + (b0 + b1);
       }
 
-      // P row -> tensor memory, over the front half of the row's S: 128 keys = 64 columns of two
-      // 16-bit values
-      tmem_st32(tmem + lane_base + col_s, *reinterpret_cast<uint32_t(*)[32]>(&packed[0]));
-      tmem_st32(tmem + lane_base + col_s + 32, *reinterpret_cast<uint32_t(*)[32]>(&packed[32]));
+      // P V of the tile before (the other group's) has completed: then so has this group's
+      // previous one, which read the P columns, and O holds every tile up to j - 1
+      if (j > 0 && !wait_or_flag(&ss->pv_done[g ^ 1], (uint32_t)(((j - 1) >> 1) & 1), ss)) {
+        ok = false;
+        break;
+      }
+      tc_fence_after_sync();
+      // P row -> tensor memory: 128 keys = 64 columns of two 16-bit values
+      tmem_st32(tmem + lane_base + col_p, *reinterpret_cast<uint32_t(*)[32]>(&packed[0]));
+      tmem_st32(tmem + lane_base + col_p + 32, *reinterpret_cast<uint32_t(*)[32]>(&packed[32]));
       if (rescale) {
-        const uint32_t base = tmem + lane_base + col_o;
+        const uint32_t base = tmem + lane_base + kColO;
 #pragma unroll
         for (int c = 0; c < 4; ++c) {
           uint32_t r[32];
@@ -433,7 +480,7 @@ __global__ void __launch_bounds__(kThreads, 1)
           tmem_wait_ld();
 #pragma unroll
           for (int q = 0; q < 32; ++q)
-            r[q] = __float_as_uint(__uint_as_float(r[q]) * alpha);
+            r[q] = __float_as_uint(__uint_as_float(r[q]) * a_step);
           tmem_st32(base + c * 32, r);
         }
       }
@@ -444,46 +491,41 @@ __global__ void __launch_bounds__(kThreads, 1)
         mbar_arrive(&ss->p_full[g]);
     }
 
-    // ---- epilogue: merge the two groups' partial results, O / l -> 16 bit -> shared -> TMA store; LSE
-    if (ok && n_mine > 0)
-      ok = wait_or_flag(&ss->o_done[g], 0, ss);
-    ss->xch[g][row] = make_float2(m_used, l);
+    // ---- epilogue: O / l -> 16 bit -> shared -> TMA store; LSE
+    // the last P V: products complete in issue order, so it is the only one to wait for
+    if (ok && n > 0)
+      ok = wait_or_flag(&ss->pv_done[(n - 1) & 1], (uint32_t)(((n - 1) >> 1) & 1), ss);
+    ss->xch[g][row] = make_float2(ref, l);
     tc_fence_before_sync();
-    const bool give_up = named_bar_or_n<256>(!ok); // both groups; every product and load is complete
+    const bool give_up = named_bar_or_n<256>(!ok); // both groups
     tc_fence_after_sync();
+    // the two threads of a row may be one step apart: the later reference is the one O is scaled with
     const float2 other = ss->xch[g ^ 1][row];
-    const float m_tot = fmaxf(m_used, other.x);
-    const float a_mine = (m_used == -INFINITY) ? 0.f : fast_exp2(m_used - m_tot);
+    const float m_tot = fmaxf(ref, other.x);
+    const float a_mine = (ref == -INFINITY) ? 0.f : fast_exp2(ref - m_tot);
     const float a_other = (other.x == -INFINITY) ? 0.f : fast_exp2(other.x - m_tot);
     const float l_tot = l * a_mine + other.y * a_other;
     const float inv_l = (l_tot > 0.f) ? 1.f / l_tot : 0.f;
-    const float w0 = (g == 0 ? a_mine : a_other) * inv_l; // weight of group 0's accumulator
-    const float w1 = (g == 0 ? a_other : a_mine) * inv_l;
-    const bool have0 = !give_up && n > 0, have1 = !give_up && n > 1;
+    const bool have = !give_up && n > 0;
     // this thread finishes head-dim columns [64 g, 64 g + 64) of its row; staging in Q's tile
 #pragma unroll
     for (int c = 0; c < 2; ++c) {
-      uint32_t r0[32], r1[32];
-      if (have0)
-        tmem_ld32(tmem + lane_base + kColO0 + g * 64 + c * 32, r0);
-      if (have1)
-        tmem_ld32(tmem + lane_base + kColO1 + g * 64 + c * 32, r1);
-      tmem_wait_ld();
-      float o[32];
+      uint32_t r[32];
+      if (have) {
+        tmem_ld32(tmem + lane_base + kColO + g * 64 + c * 32, r);
+        tmem_wait_ld();
+      } else {
 #pragma unroll
-      for (int q = 0; q < 32; ++q) {
-        float acc = have0 ? __uint_as_float(r0[q]) * w0 : 0.f;
-        if (have1)
-          acc = fmaf(__uint_as_float(r1[q]), w1, acc);
-        o[q] = acc;
+        for (int q = 0; q < 32; ++q)
+          r[q] = 0u;
       }
 #pragma unroll
       for (int q = 0; q < 4; ++q) { // 8 columns = one 16-byte chunk
         uint4 v;
-        v.x = pack2(o[q * 8 + 0], o[q * 8 + 1], kBF16);
-        v.y = pack2(o[q * 8 + 2], o[q * 8 + 3], kBF16);
-        v.z = pack2(o[q * 8 + 4], o[q * 8 + 5], kBF16);
-        v.w = pack2(o[q * 8 + 6], o[q * 8 + 7], kBF16);
+        v.x = pack2(__uint_as_float(r[q * 8 + 0]) * inv_l, __uint_as_float(r[q * 8 + 1]) * inv_l, kBF16);
+        v.y = pack2(__uint_as_float(r[q * 8 + 2]) * inv_l, __uint_as_float(r[q * 8 + 3]) * inv_l, kBF16);
+        v.z = pack2(__uint_as_float(r[q * 8 + 4]) * inv_l, __uint_as_float(r[q * 8 + 5]) * inv_l, kBF16);
+        v.w = pack2(__uint_as_float(r[q * 8 + 6]) * inv_l, __uint_as_float(r[q * 8 + 7]) * inv_l, kBF16);
         const int chunk = c * 4 + q;
         *reinterpret_cast<uint4 *>(sQ + g * kHalfTile + row * 128 + ((chunk ^ (row & 7)) << 4)) = v;
       }
