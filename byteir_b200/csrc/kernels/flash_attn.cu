@@ -171,7 +171,8 @@ __device__ __forceinline__ bool elect_one() {
                : "=r"(pred));
   return pred != 0;
 }
-// all 32 lanes wait; the verdict is the same in every lane
+// all 32 lanes wait; the verdict is the same in every lane, so a warp gives up as a whole and
+// the warp-wide votes and tensor-memory instructions that follow a wait stay convergent
 __device__ __forceinline__ bool warp_wait_or_flag(uint64_t *bar, uint32_t parity, SharedStorage *ss) {
   const bool ok = __all_sync(0xffffffffu, mbar_wait(bar, parity));
   if (!ok)
@@ -373,7 +374,7 @@ __global__ void __launch_bounds__(kThreads, 1)
 
     for (int i = 0; ok && i < n_mine; ++i) {
       const int j = 2 * i + g;
-      if (!wait_or_flag(&ss->s_full[g], (uint32_t)(i & 1), ss)) {
+      if (!warp_wait_or_flag(&ss->s_full[g], (uint32_t)(i & 1), ss)) {
         ok = false;
         break;
       }
@@ -428,7 +429,7 @@ __global__ void __launch_bounds__(kThreads, 1)
       alpha = 1.f;
       if (j > 0) {
         const int io = (j - 1) >> 1; // tile j - 1 is the io-th tile of the other group
-        if (!wait_or_flag(&ss->mx_ready[g ^ 1], (uint32_t)(io & 1), ss)) {
+        if (!warp_wait_or_flag(&ss->mx_ready[g ^ 1], (uint32_t)(io & 1), ss)) {
           ok = false;
           break;
         }
@@ -463,7 +464,7 @@ __global__ void __launch_bounds__(kThreads, 1)
 
       // P V of the tile before (the other group's) has completed: then so has this group's
       // previous one, which read the P columns, and O holds every tile up to j - 1
-      if (j > 0 && !wait_or_flag(&ss->pv_done[g ^ 1], (uint32_t)(((j - 1) >> 1) & 1), ss)) {
+      if (j > 0 && !warp_wait_or_flag(&ss->pv_done[g ^ 1], (uint32_t)(((j - 1) >> 1) & 1), ss)) {
         ok = false;
         break;
       }
@@ -494,7 +495,7 @@ __global__ void __launch_bounds__(kThreads, 1)
     // ---- epilogue: O / l -> 16 bit -> shared -> TMA store; LSE
     // the last P V: products complete in issue order, so it is the only one to wait for
     if (ok && n > 0)
-      ok = wait_or_flag(&ss->pv_done[(n - 1) & 1], (uint32_t)(((n - 1) >> 1) & 1), ss);
+      ok = warp_wait_or_flag(&ss->pv_done[(n - 1) & 1], (uint32_t)(((n - 1) >> 1) & 1), ss);
     ss->xch[g][row] = make_float2(ref, l);
     tc_fence_before_sync();
     const bool give_up = named_bar_or_n<256>(!ok); // both groups
