@@ -502,8 +502,8 @@ __global__ void __launch_bounds__(kBlock)
 }
 
 // plan constants of the column path (threads that cover one row of a slab; blocks per SM aimed at)
-int g_cols_threads_per_row = 32;
-int g_cols_blocks_per_sm = 4;
+constexpr int kColsThreadsPerRow = 32;
+constexpr int kColsBlocksPerSm = 4;
 
 // ---- launch plan: a pure function of the shape -----------------------------
 struct Plan {
@@ -544,11 +544,11 @@ Plan make_plan(int esize, int64_t A, int64_t B, int64_t C, bool vec_cols) {
   } else {
     p.rows = false;
     const int NV = vec_cols ? N : 1;
-    p.lpr = (int)std::min<int64_t>(g_cols_threads_per_row, pow2_ceil(ceil_div<int64_t>(C, NV)));
+    p.lpr = (int)std::min<int64_t>(kColsThreadsPerRow, pow2_ceil(ceil_div<int64_t>(C, NV)));
     p.slabs = (int)ceil_div<int64_t>(C, (int64_t)p.lpr * NV);
     const int64_t rows_per_step = kBlock / p.lpr;
     const int64_t blocks = A * p.slabs;
-    int64_t splits = std::max<int64_t>(1, ceil_div<int64_t>((int64_t)g_cols_blocks_per_sm * kNumSMs, blocks));
+    int64_t splits = std::max<int64_t>(1, ceil_div<int64_t>((int64_t)kColsBlocksPerSm * kNumSMs, blocks));
     splits = std::min<int64_t>(splits, std::max<int64_t>(1, B / (rows_per_step * 4)));
     p.rows_per_split = ceil_div<int64_t>(B, splits);
     p.splits = (int)ceil_div<int64_t>(B, p.rows_per_split);
@@ -629,7 +629,7 @@ int launch(const T *in, OutT *out, int64_t A, int64_t B, int64_t C, void *ws,
   // the split plan is fixed by the shape; only the lane layout follows `vec`
   Plan q = p;
   if (!vec && cols_vec_by_shape(sizeof(T), C)) {
-    q.lpr = (int)std::min<int64_t>(g_cols_threads_per_row, pow2_ceil(C));
+    q.lpr = (int)std::min<int64_t>(kColsThreadsPerRow, pow2_ceil(C));
     q.slabs = (int)ceil_div<int64_t>(C, q.lpr);
   }
   const int64_t grid = A * q.slabs * q.splits;
@@ -787,13 +787,4 @@ extern "C" int b200_reduce_no_alloc(int op, int dtype, const void *in, void *out
     if (int rc = static_scratch_for_current_device(&scratch))
       return rc;
   return b200_reduce(op, dtype, in, out, A, B, C, scratch, need ? kStaticScratchBytes : 0, stream);
-}
-
-// tuning door used by the measurement scripts (not part of the ABI): changes the plan of the column
-// path for subsequent calls; workspace sizes change with it
-extern "C" void b200_reduce_tune(int threads_per_row, int blocks_per_sm) {
-  if (threads_per_row >= 1 && threads_per_row <= kBlock && (threads_per_row & (threads_per_row - 1)) == 0)
-    g_cols_threads_per_row = threads_per_row;
-  if (blocks_per_sm >= 1 && blocks_per_sm <= 16)
-    g_cols_blocks_per_sm = blocks_per_sm;
 }
