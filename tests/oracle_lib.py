@@ -164,11 +164,11 @@ def attn_params(b, sq, sk, h, hk, d, scale, causal=True, window=(-1, -1)):
     return p
 
 
-def flash_attn_fwd(q, k, v, scale, causal=True, round_p=False):
+def flash_attn_fwd(q, k, v, scale, causal=True, round_p=False, window=(-1, -1)):
     b, sq, h, d = q.shape
     sk, hk = k.shape[1], k.shape[2]
     q, k, v = (np.ascontiguousarray(t) for t in (q, k, v))
-    p = attn_params(b, sq, sk, h, hk, d, scale, causal)
+    p = attn_params(b, sq, sk, h, hk, d, scale, causal, window)
     out = np.empty_like(q)
     lse = np.empty((b, h, sq), np.float32)
     rc = lib().oracle_flash_attn_fwd(dtype_code(q), _p(q), _p(k), _p(v), _p(out), _p(lse),
@@ -177,12 +177,12 @@ def flash_attn_fwd(q, k, v, scale, causal=True, round_p=False):
     return out, lse
 
 
-def flash_attn_bwd(dout, q, k, v, out, lse, scale, causal=True):
+def flash_attn_bwd(dout, q, k, v, out, lse, scale, causal=True, window=(-1, -1)):
     b, sq, h, d = q.shape
     sk, hk = k.shape[1], k.shape[2]
     dout, q, k, v, out = (np.ascontiguousarray(t) for t in (dout, q, k, v, out))
     lse = np.ascontiguousarray(lse, dtype=np.float32)
-    p = attn_params(b, sq, sk, h, hk, d, scale, causal)
+    p = attn_params(b, sq, sk, h, hk, d, scale, causal, window)
     dq, dk, dv = np.empty_like(q), np.empty_like(k), np.empty_like(v)
     rc = lib().oracle_flash_attn_bwd(dtype_code(q), _p(dout), _p(q), _p(k), _p(v), _p(out), _p(lse),
                                      _p(dq), _p(dk), _p(dv), C.byref(p))
