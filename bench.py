@@ -41,14 +41,14 @@ L2_BYTES = 126 * 1024 * 1024
 
 # dram__bytes_read.sum + dram__bytes_write.sum per launch of the dominant kernel, in bytes,
 # from the ncu captures summarised under profiles/ (absent = not captured).  The attention
-# figure was captured on B=1, H=16 (50.4 MB read + 2.1 MB written) and is scaled by the
+# figure was captured on B=1, H=16 (50.4 MB read + 2.4 MB written) and is scaled by the
 # 16x more (batch, head) pairs of the bench workload; the writes of a launch mostly stay
 # in L2 until after the kernel, so they under-count.
 NCU_TRAFFIC = {
     "reduce_c2": 67.126e6 + 0.57e6,      # reduce_cols_kernel (profiles/cols_ncu_full.md)
-    "gather": 61.92e6 + 17.37e6,         # gather_rows_bulk_kernel (profiles/gather_ncu_full.md)
+    "gather": 62.25e6 + 24.40e6,         # gather_generic_kernel (profiles/gather_ncu_full.md)
     "scatter": 81.86e6 + 5.33e6,         # scatter_chunk_kernel alone (profiles/chunk_ncu_full.md)
-    "attn": 16 * (50.39e6 + 2.15e6),     # flash_fwd_kernel<bf16> (profiles/flash_fwd_ncu_full.md)
+    "attn": 16 * (50.39e6 + 2.40e6),     # flash_fwd_kernel<bf16> (profiles/flash_fwd_ncu_full.md)
 }
 
 
@@ -341,7 +341,7 @@ class GatherC3(Workload):
         return 1
 
     def dominant(self):
-        return "gather_rows_bulk_kernel", self.BYTES
+        return "gather_generic_kernel (256-byte rows: vector loads)", self.BYTES
 
     def setup_gpu(self, torch, ops, xs):
         self.ops = ops

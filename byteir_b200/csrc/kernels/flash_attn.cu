@@ -143,7 +143,10 @@ struct SharedStorage {
   uint64_t s_full[2], s_empty[2]; // per softmax group: S of its tile is in tensor memory / in registers
   uint64_t p_full[2];             // per softmax group: P of its tile is in tensor memory, O is rescaled
   uint64_t pv_done[2];            // per softmax group: the P V of its tile has completed
-  uint64_t mx_ready[2];           // per softmax group: the row maxima of its tile are in `rowmax`
+  // per softmax group and tile parity: the row maxima of the group's tile are in `rowmax`.  A
+  // group publishes its maxima before it waits for the other group's, so it can be one tile
+  // ahead of the reader; with one barrier per tile parity the reader still sees each phase.
+  uint64_t mx_ready[2][2];
   uint32_t tmem_base;
   int failed;
   float rowmax[2][2][kBM]; // [group][tile parity][row]: scaled row maximum of the group's tile
@@ -252,7 +255,8 @@ __global__ void __launch_bounds__(kThreads, 1)
       mbar_init(&ss->s_empty[g], 4);
       mbar_init(&ss->p_full[g], 4);
       mbar_init(&ss->pv_done[g], 1);
-      mbar_init(&ss->mx_ready[g], 4);
+      mbar_init(&ss->mx_ready[g][0], 4);
+      mbar_init(&ss->mx_ready[g][1], 4);
     }
     ss->failed = 0;
     mbar_fence_init();
@@ -423,13 +427,13 @@ __global__ void __launch_bounds__(kThreads, 1)
       ss->rowmax[g][i & 1][row] = m_mine;
       __syncwarp();
       if (lane == 0)
-        mbar_arrive(&ss->mx_ready[g]);
+        mbar_arrive(&ss->mx_ready[g][i & 1]);
       float alpha, a_step;
       bool rescale = false;
       alpha = 1.f;
       if (j > 0) {
         const int io = (j - 1) >> 1; // tile j - 1 is the io-th tile of the other group
-        if (!warp_wait_or_flag(&ss->mx_ready[g ^ 1], (uint32_t)(io & 1), ss)) {
+        if (!warp_wait_or_flag(&ss->mx_ready[g ^ 1][io & 1], (uint32_t)((io >> 1) & 1), ss)) {
           ok = false;
           break;
         }
