@@ -8,8 +8,8 @@ softmax scale 0.5.  The reference's own tests round these values to fp16 and
 demand a bit-exact match (runtime/test/backends/cuda/providers/default/kernel/
 flash_attn_fwd_test.cc:142), so fp16 is a lossless container for them.
 
-Run in a checkout that has the reference mounted:
-    python tests/golden/make_flash_attn_golden.py /root/reference
+Run where a checkout of the reference is at hand:
+    python tests/golden/make_flash_attn_golden.py <path to the byteir checkout>
 """
 import sys
 from pathlib import Path
