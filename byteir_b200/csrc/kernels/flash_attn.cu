@@ -844,7 +844,11 @@ __global__ void __launch_bounds__(kThreads, 1)
       for (int it = 0; ok && it < T; ++it) {
         const int st = it % kBwdStages, g = it & 1;
         const uint32_t t0 = str + st * 2 * kStrTileBytes, t1 = t0 + kStrTileBytes;
-        ok = bwd_warp_wait(&ss->pds_full[g], (uint32_t)((it >> 1) & 1), ss);
+        // the streamed tile after next arrived long ago (the ring is four deep): look at its
+        // barrier while the group still computes, not between the two batches of products
+        if (it + 2 < T)
+          ok = bwd_warp_wait(&ss->full[(it + 2) % kBwdStages], (uint32_t)(((it + 2) / kBwdStages) & 1), ss);
+        ok = ok && bwd_warp_wait(&ss->pds_full[g], (uint32_t)((it >> 1) & 1), ss);
         if (!ok)
           break;
         tc_fence_after_sync();
@@ -868,13 +872,8 @@ __global__ void __launch_bounds__(kThreads, 1)
           umma_commit(&ss->empty[st]);
         // the group's buffers are free for its next tile as soon as the products above have
         // read P / dS: the tensor core runs what this lane issues in order
-        if (it + 2 < T) {
-          ok = bwd_warp_wait(&ss->full[(it + 2) % kBwdStages], (uint32_t)(((it + 2) / kBwdStages) & 1), ss);
-          if (!ok)
-            break;
-          tc_fence_after_sync();
+        if (it + 2 < T)
           issue_sdp(it + 2);
-        }
       }
       if (ok && elect_one())
         umma_commit(&ss->all_done);
