@@ -143,9 +143,9 @@ struct SharedStorage {
   uint64_t s_full[2], s_empty[2]; // per softmax group: S of its tile is in tensor memory / in registers
   uint64_t p_full[2];             // per softmax group: P of its tile is in tensor memory, O is rescaled
   uint64_t pv_done[2];            // per softmax group: the P V of its tile has completed
-  // per softmax group and tile parity: the row maxima of the group's tile are in `rowmax`.  A
-  // group publishes its maxima before it waits for the other group's, so it can be one tile
-  // ahead of the reader; with one barrier per tile parity the reader still sees each phase.
+  // per softmax group and tile parity: the row maxima of the group's tile are in `rowmax`.
+  // One barrier per tile parity, so that a reader never has to tell apart two phases of the
+  // same parity even if the publisher is a tile ahead of it.
   uint64_t mx_ready[2][2];
   uint32_t tmem_base;
   int failed;
@@ -378,6 +378,18 @@ __global__ void __launch_bounds__(kThreads, 1)
 
     for (int i = 0; ok && i < n_mine; ++i) {
       const int j = 2 * i + g;
+      // The other group's maxima of the tile before: it published them early in its tile, half
+      // a period ago, so this wait is a formality; it is taken here, where the thread would
+      // otherwise idle until its S arrives, and not between the maximum and the exponentials.
+      float m_other = -INFINITY;
+      if (j > 0) {
+        const int io = (j - 1) >> 1; // tile j - 1 is the io-th tile of the other group
+        if (!warp_wait_or_flag(&ss->mx_ready[g ^ 1][io & 1], (uint32_t)((io >> 1) & 1), ss)) {
+          ok = false;
+          break;
+        }
+        m_other = ss->rowmax[g ^ 1][io & 1][row];
+      }
       if (!warp_wait_or_flag(&ss->s_full[g], (uint32_t)(i & 1), ss)) {
         ok = false;
         break;
@@ -423,7 +435,7 @@ __global__ void __launch_bounds__(kThreads, 1)
       }
       const float m_mine =
           fmax3(fmax3(mx8[0], mx8[1], mx8[2]), fmax3(mx8[3], mx8[4], mx8[5]), fmaxf(mx8[6], mx8[7])) * p.scale_log2;
-      // publish this tile's maxima for the other group, then take its maxima of the tile before
+      // publish this tile's maxima for the other group
       ss->rowmax[g][i & 1][row] = m_mine;
       __syncwarp();
       if (lane == 0)
@@ -432,12 +444,6 @@ __global__ void __launch_bounds__(kThreads, 1)
       bool rescale = false;
       alpha = 1.f;
       if (j > 0) {
-        const int io = (j - 1) >> 1; // tile j - 1 is the io-th tile of the other group
-        if (!warp_wait_or_flag(&ss->mx_ready[g ^ 1][io & 1], (uint32_t)((io >> 1) & 1), ss)) {
-          ok = false;
-          break;
-        }
-        const float m_other = ss->rowmax[g ^ 1][io & 1][row];
         ref_step(j - 1, m_other, ref, a_step); // the other group rescaled O for this step
         alpha = a_step;
       }
