@@ -1,8 +1,13 @@
 // Flash-attention forward for sm_100a (head dim 128, f16 / bf16, f32 accumulate).
 //
-// One block owns 128 query rows of one (batch, head) and walks over the key/value
-// tiles of 128 rows that the mask lets it see.  Warp roles (three warpgroups):
-//   warp 0        TMA producer of Q (once) and of the K tiles (3-stage ring)
+// Persistent blocks, one per SM.  A block takes query tiles (128 query rows of one (batch,
+// head)) from a static list and, for each, walks over the key/value tiles of 128 rows that
+// the mask lets it see.  A work item is one (batch, head) and a pair of query tiles, the t-th
+// longest and the t-th shortest, so that under a causal mask all items cost the same; items
+// go round-robin over the blocks, consecutive items share K and V in L2.  Every barrier keeps
+// counting across query tiles, so the loads and the first S of the next query tile overlap
+// the epilogue of the current one.  Warp roles (three warpgroups):
+//   warp 0        TMA producer of Q (per query tile) and of the K tiles (2-stage ring)
 //   warp 2        TMA producer of the V tiles (2-stage ring)
 //   warp 1        issuer of S = Q K^T  (tcgen05.mma; all lanes run the loop and the waits,
 //   warp 3        issuer of O += P V    one elected lane executes the tcgen05 instructions)
@@ -53,7 +58,7 @@ constexpr uint32_t kHalfTile = kTileBytes / 2; // one 64-column block
 constexpr int kThreads = 384;    // four control warps, two groups of four softmax / elementwise warps
 constexpr uint32_t kTmemCols = 512;
 // forward: two S tiles, two P tiles and one O accumulator fill the 512 columns of tensor memory
-constexpr int kFwdKStages = 3, kFwdVStages = 2; // K / V ring depths of the forward kernel
+constexpr int kFwdKStages = 2, kFwdVStages = 2; // K / V ring depths of the forward kernel
 constexpr uint32_t kColS0 = 0, kColS1 = 128, kColP0 = 256, kColP1 = 320, kColO = 384;
 constexpr int kCtrlRegs = 56, kSoftmaxRegs = 224; // 128 * 56 + 256 * 224 <= 64 Ki registers
 constexpr float kRescaleThreshold = 8.0f; // log2 units
@@ -62,6 +67,8 @@ struct FwdParams {
   float *lse;
   int *status;
   int64_t H, Hk, Sq, Sk;
+  int n_q_tiles, pairs; // query tiles per (batch, head); pairs of them per work item
+  int64_t total_items;  // pairs * H * B
   float scale_log2;
   int64_t window_left, window_right; // < 0: unbounded
 };
@@ -138,7 +145,7 @@ template <int N> __device__ __forceinline__ void reg_inc() {
 }
 
 struct SharedStorage {
-  uint64_t bar_q;
+  uint64_t bar_q, q_empty; // Q of a query tile has arrived / is no longer read
   uint64_t k_full[kFwdKStages], k_empty[kFwdKStages], v_full[kFwdVStages], v_empty[kFwdVStages];
   uint64_t s_full[2], s_empty[2]; // per softmax group: S of its tile is in tensor memory / in registers
   uint64_t p_full[2];             // per softmax group: P of its tile is in tensor memory, O is rescaled
@@ -218,30 +225,64 @@ __global__ void __launch_bounds__(kThreads, 1)
   extern __shared__ __align__(1024) unsigned char smem_raw[];
   unsigned char *smem =
       reinterpret_cast<unsigned char *>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
-  unsigned char *sQ = smem; // Q; the finished O tile at the end
-  unsigned char *sK = sQ + kTileBytes;
+  unsigned char *sQ = smem;              // Q of the current query tile
+  unsigned char *sO = sQ + kTileBytes;   // the finished O tile on its way out
+  unsigned char *sK = sO + kTileBytes;
   unsigned char *sV = sK + kFwdKStages * kTileBytes;
   SharedStorage *ss = reinterpret_cast<SharedStorage *>(sV + kFwdVStages * kTileBytes);
 
   const int warp = __shfl_sync(0xffffffffu, threadIdx.x >> 5, 0), lane = threadIdx.x & 31; // warp: known uniform
-  const int n_q_tiles = (int)((p.Sq + kBM - 1) / kBM);
-  const int q_tile = n_q_tiles - 1 - (int)blockIdx.x; // longest rows first
-  const int h = blockIdx.y, b = blockIdx.z;
-  const int hk = (int)(h / (p.H / p.Hk));
-  const int64_t q0 = (int64_t)q_tile * kBM;
   const int64_t shift = p.Sk - p.Sq;
   const bool right_bounded = p.window_right >= 0;
   const bool left_bounded = p.window_left >= 0;
+  const int kv_group = (int)(p.H / p.Hk);
 
-  // key tiles (128 keys each) this block visits: [0, n)
-  int n = (int)((p.Sk + kBN - 1) / kBN);
-  if (right_bounded) {
-    const int64_t last_visible = q0 + kBM - 1 + shift + p.window_right;
-    n = last_visible < 0 ? 0 : (int)min((int64_t)n, last_visible / kBN + 1);
-  }
+  // The block's work list.  The blocks are persistent (one per SM).  An item is one (batch, head)
+  // and a pair of query tiles, the t-th longest and the t-th shortest, so that under a causal
+  // mask every item costs the same; items go round-robin over the blocks, consecutive items
+  // share K and V.  Every role walks the same list of query tiles, two per item, and every
+  // barrier keeps counting across query tiles, so loads and the first products of the next
+  // query tile overlap the epilogue of the current one.
+  struct Work {
+    int h, b, hk, n; // n: key tiles (128 keys each) this query tile visits, [0, n)
+    int64_t q0;
+  };
+  auto work_at = [&](int idx, Work &w) -> int { // 1: work, 0: nothing at idx (odd middle tile), -1: list ended
+    const int64_t item = (int64_t)blockIdx.x + (int64_t)(idx >> 1) * gridDim.x;
+    if (item >= p.total_items)
+      return -1;
+    const int pr = (int)(item % p.pairs);
+    const int64_t bh = item / p.pairs;
+    const int hi = p.n_q_tiles - 1 - pr;
+    if ((idx & 1) && pr == hi)
+      return 0;
+    const int q_tile = (idx & 1) ? pr : hi;
+    w.h = (int)(bh % p.H);
+    w.b = (int)(bh / p.H);
+    w.hk = w.h / kv_group;
+    w.q0 = (int64_t)q_tile * kBM;
+    int n = (int)((p.Sk + kBN - 1) / kBN);
+    if (right_bounded) {
+      const int64_t last_visible = w.q0 + kBM - 1 + shift + p.window_right;
+      n = last_visible < 0 ? 0 : (int)min((int64_t)n, last_visible / kBN + 1);
+    }
+    w.n = n;
+    return 1;
+  };
+  auto next_work = [&](int &idx, Work &w) -> bool { // advances idx to the next query tile of the list
+    for (;;) {
+      const int r = work_at(idx, w);
+      if (r < 0)
+        return false;
+      ++idx;
+      if (r > 0)
+        return true;
+    }
+  };
 
   if (threadIdx.x == 0) {
     mbar_init(&ss->bar_q, 1);
+    mbar_init(&ss->q_empty, 1);
     for (int s = 0; s < kFwdKStages; ++s) {
       mbar_init(&ss->k_full[s], 1);
       mbar_init(&ss->k_empty[s], 1);
@@ -274,49 +315,79 @@ __global__ void __launch_bounds__(kThreads, 1)
     reg_dec<kCtrlRegs>(); // the four control warps hand registers to the softmax warps
   if (warp == 0) {
     // ----------------------------------------------------------- producer of Q and K
-    if (lane == 0 && n > 0) {
+    if (lane == 0) {
       prefetch_tensormap(&q_map);
       prefetch_tensormap(&k_map);
-      mbar_arrive_expect_tx(&ss->bar_q, kTileBytes);
-      tma_load_4d(sQ, &q_map, 0, h, (int)q0, b, &ss->bar_q);
-      tma_load_4d(sQ + kHalfTile, &q_map, 64, h, (int)q0, b, &ss->bar_q);
-      for (int j = 0; j < n; ++j) {
-        const int st = j % kFwdKStages;
-        if (!wait_or_flag(&ss->k_empty[st], (uint32_t)(((j / kFwdKStages) & 1) ^ 1), ss))
+      uint32_t kc = 0, qc = 0; // K tiles and Q tiles loaded so far
+      int idx = 0;
+      Work w;
+      bool ok = true;
+      while (ok && next_work(idx, w)) {
+        if (w.n == 0)
+          continue;
+        // Q's buffer is free once the last Q K^T of the previous query tile has completed
+        if (qc > 0 && !wait_or_flag(&ss->q_empty, (qc - 1) & 1, ss))
           break;
-        mbar_arrive_expect_tx(&ss->k_full[st], kTileBytes);
-        tma_load_4d(sK + st * kTileBytes, &k_map, 0, hk, j * kBN, b, &ss->k_full[st]);
-        tma_load_4d(sK + st * kTileBytes + kHalfTile, &k_map, 64, hk, j * kBN, b, &ss->k_full[st]);
+        mbar_arrive_expect_tx(&ss->bar_q, kTileBytes);
+        tma_load_4d(sQ, &q_map, 0, w.h, (int)w.q0, w.b, &ss->bar_q);
+        tma_load_4d(sQ + kHalfTile, &q_map, 64, w.h, (int)w.q0, w.b, &ss->bar_q);
+        ++qc;
+        for (int j = 0; j < w.n; ++j, ++kc) {
+          const int st = kc % kFwdKStages;
+          if (!wait_or_flag(&ss->k_empty[st], ((kc / kFwdKStages) & 1) ^ 1, ss)) {
+            ok = false;
+            break;
+          }
+          mbar_arrive_expect_tx(&ss->k_full[st], kTileBytes);
+          tma_load_4d(sK + st * kTileBytes, &k_map, 0, w.hk, j * kBN, w.b, &ss->k_full[st]);
+          tma_load_4d(sK + st * kTileBytes + kHalfTile, &k_map, 64, w.hk, j * kBN, w.b, &ss->k_full[st]);
+        }
       }
     }
   } else if (warp == 2) {
     // ----------------------------------------------------------- producer of V
-    if (lane == 0 && n > 0) {
+    if (lane == 0) {
       prefetch_tensormap(&v_map);
-      for (int j = 0; j < n; ++j) {
-        const int st = j % kFwdVStages;
-        if (!wait_or_flag(&ss->v_empty[st], (uint32_t)(((j / kFwdVStages) & 1) ^ 1), ss))
-          break;
-        mbar_arrive_expect_tx(&ss->v_full[st], kTileBytes);
-        tma_load_4d(sV + st * kTileBytes, &v_map, 0, hk, j * kBN, b, &ss->v_full[st]);
-        tma_load_4d(sV + st * kTileBytes + kHalfTile, &v_map, 64, hk, j * kBN, b, &ss->v_full[st]);
+      uint32_t vc = 0;
+      int idx = 0;
+      Work w;
+      bool ok = true;
+      while (ok && next_work(idx, w)) {
+        for (int j = 0; j < w.n; ++j, ++vc) {
+          const int st = vc % kFwdVStages;
+          if (!wait_or_flag(&ss->v_empty[st], ((vc / kFwdVStages) & 1) ^ 1, ss)) {
+            ok = false;
+            break;
+          }
+          mbar_arrive_expect_tx(&ss->v_full[st], kTileBytes);
+          tma_load_4d(sV + st * kTileBytes, &v_map, 0, w.hk, j * kBN, w.b, &ss->v_full[st]);
+          tma_load_4d(sV + st * kTileBytes + kHalfTile, &v_map, 64, w.hk, j * kBN, w.b, &ss->v_full[st]);
+        }
       }
     }
   } else if (warp == 1) {
     // ----------------------------------------------------------- issuer of S = Q K^T
     // S of a group is free as soon as the group has its previous tile in registers, so the
-    // next S is normally ready before the group asks for it.
-    if (n > 0) {
-      constexpr uint32_t idesc_qk = umma_idesc_f16(kBF16, kBM, kBN, false, false);
-      const uint32_t tm = __shfl_sync(0xffffffffu, tmem, 0);
-      const uint32_t q_addr = smem_addr(sQ), k_addr = smem_addr(sK);
-      bool ok = warp_wait_or_flag(&ss->bar_q, 0, ss);
-      for (int j = 0; ok && j < n; ++j) {
-        const int g = j & 1, i = j >> 1, st = j % kFwdKStages; // tile j is the i-th tile of softmax group g
-        ok = warp_wait_or_flag(&ss->k_full[st], (uint32_t)((j / kFwdKStages) & 1), ss) &&
-             warp_wait_or_flag(&ss->s_empty[g], (uint32_t)((i & 1) ^ 1), ss);
+    // next S is normally ready before the group asks for it, across query tiles as well.
+    constexpr uint32_t idesc_qk = umma_idesc_f16(kBF16, kBM, kBN, false, false);
+    const uint32_t tm = __shfl_sync(0xffffffffu, tmem, 0);
+    const uint32_t q_addr = smem_addr(sQ), k_addr = smem_addr(sK);
+    uint32_t kc = 0, qc = 0, tc[2] = {0, 0}; // K tiles, Q tiles, tiles per softmax group so far
+    int idx = 0;
+    Work w;
+    bool ok = true;
+    while (ok && next_work(idx, w)) {
+      if (w.n == 0)
+        continue;
+      ok = warp_wait_or_flag(&ss->bar_q, qc & 1, ss);
+      ++qc;
+      for (int j = 0; ok && j < w.n; ++j, ++kc) {
+        const int g = j & 1, st = kc % kFwdKStages;
+        ok = warp_wait_or_flag(&ss->k_full[st], (kc / kFwdKStages) & 1, ss) &&
+             warp_wait_or_flag(&ss->s_empty[g], (tc[g] & 1) ^ 1, ss);
         if (!ok)
           break;
+        ++tc[g];
         tc_fence_after_sync();
         const uint32_t d_tmem = tm + (g ? kColS1 : kColS0);
 #pragma unroll
@@ -330,22 +401,28 @@ __global__ void __launch_bounds__(kThreads, 1)
         if (elect_one()) {
           umma_commit(&ss->s_full[g]);
           umma_commit(&ss->k_empty[st]);
+          if (j + 1 == w.n)
+            umma_commit(&ss->q_empty); // the query tile's last product: Q may be replaced
         }
       }
     }
   } else if (warp == 3) {
     // ----------------------------------------------------------- issuer of O += P V
-    if (n > 0) {
-      constexpr uint32_t idesc_pv = umma_idesc_f16(kBF16, kBM, kD, false, true);
-      const uint32_t tm = __shfl_sync(0xffffffffu, tmem, 0);
-      const uint32_t v_addr = smem_addr(sV);
-      bool ok = true;
-      for (int j = 0; ok && j < n; ++j) {
-        const int g = j & 1, i = j >> 1, st = j % kFwdVStages;
-        ok = warp_wait_or_flag(&ss->v_full[st], (uint32_t)((j / kFwdVStages) & 1), ss) &&
-             warp_wait_or_flag(&ss->p_full[g], (uint32_t)(i & 1), ss);
+    constexpr uint32_t idesc_pv = umma_idesc_f16(kBF16, kBM, kD, false, true);
+    const uint32_t tm = __shfl_sync(0xffffffffu, tmem, 0);
+    const uint32_t v_addr = smem_addr(sV);
+    uint32_t vc = 0, tc[2] = {0, 0};
+    int idx = 0;
+    Work w;
+    bool ok = true;
+    while (ok && next_work(idx, w)) {
+      for (int j = 0; ok && j < w.n; ++j, ++vc) {
+        const int g = j & 1, st = vc % kFwdVStages;
+        ok = warp_wait_or_flag(&ss->v_full[st], (vc / kFwdVStages) & 1, ss) &&
+             warp_wait_or_flag(&ss->p_full[g], tc[g] & 1, ss);
         if (!ok)
           break;
+        ++tc[g];
         tc_fence_after_sync();
 #pragma unroll
         for (int kk = 0; kk < 8; ++kk) { // 8 steps of 16 keys
@@ -363,195 +440,217 @@ __global__ void __launch_bounds__(kThreads, 1)
   } else if (warp >= 4) {
     // ------------------------------------------------------------- softmax
     reg_inc<kSoftmaxRegs>();
-    const int g = (warp - 4) >> 2;           // group: key tiles g, g + 2, g + 4, ...
+    const int g = (warp - 4) >> 2;           // group: key tiles g, g + 2, g + 4, ... of a query tile
     const int quarter = warp & 3;            // tensor-memory lanes 32 * quarter .. + 31
     const int row = quarter * 32 + lane;     // query row inside the tile
-    const int64_t qrow = q0 + row;           // global query row
     const uint32_t lane_base = (uint32_t)(quarter * 32) << 16;
     const uint32_t col_s = g ? kColS1 : kColS0, col_p = g ? kColP1 : kColP0;
-    const int n_mine = (n + 1 - g) >> 1;
-    // `ref` is the reference maximum of the row after the last tile this thread knows about:
-    // both threads of a row replay the same sequence of steps (ref_step) over all key tiles,
-    // the other group's tiles from the maxima it publishes.
-    float ref = -INFINITY, l = 0.f;
+    uint32_t tc[2] = {0, 0}; // key tiles of [this group, the other group] over all query tiles so far
     bool ok = true;
-
-    for (int i = 0; ok && i < n_mine; ++i) {
-      const int j = 2 * i + g;
-      // The other group's maxima of the tile before: it published them early in its tile, half
-      // a period ago, so this wait is a formality; it is taken here, where the thread would
-      // otherwise idle until its S arrives, and not between the maximum and the exponentials.
-      float m_other = -INFINITY;
-      if (j > 0) {
-        const int io = (j - 1) >> 1; // tile j - 1 is the io-th tile of the other group
-        if (!warp_wait_or_flag(&ss->mx_ready[g ^ 1][io & 1], (uint32_t)((io >> 1) & 1), ss)) {
+    int idx = 0;
+    Work w;
+    while (next_work(idx, w)) {
+      const int n = w.n;
+      const int64_t q0 = w.q0, qrow = q0 + row;
+      const int n_mine = (n + 1 - g) >> 1, n_other = (n + g) >> 1;
+      // `ref` is the reference maximum of the row after the last tile this thread knows about:
+      // both threads of a row replay the same sequence of steps (ref_step) over all key tiles,
+      // the other group's tiles from the maxima it publishes.
+      float ref = -INFINITY, l = 0.f;
+      for (int i = 0; ok && i < n_mine; ++i) {
+        const int j = 2 * i + g;
+        const uint32_t ti = tc[0] + i; // this tile's number among the group's tiles of the whole list
+        // The other group's maxima of the tile before: it published them early in its tile, half
+        // a period ago, so this wait is a formality; it is taken here, where the thread would
+        // otherwise idle until its S arrives, and not between the maximum and the exponentials.
+        float m_other = -INFINITY;
+        if (j > 0) {
+          const uint32_t to = tc[1] + ((j - 1) >> 1); // tile j - 1 among the other group's tiles
+          if (!warp_wait_or_flag(&ss->mx_ready[g ^ 1][to & 1], (to >> 1) & 1, ss)) {
+            ok = false;
+            break;
+          }
+          m_other = ss->rowmax[g ^ 1][to & 1][row];
+        }
+        if (!warp_wait_or_flag(&ss->s_full[g], ti & 1, ss)) {
           ok = false;
           break;
         }
-        m_other = ss->rowmax[g ^ 1][io & 1][row];
-      }
-      if (!warp_wait_or_flag(&ss->s_full[g], (uint32_t)(i & 1), ss)) {
-        ok = false;
-        break;
-      }
-      tc_fence_after_sync();
-      // the whole row of S into registers; S may then be overwritten by the group's next Q K^T
-      uint32_t s[kBN];
-      {
-        const uint32_t base = tmem + lane_base + col_s;
+        tc_fence_after_sync();
+        // the whole row of S into registers; S may then be overwritten by the group's next Q K^T
+        uint32_t s[kBN];
+        {
+          const uint32_t base = tmem + lane_base + col_s;
 #pragma unroll
-        for (int c = 0; c < 4; ++c)
-          tmem_ld32(base + c * 32, *reinterpret_cast<uint32_t(*)[32]>(&s[c * 32]));
-        tmem_wait_ld();
-      }
-      tc_fence_before_sync();
-      __syncwarp();
-      if (lane == 0)
-        mbar_arrive(&ss->s_empty[g]);
+          for (int c = 0; c < 4; ++c)
+            tmem_ld32(base + c * 32, *reinterpret_cast<uint32_t(*)[32]>(&s[c * 32]));
+          tmem_wait_ld();
+        }
+        tc_fence_before_sync();
+        __syncwarp();
+        if (lane == 0)
+          mbar_arrive(&ss->s_empty[g]);
 
-      const int64_t kv0 = (int64_t)j * kBN;
-      const bool need_mask = (right_bounded && kv0 + kBN - 1 > q0 + shift + p.window_right) ||
-                             (kv0 + kBN > p.Sk) || left_bounded;
-      if (need_mask) { // visible columns of this tile for this row: [lo, hi]
-        const int64_t hi64 = (right_bounded ? min(p.Sk - 1, qrow + shift + p.window_right) : p.Sk - 1) - kv0;
-        const int64_t lo64 = (left_bounded ? qrow + shift - p.window_left : 0) - kv0;
-        const int hi = (int)max((int64_t)-1, min((int64_t)kBN - 1, hi64));
-        const int lo = (int)max((int64_t)0, min((int64_t)kBN, lo64));
+        const int64_t kv0 = (int64_t)j * kBN;
+        const bool need_mask = (right_bounded && kv0 + kBN - 1 > q0 + shift + p.window_right) ||
+                               (kv0 + kBN > p.Sk) || left_bounded;
+        if (need_mask) { // visible columns of this tile for this row: [lo, hi]
+          const int64_t hi64 = (right_bounded ? min(p.Sk - 1, qrow + shift + p.window_right) : p.Sk - 1) - kv0;
+          const int64_t lo64 = (left_bounded ? qrow + shift - p.window_left : 0) - kv0;
+          const int hi = (int)max((int64_t)-1, min((int64_t)kBN - 1, hi64));
+          const int lo = (int)max((int64_t)0, min((int64_t)kBN, lo64));
 #pragma unroll
-        for (int c = 0; c < kBN; ++c)
-          if (c > hi || c < lo)
-            s[c] = 0xff800000u; // -inf
-      }
-      // row maximum: eight independent chains of 3-input max
-      float mx8[8];
-#pragma unroll
-      for (int e = 0; e < 8; ++e)
-        mx8[e] = fmaxf(__uint_as_float(s[2 * e]), __uint_as_float(s[2 * e + 1]));
-#pragma unroll
-      for (int c = 16; c < kBN; c += 16) {
+          for (int c = 0; c < kBN; ++c)
+            if (c > hi || c < lo)
+              s[c] = 0xff800000u; // -inf
+        }
+        // row maximum: eight independent chains of 3-input max
+        float mx8[8];
 #pragma unroll
         for (int e = 0; e < 8; ++e)
-          mx8[e] = fmax3(mx8[e], __uint_as_float(s[c + 2 * e]), __uint_as_float(s[c + 2 * e + 1]));
-      }
-      const float m_mine =
-          fmax3(fmax3(mx8[0], mx8[1], mx8[2]), fmax3(mx8[3], mx8[4], mx8[5]), fmaxf(mx8[6], mx8[7])) * p.scale_log2;
-      // publish this tile's maxima for the other group
-      ss->rowmax[g][i & 1][row] = m_mine;
-      __syncwarp();
-      if (lane == 0)
-        mbar_arrive(&ss->mx_ready[g][i & 1]);
-      float alpha, a_step;
-      bool rescale = false;
-      alpha = 1.f;
-      if (j > 0) {
-        ref_step(j - 1, m_other, ref, a_step); // the other group rescaled O for this step
-        alpha = a_step;
-      }
-      rescale = ref_step(j, m_mine, ref, a_step); // this thread rescales O for this step
-      alpha *= a_step;
-      l *= alpha; // this group's partial row sum follows every move of the reference
-      const float m_safe = (ref == -INFINITY) ? 0.f : ref;
-      // probabilities: x = s * scale - m for two columns per packed FMA, 2^x on the MUFU unit,
-      // four independent packed partial sums; the 16-bit P reuses the front of the row's registers
-      const uint64_t scale2 = f2_pack(p.scale_log2, p.scale_log2), negm2 = f2_pack(-m_safe, -m_safe);
-      uint64_t sum2[4] = {0ull, 0ull, 0ull, 0ull};
-      uint32_t(&packed)[kBN] = s;
+          mx8[e] = fmaxf(__uint_as_float(s[2 * e]), __uint_as_float(s[2 * e + 1]));
 #pragma unroll
-      for (int c = 0; c < kBN; c += 2) {
-        const uint64_t x2 = f2_fma(f2_pack(__uint_as_float(s[c]), __uint_as_float(s[c + 1])), scale2, negm2);
-        float x0, x1;
-        f2_unpack(x2, x0, x1);
-        const float p0 = fast_exp2(x0), p1 = fast_exp2(x1);
-        sum2[(c >> 1) & 3] = f2_add(sum2[(c >> 1) & 3], f2_pack(p0, p1));
-        packed[c >> 1] = pack2(p0, p1, kBF16);
-      }
-      {
-        float a0, a1, b0, b1;
-        f2_unpack(f2_add(sum2[0], sum2[1]), a0, a1);
-        f2_unpack(f2_add(sum2[2], sum2[3]), b0, b1);
-        l += (a0 + a1) + (b0 + b1);
+        for (int c = 16; c < kBN; c += 16) {
+#pragma unroll
+          for (int e = 0; e < 8; ++e)
+            mx8[e] = fmax3(mx8[e], __uint_as_float(s[c + 2 * e]), __uint_as_float(s[c + 2 * e + 1]));
+        }
+        const float m_mine =
+            fmax3(fmax3(mx8[0], mx8[1], mx8[2]), fmax3(mx8[3], mx8[4], mx8[5]), fmaxf(mx8[6], mx8[7])) * p.scale_log2;
+        // publish this tile's maxima for the other group
+        ss->rowmax[g][ti & 1][row] = m_mine;
+        __syncwarp();
+        if (lane == 0)
+          mbar_arrive(&ss->mx_ready[g][ti & 1]);
+        float alpha, a_step;
+        bool rescale = false;
+        alpha = 1.f;
+        if (j > 0) {
+          ref_step(j - 1, m_other, ref, a_step); // the other group rescaled O for this step
+          alpha = a_step;
+        }
+        rescale = ref_step(j, m_mine, ref, a_step); // this thread rescales O for this step
+        alpha *= a_step;
+        l *= alpha; // this group's partial row sum follows every move of the reference
+        const float m_safe = (ref == -INFINITY) ? 0.f : ref;
+        // probabilities: x = s * scale - m for two columns per packed FMA, 2^x on the MUFU unit,
+        // four independent packed partial sums; the 16-bit P reuses the front of the row's registers
+        const uint64_t scale2 = f2_pack(p.scale_log2, p.scale_log2), negm2 = f2_pack(-m_safe, -m_safe);
+        uint64_t sum2[4] = {0ull, 0ull, 0ull, 0ull};
+        uint32_t(&packed)[kBN] = s;
+#pragma unroll
+        for (int c = 0; c < kBN; c += 2) {
+          const uint64_t x2 = f2_fma(f2_pack(__uint_as_float(s[c]), __uint_as_float(s[c + 1])), scale2, negm2);
+          float x0, x1;
+          f2_unpack(x2, x0, x1);
+          const float p0 = fast_exp2(x0), p1 = fast_exp2(x1);
+          sum2[(c >> 1) & 3] = f2_add(sum2[(c >> 1) & 3], f2_pack(p0, p1));
+          packed[c >> 1] = pack2(p0, p1, kBF16);
+        }
+        {
+          float a0, a1, b0, b1;
+          f2_unpack(f2_add(sum2[0], sum2[1]), a0, a1);
+          f2_unpack(f2_add(sum2[2], sum2[3]), b0, b1);
+          l += (a0 + a1) + (b0 + b1);
+        }
+
+        // P V of the tile before (the other group's) has completed: then so has this group's
+        // previous one, which read the P columns, and O holds every tile up to j - 1
+        if (j > 0) {
+          const uint32_t to = tc[1] + ((j - 1) >> 1);
+          if (!warp_wait_or_flag(&ss->pv_done[g ^ 1], to & 1, ss)) {
+            ok = false;
+            break;
+          }
+        }
+        tc_fence_after_sync();
+        // P row -> tensor memory: 128 keys = 64 columns of two 16-bit values
+        tmem_st32(tmem + lane_base + col_p, *reinterpret_cast<uint32_t(*)[32]>(&packed[0]));
+        tmem_st32(tmem + lane_base + col_p + 32, *reinterpret_cast<uint32_t(*)[32]>(&packed[32]));
+        if (rescale) {
+          const uint32_t base = tmem + lane_base + kColO;
+#pragma unroll
+          for (int c = 0; c < 4; ++c) {
+            uint32_t r[32];
+            tmem_ld32(base + c * 32, r);
+            tmem_wait_ld();
+#pragma unroll
+            for (int q = 0; q < 32; ++q)
+              r[q] = __float_as_uint(__uint_as_float(r[q]) * a_step);
+            tmem_st32(base + c * 32, r);
+          }
+        }
+        tmem_wait_st();
+        tc_fence_before_sync();
+        __syncwarp();
+        if (lane == 0)
+          mbar_arrive(&ss->p_full[g]);
       }
 
-      // P V of the tile before (the other group's) has completed: then so has this group's
-      // previous one, which read the P columns, and O holds every tile up to j - 1
-      if (j > 0 && !warp_wait_or_flag(&ss->pv_done[g ^ 1], (uint32_t)(((j - 1) >> 1) & 1), ss)) {
-        ok = false;
-        break;
+      // ---- epilogue of the query tile: O / l -> 16 bit -> shared -> TMA store; LSE
+      // the last P V: products complete in issue order, so it is the only one to wait for
+      if (ok && n > 0) {
+        const int gl = (n - 1) & 1; // group of the last key tile
+        const uint32_t tl = (gl == g ? tc[0] : tc[1]) + ((n - 1) >> 1);
+        ok = warp_wait_or_flag(&ss->pv_done[gl], tl & 1, ss);
       }
+      tc[0] += n_mine;
+      tc[1] += n_other;
+      if (warp == 4 && lane == 0)
+        bulk_wait_read<0>(); // the previous query tile's store has read the staging buffer
+      ss->xch[g][row] = make_float2(ref, l);
+      tc_fence_before_sync();
+      const bool give_up = named_bar_or_n<256>(!ok); // both groups
       tc_fence_after_sync();
-      // P row -> tensor memory: 128 keys = 64 columns of two 16-bit values
-      tmem_st32(tmem + lane_base + col_p, *reinterpret_cast<uint32_t(*)[32]>(&packed[0]));
-      tmem_st32(tmem + lane_base + col_p + 32, *reinterpret_cast<uint32_t(*)[32]>(&packed[32]));
-      if (rescale) {
-        const uint32_t base = tmem + lane_base + kColO;
+      // the two threads of a row may be one step apart: the later reference is the one O is scaled with
+      const float2 other = ss->xch[g ^ 1][row];
+      const float m_tot = fmaxf(ref, other.x);
+      const float a_mine = (ref == -INFINITY) ? 0.f : fast_exp2(ref - m_tot);
+      const float a_other = (other.x == -INFINITY) ? 0.f : fast_exp2(other.x - m_tot);
+      const float l_tot = l * a_mine + other.y * a_other;
+      const float inv_l = (l_tot > 0.f) ? 1.f / l_tot : 0.f;
+      const bool have = !give_up && n > 0;
+      // this thread finishes head-dim columns [64 g, 64 g + 64) of its row
 #pragma unroll
-        for (int c = 0; c < 4; ++c) {
-          uint32_t r[32];
-          tmem_ld32(base + c * 32, r);
+      for (int c = 0; c < 2; ++c) {
+        uint32_t r[32];
+        if (have) {
+          tmem_ld32(tmem + lane_base + kColO + g * 64 + c * 32, r);
           tmem_wait_ld();
+        } else {
 #pragma unroll
           for (int q = 0; q < 32; ++q)
-            r[q] = __float_as_uint(__uint_as_float(r[q]) * a_step);
-          tmem_st32(base + c * 32, r);
+            r[q] = 0u;
+        }
+#pragma unroll
+        for (int q = 0; q < 4; ++q) { // 8 columns = one 16-byte chunk
+          uint4 v;
+          v.x = pack2(__uint_as_float(r[q * 8 + 0]) * inv_l, __uint_as_float(r[q * 8 + 1]) * inv_l, kBF16);
+          v.y = pack2(__uint_as_float(r[q * 8 + 2]) * inv_l, __uint_as_float(r[q * 8 + 3]) * inv_l, kBF16);
+          v.z = pack2(__uint_as_float(r[q * 8 + 4]) * inv_l, __uint_as_float(r[q * 8 + 5]) * inv_l, kBF16);
+          v.w = pack2(__uint_as_float(r[q * 8 + 6]) * inv_l, __uint_as_float(r[q * 8 + 7]) * inv_l, kBF16);
+          const int chunk = c * 4 + q;
+          *reinterpret_cast<uint4 *>(sO + g * kHalfTile + row * 128 + ((chunk ^ (row & 7)) << 4)) = v;
         }
       }
-      tmem_wait_st();
+      fence_proxy_async_smem();
+      if (g == 0 && qrow < p.Sq)
+        p.lse[((int64_t)w.b * p.H + w.h) * p.Sq + qrow] =
+            (l_tot > 0.f) ? (m_tot + log2f(l_tot)) * 0.6931471805599453f : INFINITY;
+      // both groups: O is staged and read out of tensor memory, the next query tile may overwrite it
       tc_fence_before_sync();
-      __syncwarp();
-      if (lane == 0)
-        mbar_arrive(&ss->p_full[g]);
-    }
-
-    // ---- epilogue: O / l -> 16 bit -> shared -> TMA store; LSE
-    // the last P V: products complete in issue order, so it is the only one to wait for
-    if (ok && n > 0)
-      ok = warp_wait_or_flag(&ss->pv_done[(n - 1) & 1], (uint32_t)(((n - 1) >> 1) & 1), ss);
-    ss->xch[g][row] = make_float2(ref, l);
-    tc_fence_before_sync();
-    const bool give_up = named_bar_or_n<256>(!ok); // both groups
-    tc_fence_after_sync();
-    // the two threads of a row may be one step apart: the later reference is the one O is scaled with
-    const float2 other = ss->xch[g ^ 1][row];
-    const float m_tot = fmaxf(ref, other.x);
-    const float a_mine = (ref == -INFINITY) ? 0.f : fast_exp2(ref - m_tot);
-    const float a_other = (other.x == -INFINITY) ? 0.f : fast_exp2(other.x - m_tot);
-    const float l_tot = l * a_mine + other.y * a_other;
-    const float inv_l = (l_tot > 0.f) ? 1.f / l_tot : 0.f;
-    const bool have = !give_up && n > 0;
-    // this thread finishes head-dim columns [64 g, 64 g + 64) of its row; staging in Q's tile
-#pragma unroll
-    for (int c = 0; c < 2; ++c) {
-      uint32_t r[32];
-      if (have) {
-        tmem_ld32(tmem + lane_base + kColO + g * 64 + c * 32, r);
-        tmem_wait_ld();
-      } else {
-#pragma unroll
-        for (int q = 0; q < 32; ++q)
-          r[q] = 0u;
+      asm volatile("bar.sync 2, 256;" ::: "memory");
+      tc_fence_after_sync();
+      if (warp == 4 && lane == 0 && !give_up) {
+        tma_store_4d(&o_map, sO, 0, w.h, (int)q0, w.b);
+        tma_store_4d(&o_map, sO + kHalfTile, 64, w.h, (int)q0, w.b);
+        bulk_commit();
       }
-#pragma unroll
-      for (int q = 0; q < 4; ++q) { // 8 columns = one 16-byte chunk
-        uint4 v;
-        v.x = pack2(__uint_as_float(r[q * 8 + 0]) * inv_l, __uint_as_float(r[q * 8 + 1]) * inv_l, kBF16);
-        v.y = pack2(__uint_as_float(r[q * 8 + 2]) * inv_l, __uint_as_float(r[q * 8 + 3]) * inv_l, kBF16);
-        v.z = pack2(__uint_as_float(r[q * 8 + 4]) * inv_l, __uint_as_float(r[q * 8 + 5]) * inv_l, kBF16);
-        v.w = pack2(__uint_as_float(r[q * 8 + 6]) * inv_l, __uint_as_float(r[q * 8 + 7]) * inv_l, kBF16);
-        const int chunk = c * 4 + q;
-        *reinterpret_cast<uint4 *>(sQ + g * kHalfTile + row * 128 + ((chunk ^ (row & 7)) << 4)) = v;
-      }
+      if (give_up)
+        break;
     }
-    fence_proxy_async_smem();
-    if (g == 0 && qrow < p.Sq)
-      p.lse[((int64_t)b * p.H + h) * p.Sq + qrow] =
-          (l_tot > 0.f) ? (m_tot + log2f(l_tot)) * 0.6931471805599453f : INFINITY;
-    asm volatile("bar.sync 2, 256;" ::: "memory"); // both softmax groups
-    if (warp == 4 && lane == 0 && ss->failed == 0) {
-      tma_store_4d(&o_map, sQ, 0, h, (int)q0, b);
-      tma_store_4d(&o_map, sQ + kHalfTile, 64, h, (int)q0, b);
-      bulk_commit();
-      bulk_wait_read<0>(); // shared memory must outlive the store's reads, not its completion
-    }
+    if (warp == 4 && lane == 0)
+      bulk_wait_read<0>(); // shared memory must outlive the last store's reads
   }
 
   tc_fence_before_sync();
@@ -1145,7 +1244,10 @@ extern "C" int b200_flash_attn_fwd(int dtype, const void *q, const void *k, cons
   p.scale_log2 = a.softmax_scale * 1.4426950408889634f;
   p.window_left = a.window_size_left;
   p.window_right = a.window_size_right;
-  const size_t smem = (size_t)(1 + kFwdKStages + kFwdVStages) * kTileBytes + sizeof(SharedStorage) + 1024;
+  p.n_q_tiles = (int)((a.seqlen_q + kBM - 1) / kBM);
+  p.pairs = (p.n_q_tiles + 1) / 2;
+  p.total_items = (int64_t)p.pairs * a.h * a.b;
+  const size_t smem = (size_t)(2 + kFwdKStages + kFwdVStages) * kTileBytes + sizeof(SharedStorage) + 1024;
   static bool attr_set[2] = {false, false};
   if (!attr_set[bf16]) {
     cudaError_t e = bf16 ? cudaFuncSetAttribute(flash_fwd_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem)
@@ -1154,7 +1256,7 @@ extern "C" int b200_flash_attn_fwd(int dtype, const void *q, const void *k, cons
       return rc;
     attr_set[bf16] = true;
   }
-  const dim3 grid((unsigned)((a.seqlen_q + kBM - 1) / kBM), (unsigned)a.h, (unsigned)a.b);
+  const dim3 grid((unsigned)(p.total_items < kNumSMs ? p.total_items : kNumSMs)); // persistent blocks, one per SM
   if (bf16)
     flash_fwd_kernel<true><<<grid, kThreads, smem, stream>>>(q_map, k_map, v_map, o_map, p);
   else
