@@ -772,7 +772,13 @@ int get_side_stream(cudaStream_t user, SideStream *out) {
   auto it = pool.find({dev, user});
   if (it == pool.end()) {
     SideStream s;
-    if (int rc = check_cuda(cudaStreamCreateWithFlags(&s.stream, cudaStreamNonBlocking)))
+    // Highest priority: the helper stream carries the sort, a chain of nine small kernels, beside
+    // the table copy, whose sixteen thousand blocks would otherwise sit in front of every one of
+    // them in the block scheduler's queue.
+    int least = 0, greatest = 0;
+    if (int rc = check_cuda(cudaDeviceGetStreamPriorityRange(&least, &greatest)))
+      return rc;
+    if (int rc = check_cuda(cudaStreamCreateWithPriority(&s.stream, cudaStreamNonBlocking, greatest)))
       return rc;
     if (int rc = check_cuda(cudaEventCreateWithFlags(&s.fork, cudaEventDisableTiming)))
       return rc;
