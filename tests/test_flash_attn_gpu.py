@@ -35,6 +35,8 @@ FWD_CASES = [
     (1, 300, 300, 3, 1, True),     # ragged, grouped heads
     (1, 200, 456, 2, 2, True),     # bottom-right aligned causal, Sk > Sq
     (1, 1024, 1024, 2, 2, True),
+    (4, 1024, 1152, 40, 8, True),  # 640 work items on 148 persistent blocks: several query tiles per block
+    (3, 640, 640, 56, 56, False),  # odd number of query tiles: the middle one has no partner
 ]
 
 
