@@ -86,14 +86,18 @@ class ArgInfo:
 
 
 class Session:
-    """device: "cuda" (default CUDA provider + CUDA allocators) or "cpu"."""
+    """device: "cuda" (default CUDA provider + CUDA allocators) or "cpu"; host_space=True adds the
+    CPU allocator and provider to a CUDA session, for modules with memrefs in the "cpu" space
+    (cpu2cuda / cuda2cpu copies)."""
 
-    def __init__(self, device="cuda", device_id=0):
+    def __init__(self, device="cuda", device_id=0, host_space=False):
         self._h = lib().brt_session_create()
         if not self._h:
             raise BrtError(lib().brt_last_error().decode())
         if device == "cuda":
             _check(lib().brt_session_add_cuda(self._h, device_id))
+            if host_space:
+                _check(lib().brt_session_add_cpu(self._h))
         elif device == "cpu":
             _check(lib().brt_session_add_cpu(self._h))
         else:

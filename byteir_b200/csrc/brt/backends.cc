@@ -98,9 +98,11 @@ common::Status CUDAWorkQueue::AddTask(int task_type, const void *, void **args, 
                           "kernels launch on GetComputeStream()");
   }
   env_.Activate();
+  // the reference's convention (cuda_work_queue.cc:36-58): args = {&dst, &src, &bytes}
+  void *dst = *static_cast<void **>(args[0]);
+  void *src = *static_cast<void **>(args[1]);
   const size_t bytes = *static_cast<size_t *>(args[2]);
-  return BRT_CUDA_CALL(
-      cudaMemcpyAsync(args[0], args[1], bytes, kind, reinterpret_cast<cudaStream_t>(GetComputeStream())));
+  return BRT_CUDA_CALL(cudaMemcpyAsync(dst, src, bytes, kind, reinterpret_cast<cudaStream_t>(GetComputeStream())));
 }
 
 common::Status CUDAWorkQueue::Sync() {

@@ -6,10 +6,12 @@
 #include "b200_kernels.h"
 #include "brt/backends/common.h"
 #include "brt/backends/cuda/device/utils/op_kernel_impl_helpers.h"
+#include "brt/backends/cuda/providers/default/copy/op_registration.h"
 #include "brt/backends/cuda/providers/default/cuda_provider.h"
 #include "brt/backends/cuda/providers/default/custom/op_registration.h"
 #include "brt/backends/cuda/providers/default/indexing/op_registration.h"
 #include "brt/backends/cuda/providers/default/reduction/op_registration.h"
+#include "brt/backends/cuda/providers/default/tensor_generate/op_registration.h"
 #include "brt/backends/cuda/providers/default/tensor_manipulate/op_registration.h"
 #include "brt/core/common/common.h"
 #include "brt/core/session/session.h"
@@ -301,6 +303,120 @@ private:
   size_t bytes_;
 };
 
+// byre.compute @cpu2cuda / @cuda2cpu (copy/copy.cc:38-72, copy/op_registration.cc): host <-> device
+// copies routed through the work queue's copy tasks, as the reference does
+class HostDeviceCopy final : public OpKernel {
+public:
+  HostDeviceCopy(const OpKernelInfo &info, int task_type) : OpKernel(info), task_type_(task_type) {
+    OpAccessor accessor(info_);
+    bytes_ = (size_t)OpAccessor::GetNumElementsOfShape(accessor.GetArgShape(0)) *
+             GetDTypeByte(accessor.GetArgDTypeEnum(0));
+  }
+  common::Status RunImpl(const ExecutionContext &ctx) override {
+    OpAccessor accessor(info_, ctx.exec_frame);
+    void *src = accessor.GetArgAsyncValueRef(0), *dst = accessor.GetArgAsyncValueRef(1);
+    if (src == dst)
+      return common::Status::OK();
+    void *args[3] = {&dst, &src, &bytes_};
+    return ctx.work_queue->AddTask(task_type_, nullptr, args, info_.GetOpId(), info_.GetDependency());
+  }
+
+private:
+  int task_type_;
+  size_t bytes_;
+};
+
+// 16-bit storage formats of a host double, round to nearest even
+uint16_t ToF16Bits(double d) {
+  const float f = (float)d;
+  uint32_t x;
+  std::memcpy(&x, &f, 4);
+  const uint32_t sign = (x >> 16) & 0x8000u;
+  const int32_t exp = (int32_t)((x >> 23) & 0xff) - 127 + 15;
+  uint32_t man = x & 0x7fffffu;
+  if (((x >> 23) & 0xff) == 0xff)
+    return (uint16_t)(sign | 0x7c00u | (man ? 0x200u : 0));
+  if (exp >= 31)
+    return (uint16_t)(sign | 0x7c00u);
+  if (exp <= 0) {
+    if (exp < -10)
+      return (uint16_t)sign;
+    man |= 0x800000u;
+    const int shift = 14 - exp;
+    uint32_t half = man >> shift;
+    const uint32_t rem = man & ((1u << shift) - 1), mid = 1u << (shift - 1);
+    if (rem > mid || (rem == mid && (half & 1)))
+      ++half;
+    return (uint16_t)(sign | half);
+  }
+  uint32_t half = ((uint32_t)exp << 10) | (man >> 13);
+  const uint32_t rem = man & 0x1fffu;
+  if (rem > 0x1000u || (rem == 0x1000u && (half & 1)))
+    ++half;
+  return (uint16_t)(sign | half);
+}
+uint16_t ToBF16Bits(double d) {
+  const float f = (float)d;
+  uint32_t x;
+  std::memcpy(&x, &f, 4);
+  if ((x & 0x7fffffffu) > 0x7f800000u)
+    return (uint16_t)((x >> 16) | 0x40u);
+  x += 0x7fffu + ((x >> 16) & 1u);
+  return (uint16_t)(x >> 16);
+}
+
+// byre.compute @FillOp (tensor_generate/fill.cc:36-95): attribute `value` is a dense constant of the
+// tensor's type; a splat fills on the device, anything else is copied from the host
+class FillOpKernel final : public OpKernel {
+public:
+  explicit FillOpKernel(const OpKernelInfo &info) : OpKernel(info) {
+    OpAccessor accessor(info_);
+    dtype_ = accessor.GetArgDTypeEnum(0);
+    count_ = OpAccessor::GetNumElementsOfShape(accessor.GetArgShape(0));
+    elt_ = GetDTypeByte(dtype_);
+    BRT_ENFORCE(accessor.HasAttr("value"), "FillOp needs a `value` attribute");
+    splat_ = accessor.HasAttrOfSplatValue<double>("value");
+    const std::vector<double> vals =
+        splat_ ? std::vector<double>{accessor.GetAttrAsSplatValue<double>("value")} : accessor.GetAttrAsVector<double>("value");
+    BRT_ENFORCE(splat_ || (int64_t)vals.size() == count_, "FillOp: `value` has ", vals.size(), " elements, the tensor ",
+                count_);
+    host_.resize(vals.size() * elt_);
+    for (size_t i = 0; i < vals.size(); ++i)
+      Encode(vals[i], host_.data() + i * elt_);
+  }
+  common::Status RunImpl(const ExecutionContext &ctx) override {
+    OpAccessor accessor(info_, ctx.exec_frame);
+    cudaStream_t stream = detail::StreamOf(ctx);
+    void *out = accessor.GetArgAsyncValueRef(0);
+    if (splat_) {
+      uint64_t bits = 0;
+      std::memcpy(&bits, host_.data(), elt_);
+      return FromRc(b200_fill((int)elt_, out, count_, bits, stream), "FillOp");
+    }
+    return BRT_CUDA_CALL(cudaMemcpyAsync(out, host_.data(), host_.size(), cudaMemcpyHostToDevice, stream));
+  }
+
+private:
+  void Encode(double v, char *dst) const {
+    switch (dtype_) {
+    case DTypeEnum::Float32: { const float f = (float)v; std::memcpy(dst, &f, 4); break; }
+    case DTypeEnum::Float64: std::memcpy(dst, &v, 8); break;
+    case DTypeEnum::Float16: { const uint16_t h = ToF16Bits(v); std::memcpy(dst, &h, 2); break; }
+    case DTypeEnum::BFloat16: { const uint16_t h = ToBF16Bits(v); std::memcpy(dst, &h, 2); break; }
+    case DTypeEnum::Int64: case DTypeEnum::UInt64: { const int64_t i = (int64_t)v; std::memcpy(dst, &i, 8); break; }
+    case DTypeEnum::Int32: case DTypeEnum::UInt32: { const int32_t i = (int32_t)v; std::memcpy(dst, &i, 4); break; }
+    case DTypeEnum::Int16: case DTypeEnum::UInt16: { const int16_t i = (int16_t)v; std::memcpy(dst, &i, 2); break; }
+    case DTypeEnum::Int8: case DTypeEnum::UInt8: case DTypeEnum::Bool: { const int8_t i = (int8_t)v; std::memcpy(dst, &i, 1); break; }
+    default: BRT_THROW("FillOp: element type ", DTypeName(dtype_), " is not supported");
+    }
+  }
+  DTypeEnum dtype_;
+  int64_t count_;
+  size_t elt_;
+  bool splat_;
+  std::vector<char> host_; // the value(s) in the tensor's storage format; lives as long as the kernel
+};
+
 template <typename K> KernelCreateFn Creator() {
   return [](const OpKernelInfo &info) -> std::shared_ptr<OpKernel> { return std::make_shared<K>(info); };
 }
@@ -332,6 +448,21 @@ void RegisterTensorManipulateOps(KernelRegistry *registry) {
 
 void RegisterCustomOps(KernelRegistry *registry) { registry->Register("custom", Creator<CustomOpKernel>()); }
 
+// the ops on either side of the compute ops in host-driven modules
+void RegisterCopyOps(KernelRegistry *registry) { // copy/op_registration.cc
+  registry->Register("cpu2cuda", [](const OpKernelInfo &info) -> std::shared_ptr<OpKernel> {
+    return std::make_shared<HostDeviceCopy>(info, (int)kH2D);
+  });
+  registry->Register("cuda2cpu", [](const OpKernelInfo &info) -> std::shared_ptr<OpKernel> {
+    return std::make_shared<HostDeviceCopy>(info, (int)kD2H);
+  });
+  registry->Register("cuda2cuda", Creator<Cuda2CudaCopy>());
+}
+
+void RegisterTensorGenerateOps(KernelRegistry *registry) { // tensor_generate/op_registration.cc: FillOp only
+  registry->Register("FillOp", Creator<FillOpKernel>());
+}
+
 } // namespace cuda
 
 namespace {
@@ -341,7 +472,8 @@ BRT_STATIC_KERNEL_REGISTRATION(DeviceKind::CUDA, ProviderType::BRT, [](KernelReg
   cuda::RegisterIndexingOps(registry);
   cuda::RegisterTensorManipulateOps(registry);
   cuda::RegisterCustomOps(registry);
-  registry->Register("cuda2cuda", cuda::Creator<cuda::Cuda2CudaCopy>());
+  cuda::RegisterCopyOps(registry);
+  cuda::RegisterTensorGenerateOps(registry);
   RegisterCommonBuiltinOps(registry);
 })
 } // namespace

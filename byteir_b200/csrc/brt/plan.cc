@@ -70,8 +70,6 @@ Status StaticBRTExecutionPlan::ProloguePerSession(const AllocatorMap &allocators
     if (ai < 0)
       return Fail(common::INVALID_GRAPH, "no allocator registered for memory space \"" + v.type.space +
                                              "\" of argument " + info.name);
-    if (i == 0)
-      first_space_ = v.type.space;
     ExecutionFrame::ConstructInfo::Arg a;
     a.bytes = v.type.SizeInBytes();
     a.allocator = ai;
@@ -90,7 +88,9 @@ Status StaticBRTExecutionPlan::ProloguePerSession(const AllocatorMap &allocators
 
   // ---- tensors: arguments, planned intermediates, aliases (execution_plan.cc:161-241,508-559)
   frame_info_.tensors.resize(fn.values.size());
+  uses_cuda_ = false;
   for (const ir::Value &v : fn.values) {
+    uses_cuda_ = uses_cuda_ || v.type.space == "cuda";
     auto &loc = frame_info_.tensors[v.id];
     if (v.arg_index >= 0) {
       loc = {ExecutionFrame::ConstructInfo::TensorLoc::kArg, v.arg_index, 0};
@@ -221,8 +221,9 @@ void StaticBRTExecutionPlan::CreateExecutinFrame(std::unique_ptr<ExecutionFrame>
 }
 
 void StaticBRTExecutionPlan::CreateWorkQueue(std::unique_ptr<WorkQueue> *wq, int rank) {
-  // the device of the first argument decides (execution_plan.cc:592-601)
-  if (first_space_ == "cuda")
+  // the reference always makes a single-stream CUDA queue in a CUDA build (execution_plan.cc:592-601);
+  // here any value in device memory asks for one, whichever memory space the first argument is in
+  if (uses_cuda_)
     wq->reset(new CUDASingleStreamWorkQueue(rank));
   else
     wq->reset(new cpu::CPUNaiveWorkQueue());
@@ -387,9 +388,12 @@ std::string Session::GetSpace(size_t id) {
 RequestContext::RequestContext(Session &session) : session_(session), events_(new EventListenerManager()) {}
 
 RequestContext::~RequestContext() {
-  if (wq_)
-    (void)wq_->Sync();
-  session_.Cleanup(*this);
+  try { // a device that went away must not turn the destructor into std::terminate
+    if (wq_)
+      (void)wq_->Sync();
+    session_.Cleanup(*this);
+  } catch (const std::exception &) {
+  }
 }
 
 Status RequestContext::BindArg(size_t offset, const void *value, BrtOwnershipType ownership) {

@@ -164,6 +164,13 @@ int b200_permute(int elt_bytes, const void *in, void *out, int rank,
                  const int64_t *shape, const int64_t *perm,
                  cudaStream_t stream);
 
+/* ---- FillOp -----------------------------------------------------------------
+ * Replaces kernel::Fill (tensor_generate/kernels/fill.h; caller tensor_generate/
+ * fill.cc:36-62): out[i] = value for i in [0, n).  elt_bytes in {1,2,4,8}; the
+ * value is passed as its bit pattern in the low elt_bytes bytes of value_bits.
+ */
+int b200_fill(int elt_bytes, void *out, int64_t n, uint64_t value_bits, cudaStream_t stream);
+
 /* ---- Flash attention ------------------------------------------------------
  * Typed doors behind the byre.custom entry points run_flash_attn_fwd / _bwd
  * (external_libs/runtime/flash_attn/lib/flash_api.h:75-82, argument unpacking

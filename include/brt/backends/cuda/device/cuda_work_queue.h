@@ -16,7 +16,7 @@ class CUDAWorkQueue : public WorkQueue {
 public:
   explicit CUDAWorkQueue(cuda::CudaEnv env, const std::string &name = "cuda_default_stream")
       : WorkQueue(name), env_(env) {}
-  // kH2D / kD2H / kD2D: args = {dst, src, &size_t bytes}; other types are not
+  // kH2D / kD2H / kD2D: args = {&dst, &src, &bytes} (void **, void **, size_t *); other types are not
   // used by this provider's kernels and return NOT_IMPLEMENTED
   common::Status AddTask(int task_type, const void *func, void **args, int op_id,
                          const std::vector<int> &dependency) override;

@@ -36,7 +36,8 @@ template <typename F> common::Status CallToStatus(F &&f) {
   }
 }
 inline cudaStream_t StreamOf(const ExecutionContext &ctx) {
-  auto *wq = static_cast<CUDAWorkQueue *>(ctx.work_queue);
+  auto *wq = dynamic_cast<CUDAWorkQueue *>(ctx.work_queue);
+  BRT_ENFORCE(wq, "a CUDA op needs a CUDA work queue on the request");
   wq->GetCudaEnv().Activate();
   return reinterpret_cast<cudaStream_t>(wq->GetComputeStream());
 }

@@ -65,7 +65,7 @@ private:
   ExecutionFrame::ConstructInfo frame_info_;
   std::vector<AsyncValue> weights_;
   std::vector<std::pair<IAllocator *, void *>> owned_weights_;
-  std::string first_space_;
+  bool uses_cuda_ = false; // some value of the entry function lives in device memory
 };
 
 } // namespace brt

@@ -9,7 +9,7 @@ import torch
 
 import oracle_lib as O
 from byteir_b200 import brt
-from test_brt_host import INDEX, TRANSPOSE, reduce_mlir
+from test_brt_host import HOST_DEVICE, INDEX, TRANSPOSE, reduce_mlir
 
 pytestmark = pytest.mark.gpu
 
@@ -168,3 +168,32 @@ def test_flash_attn_fwd_bwd_custom_call_through_session(t):
     wq, wk, wv = O.flash_attn_bwd(do, q, k, v, out["Out"], out["SoftmaxLse"], scale, True)
     for name, want in (("d_Q", wq), ("d_K", wk), ("d_V", wv)):
         np.testing.assert_allclose(O.to_f32(out[name]), O.to_f32(want), rtol=2e-2, atol=1e-2, err_msg=name)
+
+
+def test_host_device_copies_and_fill_through_session():
+    """the ops on either side of the compute ops in host-driven modules (the reference's
+    custom_add_cpu2cuda.mlir and fill_cuda.mlir patterns): cpu2cuda, cuda2cpu, FillOp"""
+    rng = np.random.default_rng(11)
+    a_host = torch.from_numpy(rng.uniform(-1, 1, (1024, 256)).astype(np.float32)).pin_memory()
+    sum_host = torch.zeros(1024, dtype=torch.float32).pin_memory()
+    three = torch.zeros(3, dtype=torch.float16, device="cuda")
+    halves = torch.zeros(1001, dtype=torch.float16, device="cuda")
+    sevens = torch.zeros(37, dtype=torch.int64, device="cuda")
+    s = brt.Session("cuda", host_space=True)
+    s.load_from_memory(HOST_DEVICE)
+    req = s.new_request(torch.cuda.current_stream().cuda_stream)
+    for name, t in (("A", a_host), ("Sum", sum_host), ("Three", three), ("Halves", halves), ("Sevens", sevens)):
+        info = s.arg_info(s.arg_offset(name))
+        assert info.space == ("cpu" if not t.is_cuda else "cuda") and info.nbytes == t.numel() * t.element_size()
+        req.bind_arg(info.offset, t.data_ptr())
+    req.finish_io_binding()
+    for _ in range(2):
+        req.run()
+        req.sync()
+    torch.cuda.synchronize()
+    want = O.reduce("sum", a_host.numpy(), 1024, 256, 1)
+    np.testing.assert_allclose(sum_host.numpy(), want, rtol=1e-5, atol=1e-5)
+    assert three.cpu().tolist() == [1.0, 2.0, 3.0]
+    assert torch.all(halves == 0.5) and torch.all(sevens == 7)
+    req.close()
+    s.close()

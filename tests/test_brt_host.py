@@ -297,3 +297,38 @@ def test_cuda_request_without_a_gpu_fails_with_a_status_not_a_crash():
     s.load_from_memory(reduce_mlir("ReduceSumOp_f32_f32", "f32", (8, 8), (8,), "dense<1> : tensor<1xi64>"))
     with pytest.raises(brt.BrtError):
         s.new_request()
+
+
+HOST_DEVICE = """
+module attributes {byre.container_module} {
+  func.func @main(%arg0: memref<1024x256xf32, "cpu"> {byre.argname = "A", byre.argtype = 1 : i32},
+                  %arg1: memref<1024xf32, "cpu"> {byre.argname = "Sum", byre.argtype = 2 : i32},
+                  %arg2: memref<3xf16, "cuda"> {byre.argname = "Three", byre.argtype = 2 : i32},
+                  %arg3: memref<1001xf16, "cuda"> {byre.argname = "Halves", byre.argtype = 2 : i32},
+                  %arg4: memref<37xi64, "cuda"> {byre.argname = "Sevens", byre.argtype = 2 : i32}) attributes {byre.entry_point} {
+    %0 = memref.alloc() : memref<1024x256xf32, "cuda">
+    %1 = memref.alloc() : memref<1024xf32, "cuda">
+    byre.compute @cpu2cuda(%arg0, %0) {memory_effects = [1 : i32, 2 : i32]} : memref<1024x256xf32, "cpu">, memref<1024x256xf32, "cuda">
+    byre.compute @ReduceSumOp_f32_f32(%0, %1) {dimensions = dense<1> : tensor<1xi64>, memory_effects = [1 : i32, 2 : i32]} : memref<1024x256xf32, "cuda">, memref<1024xf32, "cuda">
+    byre.compute @cuda2cpu(%1, %arg1) {memory_effects = [1 : i32, 2 : i32]} : memref<1024xf32, "cuda">, memref<1024xf32, "cpu">
+    byre.compute @FillOp(%arg2) {value = dense<[1.000000e+00, 2.000000e+00, 3.000000e+00]> : tensor<3xf16>} : memref<3xf16, "cuda">
+    byre.compute @FillOp(%arg3) {value = dense<5.000000e-01> : tensor<1001xf16>} : memref<1001xf16, "cuda">
+    byre.compute @FillOp(%arg4) {value = dense<7> : tensor<37xi64>} : memref<37xi64, "cuda">
+    return
+  }
+}
+"""
+
+
+def test_host_device_copies_and_fill_load():
+    """cpu2cuda / cuda2cpu / FillOp are registered, take "cpu"-space memrefs in a CUDA session that also
+    has the host allocator, and FillOp checks its constant against the tensor"""
+    s = brt.Session("cuda", host_space=True)
+    s.load_from_memory(HOST_DEVICE)
+    assert [s.arg_info(i).space for i in range(5)] == ["cpu", "cpu", "cuda", "cuda", "cuda"]
+    with pytest.raises(brt.BrtError, match="FillOp"):
+        brt.Session("cuda", host_space=True).load_from_memory(
+            HOST_DEVICE.replace("dense<[1.000000e+00, 2.000000e+00, 3.000000e+00]> : tensor<3xf16>",
+                                "dense<[1.000000e+00, 2.000000e+00]> : tensor<2xf16>"))
+    with pytest.raises(brt.BrtError, match="no allocator registered for memory space \"cpu\""):
+        brt.Session("cuda").load_from_memory(HOST_DEVICE)  # a plain CUDA session has no host allocator

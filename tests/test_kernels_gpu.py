@@ -346,3 +346,19 @@ def test_sharded_sum_finish_times_out_instead_of_hanging(ops):
     assert int(status.item()) == 3
     assert int(flags1[0].item()) == 1  # rank 0 did publish to its peer
     assert float(torch.ones(4, device="cuda").sum().item()) == 4.0
+
+
+@pytest.mark.parametrize("dtype", [torch.uint8, torch.float16, torch.float32, torch.int64])
+@pytest.mark.parametrize("n,head", [(1, 0), (5, 1), (4099, 3), (1 << 20, 0), ((1 << 20) + 7, 5)])
+def test_fill_any_alignment(dtype, n, head):
+    """b200_fill writes exactly [0, n): unaligned starts and ragged ends, all element sizes"""
+    from byteir_b200 import _native as N
+    buf = torch.zeros(n + head + 16, dtype=dtype, device="cuda")
+    value = torch.tensor([3], dtype=dtype)
+    bits = int.from_bytes(value.numpy().tobytes(), "little")
+    rc = N.lib().b200_fill(buf.element_size(), buf.data_ptr() + head * buf.element_size(), n, bits,
+                           torch.cuda.current_stream().cuda_stream)
+    assert rc == 0
+    torch.cuda.synchronize()
+    assert torch.all(buf[head:head + n] == 3)
+    assert torch.all(buf[:head] == 0) and torch.all(buf[head + n:] == 0)
