@@ -29,6 +29,21 @@ class FlashAttnParams(C.Structure):
     )
 
 
+class FlashKvCacheParams(C.Structure):
+    _fields_ = (
+        [(n, C.c_int64) for n in (
+            "q_batch_stride", "k_batch_stride", "v_batch_stride", "knew_batch_stride", "vnew_batch_stride",
+            "o_batch_stride",
+            "q_row_stride", "k_row_stride", "v_row_stride", "knew_row_stride", "vnew_row_stride", "o_row_stride",
+            "q_head_stride", "k_head_stride", "v_head_stride", "knew_head_stride", "vnew_head_stride",
+            "o_head_stride",
+            "b", "h", "h_k", "d", "d_rounded", "seqlen_knew")]
+        + [("softmax_scale", C.c_float)]
+        + [(n, C.c_int64) for n in ("seqlen_q", "seqlen_k", "seqlen_q_rounded", "seqlen_k_rounded",
+                                    "window_size_left", "window_size_right")]
+    )
+
+
 _vp, _i64, _int, _sz = C.c_void_p, C.c_int64, C.c_int, C.c_size_t
 
 # symbol -> (restype, argtypes); every symbol include/b200_kernels.h declares
@@ -52,6 +67,8 @@ SIGNATURES = {
     "b200_permute": (_int, [_int, _vp, _vp, _int, C.POINTER(_i64), C.POINTER(_i64), _vp]),
     "b200_flash_attn_fwd": (_int, [_int, _vp, _vp, _vp, _vp, _vp, C.POINTER(FlashAttnParams), _vp]),
     "b200_flash_attn_bwd": (_int, [_int] + [_vp] * 11 + [C.POINTER(FlashAttnParams), _vp]),
+    "b200_flash_attn_kvcache_workspace_bytes": (_i64, [C.POINTER(FlashKvCacheParams)]),
+    "b200_flash_attn_kvcache": (_int, [_int] + [_vp] * 8 + [C.POINTER(FlashKvCacheParams), _vp, _sz, _vp]),
 }
 # tuning doors that pick a code path explicitly (0 = automatic); not in the header
 EXTRA = {

@@ -2,9 +2,9 @@
 // library (external_libs/runtime/flash_attn/lib/flash_api.h:75-82), backed by the
 // sm_100a kernels.  The custom-call ABI is
 //     void f(void **tensors, void *extra_args, cudaStream_t stream)
-// where extra_args is the packed attribute blob of the byre.custom op: 25 fields,
-// integers as int64 and floats as float32, unaligned, in the order listed in
-// flash_api.cu:588-624.  The ABI has no return value and carries no element type:
+// where extra_args is the packed attribute blob of the byre.custom op (25 fields for
+// fwd and bwd, flash_api.cu:588-624; 31 for the kv-cache entry, flash_api.cu:729-776),
+// integers as int64 and floats as float32, unaligned.  The ABI has no return value and carries no element type:
 // the reference library assumes fp16; `_bf16` siblings of the entry points do the
 // same with bf16 operands.  A failed call leaves a code that
 // b200_custom_last_error() returns (and clears).
@@ -89,6 +89,49 @@ void Bwd(int dtype, void **tensors, void *extra_args, cudaStream_t stream) {
     g_last_error = rc;
 }
 
+void KvCache(int dtype, void **tensors, void *extra_args, cudaStream_t stream) {
+  // tensors: q, kcache, vcache, knew, vnew, seqlens_k, out, softmax_lse; 31 packed fields
+  // (flash_api.cu:727-811)
+  Reader r{static_cast<const char *>(extra_args)};
+  b200_flash_kvcache_params p;
+  p.q_batch_stride = r.Int();
+  p.k_batch_stride = r.Int();
+  p.v_batch_stride = r.Int();
+  p.knew_batch_stride = r.Int();
+  p.vnew_batch_stride = r.Int();
+  p.o_batch_stride = r.Int();
+  p.q_row_stride = r.Int();
+  p.k_row_stride = r.Int();
+  p.v_row_stride = r.Int();
+  p.knew_row_stride = r.Int();
+  p.vnew_row_stride = r.Int();
+  p.o_row_stride = r.Int();
+  p.q_head_stride = r.Int();
+  p.k_head_stride = r.Int();
+  p.v_head_stride = r.Int();
+  p.knew_head_stride = r.Int();
+  p.vnew_head_stride = r.Int();
+  p.o_head_stride = r.Int();
+  p.b = r.Int();
+  p.h = r.Int();
+  p.h_k = r.Int();
+  p.d = r.Int();
+  p.d_rounded = r.Int();
+  p.seqlen_knew = r.Int();
+  p.softmax_scale = r.Float();
+  p.seqlen_q = r.Int();
+  p.seqlen_k = r.Int();
+  p.seqlen_q_rounded = r.Int();
+  p.seqlen_k_rounded = r.Int();
+  p.window_size_left = (int32_t)(uint32_t)r.Int();
+  p.window_size_right = (int32_t)(uint32_t)r.Int();
+  const int rc = b200_flash_attn_kvcache(dtype, tensors[0], tensors[1], tensors[2], tensors[3], tensors[4],
+                                         static_cast<const int32_t *>(tensors[5]), tensors[6],
+                                         static_cast<float *>(tensors[7]), &p, nullptr, 0, stream);
+  if (rc)
+    g_last_error = rc;
+}
+
 } // namespace
 
 extern "C" {
@@ -108,10 +151,12 @@ void run_flash_attn_fwd_bf16(void **tensors, void *extra_args, cudaStream_t stre
 void run_flash_attn_bwd_bf16(void **tensors, void *extra_args, cudaStream_t stream) {
   Bwd(B200_BF16, tensors, extra_args, stream);
 }
-// the kv-cache decode entry point exists so that dlsym succeeds; it is not
-// implemented and reports B200_ERR_UNSUPPORTED
-void run_flash_attn_kvcache(void **, void *, cudaStream_t) { g_last_error = B200_ERR_UNSUPPORTED; }
-void run_flash_attn_kvcache_bf16(void **, void *, cudaStream_t) { g_last_error = B200_ERR_UNSUPPORTED; }
+void run_flash_attn_kvcache(void **tensors, void *extra_args, cudaStream_t stream) {
+  KvCache(B200_F16, tensors, extra_args, stream);
+}
+void run_flash_attn_kvcache_bf16(void **tensors, void *extra_args, cudaStream_t stream) {
+  KvCache(B200_BF16, tensors, extra_args, stream);
+}
 
 int b200_custom_last_error(void) {
   const int e = g_last_error;

@@ -1,0 +1,478 @@
+// Attention over a key/value cache (decode): the kernel behind run_flash_attn_kvcache
+// (reference: external_libs/runtime/flash_attn/lib/flash_api.cu:434-566,727-811; the
+// kernel it dispatches is lib/flash_fwd_kernel.h:474-1060, lengths per batch entry from
+// lib/block_info.h:11-41).
+//
+// Per batch entry b:  cache_len = seqlens_k[b];  the new rows knew/vnew are appended to
+// the cache at [cache_len, cache_len + seqlen_knew);  then every query row attends to the
+// first len = cache_len + seqlen_knew rows, the mask aligned to the END of the keys: query
+// i sees key j iff  j <= i + (len - seqlen_q) + window_right  and
+// j >= i + (len - seqlen_q) - window_left, a negative window being unbounded.  Blocks read
+// the new rows from knew/vnew, so none waits for another's append.
+//
+// The work is a stream over the cache: 4*d bytes per key against 4*d flops per key and
+// query row, so with the few query rows of a decode step it is bound by HBM.  The
+// reference runs one block per (batch, head) (num_splits = 1), which leaves most of a
+// B200 idle when batch * heads < 148; here the keys of one (batch, kv head) are split
+// over enough blocks to fill the GPU and a second small kernel merges the partial
+// results.  All query heads that share a kv head are rows of the same block, so a grouped
+// cache is read once per row chunk.
+//
+// Thread mapping: a key row of d 16-bit values is read by LPK = pow2(d / 8) lanes, 16
+// bytes each, so a warp takes 32 / LPK keys per step and the 8 warps of a block
+// 8 * 32 / LPK.  Every lane group keeps a running (max, sum, output slice) per query
+// row in registers, rescaled only when the maximum grows; groups are merged by shuffles,
+// warps through shared memory, splits by the merge kernel.
+#include "common.cuh"
+
+#include <algorithm>
+#include <cmath>
+
+namespace b200 {
+namespace {
+
+constexpr int kDecodeWarps = 8;
+constexpr int kDecodeThreads = kDecodeWarps * 32;
+constexpr int kMaxSplits = 128;
+constexpr float kLog2e = 1.4426950408889634f;
+constexpr float kLn2 = 0.6931471805599453f;
+
+struct DecodeParams {
+  const void *q;
+  void *kcache, *vcache;
+  const void *knew, *vnew;
+  const int *seqlens_k;
+  void *o;
+  float *lse;
+  float *part_o;  // [rows][splits][d]   (rows = b * h * seqlen_q), only when splits > 1
+  float *part_ml; // [rows][splits][2]   running maximum (log2 units) and sum
+  int64_t q_bs, k_bs, v_bs, kn_bs, vn_bs, o_bs;
+  int64_t q_rs, k_rs, v_rs, kn_rs, vn_rs, o_rs;
+  int64_t q_hs, k_hs, v_hs, kn_hs, vn_hs, o_hs;
+  int b, h, h_k, d, group;
+  int seqlen_q, seqlen_k, seqlen_knew;
+  int window_left, window_right;
+  int splits, chunks, rows_per_kv; // rows_per_kv = seqlen_q * group
+  float scale_log2;
+};
+
+template <bool kBF16> __device__ __forceinline__ void unpack8(const uint4 &raw, float (&f)[8]) {
+  const uint32_t w[4] = {raw.x, raw.y, raw.z, raw.w};
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    if constexpr (kBF16) {
+      f[2 * i] = __uint_as_float(w[i] << 16);
+      f[2 * i + 1] = __uint_as_float(w[i] & 0xffff0000u);
+    } else {
+      const float2 t = __half22float2(*reinterpret_cast<const __half2 *>(&w[i]));
+      f[2 * i] = t.x;
+      f[2 * i + 1] = t.y;
+    }
+  }
+}
+
+// 2^(a - b) for running maxima, where "nothing seen yet" is -inf on either side
+__device__ __forceinline__ float scale_of(float m, float m_new) {
+  return m == -INFINITY ? 0.f : exp2f(m - m_new);
+}
+
+template <int LPK, int RC, bool kBF16>
+__global__ void __launch_bounds__(kDecodeThreads) decode_split_kernel(const DecodeParams p) {
+  using T = typename std::conditional<kBF16, __nv_bfloat16, __half>::type;
+  constexpr int KPW = 32 / LPK;             // keys per warp step
+  constexpr int KPB = KPW * kDecodeWarps;   // keys per block step
+  constexpr int kDPad = LPK * 8;
+  __shared__ float sm_acc[kDecodeWarps][RC][kDPad];
+  __shared__ float sm_m[kDecodeWarps][RC], sm_l[kDecodeWarps][RC];
+
+  const int split = blockIdx.x;
+  const int chunk = blockIdx.y % p.chunks, hk = blockIdx.y / p.chunks;
+  const int b = blockIdx.z;
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  const int sub = lane % LPK, kslot = warp * KPW + lane / LPK;
+  const int e0 = sub * 8;
+  const bool active = e0 < p.d;
+
+  // lengths of this batch entry; a cache that would overflow keeps what fits
+  const int n_new = p.knew ? p.seqlen_knew : 0;
+  int cache_len = p.seqlens_k ? p.seqlens_k[b] : p.seqlen_k;
+  cache_len = max(0, min(cache_len, p.seqlen_k));
+  const int len = min(cache_len + n_new, p.seqlen_k);
+  const int shift = len - p.seqlen_q;
+
+  // the query rows of this block: row r = i * group + g  (query position i, head hk*group + g)
+  const int r0 = chunk * RC;
+  int qi[RC];
+  bool valid[RC];
+  float qf[RC][8];
+  const T *qb = static_cast<const T *>(p.q) + (int64_t)b * p.q_bs;
+#pragma unroll
+  for (int t = 0; t < RC; ++t) {
+    const int r = r0 + t;
+    valid[t] = r < p.rows_per_kv;
+    qi[t] = valid[t] ? r / p.group : 0;
+    const int head = hk * p.group + (valid[t] ? r % p.group : 0);
+    uint4 raw = make_uint4(0, 0, 0, 0);
+    if (valid[t] && active)
+      raw = ld_nc_v4(qb + (int64_t)qi[t] * p.q_rs + (int64_t)head * p.q_hs + e0);
+    unpack8<kBF16>(raw, qf[t]);
+  }
+
+  // keys any row of this block can see, cut into `splits` ranges of whole block steps
+  const int i_min = r0 / p.group;
+  const int i_max = min(r0 + RC - 1, p.rows_per_kv - 1) / p.group;
+  const int lo = p.window_left >= 0 ? max(0, i_min + shift - p.window_left) : 0;
+  const int hi = p.window_right >= 0 ? min(len, i_max + shift + p.window_right + 1) : len;
+  const int span = max(hi - lo, 0);
+  int per = (span + p.splits - 1) / p.splits;
+  per = (per + KPB - 1) / KPB * KPB;
+  const int j_begin = lo + split * per;
+  const int j_end = min(hi, j_begin + per);
+
+  float m[RC], l[RC], acc[RC][8];
+#pragma unroll
+  for (int t = 0; t < RC; ++t) {
+    m[t] = -INFINITY;
+    l[t] = 0.f;
+#pragma unroll
+    for (int e = 0; e < 8; ++e)
+      acc[t][e] = 0.f;
+  }
+
+  T *kc = static_cast<T *>(p.kcache) + (int64_t)b * p.k_bs + (int64_t)hk * p.k_hs + e0;
+  T *vc = static_cast<T *>(p.vcache) + (int64_t)b * p.v_bs + (int64_t)hk * p.v_hs + e0;
+  const T *kn = static_cast<const T *>(p.knew) + (int64_t)b * p.kn_bs + (int64_t)hk * p.kn_hs + e0;
+  const T *vn = static_cast<const T *>(p.vnew) + (int64_t)b * p.vn_bs + (int64_t)hk * p.vn_hs + e0;
+
+  // append: the blocks of the first row chunk copy the new rows into the cache, all of them,
+  // also those no query row of this block can see
+  if (chunk == 0 && active) {
+    for (int jn = split * KPB + kslot; jn < len - cache_len; jn += p.splits * KPB) {
+      *reinterpret_cast<uint4 *>(kc + (int64_t)(cache_len + jn) * p.k_rs) = ld_nc_v4(kn + (int64_t)jn * p.kn_rs);
+      *reinterpret_cast<uint4 *>(vc + (int64_t)(cache_len + jn) * p.v_rs) = ld_nc_v4(vn + (int64_t)jn * p.vn_rs);
+    }
+  }
+
+  for (int j0 = j_begin; j0 < j_end; j0 += KPB) {
+    const int j = j0 + kslot;
+    const bool have = j < j_end;
+    uint4 kraw = make_uint4(0, 0, 0, 0), vraw = make_uint4(0, 0, 0, 0);
+    if (have && active) {
+      if (j < cache_len) {
+        kraw = ld_nc_v4(kc + (int64_t)j * p.k_rs);
+        vraw = ld_nc_v4(vc + (int64_t)j * p.v_rs);
+      } else { // a new row: read where it comes from, whether or not it is in the cache yet
+        kraw = ld_nc_v4(kn + (int64_t)(j - cache_len) * p.kn_rs);
+        vraw = ld_nc_v4(vn + (int64_t)(j - cache_len) * p.vn_rs);
+      }
+    }
+    float kf[8], vf[8];
+    unpack8<kBF16>(kraw, kf);
+    unpack8<kBF16>(vraw, vf);
+#pragma unroll
+    for (int t = 0; t < RC; ++t) {
+      float s = 0.f;
+#pragma unroll
+      for (int e = 0; e < 8; ++e)
+        s = fmaf(qf[t][e], kf[e], s);
+#pragma unroll
+      for (int o = LPK / 2; o > 0; o >>= 1)
+        s += __shfl_xor_sync(0xffffffffu, s, o);
+      s *= p.scale_log2;
+      bool visible = have && valid[t];
+      if (p.window_right >= 0 && j > qi[t] + shift + p.window_right)
+        visible = false;
+      if (p.window_left >= 0 && j < qi[t] + shift - p.window_left)
+        visible = false;
+      if (visible) {
+        if (s > m[t]) { // the running maximum grows: rescale what was accumulated
+          const float alpha = scale_of(m[t], s);
+          l[t] *= alpha;
+#pragma unroll
+          for (int e = 0; e < 8; ++e)
+            acc[t][e] *= alpha;
+          m[t] = s;
+        }
+        const float pr = exp2f(s - m[t]);
+        l[t] += pr;
+#pragma unroll
+        for (int e = 0; e < 8; ++e)
+          acc[t][e] = fmaf(pr, vf[e], acc[t][e]);
+      }
+    }
+  }
+
+  // merge the lane groups of the warp
+#pragma unroll
+  for (int t = 0; t < RC; ++t) {
+#pragma unroll
+    for (int off = LPK; off < 32; off <<= 1) {
+      const float m_o = __shfl_xor_sync(0xffffffffu, m[t], off);
+      const float l_o = __shfl_xor_sync(0xffffffffu, l[t], off);
+      const float m_n = fmaxf(m[t], m_o);
+      const float a = scale_of(m[t], m_n), a_o = scale_of(m_o, m_n);
+      l[t] = l[t] * a + l_o * a_o;
+#pragma unroll
+      for (int e = 0; e < 8; ++e) {
+        const float other = __shfl_xor_sync(0xffffffffu, acc[t][e], off);
+        acc[t][e] = acc[t][e] * a + other * a_o;
+      }
+      m[t] = m_n;
+    }
+    if (lane < LPK) {
+#pragma unroll
+      for (int e = 0; e < 8; ++e)
+        sm_acc[warp][t][e0 + e] = acc[t][e];
+      if (lane == 0) {
+        sm_m[warp][t] = m[t];
+        sm_l[warp][t] = l[t];
+      }
+    }
+  }
+  __syncthreads();
+
+  // merge the warps; one thread per (row, element)
+  for (int idx = threadIdx.x; idx < RC * p.d; idx += kDecodeThreads) {
+    const int t = idx / p.d, e = idx % p.d;
+    const int r = r0 + t;
+    if (r >= p.rows_per_kv)
+      continue;
+    float mx = -INFINITY;
+#pragma unroll
+    for (int w = 0; w < kDecodeWarps; ++w)
+      mx = fmaxf(mx, sm_m[w][t]);
+    float sum = 0.f, val = 0.f;
+#pragma unroll
+    for (int w = 0; w < kDecodeWarps; ++w) {
+      const float a = scale_of(sm_m[w][t], mx);
+      sum += sm_l[w][t] * a;
+      val += sm_acc[w][t][e] * a;
+    }
+    const int i = r / p.group, head = hk * p.group + r % p.group;
+    const int64_t row = ((int64_t)b * p.h + head) * p.seqlen_q + i;
+    if (p.splits == 1) {
+      T *op = static_cast<T *>(p.o) + (int64_t)b * p.o_bs + (int64_t)i * p.o_rs + (int64_t)head * p.o_hs;
+      op[e] = Elt<T>::from_f32(sum > 0.f ? val / sum : 0.f);
+      if (e == 0) // a row that sees no key: output 0, LSE +inf, as the reference's kernel leaves it
+        p.lse[row] = sum > 0.f ? mx * kLn2 + logf(sum) : INFINITY;
+    } else {
+      const int64_t slot = row * p.splits + split;
+      p.part_o[slot * p.d + e] = val;
+      if (e == 0) {
+        p.part_ml[slot * 2] = mx;
+        p.part_ml[slot * 2 + 1] = sum;
+      }
+    }
+  }
+}
+
+// one block per query row: merges the partial results of the splits
+template <bool kBF16>
+__global__ void __launch_bounds__(128) decode_merge_kernel(const DecodeParams p) {
+  using T = typename std::conditional<kBF16, __nv_bfloat16, __half>::type;
+  __shared__ float weight[kMaxSplits];
+  __shared__ float total;
+  const int64_t row = blockIdx.x;
+  const int i = (int)(row % p.seqlen_q);
+  const int head = (int)((row / p.seqlen_q) % p.h);
+  const int b = (int)(row / ((int64_t)p.seqlen_q * p.h));
+  const float *ml = p.part_ml + row * p.splits * 2;
+  float mx = -INFINITY;
+  for (int s = 0; s < p.splits; ++s)
+    mx = fmaxf(mx, ml[2 * s]);
+  if (threadIdx.x < 32) {
+    float sum = 0.f;
+    for (int s = threadIdx.x; s < p.splits; s += 32) {
+      const float a = scale_of(ml[2 * s], mx);
+      weight[s] = a;
+      sum += ml[2 * s + 1] * a;
+    }
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1)
+      sum += __shfl_xor_sync(0xffffffffu, sum, o);
+    if (threadIdx.x == 0) {
+      total = sum;
+      p.lse[row] = sum > 0.f ? mx * kLn2 + logf(sum) : INFINITY;
+    }
+  }
+  __syncthreads();
+  const float inv = total > 0.f ? 1.f / total : 0.f;
+  const float *po = p.part_o + row * p.splits * p.d;
+  T *op = static_cast<T *>(p.o) + (int64_t)b * p.o_bs + (int64_t)i * p.o_rs + (int64_t)head * p.o_hs;
+  for (int e = threadIdx.x; e < p.d; e += blockDim.x) {
+    float val = 0.f;
+    for (int s = 0; s < p.splits; ++s)
+      val = fmaf(po[(int64_t)s * p.d + e], weight[s], val);
+    op[e] = Elt<T>::from_f32(val * inv);
+  }
+}
+
+struct DecodePlan {
+  int lpk, rc, chunks, splits;
+  int64_t rows;
+  size_t workspace_bytes;
+};
+
+bool strides_ok(const b200_flash_kvcache_params &p) {
+  const int64_t s[] = {p.q_batch_stride,  p.k_batch_stride,    p.v_batch_stride,    p.knew_batch_stride,
+                       p.vnew_batch_stride, p.o_batch_stride,  p.q_row_stride,      p.k_row_stride,
+                       p.v_row_stride,    p.knew_row_stride,   p.vnew_row_stride,   p.o_row_stride,
+                       p.q_head_stride,   p.k_head_stride,     p.v_head_stride,     p.knew_head_stride,
+                       p.vnew_head_stride, p.o_head_stride};
+  for (int64_t v : s)
+    if (v < 0)
+      return false;
+  return true;
+}
+
+// a pure function of the shapes, so the workspace size is known without a device
+int make_plan(const b200_flash_kvcache_params &p, DecodePlan *plan) {
+  if (p.b <= 0 || p.h <= 0 || p.h_k <= 0 || p.h % p.h_k != 0 || p.seqlen_q <= 0 || p.seqlen_k <= 0 || p.seqlen_knew < 0)
+    return B200_ERR_INVALID_ARG;
+  if (p.d <= 0 || p.d > 256 || p.d % 8 != 0)
+    return B200_ERR_UNSUPPORTED;
+  if (!strides_ok(p))
+    return B200_ERR_INVALID_ARG;
+  const int64_t group = p.h / p.h_k;
+  const int64_t rows_per_kv = p.seqlen_q * group;
+  plan->lpk = std::max(4, pow2_ceil(p.d / 8));
+  plan->rc = rows_per_kv >= 4 ? 4 : (rows_per_kv >= 2 ? 2 : 1);
+  plan->chunks = (int)ceil_div<int64_t>(rows_per_kv, plan->rc);
+  if ((int64_t)plan->chunks * p.h_k > 65535 || p.b > 65535)
+    return B200_ERR_UNSUPPORTED;
+  const int64_t keys_per_step = (int64_t)kDecodeWarps * 32 / plan->lpk;
+  const int64_t base = p.b * p.h_k * plan->chunks;
+  // enough blocks for four per SM, as long as every split keeps four block steps of keys
+  const int64_t want = ceil_div<int64_t>((int64_t)kNumSMs * 4, base);
+  const int64_t room = std::max<int64_t>(1, p.seqlen_k / (4 * keys_per_step));
+  plan->splits = (int)std::max<int64_t>(1, std::min<int64_t>({want, room, (int64_t)kMaxSplits}));
+  plan->rows = p.b * p.h * p.seqlen_q;
+  plan->workspace_bytes =
+      plan->splits > 1 ? (size_t)plan->rows * plan->splits * ((size_t)p.d + 2) * sizeof(float) : 0;
+  return B200_OK;
+}
+
+template <int LPK, bool kBF16> int launch_split(const DecodeParams &dp, int rc, dim3 grid, cudaStream_t stream) {
+  switch (rc) {
+  case 1:
+    decode_split_kernel<LPK, 1, kBF16><<<grid, kDecodeThreads, 0, stream>>>(dp);
+    break;
+  case 2:
+    decode_split_kernel<LPK, 2, kBF16><<<grid, kDecodeThreads, 0, stream>>>(dp);
+    break;
+  default:
+    decode_split_kernel<LPK, 4, kBF16><<<grid, kDecodeThreads, 0, stream>>>(dp);
+  }
+  return check_launch();
+}
+
+template <bool kBF16> int launch_decode(const DecodeParams &dp, const DecodePlan &plan, cudaStream_t stream) {
+  const dim3 grid((unsigned)plan.splits, (unsigned)(plan.chunks * dp.h_k), (unsigned)dp.b);
+  int rc;
+  switch (plan.lpk) {
+  case 4:
+    rc = launch_split<4, kBF16>(dp, plan.rc, grid, stream);
+    break;
+  case 8:
+    rc = launch_split<8, kBF16>(dp, plan.rc, grid, stream);
+    break;
+  case 16:
+    rc = launch_split<16, kBF16>(dp, plan.rc, grid, stream);
+    break;
+  default:
+    rc = launch_split<32, kBF16>(dp, plan.rc, grid, stream);
+  }
+  if (rc != B200_OK || plan.splits == 1)
+    return rc;
+  decode_merge_kernel<kBF16><<<(unsigned)plan.rows, 128, 0, stream>>>(dp);
+  return check_launch();
+}
+
+} // namespace
+} // namespace b200
+
+using namespace b200;
+
+extern "C" int64_t b200_flash_attn_kvcache_workspace_bytes(const b200_flash_kvcache_params *params) {
+  DecodePlan plan;
+  if (!params || make_plan(*params, &plan) != B200_OK)
+    return -1;
+  return (int64_t)plan.workspace_bytes;
+}
+
+extern "C" int b200_flash_attn_kvcache(int dtype, const void *q, void *kcache, void *vcache, const void *knew,
+                                       const void *vnew, const int32_t *seqlens_k, void *out, float *softmax_lse,
+                                       const b200_flash_kvcache_params *params, void *workspace,
+                                       size_t workspace_bytes, cudaStream_t stream) {
+  if (!params || !q || !kcache || !vcache || !out || !softmax_lse)
+    return B200_ERR_INVALID_ARG;
+  if (dtype != B200_F16 && dtype != B200_BF16)
+    return B200_ERR_UNSUPPORTED;
+  const b200_flash_kvcache_params &p = *params;
+  DecodePlan plan;
+  if (int rc = make_plan(p, &plan))
+    return rc;
+  const bool has_new = knew != nullptr && vnew != nullptr && p.seqlen_knew > 0;
+  if ((knew != nullptr) != (vnew != nullptr))
+    return B200_ERR_INVALID_ARG;
+  // rows are read and written as 16-byte vectors
+  const int64_t vec_strides[] = {p.q_batch_stride, p.q_row_stride, p.q_head_stride, p.k_batch_stride, p.k_row_stride,
+                                 p.k_head_stride,  p.v_batch_stride, p.v_row_stride, p.v_head_stride};
+  for (int64_t s : vec_strides)
+    if (s % 8 != 0)
+      return B200_ERR_ALIGNMENT;
+  if (!aligned16(q) || !aligned16(kcache) || !aligned16(vcache))
+    return B200_ERR_ALIGNMENT;
+  if (has_new) {
+    const int64_t new_strides[] = {p.knew_batch_stride, p.knew_row_stride, p.knew_head_stride,
+                                   p.vnew_batch_stride, p.vnew_row_stride, p.vnew_head_stride};
+    for (int64_t s : new_strides)
+      if (s % 8 != 0)
+        return B200_ERR_ALIGNMENT;
+    if (!aligned16(knew) || !aligned16(vnew))
+      return B200_ERR_ALIGNMENT;
+  }
+  if (reinterpret_cast<uintptr_t>(out) % 2 != 0 || reinterpret_cast<uintptr_t>(softmax_lse) % 4 != 0)
+    return B200_ERR_ALIGNMENT;
+
+  DecodeParams dp{};
+  dp.q = q;
+  dp.kcache = kcache;
+  dp.vcache = vcache;
+  dp.knew = has_new ? knew : nullptr;
+  dp.vnew = has_new ? vnew : nullptr;
+  dp.seqlens_k = seqlens_k;
+  dp.o = out;
+  dp.lse = softmax_lse;
+  dp.q_bs = p.q_batch_stride, dp.k_bs = p.k_batch_stride, dp.v_bs = p.v_batch_stride;
+  dp.kn_bs = p.knew_batch_stride, dp.vn_bs = p.vnew_batch_stride, dp.o_bs = p.o_batch_stride;
+  dp.q_rs = p.q_row_stride, dp.k_rs = p.k_row_stride, dp.v_rs = p.v_row_stride;
+  dp.kn_rs = p.knew_row_stride, dp.vn_rs = p.vnew_row_stride, dp.o_rs = p.o_row_stride;
+  dp.q_hs = p.q_head_stride, dp.k_hs = p.k_head_stride, dp.v_hs = p.v_head_stride;
+  dp.kn_hs = p.knew_head_stride, dp.vn_hs = p.vnew_head_stride, dp.o_hs = p.o_head_stride;
+  dp.b = (int)p.b, dp.h = (int)p.h, dp.h_k = (int)p.h_k, dp.d = (int)p.d, dp.group = (int)(p.h / p.h_k);
+  dp.seqlen_q = (int)p.seqlen_q, dp.seqlen_k = (int)p.seqlen_k, dp.seqlen_knew = has_new ? (int)p.seqlen_knew : 0;
+  dp.window_left = (int)p.window_size_left, dp.window_right = (int)p.window_size_right;
+  dp.splits = plan.splits, dp.chunks = plan.chunks, dp.rows_per_kv = (int)(p.seqlen_q * (p.h / p.h_k));
+  dp.scale_log2 = p.softmax_scale * kLog2e;
+
+  void *owned = nullptr;
+  if (plan.workspace_bytes > 0) {
+    if (workspace) {
+      if (workspace_bytes < plan.workspace_bytes || !aligned16(workspace))
+        return B200_ERR_WORKSPACE;
+    } else { // the custom-call ABI has no workspace operand: take it from the stream's pool
+      if (int rc = check_cuda(cudaMallocAsync(&owned, plan.workspace_bytes, stream)))
+        return rc;
+      workspace = owned;
+    }
+    dp.part_o = static_cast<float *>(workspace);
+    dp.part_ml = dp.part_o + (size_t)plan.rows * plan.splits * (size_t)p.d;
+  }
+  const int rc = dtype == B200_BF16 ? launch_decode<true>(dp, plan, stream) : launch_decode<false>(dp, plan, stream);
+  if (owned) {
+    const int rc_free = check_cuda(cudaFreeAsync(owned, stream));
+    return rc != B200_OK ? rc : rc_free;
+  }
+  return rc;
+}

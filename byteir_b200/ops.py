@@ -246,6 +246,52 @@ def flash_attn_bwd(dout, q, k, v, out, lse, softmax_scale, causal=True, window=(
     return dq, dk, dv
 
 
+def kvcache_params(q, kcache, vcache, knew, vnew, out, softmax_scale, causal=True, window=(-1, -1)):
+    """The packed arguments of run_flash_attn_kvcache for tensors laid out [B, S, H, D]."""
+    p = N.FlashKvCacheParams()
+    for name, t in (("q", q), ("k", kcache), ("v", vcache), ("knew", knew), ("vnew", vnew), ("o", out)):
+        bs, rs, hs = (t.stride(0), t.stride(1), t.stride(2)) if t is not None else (0, 0, 0)
+        setattr(p, name + "_batch_stride", bs)
+        setattr(p, name + "_row_stride", rs)
+        setattr(p, name + "_head_stride", hs)
+    p.b, p.seqlen_q, p.h, p.d = q.shape
+    p.seqlen_k, p.h_k = kcache.shape[1], kcache.shape[2]
+    p.seqlen_knew = knew.shape[1] if knew is not None else 0
+    p.d_rounded = (p.d + 31) // 32 * 32
+    p.seqlen_q_rounded = (p.seqlen_q + 127) // 128 * 128
+    p.seqlen_k_rounded = (p.seqlen_k + 127) // 128 * 128
+    p.softmax_scale = softmax_scale
+    p.window_size_left = window[0]
+    p.window_size_right = 0 if causal else window[1]
+    return p
+
+
+def flash_attn_kvcache(q, kcache, vcache, knew=None, vnew=None, seqlens_k=None, softmax_scale=None,
+                       causal=True, window=(-1, -1), out=None, lse=None, workspace=None):
+    """One decode step: append knew/vnew [B, S_new, H_k, D] to the caches [B, S_max, H_k, D] at row
+    seqlens_k[b] (i32 [B]; None = the cache is full and nothing is appended) and attend q [B, Sq, H, D]
+    to the rows in use.  The caches are updated in place.  Returns (out, softmax_lse[B, H, Sq])."""
+    for t in (q, kcache, vcache, knew, vnew):
+        if t is not None and (not t.is_cuda or t.stride(-1) != 1):
+            raise ValueError("tensors must be CUDA tensors with a contiguous last dim")
+    if seqlens_k is not None and (seqlens_k.dtype != torch.int32 or not seqlens_k.is_contiguous()):
+        raise ValueError("seqlens_k must be a contiguous int32 tensor")
+    if softmax_scale is None:
+        softmax_scale = q.shape[-1] ** -0.5
+    if out is None:
+        out = torch.empty_like(q)
+    if lse is None:
+        lse = torch.empty((q.shape[0], q.shape[2], q.shape[1]), dtype=torch.float32, device=q.device)
+    p = kvcache_params(q, kcache, vcache, knew, vnew, out, softmax_scale, causal, window)
+    ptr = lambda t: t.data_ptr() if t is not None else None
+    rc = N.lib().b200_flash_attn_kvcache(_dt(q), q.data_ptr(), kcache.data_ptr(), vcache.data_ptr(), ptr(knew),
+                                         ptr(vnew), ptr(seqlens_k), out.data_ptr(), lse.data_ptr(), C.byref(p),
+                                         ptr(workspace), workspace.numel() * workspace.element_size()
+                                         if workspace is not None else 0, _stream())
+    N.check(rc, "b200_flash_attn_kvcache")
+    return out, lse
+
+
 class ShardedSum:
     """Exchange step of a sum whose reduced axis is sharded over ranks (one kernel over NVLink peer
     memory instead of all-reduce + cast).  `peer_inbox` / `peer_flags`: device addresses per rank of

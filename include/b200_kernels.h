@@ -202,6 +202,34 @@ int b200_flash_attn_bwd(int dtype, const void *dout, const void *q,
                         const b200_flash_attn_params *params,
                         cudaStream_t stream);
 
+/* Attention over a key/value cache (decode): the typed door behind
+ * run_flash_attn_kvcache (flash_api.h:75-82, unpacking flash_api.cu:727-811, setup
+ * flash_api.cu:434-566).  q, out: [B, seqlen_q, H, D]; kcache, vcache:
+ * [B, seqlen_k, H_k, D] (seqlen_k = capacity of the cache); knew, vnew:
+ * [B, seqlen_knew, H_k, D] or NULL; seqlens_k: i32 [B], rows of the cache in use
+ * (NULL = all of it); softmax_lse: f32 [B, H, seqlen_q].  Per batch entry the new rows
+ * are written into the cache at seqlens_k[b] and the queries attend to the first
+ * seqlens_k[b] + seqlen_knew rows, the mask aligned to the end of the keys; new rows
+ * that would not fit the cache are dropped.  D is a multiple of 8, at most 256.
+ * workspace: scratch of b200_flash_attn_kvcache_workspace_bytes(params) bytes, or NULL
+ * to take it from the stream's memory pool for the duration of the call. */
+typedef struct {
+  int64_t q_batch_stride, k_batch_stride, v_batch_stride, knew_batch_stride, vnew_batch_stride, o_batch_stride;
+  int64_t q_row_stride, k_row_stride, v_row_stride, knew_row_stride, vnew_row_stride, o_row_stride;
+  int64_t q_head_stride, k_head_stride, v_head_stride, knew_head_stride, vnew_head_stride, o_head_stride;
+  int64_t b, h, h_k, d, d_rounded, seqlen_knew;
+  float softmax_scale;
+  int64_t seqlen_q, seqlen_k, seqlen_q_rounded, seqlen_k_rounded;
+  int64_t window_size_left, window_size_right;
+} b200_flash_kvcache_params;
+
+int64_t b200_flash_attn_kvcache_workspace_bytes(const b200_flash_kvcache_params *params);
+int b200_flash_attn_kvcache(int dtype, const void *q, void *kcache, void *vcache,
+                            const void *knew, const void *vnew, const int32_t *seqlens_k,
+                            void *out, float *softmax_lse,
+                            const b200_flash_kvcache_params *params, void *workspace,
+                            size_t workspace_bytes, cudaStream_t stream);
+
 #ifdef __cplusplus
 }
 #endif

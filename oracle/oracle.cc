@@ -637,6 +637,70 @@ int oracle_flash_attn_bwd(int dtype, const void *dout, const void *q,
   return 0;
 }
 
+// ---------------------------------------------------------------------------
+// Flash attention over a key/value cache (one decode step).  Argument meaning
+// follows run_flash_attn_kvcache (lib/flash_api.cu:434-566,727-811): kcache,
+// vcache are [B, seqlen_k, H_k, D] with seqlen_k the capacity, knew/vnew are
+// [B, seqlen_knew, H_k, D] (or null), seqlens_k[b] is the number of cache rows
+// in use (null = seqlen_k).  Per batch entry (lib/block_info.h:27-41):
+//   cache_len = seqlens_k[b];  len = cache_len + seqlen_knew;
+//   kcache[b, cache_len:len] = knew[b];  vcache likewise
+//   (lib/flash_fwd_kernel.h:660-740);
+//   then the forward pass above over the first `len` rows of the cache, the
+//   mask aligned to the end of those rows.
+// New rows that would not fit the cache are dropped (the reference would write
+// out of bounds).
+// ---------------------------------------------------------------------------
+struct OracleKvNewStrides {
+  int64_t knew_batch_stride, vnew_batch_stride;
+  int64_t knew_row_stride, vnew_row_stride;
+  int64_t knew_head_stride, vnew_head_stride;
+  int64_t seqlen_knew;
+};
+
+int oracle_flash_attn_kvcache(int dtype, const void *q, void *kcache,
+                              void *vcache, const void *knew, const void *vnew,
+                              const int32_t *seqlens_k, void *o, float *lse,
+                              const OracleAttnParams *pp,
+                              const OracleKvNewStrides *nn) {
+  if (dtype != kF16 && dtype != kBF16)
+    return -1;
+  const OracleAttnParams p = *pp;
+  const OracleKvNewStrides n = *nn;
+  uint16_t *kc = static_cast<uint16_t *>(kcache);
+  uint16_t *vc = static_cast<uint16_t *>(vcache);
+  const uint16_t *kn = static_cast<const uint16_t *>(knew);
+  const uint16_t *vn = static_cast<const uint16_t *>(vnew);
+  const int64_t n_new = (kn && vn) ? n.seqlen_knew : 0;
+  for (int64_t b = 0; b < p.b; ++b) {
+    int64_t cache_len = seqlens_k ? seqlens_k[b] : p.seqlen_k;
+    cache_len = std::max<int64_t>(0, std::min<int64_t>(cache_len, p.seqlen_k));
+    const int64_t len = std::min<int64_t>(cache_len + n_new, p.seqlen_k);
+    for (int64_t j = cache_len; j < len; ++j)
+      for (int64_t hk = 0; hk < p.h_k; ++hk)
+        for (int64_t t = 0; t < p.d; ++t) {
+          kc[b * p.k_batch_stride + j * p.k_row_stride + hk * p.k_head_stride + t] =
+              kn[b * n.knew_batch_stride + (j - cache_len) * n.knew_row_stride +
+                 hk * n.knew_head_stride + t];
+          vc[b * p.v_batch_stride + j * p.v_row_stride + hk * p.v_head_stride + t] =
+              vn[b * n.vnew_batch_stride + (j - cache_len) * n.vnew_row_stride +
+                 hk * n.vnew_head_stride + t];
+        }
+    // one batch entry at a time: its own key count
+    OracleAttnParams one = p;
+    one.b = 1;
+    one.seqlen_k = len;
+    const int rc = oracle_flash_attn_fwd(
+        dtype, static_cast<const uint16_t *>(q) + b * p.q_batch_stride,
+        kc + b * p.k_batch_stride, vc + b * p.v_batch_stride,
+        static_cast<uint16_t *>(o) + b * p.o_batch_stride,
+        lse + b * p.h * p.seqlen_q, &one, 0);
+    if (rc)
+      return rc;
+  }
+  return 0;
+}
+
 // Storage-type conversions exposed for the tests (round to nearest even).
 void oracle_f32_to_f16(const float *in, uint16_t *out, int64_t n) {
   for (int64_t i = 0; i < n; ++i)

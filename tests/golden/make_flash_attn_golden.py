@@ -8,6 +8,11 @@ softmax scale 0.5.  The reference's own tests round these values to fp16 and
 demand a bit-exact match (runtime/test/backends/cuda/providers/default/kernel/
 flash_attn_fwd_test.cc:142), so fp16 is a lossless container for them.
 
+The kv-cache vectors (flash_attn_kvcache_*.data, same generator script, lines 56-105)
+go to a second file: b=2, cache of 128 rows with 64 in use, one new row, heads=3,
+head_dim=32, fp16, scale 0.5; inputs q/k/v/kcache/vcache/cache_seqlens, outputs out
+and the two updated caches.
+
 Run where a checkout of the reference is at hand:
     python tests/golden/make_flash_attn_golden.py <path to the byteir checkout>
 """
@@ -29,8 +34,39 @@ NAMES = {
 }
 
 
+KV_NAMES = {  # key -> (file, shape)
+    "q": ("flash_attn_kvcache_inputs_q.data", (2, 1, 3, 32)),
+    "k": ("flash_attn_kvcache_inputs_k.data", (2, 1, 3, 32)),
+    "v": ("flash_attn_kvcache_inputs_v.data", (2, 1, 3, 32)),
+    "kcache": ("flash_attn_kvcache_inputs_kcache.data", (2, 128, 3, 32)),
+    "vcache": ("flash_attn_kvcache_inputs_vcache.data", (2, 128, 3, 32)),
+    "out": ("flash_attn_kvcache_outputs.data", (2, 1, 3, 32)),
+    "kcache_out": ("flash_attn_kvcache_outputs_kcache.data", (2, 128, 3, 32)),
+    "vcache_out": ("flash_attn_kvcache_outputs_vcache.data", (2, 128, 3, 32)),
+}
+
+
+def read_f16(path: Path, shape) -> np.ndarray:
+    vals = np.array(path.read_text().split(), dtype=np.float64)
+    assert vals.size == int(np.prod(shape)), (path.name, vals.size)
+    f16 = vals.astype(np.float16)
+    assert np.array_equal(f16.astype(np.float64), vals), path.name
+    return f16.reshape(shape)
+
+
+def kvcache(src: Path) -> None:
+    arrays = {key: read_f16(src / fname, shape) for key, (fname, shape) in KV_NAMES.items()}
+    lens = np.array((src / "flash_attn_kvcache_inputs_cache_seqlens.data").read_text().split(), dtype=np.int32)
+    assert lens.shape == (2,)
+    arrays["cache_seqlens"] = lens
+    out = Path(__file__).with_name("flash_attn_kvcache_b2_s128_h3_d32_f16.npz")
+    np.savez_compressed(out, **arrays)
+    print("wrote", out, out.stat().st_size, "bytes")
+
+
 def main(ref_root: str) -> None:
     src = Path(ref_root) / "runtime" / "test" / "test_files"
+    kvcache(src)
     arrays = {}
     for key, fname in NAMES.items():
         vals = np.array((src / fname).read_text().split(), dtype=np.float64)

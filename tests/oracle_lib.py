@@ -177,6 +177,39 @@ def flash_attn_fwd(q, k, v, scale, causal=True, round_p=False, window=(-1, -1)):
     return out, lse
 
 
+class KvNewStrides(C.Structure):
+    _fields_ = [(n, C.c_int64) for n in (
+        "knew_batch_stride", "vnew_batch_stride", "knew_row_stride", "vnew_row_stride",
+        "knew_head_stride", "vnew_head_stride", "seqlen_knew")]
+
+
+def flash_attn_kvcache(q, kcache, vcache, knew, vnew, seqlens_k, scale, causal=True, window=(-1, -1)):
+    """One decode step on contiguous arrays.  kcache / vcache are updated in place (pass copies).
+    Returns (out, lse)."""
+    b, sq, h, d = q.shape
+    cap, hk = kcache.shape[1], kcache.shape[2]
+    for t in (q, kcache, vcache):
+        assert t.flags.c_contiguous
+    p = attn_params(b, sq, cap, h, hk, d, scale, causal, window)
+    n = KvNewStrides()
+    if knew is not None:
+        knew, vnew = np.ascontiguousarray(knew), np.ascontiguousarray(vnew)
+        s_new = knew.shape[1]
+        n.knew_batch_stride = n.vnew_batch_stride = s_new * hk * d
+        n.knew_row_stride = n.vnew_row_stride = hk * d
+        n.knew_head_stride = n.vnew_head_stride = d
+        n.seqlen_knew = s_new
+    if seqlens_k is not None:
+        seqlens_k = np.ascontiguousarray(seqlens_k, dtype=np.int32)
+    out = np.empty_like(q)
+    lse = np.empty((b, h, sq), np.float32)
+    ptr = lambda a: _p(a) if a is not None else None
+    rc = lib().oracle_flash_attn_kvcache(dtype_code(q), _p(q), _p(kcache), _p(vcache), ptr(knew), ptr(vnew),
+                                         ptr(seqlens_k), _p(out), _p(lse), C.byref(p), C.byref(n))
+    assert rc == 0
+    return out, lse
+
+
 def flash_attn_bwd(dout, q, k, v, out, lse, scale, causal=True, window=(-1, -1)):
     b, sq, h, d = q.shape
     sk, hk = k.shape[1], k.shape[2]

@@ -197,3 +197,50 @@ def test_host_device_copies_and_fill_through_session():
     assert torch.all(halves == 0.5) and torch.all(sevens == 7)
     req.close()
     s.close()
+
+
+KVCACHE = """
+module attributes {byre.container_module} {
+  func.func @test_flash_attn_kvcache(%arg0 : memref<2x1x3x32xf16, "cuda"> {byre.argname = "Q", byre.argtype = 2: i32},
+                 %arg1 : memref<2x128x3x32xf16, "cuda"> {byre.argname = "KCache", byre.argtype = 2: i32},
+                 %arg2 : memref<2x128x3x32xf16, "cuda"> {byre.argname = "VCache", byre.argtype = 2: i32},
+                 %arg3 : memref<2x1x3x32xf16, "cuda"> {byre.argname = "K", byre.argtype = 2: i32},
+                 %arg4 : memref<2x1x3x32xf16, "cuda"> {byre.argname = "V", byre.argtype = 2: i32},
+                 %arg5: memref<2xi32, "cuda"> {byre.argname = "SeqLenK", byre.argtype = 2: i32},
+                 %arg6: memref<2x1x3x32xf16, "cuda"> {byre.argname = "Output", byre.argtype = 2: i32},
+                 %arg7 : memref<2x3x1xf32, "cuda"> {byre.argname = "SoftmaxLse", byre.argtype = 2: i32}) attributes {byre.entry_point} {
+    "byre.custom"(%arg0, %arg1, %arg2, %arg3, %arg4, %arg5, %arg6, %arg7) {callee = "custom", lib_path = "%LIB", api_name = "run_flash_attn_kvcache", version = "2.5.3", extra_args = [96 : i64, 12288 : i64, 12288 : i64, 96 : i64, 96 : i64, 96 : i64, 96 : i64, 96 : i64, 96 : i64, 96 : i64, 96 : i64, 96 : i64, 32 : i64, 32 : i64, 32 : i64, 32 : i64, 32 : i64, 32 : i64, 2 : i64, 3 : i64, 3 : i64, 32 : i64, 32 : i64, 1 : i64, 0.5 : f32, 1 : i64, 128 : i64, 128 : i64, 128 : i64, -1 : i64, -1 : i64]} : (memref<2x1x3x32xf16, "cuda">, memref<2x128x3x32xf16, "cuda">, memref<2x128x3x32xf16, "cuda">, memref<2x1x3x32xf16, "cuda">, memref<2x1x3x32xf16, "cuda">, memref<2xi32, "cuda">, memref<2x1x3x32xf16, "cuda">, memref<2x3x1xf32, "cuda">) -> ()
+    return
+  }
+}
+"""
+
+
+def test_flash_attn_kvcache_custom_call_through_session():
+    """the module and the vectors of the reference's kv-cache test (runtime/test/test_files/
+    flash_attn_kvcache.mlir, flash_attn_fwd_test.cc:183-330) through byre.custom -> libflash_attn.so"""
+    from pathlib import Path
+    root = Path(__file__).resolve().parent
+    lib = str(root.parent / "byteir_b200" / "_lib" / "libflash_attn.so")
+    g = np.load(root / "golden" / "flash_attn_kvcache_b2_s128_h3_d32_f16.npz")
+    dev = {"Q": g["q"], "KCache": g["kcache"], "VCache": g["vcache"], "K": g["k"], "V": g["v"],
+           "SeqLenK": g["cache_seqlens"], "Output": np.zeros((2, 1, 3, 32), np.float16),
+           "SoftmaxLse": np.zeros((2, 3, 1), np.float32)}
+    dev = {k: torch.from_numpy(np.ascontiguousarray(v)).cuda() for k, v in dev.items()}
+    s = brt.Session("cuda")
+    s.load_from_memory(KVCACHE.replace("%LIB", lib))
+    req = s.new_request(torch.cuda.current_stream().cuda_stream)
+    for a in s.args():
+        assert a.nbytes == dev[a.name].numel() * dev[a.name].element_size()
+        req.bind_arg(a.offset, dev[a.name].data_ptr())
+    req.finish_io_binding()
+    req.run()
+    req.sync()
+    torch.cuda.synchronize()
+    assert np.array_equal(dev["KCache"].cpu().numpy(), g["kcache_out"])
+    assert np.array_equal(dev["VCache"].cpu().numpy(), g["vcache_out"])
+    got, want = dev["Output"].cpu().numpy().astype(np.float32), g["out"].astype(np.float32)
+    np.testing.assert_allclose(got, want, rtol=2e-3, atol=0)
+    assert torch.isfinite(dev["SoftmaxLse"]).all()
+    req.close()
+    s.close()

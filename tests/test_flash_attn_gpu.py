@@ -144,3 +144,99 @@ def test_flash_attn_windows_and_rows_without_keys(causal, window, sq, sk, dt):
     q, k, v = _mk(rng, (b, sq, h, 128), dt), _mk(rng, (b, sk, hk, 128), dt), _mk(rng, (b, sk, hk, 128), dt)
     do = _mk(rng, (b, sq, h, 128), dt)
     _fwd_bwd_check(q, k, v, do, causal, window)
+
+
+# ---- decode step over a key/value cache -------------------------------------------------------------
+KV_GOLDEN = __import__("pathlib").Path(__file__).parent / "golden" / "flash_attn_kvcache_b2_s128_h3_d32_f16.npz"
+
+
+def test_flash_attn_kvcache_reference_golden():
+    """the vectors of the reference's own kv-cache test (flash_attn_fwd_test.cc:183-330): output and
+    both updated caches"""
+    from byteir_b200 import ops
+    g = np.load(KV_GOLDEN)
+    kc, vc = _dev(g["kcache"].copy()), _dev(g["vcache"].copy())
+    lens = torch.from_numpy(g["cache_seqlens"]).cuda()
+    o, lse = ops.flash_attn_kvcache(_dev(g["q"]), kc, vc, _dev(g["k"]), _dev(g["v"]), lens, 0.5, causal=True)
+    torch.cuda.synchronize()
+    assert np.array_equal(_host(kc), g["kcache_out"]) and np.array_equal(_host(vc), g["vcache_out"])
+    got, want = _host(o), g["out"]
+    key = lambda x: np.where(x.view(np.uint16) & 0x8000, -(x.view(np.uint16).astype(np.int32) & 0x7fff),
+                             x.view(np.uint16).astype(np.int32))
+    assert np.abs(key(got) - key(want)).max() <= 1
+    assert torch.isfinite(lse).all()
+
+
+KV_CASES = [
+    # b, sq, h, hk, d, capacity, new rows, causal, window, lengths ("full" = no length tensor)
+    (2, 1, 8, 8, 128, 4096, 1, True, (-1, -1), [4000, 77]),            # one query row per head, many splits
+    (4, 1, 32, 4, 128, 2048, 1, True, (-1, -1), [2047, 0, 1000, 513]),   # eight heads share a cache head
+    (1, 1, 4, 4, 64, 8192, 1, False, (-1, -1), [8191]),                # the most splits
+    (3, 5, 6, 2, 96, 300, 4, True, (-1, -1), [296, 10, 0]),            # several query rows, 12 of 16 lanes active
+    (2, 3, 4, 4, 256, 700, 0, True, (-1, -1), [700, 1]),               # nothing appended, widest head
+    (2, 2, 4, 2, 32, 500, 2, True, (100, 0), [498, 250]),              # sliding window
+    (2, 2, 4, 2, 32, 500, 2, False, (64, 3), [499, 30]),               # window on both sides; one new row dropped
+    (2, 1, 2, 2, 128, 256, 0, True, (-1, -1), "full"),                 # no length tensor: the whole cache
+    (2, 4, 2, 1, 128, 64, 0, True, (-1, -1), [0, 2]),                  # rows that see no key at all
+    (1, 1, 128, 8, 128, 16384, 1, True, (-1, -1), [16000]),            # 16 heads per cache head: four row chunks
+]
+
+
+@pytest.mark.parametrize("dt", ["bf16", "f16"])
+@pytest.mark.parametrize("b,sq,h,hk,d,cap,s_new,causal,window,lens", KV_CASES)
+def test_flash_attn_kvcache(b, sq, h, hk, d, cap, s_new, causal, window, lens, dt):
+    from byteir_b200 import ops
+    rng = np.random.default_rng(cap + d + h)
+    q = _mk(rng, (b, sq, h, d), dt)
+    kc, vc = _mk(rng, (b, cap, hk, d), dt), _mk(rng, (b, cap, hk, d), dt)
+    kn = _mk(rng, (b, s_new, hk, d), dt) if s_new else None
+    vn = _mk(rng, (b, s_new, hk, d), dt) if s_new else None
+    lens_h = None if lens == "full" else np.array(lens, np.int32)
+    scale = 1.0 / np.sqrt(d)
+    want_k, want_v = kc.copy(), vc.copy()
+    want_o, want_lse = O.flash_attn_kvcache(q, want_k, want_v, kn, vn, lens_h, scale, causal, window)
+    kd, vd = _dev(kc), _dev(vc)
+    o, lse = ops.flash_attn_kvcache(_dev(q), kd, vd, None if kn is None else _dev(kn),
+                                    None if vn is None else _dev(vn),
+                                    None if lens_h is None else torch.from_numpy(lens_h).cuda(),
+                                    scale, causal, window)
+    torch.cuda.synchronize()
+    assert np.array_equal(_host(kd), want_k) and np.array_equal(_host(vd), want_v)
+    gl = lse.cpu().numpy()
+    assert np.array_equal(np.isinf(gl), np.isinf(want_lse))
+    fin = np.isfinite(want_lse)
+    np.testing.assert_allclose(gl[fin], want_lse[fin], rtol=1e-3, atol=1e-3)
+    np.testing.assert_allclose(O.to_f32(_host(o)), O.to_f32(want_o), rtol=2e-2, atol=1e-2)
+
+
+def test_flash_attn_kvcache_caller_workspace_and_strided_cache():
+    """a caller-provided workspace, and caches that are views into a larger allocation"""
+    from byteir_b200 import ops, _native as N
+    import ctypes as C
+    rng = np.random.default_rng(5)
+    b, h, d, cap = 2, 4, 128, 3000
+    q = _mk(rng, (b, 1, h, d), "f16")
+    big_k, big_v = _mk(rng, (b, cap, h, 2 * d), "f16"), _mk(rng, (b, cap, h, 2 * d), "f16")
+    kn, vn = _mk(rng, (b, 1, h, d), "f16"), _mk(rng, (b, 1, h, d), "f16")
+    lens = np.array([2999, 1500], np.int32)
+    want_k, want_v = np.ascontiguousarray(big_k[..., d:]), np.ascontiguousarray(big_v[..., :d])
+    want_o, want_lse = O.flash_attn_kvcache(q, want_k, want_v, kn, vn, lens, 0.09, True)
+    bk, bv = _dev(big_k), _dev(big_v)
+    kd, vd = bk[..., d:], bv[..., :d]
+    qd = _dev(q)
+    out = torch.empty_like(qd)
+    p = ops.kvcache_params(qd, kd, vd, _dev(kn), _dev(vn), out, 0.09, True)
+    need = N.lib().b200_flash_attn_kvcache_workspace_bytes(C.byref(p))
+    assert need > 0
+    ws = torch.empty(need, dtype=torch.uint8, device="cuda")
+    o, lse = ops.flash_attn_kvcache(qd, kd, vd, _dev(kn), _dev(vn), torch.from_numpy(lens).cuda(), 0.09, True,
+                                    out=out, workspace=ws)
+    torch.cuda.synchronize()
+    assert np.array_equal(_host(kd.contiguous()), want_k) and np.array_equal(_host(vd.contiguous()), want_v)
+    # the halves of the large allocation next to the caches are untouched
+    assert np.array_equal(_host(bk[..., :d].contiguous()), big_k[..., :d])
+    assert np.array_equal(_host(bv[..., d:].contiguous()), big_v[..., d:])
+    np.testing.assert_allclose(lse.cpu().numpy(), want_lse, rtol=1e-3, atol=1e-3)
+    np.testing.assert_allclose(O.to_f32(_host(o)), O.to_f32(want_o), rtol=2e-2, atol=1e-2)
+    with pytest.raises(Exception):
+        ops.flash_attn_kvcache(qd, kd, vd, None, None, None, 0.09, True, workspace=ws[:64])

@@ -43,6 +43,46 @@ def test_flash_attn_bwd_matches_reference_golden():
         assert np.median(ulp) <= 1, (name, np.median(ulp))
 
 
+# ---- golden pin of the decode step: b2, cache of 128 rows with 64 in use, one new row
+KV_GOLDEN = Path(__file__).parent / "golden" / "flash_attn_kvcache_b2_s128_h3_d32_f16.npz"
+
+
+def test_flash_attn_kvcache_matches_reference_golden():
+    g = np.load(KV_GOLDEN)
+    kcache, vcache = g["kcache"].copy(), g["vcache"].copy()
+    out, lse = O.flash_attn_kvcache(g["q"], kcache, vcache, g["k"], g["v"], g["cache_seqlens"], 0.5, causal=True)
+    # the updated caches are copies of 16-bit values: exact
+    assert np.array_equal(kcache, g["kcache_out"]) and np.array_equal(vcache, g["vcache_out"])
+    ulp = _ulp_diff_f16(out, g["out"])
+    assert ulp.max() <= 1, ulp.max()
+    assert (ulp == 0).mean() > 0.9, (ulp == 0).mean()
+    assert np.isfinite(lse).all()
+
+
+def test_flash_attn_kvcache_equals_forward_on_the_rows_in_use():
+    """ragged lengths, grouped heads, several query rows, a window; new rows that do not fit are dropped"""
+    rng = np.random.default_rng(3)
+    b, sq, h, hk, d, cap, s_new = 3, 2, 4, 2, 16, 40, 3
+    q = rng.standard_normal((b, sq, h, d)).astype(np.float16)
+    kc = rng.standard_normal((b, cap, hk, d)).astype(np.float16)
+    vc = rng.standard_normal((b, cap, hk, d)).astype(np.float16)
+    kn = rng.standard_normal((b, s_new, hk, d)).astype(np.float16)
+    vn = rng.standard_normal((b, s_new, hk, d)).astype(np.float16)
+    lens = np.array([0, 17, 38], np.int32)  # the last one has room for two of the three new rows
+    for causal, window in ((True, (-1, -1)), (False, (-1, -1)), (False, (5, 1))):
+        k2, v2 = kc.copy(), vc.copy()
+        out, lse = O.flash_attn_kvcache(q, k2, v2, kn, vn, lens, 0.3, causal=causal, window=window)
+        for i in range(b):
+            n = min(int(lens[i]) + s_new, cap)
+            kk = np.concatenate([kc[i, :lens[i]], kn[i, :n - lens[i]]])[None]
+            vv = np.concatenate([vc[i, :lens[i]], vn[i, :n - lens[i]]])[None]
+            assert np.array_equal(k2[i, :n], kk[0]) and np.array_equal(k2[i, n:], kc[i, n:])
+            assert np.array_equal(v2[i, :n], vv[0]) and np.array_equal(v2[i, n:], vc[i, n:])
+            want, want_lse = O.flash_attn_fwd(q[i:i + 1], kk, vv, 0.3, causal=causal, window=window)
+            assert np.array_equal(out[i:i + 1], want)
+            np.testing.assert_array_equal(lse[i:i + 1], want_lse)
+
+
 def test_flash_attn_fwd_vs_numpy_noncausal_gqa():
     rng = np.random.default_rng(7)
     q = rng.standard_normal((2, 40, 4, 16)).astype(np.float16)
