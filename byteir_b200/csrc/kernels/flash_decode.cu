@@ -153,11 +153,11 @@ __global__ void __launch_bounds__(kDecodeThreads) decode_split_kernel(const Deco
     }
   }
 
-  for (int j0 = j_begin; j0 < j_end; j0 += KPB) {
+  // the loads of the next step are issued before the arithmetic of the current one
+  auto load_kv = [&](int j0, uint4 &kraw, uint4 &vraw) {
     const int j = j0 + kslot;
-    const bool have = j < j_end;
-    uint4 kraw = make_uint4(0, 0, 0, 0), vraw = make_uint4(0, 0, 0, 0);
-    if (have && active) {
+    kraw = vraw = make_uint4(0, 0, 0, 0);
+    if (j < j_end && active) {
       if (j < cache_len) {
         kraw = ld_nc_v4(kc + (int64_t)j * p.k_rs);
         vraw = ld_nc_v4(vc + (int64_t)j * p.v_rs);
@@ -166,6 +166,13 @@ __global__ void __launch_bounds__(kDecodeThreads) decode_split_kernel(const Deco
         vraw = ld_nc_v4(vn + (int64_t)(j - cache_len) * p.vn_rs);
       }
     }
+  };
+  uint4 kraw, vraw, knext, vnext;
+  load_kv(j_begin, kraw, vraw);
+  for (int j0 = j_begin; j0 < j_end; j0 += KPB, kraw = knext, vraw = vnext) {
+    const int j = j0 + kslot;
+    const bool have = j < j_end;
+    load_kv(j0 + KPB, knext, vnext);
     float kf[8], vf[8];
     unpack8<kBF16>(kraw, kf);
     unpack8<kBF16>(vraw, vf);
@@ -266,6 +273,316 @@ __global__ void __launch_bounds__(kDecodeThreads) decode_split_kernel(const Deco
   }
 }
 
+// ---- head dims 64 and 128: the same split, scores and outputs on mma.sync tiles ----------------
+// With grouped heads a block has up to 16 query rows per key, more multiply-adds than the scalar
+// cores sustain at HBM speed; as one m16n8k16 tile they cost nothing.  Every warp walks its own
+// 16-key tiles: K and V go from global memory straight into the B-operand registers, with no
+// shared-memory stage, by permuting the contraction index: in S = Q K^T lane (g, c) of a quad
+// contributes the 8 consecutive head-dim values [32 s + 8 c, +8) of key g to two k-steps, and Q's
+// A fragments are loaded with the same permutation; in O = P V the lane takes the 8 consecutive
+// output columns [64 hb + 8 g, +8) of its four keys, so that every load is one 16-byte vector
+// and a warp reads whole 128-byte lines.  The output column of accumulator (n-tile t, logical
+// column n) is 64 (t / 8) + 8 n + t % 8.  The vectors travel through a ring of cp.async stages
+// in shared memory in which every thread owns the slots it later reads itself, so the ring
+// needs no barrier: it only takes the loads of the next two tiles off the registers' hands
+// (16 KB in flight per warp).
+template <bool kBF16>
+__device__ __forceinline__ void mma16816(float (&acc)[4], const uint32_t (&a)[4], uint32_t b0, uint32_t b1) {
+  if constexpr (kBF16)
+    asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, "
+                 "{%0,%1,%2,%3};"
+                 : "+f"(acc[0]), "+f"(acc[1]), "+f"(acc[2]), "+f"(acc[3])
+                 : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
+  else
+    asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.f16.f16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, "
+                 "{%0,%1,%2,%3};"
+                 : "+f"(acc[0]), "+f"(acc[1]), "+f"(acc[2]), "+f"(acc[3])
+                 : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
+}
+
+template <bool kBF16> __device__ __forceinline__ uint32_t pack2(float lo, float hi) {
+  if constexpr (kBF16) {
+    const __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);
+    return *reinterpret_cast<const uint32_t *>(&v);
+  } else {
+    const __half2 v = __floats2half2_rn(lo, hi);
+    return *reinterpret_cast<const uint32_t *>(&v);
+  }
+}
+
+__device__ __forceinline__ uint32_t word_of(const uint4 &v, int w) {
+  return w == 0 ? v.x : (w == 1 ? v.y : (w == 2 ? v.z : v.w));
+}
+
+__device__ __forceinline__ void cp_async16(uint32_t smem_addr, const void *src, bool real) {
+  const int bytes = real ? 16 : 0; // 0: the 16 bytes are filled with zeros and src is not read
+  asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(smem_addr), "l"(src), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
+template <int N> __device__ __forceinline__ void cp_async_wait() {
+  asm volatile("cp.async.wait_group %0;" ::"n"(N) : "memory");
+}
+__device__ __forceinline__ uint4 lds_v4(uint32_t smem_addr) {
+  uint4 v;
+  asm volatile("ld.shared.v4.u32 {%0,%1,%2,%3}, [%4];" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "r"(smem_addr));
+  return v;
+}
+
+constexpr int kMmaRows = 16;                   // query rows of one block
+constexpr int kMmaStages = 3;                  // tiles of the cp.async ring
+constexpr int kMmaKeysPerStep = 16 * kDecodeWarps;
+
+template <int D, bool kBF16>
+__global__ void __launch_bounds__(kDecodeThreads, 1) decode_mma_kernel(const DecodeParams p) {
+  using T = typename std::conditional<kBF16, __nv_bfloat16, __half>::type;
+  constexpr int NT = D / 8;  // output n-tiles
+  constexpr int KS2 = D / 32; // pairs of k-steps of Q K^T
+  constexpr int HB = D / 64;
+  constexpr int NV = 2 * KS2 + 4 * HB; // 16-byte vectors of K and V a thread takes per tile
+  extern __shared__ __align__(16) float decode_smem[];
+  // ring: [stage][vector][thread] 16-byte slots; after the loop the same memory holds the merge buffers
+  const uint32_t ring = (uint32_t)__cvta_generic_to_shared(decode_smem) + threadIdx.x * 16u;
+  float *sm_acc = decode_smem;                                 // [warp][row][D]
+  float *sm_m = decode_smem + kDecodeWarps * kMmaRows * D;     // [warp][row]
+  float *sm_l = sm_m + kDecodeWarps * kMmaRows;
+
+  const int split = blockIdx.x;
+  const int chunk = blockIdx.y % p.chunks, hk = blockIdx.y / p.chunks;
+  const int b = blockIdx.z;
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  const int g = lane >> 2, c = lane & 3;
+
+  const int n_new = p.knew ? p.seqlen_knew : 0;
+  int cache_len = p.seqlens_k ? p.seqlens_k[b] : p.seqlen_k;
+  cache_len = max(0, min(cache_len, p.seqlen_k));
+  const int len = min(cache_len + n_new, p.seqlen_k);
+  const int shift = len - p.seqlen_q;
+
+  // this lane's two query rows: r0 + g and r0 + g + 8
+  const int r0 = chunk * kMmaRows;
+  const int r_a = r0 + g, r_b = r0 + g + 8;
+  const bool valid_a = r_a < p.rows_per_kv, valid_b = r_b < p.rows_per_kv;
+  const int qi_a = valid_a ? r_a / p.group : 0, qi_b = valid_b ? r_b / p.group : 0;
+  uint32_t qa[KS2][2][4];
+  {
+    const T *qb = static_cast<const T *>(p.q) + (int64_t)b * p.q_bs;
+    const T *row_a = qb + (int64_t)qi_a * p.q_rs + (int64_t)(hk * p.group + (valid_a ? r_a % p.group : 0)) * p.q_hs;
+    const T *row_b = qb + (int64_t)qi_b * p.q_rs + (int64_t)(hk * p.group + (valid_b ? r_b % p.group : 0)) * p.q_hs;
+#pragma unroll
+    for (int s2 = 0; s2 < KS2; ++s2) {
+      const uint4 zero = make_uint4(0, 0, 0, 0);
+      const uint4 va = valid_a ? ld_nc_v4(row_a + 32 * s2 + 8 * c) : zero;
+      const uint4 vb = valid_b ? ld_nc_v4(row_b + 32 * s2 + 8 * c) : zero;
+      qa[s2][0][0] = va.x, qa[s2][0][1] = vb.x, qa[s2][0][2] = va.y, qa[s2][0][3] = vb.y;
+      qa[s2][1][0] = va.z, qa[s2][1][1] = vb.z, qa[s2][1][2] = va.w, qa[s2][1][3] = vb.w;
+    }
+  }
+
+  const int i_min = r0 / p.group;
+  const int i_max = min(r0 + kMmaRows - 1, p.rows_per_kv - 1) / p.group;
+  const int lo = p.window_left >= 0 ? max(0, i_min + shift - p.window_left) : 0;
+  const int hi = p.window_right >= 0 ? min(len, i_max + shift + p.window_right + 1) : len;
+  const int span = max(hi - lo, 0);
+  int per = (span + p.splits - 1) / p.splits;
+  per = (per + kMmaKeysPerStep - 1) / kMmaKeysPerStep * kMmaKeysPerStep;
+  const int j_begin = lo + split * per;
+  const int j_end = min(hi, j_begin + per);
+
+  T *kc = static_cast<T *>(p.kcache) + (int64_t)b * p.k_bs + (int64_t)hk * p.k_hs;
+  T *vc = static_cast<T *>(p.vcache) + (int64_t)b * p.v_bs + (int64_t)hk * p.v_hs;
+  const T *kn = static_cast<const T *>(p.knew) + (int64_t)b * p.kn_bs + (int64_t)hk * p.kn_hs;
+  const T *vn = static_cast<const T *>(p.vnew) + (int64_t)b * p.vn_bs + (int64_t)hk * p.vn_hs;
+
+  // append: the blocks of the first row chunk copy all new rows into the cache, 16 bytes a thread
+  if (chunk == 0) {
+    const int pieces = (len - cache_len) * (D / 8);
+    for (int idx = split * kDecodeThreads + (int)threadIdx.x; idx < pieces; idx += p.splits * kDecodeThreads) {
+      const int jn = idx / (D / 8), e = (idx % (D / 8)) * 8;
+      *reinterpret_cast<uint4 *>(kc + (int64_t)(cache_len + jn) * p.k_rs + e) = ld_nc_v4(kn + (int64_t)jn * p.kn_rs + e);
+      *reinterpret_cast<uint4 *>(vc + (int64_t)(cache_len + jn) * p.v_rs + e) = ld_nc_v4(vn + (int64_t)jn * p.vn_rs + e);
+    }
+  }
+
+  // vectors of a tile: K of keys j0 + 8 nt + g, head-dim values [32 s2 + 8 c, +8)  (index nt * KS2 + s2);
+  // V of keys j0 + 8 (ki / 2) + 2 c + ki % 2, columns [64 hb + 8 g, +8)  (index 2 KS2 + ki * HB + hb)
+  auto issue_tile = [&](int j0, int stage) {
+    const uint32_t base = ring + (uint32_t)stage * (NV * kDecodeThreads * 16);
+#pragma unroll
+    for (int nt = 0; nt < 2; ++nt) {
+      const int j = j0 + 8 * nt + g;
+      const bool real = j < j_end;
+      const T *row = !real ? kc : (j < cache_len ? kc + (int64_t)j * p.k_rs : kn + (int64_t)(j - cache_len) * p.kn_rs);
+#pragma unroll
+      for (int s2 = 0; s2 < KS2; ++s2)
+        cp_async16(base + (nt * KS2 + s2) * (kDecodeThreads * 16), row + 32 * s2 + 8 * c, real);
+    }
+#pragma unroll
+    for (int ki = 0; ki < 4; ++ki) {
+      const int j = j0 + 8 * (ki >> 1) + 2 * c + (ki & 1);
+      const bool real = j < j_end;
+      const T *row = !real ? vc : (j < cache_len ? vc + (int64_t)j * p.v_rs : vn + (int64_t)(j - cache_len) * p.vn_rs);
+#pragma unroll
+      for (int hb = 0; hb < HB; ++hb)
+        cp_async16(base + (2 * KS2 + ki * HB + hb) * (kDecodeThreads * 16), row + 64 * hb + 8 * g, real);
+    }
+  };
+
+  float o[NT][4];
+#pragma unroll
+  for (int t = 0; t < NT; ++t)
+    o[t][0] = o[t][1] = o[t][2] = o[t][3] = 0.f;
+  float m_a = -INFINITY, m_b = -INFINITY, l_a = 0.f, l_b = 0.f;
+
+  int j0 = j_begin + warp * 16;
+#pragma unroll
+  for (int st = 0; st < kMmaStages - 1; ++st) { // one group per tile, empty past the end
+    if (j0 + st * kMmaKeysPerStep < j_end)
+      issue_tile(j0 + st * kMmaKeysPerStep, st);
+    cp_async_commit();
+  }
+  for (int it = 0; j0 < j_end; j0 += kMmaKeysPerStep, ++it) {
+    cp_async_wait<kMmaStages - 2>(); // this tile has landed
+    {
+      // the stage refilled here was read, by this thread, in the previous iteration
+      const int j_ahead = j0 + (kMmaStages - 1) * kMmaKeysPerStep;
+      if (j_ahead < j_end)
+        issue_tile(j_ahead, (it + kMmaStages - 1) % kMmaStages);
+      cp_async_commit();
+    }
+    const uint32_t base = ring + (uint32_t)(it % kMmaStages) * (NV * kDecodeThreads * 16);
+    float s[2][4];
+#pragma unroll
+    for (int nt = 0; nt < 2; ++nt) {
+      s[nt][0] = s[nt][1] = s[nt][2] = s[nt][3] = 0.f;
+#pragma unroll
+      for (int s2 = 0; s2 < KS2; ++s2) {
+        const uint4 kv = lds_v4(base + (nt * KS2 + s2) * (kDecodeThreads * 16));
+        mma16816<kBF16>(s[nt], qa[s2][0], kv.x, kv.y);
+        mma16816<kBF16>(s[nt], qa[s2][1], kv.z, kv.w);
+      }
+    }
+
+    // s[nt][e]: key j0 + 8 nt + 2 c + (e & 1), row a for e < 2, row b otherwise
+    float mx_a = -INFINITY, mx_b = -INFINITY;
+#pragma unroll
+    for (int nt = 0; nt < 2; ++nt)
+#pragma unroll
+      for (int e = 0; e < 4; ++e) {
+        const int j = j0 + 8 * nt + 2 * c + (e & 1);
+        const int qi = e < 2 ? qi_a : qi_b;
+        bool visible = j < j_end && (e < 2 ? valid_a : valid_b);
+        if (p.window_right >= 0 && j > qi + shift + p.window_right)
+          visible = false;
+        if (p.window_left >= 0 && j < qi + shift - p.window_left)
+          visible = false;
+        s[nt][e] = visible ? s[nt][e] * p.scale_log2 : -INFINITY;
+        if (e < 2)
+          mx_a = fmaxf(mx_a, s[nt][e]);
+        else
+          mx_b = fmaxf(mx_b, s[nt][e]);
+      }
+    mx_a = fmaxf(mx_a, __shfl_xor_sync(0xffffffffu, mx_a, 1));
+    mx_a = fmaxf(mx_a, __shfl_xor_sync(0xffffffffu, mx_a, 2));
+    mx_b = fmaxf(mx_b, __shfl_xor_sync(0xffffffffu, mx_b, 1));
+    mx_b = fmaxf(mx_b, __shfl_xor_sync(0xffffffffu, mx_b, 2));
+    const float new_a = fmaxf(m_a, mx_a), new_b = fmaxf(m_b, mx_b);
+    if (__any_sync(0xffffffffu, new_a > m_a || new_b > m_b)) { // some row's maximum grew: rescale
+      const float alpha_a = scale_of(m_a, new_a), alpha_b = scale_of(m_b, new_b);
+      l_a *= alpha_a;
+      l_b *= alpha_b;
+#pragma unroll
+      for (int t = 0; t < NT; ++t) {
+        o[t][0] *= alpha_a, o[t][1] *= alpha_a;
+        o[t][2] *= alpha_b, o[t][3] *= alpha_b;
+      }
+      m_a = new_a, m_b = new_b;
+    }
+#pragma unroll
+    for (int nt = 0; nt < 2; ++nt)
+#pragma unroll
+      for (int e = 0; e < 4; ++e) {
+        const float pr = s[nt][e] == -INFINITY ? 0.f : exp2f(s[nt][e] - (e < 2 ? m_a : m_b));
+        s[nt][e] = pr;
+        if (e < 2)
+          l_a += pr;
+        else
+          l_b += pr;
+      }
+    const uint32_t pa[4] = {pack2<kBF16>(s[0][0], s[0][1]), pack2<kBF16>(s[0][2], s[0][3]),
+                            pack2<kBF16>(s[1][0], s[1][1]), pack2<kBF16>(s[1][2], s[1][3])};
+#pragma unroll
+    for (int hb = 0; hb < HB; ++hb) {
+      uint4 vreg[4];
+#pragma unroll
+      for (int ki = 0; ki < 4; ++ki)
+        vreg[ki] = lds_v4(base + (2 * KS2 + ki * HB + hb) * (kDecodeThreads * 16));
+#pragma unroll
+      for (int e = 0; e < 8; ++e) {
+        const uint32_t sel = (e & 1) ? 0x7632u : 0x5410u;
+        const uint32_t b0 = __byte_perm(word_of(vreg[0], e >> 1), word_of(vreg[1], e >> 1), sel);
+        const uint32_t b1 = __byte_perm(word_of(vreg[2], e >> 1), word_of(vreg[3], e >> 1), sel);
+        mma16816<kBF16>(o[hb * 8 + e], pa, b0, b1);
+      }
+    }
+  }
+  cp_async_wait<0>();
+  __syncthreads(); // every warp is done with the ring: its memory becomes the merge buffers
+
+  // the row sums are spread over the four lanes of a quad
+  l_a += __shfl_xor_sync(0xffffffffu, l_a, 1);
+  l_a += __shfl_xor_sync(0xffffffffu, l_a, 2);
+  l_b += __shfl_xor_sync(0xffffffffu, l_b, 1);
+  l_b += __shfl_xor_sync(0xffffffffu, l_b, 2);
+  float *acc_w = sm_acc + (size_t)warp * kMmaRows * D;
+#pragma unroll
+  for (int t = 0; t < NT; ++t) {
+    const int col = 64 * (t / 8) + 16 * c + t % 8; // logical columns 2c and 2c+1 are 8 apart
+    acc_w[g * D + col] = o[t][0];
+    acc_w[g * D + col + 8] = o[t][1];
+    acc_w[(g + 8) * D + col] = o[t][2];
+    acc_w[(g + 8) * D + col + 8] = o[t][3];
+  }
+  if (c == 0) {
+    sm_m[warp * kMmaRows + g] = m_a, sm_m[warp * kMmaRows + g + 8] = m_b;
+    sm_l[warp * kMmaRows + g] = l_a, sm_l[warp * kMmaRows + g + 8] = l_b;
+  }
+  __syncthreads();
+
+  // merge the warps; one thread per (row, element)
+  for (int idx = threadIdx.x; idx < kMmaRows * D; idx += kDecodeThreads) {
+    const int t = idx / D, e = idx % D;
+    const int r = r0 + t;
+    if (r >= p.rows_per_kv)
+      continue;
+    float mx = -INFINITY;
+#pragma unroll
+    for (int w = 0; w < kDecodeWarps; ++w)
+      mx = fmaxf(mx, sm_m[w * kMmaRows + t]);
+    float sum = 0.f, val = 0.f;
+#pragma unroll
+    for (int w = 0; w < kDecodeWarps; ++w) {
+      const float a = scale_of(sm_m[w * kMmaRows + t], mx);
+      sum += sm_l[w * kMmaRows + t] * a;
+      val += sm_acc[((size_t)w * kMmaRows + t) * D + e] * a;
+    }
+    const int i = r / p.group, head = hk * p.group + r % p.group;
+    const int64_t row = ((int64_t)b * p.h + head) * p.seqlen_q + i;
+    if (p.splits == 1) {
+      T *op = static_cast<T *>(p.o) + (int64_t)b * p.o_bs + (int64_t)i * p.o_rs + (int64_t)head * p.o_hs;
+      op[e] = Elt<T>::from_f32(sum > 0.f ? val / sum : 0.f);
+      if (e == 0)
+        p.lse[row] = sum > 0.f ? mx * kLn2 + logf(sum) : INFINITY;
+    } else {
+      const int64_t slot = row * p.splits + split;
+      p.part_o[slot * p.d + e] = val;
+      if (e == 0) {
+        p.part_ml[slot * 2] = mx;
+        p.part_ml[slot * 2 + 1] = sum;
+      }
+    }
+  }
+}
+
 // one block per query row: merges the partial results of the splits
 template <bool kBF16>
 __global__ void __launch_bounds__(128) decode_merge_kernel(const DecodeParams p) {
@@ -308,6 +625,7 @@ __global__ void __launch_bounds__(128) decode_merge_kernel(const DecodeParams p)
 }
 
 struct DecodePlan {
+  bool mma; // head dim 64 or 128: the tensor-core kernel, 16 query rows a block
   int lpk, rc, chunks, splits;
   int64_t rows;
   size_t workspace_bytes;
@@ -335,15 +653,17 @@ int make_plan(const b200_flash_kvcache_params &p, DecodePlan *plan) {
     return B200_ERR_INVALID_ARG;
   const int64_t group = p.h / p.h_k;
   const int64_t rows_per_kv = p.seqlen_q * group;
+  plan->mma = p.d == 64 || p.d == 128;
   plan->lpk = std::max(4, pow2_ceil(p.d / 8));
-  plan->rc = rows_per_kv >= 4 ? 4 : (rows_per_kv >= 2 ? 2 : 1);
+  plan->rc = plan->mma ? kMmaRows : (rows_per_kv >= 4 ? 4 : (rows_per_kv >= 2 ? 2 : 1));
   plan->chunks = (int)ceil_div<int64_t>(rows_per_kv, plan->rc);
   if ((int64_t)plan->chunks * p.h_k > 65535 || p.b > 65535)
     return B200_ERR_UNSUPPORTED;
-  const int64_t keys_per_step = (int64_t)kDecodeWarps * 32 / plan->lpk;
+  const int64_t keys_per_step = plan->mma ? kMmaKeysPerStep : (int64_t)kDecodeWarps * 32 / plan->lpk;
   const int64_t base = p.b * p.h_k * plan->chunks;
-  // enough blocks for four per SM, as long as every split keeps four block steps of keys
-  const int64_t want = ceil_div<int64_t>((int64_t)kNumSMs * 4, base);
+  // enough blocks to fill every SM a few times over (the tensor-core kernel has one block per SM,
+  // the scalar one up to four), as long as every split keeps four block steps of keys
+  const int64_t want = ceil_div<int64_t>((int64_t)kNumSMs * (plan->mma ? 2 : 4), base);
   const int64_t room = std::max<int64_t>(1, p.seqlen_k / (4 * keys_per_step));
   plan->splits = (int)std::max<int64_t>(1, std::min<int64_t>({want, room, (int64_t)kMaxSplits}));
   plan->rows = p.b * p.h * p.seqlen_q;
@@ -369,6 +689,17 @@ template <int LPK, bool kBF16> int launch_split(const DecodeParams &dp, int rc, 
 template <bool kBF16> int launch_decode(const DecodeParams &dp, const DecodePlan &plan, cudaStream_t stream) {
   const dim3 grid((unsigned)plan.splits, (unsigned)(plan.chunks * dp.h_k), (unsigned)dp.b);
   int rc;
+  if (plan.mma) {
+    // the cp.async ring (16 bytes x d/8 vectors x 256 threads a stage); the merge buffers reuse it
+    const size_t ring = (size_t)kMmaStages * (dp.d / 8) * kDecodeThreads * 16;
+    const size_t smem = std::max(ring, ((size_t)kDecodeWarps * kMmaRows * (dp.d + 2)) * sizeof(float));
+    auto kernel = dp.d == 128 ? decode_mma_kernel<128, kBF16> : decode_mma_kernel<64, kBF16>;
+    // the attribute belongs to the current device's context: set it on every call
+    if (int e = check_cuda(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem)))
+      return e;
+    kernel<<<grid, kDecodeThreads, smem, stream>>>(dp);
+    rc = check_launch();
+  } else
   switch (plan.lpk) {
   case 4:
     rc = launch_split<4, kBF16>(dp, plan.rc, grid, stream);

@@ -178,7 +178,11 @@ KV_CASES = [
     (2, 2, 4, 2, 32, 500, 2, False, (64, 3), [499, 30]),               # window on both sides; one new row dropped
     (2, 1, 2, 2, 128, 256, 0, True, (-1, -1), "full"),                 # no length tensor: the whole cache
     (2, 4, 2, 1, 128, 64, 0, True, (-1, -1), [0, 2]),                  # rows that see no key at all
-    (1, 1, 128, 8, 128, 16384, 1, True, (-1, -1), [16000]),            # 16 heads per cache head: four row chunks
+    (1, 1, 128, 8, 128, 16384, 1, True, (-1, -1), [16000]),            # 16 heads per cache head: a full row tile
+    (2, 3, 16, 2, 64, 1000, 3, True, (-1, -1), [997, 5]),              # 24 rows per cache head: two row chunks
+    (2, 2, 8, 2, 128, 700, 2, True, (100, 0), [698, 300]),             # sliding window on the tensor-core path
+    (2, 2, 8, 2, 64, 700, 2, False, (30, 5), [690, 0]),                # window on both sides, head dim 64
+    (3, 7, 4, 4, 128, 50, 7, True, (-1, -1), [43, 0, 20]),             # more new rows than a block step of the append
 ]
 
 
