@@ -559,7 +559,93 @@ class AttnC5(Workload):
         np.testing.assert_allclose(O.bf16_to_f32(got), O.bf16_to_f32(o), rtol=2e-2, atol=1e-2)
 
 
-WORKLOADS = {"attn": AttnC5, "reduce_c2": ReduceC2, "reduce_c1": ReduceC1, "gather": GatherC3, "scatter": ScatterC3,
+class DecodeKv(Workload):
+    """Decode step over a kv cache: bf16 q [B=16, 1, H=32, D=128], caches [16, 8192, H_k=8, 128] N(0,1) with
+    U[6144, 8190] rows in use, one new row appended per step, scale 1/sqrt(128)"""
+    name = "flash_attn_kvcache_bf16_b16_h32_hk8_d128_cache8192"
+    dtype = "bf16 (f32 accumulate)"
+    B, H, HK, D, CAP = 16, 32, 8, 128, 8192
+    l2_policy = "every step streams the 512 MiB of the two caches (L2 is 126 MiB)"
+
+    def __init__(self, rank, world):
+        self.rank, self.world = rank, world
+        rng = np.random.default_rng(1234 + 6 + 1000 * rank)
+        self.lens = rng.integers(6144, self.CAP - 1, self.B).astype(np.int32)
+        self.rng = rng
+        self.scale = 1.0 / float(np.sqrt(self.D))
+
+    def host_inputs(self, n):
+        import oracle_lib as O
+        gen = lambda shape: O.f32_to_bf16(self.rng.standard_normal(shape, dtype=np.float32))
+        if not hasattr(self, "kcache"):
+            self.kcache = gen((self.B, self.CAP, self.HK, self.D))
+            self.vcache = gen((self.B, self.CAP, self.HK, self.D))
+        return [(gen((self.B, 1, self.H, self.D)), gen((self.B, 1, self.HK, self.D)), gen((self.B, 1, self.HK, self.D)))
+                for _ in range(n)]
+
+    def work_per_step(self):  # K and V rows in use, once each
+        return int(2 * (self.lens.astype(np.int64) + 1).sum() * self.HK * self.D * 2)
+
+    def launches_per_step(self):
+        return 2  # split kernel, merge kernel
+
+    def dominant(self):
+        return "decode_mma_kernel<128, bf16>", self.work_per_step()
+
+    def to_dev(self, torch, x):
+        return tuple(torch.from_numpy(a.view(np.int16)).cuda().view(torch.bfloat16) for a in x)
+
+    def setup_gpu(self, torch, ops, xs):
+        self.ops, self.torch = ops, torch
+        self.kc, self.vc = self.to_dev(torch, (self.kcache, self.vcache))
+        self.lens_d = torch.from_numpy(self.lens).cuda()
+        self.o = torch.empty_like(xs[0][0])
+        self.lse = torch.empty((self.B, self.H, 1), dtype=torch.float32, device="cuda")
+        p = ops.kvcache_params(xs[0][0], self.kc, self.vc, xs[0][1], xs[0][2], self.o, self.scale, True)
+        import ctypes as C
+        from byteir_b200 import _native as N
+        self.ws = torch.empty(max(16, N.lib().b200_flash_attn_kvcache_workspace_bytes(C.byref(p))), dtype=torch.uint8,
+                              device="cuda")
+
+    def step_gpu(self, x, dist=None):
+        q, kn, vn = x
+        self.ops.flash_attn_kvcache(q, self.kc, self.vc, kn, vn, self.lens_d, self.scale, True, out=self.o,
+                                    lse=self.lse, workspace=self.ws)
+        return self.o, self.lse
+
+    dominant_gpu = step_gpu
+
+    def result_bytes(self):
+        return self.B * self.H * self.D * 2 + self.B * self.H * 4
+
+    # CPU: two batch entries of the same step
+    CPU_SAMPLE = (2, 8192, 8, 128)
+
+    def cpu_sample_flops(self):  # bytes, like work_per_step
+        return int(2 * (self.lens[:2].astype(np.int64) + 1).sum() * self.HK * self.D * 2)
+
+    def step_cpu(self, O, x):
+        q, kn, vn = (a[:2] for a in x)
+        if not hasattr(self, "cpu_caches"):
+            self.cpu_caches = (self.kcache[:2].copy(), self.vcache[:2].copy())
+        O.flash_attn_kvcache(np.ascontiguousarray(q), self.cpu_caches[0], self.cpu_caches[1], kn, vn, self.lens[:2],
+                             self.scale, True)
+
+    def check(self, O, x, outs):
+        # batch entry 3 against the oracle: output, LSE, and the appended cache rows
+        b = 3
+        q, kn, vn = (np.ascontiguousarray(a[b:b + 1]) for a in x)
+        kc, vc = self.kcache[b:b + 1].copy(), self.vcache[b:b + 1].copy()
+        o, lse = O.flash_attn_kvcache(q, kc, vc, kn, vn, self.lens[b:b + 1], self.scale, True)
+        got = outs[0][b:b + 1].contiguous().view(self.torch.int16).cpu().numpy().view(np.uint16)
+        np.testing.assert_allclose(O.bf16_to_f32(got), O.bf16_to_f32(o), rtol=2e-2, atol=1e-2)
+        np.testing.assert_allclose(outs[1][b:b + 1].cpu().numpy(), lse, rtol=1e-3, atol=1e-3)
+        row = int(self.lens[b])
+        got_k = self.kc[b, row].contiguous().view(self.torch.int16).cpu().numpy().view(np.uint16)
+        assert np.array_equal(got_k, kc[0, row])
+
+
+WORKLOADS = {"attn": AttnC5, "decode": DecodeKv, "reduce_c2": ReduceC2, "reduce_c1": ReduceC1, "gather": GatherC3, "scatter": ScatterC3,
              "transpose": TransposeC4}
 METRIC = "HBM GB/s (algorithmic bytes / time) of the ByRE compute op"
 METRIC_TENSOR = "flash-attn fwd+bwd TFLOP/s (algorithmic FLOPs / time)"
@@ -665,7 +751,7 @@ def main():
     # rotate over enough distinct inputs that together they exceed L2
     first = xs_host[0]
     per_buf = sum(a.nbytes for a in (first if isinstance(first, tuple) else (first,)))
-    n_buf = max(2, -(-2 * L2_BYTES // per_buf)) if args.workload not in ("scatter", "transpose", "attn") else 2
+    n_buf = max(2, -(-2 * L2_BYTES // per_buf)) if args.workload not in ("scatter", "transpose", "attn", "decode") else 2
     if args.workload == "attn":
         n_buf = 1  # one input set is 1 GiB, far beyond L2
     n_buf = min(n_buf, 8)
@@ -870,7 +956,8 @@ def main():
         "ms_per_step": ms_per_step, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
         "dtype": wl.dtype, "data": "synthetic (seeded numpy Generator)",
         "config": {"workload": wl.name, "per_gpu_batch": wl.__doc__.strip(),
-                   "l2_policy": f"inputs rotate over {n_buf} distinct buffers ({n_buf * per_buf / 2**20:.0f} MiB, L2 is 126 MiB)",
+                   "l2_policy": getattr(wl, "l2_policy", None) or
+                   f"inputs rotate over {n_buf} distinct buffers ({n_buf * per_buf / 2**20:.0f} MiB, L2 is 126 MiB)",
                    "launch": "CUDA graph replay of the K steps" if use_graph else "eager launches",
                    "exchange": getattr(wl, "exchange", "none"),
                    "parallelism": f"dp{world}"},

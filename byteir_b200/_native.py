@@ -74,6 +74,7 @@ SIGNATURES = {
 EXTRA = {
     "b200_index_select_path": (_int, [_int, _int, _int, _vp, _vp, _vp, _i64, _i64, _i64, _i64, _vp, _vp]),
     "b200_transpose_batched_path": (_int, [_int, _int, _vp, _vp, _i64, _i64, _i64, _vp]),
+    "b200_flash_attn_kvcache_tune": (None, [_int]),
 }
 
 _lib = None

@@ -85,6 +85,7 @@ __global__ void __launch_bounds__(kDecodeThreads) decode_split_kernel(const Deco
   __shared__ float sm_acc[kDecodeWarps][RC][kDPad];
   __shared__ float sm_m[kDecodeWarps][RC], sm_l[kDecodeWarps][RC];
 
+  pdl_launch_dependents(); // the merge kernel may take free slots once every block of this grid runs
   const int split = blockIdx.x;
   const int chunk = blockIdx.y % p.chunks, hk = blockIdx.y / p.chunks;
   const int b = blockIdx.z;
@@ -284,8 +285,8 @@ __global__ void __launch_bounds__(kDecodeThreads) decode_split_kernel(const Deco
 // and a warp reads whole 128-byte lines.  The output column of accumulator (n-tile t, logical
 // column n) is 64 (t / 8) + 8 n + t % 8.  The vectors travel through a ring of cp.async stages
 // in shared memory in which every thread owns the slots it later reads itself, so the ring
-// needs no barrier: it only takes the loads of the next two tiles off the registers' hands
-// (16 KB in flight per warp).
+// needs no barrier: it only takes the loads of the next tile off the registers' hands (8 KB in
+// flight per warp, twelve warps per SM).
 template <bool kBF16>
 __device__ __forceinline__ void mma16816(float (&acc)[4], const uint32_t (&a)[4], uint32_t b0, uint32_t b1) {
   if constexpr (kBF16)
@@ -322,6 +323,11 @@ __device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commi
 template <int N> __device__ __forceinline__ void cp_async_wait() {
   asm volatile("cp.async.wait_group %0;" ::"n"(N) : "memory");
 }
+__device__ __forceinline__ float ex2_approx(float x) { // 2^x; -inf gives 0
+  float y;
+  asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+  return y;
+}
 __device__ __forceinline__ uint4 lds_v4(uint32_t smem_addr) {
   uint4 v;
   asm volatile("ld.shared.v4.u32 {%0,%1,%2,%3}, [%4];" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "r"(smem_addr));
@@ -329,11 +335,13 @@ __device__ __forceinline__ uint4 lds_v4(uint32_t smem_addr) {
 }
 
 constexpr int kMmaRows = 16;                   // query rows of one block
-constexpr int kMmaStages = 3;                  // tiles of the cp.async ring
-constexpr int kMmaKeysPerStep = 16 * kDecodeWarps;
+constexpr int kMmaStages = 2;                  // tiles of the cp.async ring: one in flight, one in use
+constexpr int kMmaWarps = 4;                   // three such blocks share an SM and overlap each other's ends
+constexpr int kMmaThreads = kMmaWarps * 32;
+constexpr int kMmaKeysPerStep = 16 * kMmaWarps;
 
 template <int D, bool kBF16>
-__global__ void __launch_bounds__(kDecodeThreads, 1) decode_mma_kernel(const DecodeParams p) {
+__global__ void __launch_bounds__(kMmaThreads, 3) decode_mma_kernel(const DecodeParams p) {
   using T = typename std::conditional<kBF16, __nv_bfloat16, __half>::type;
   constexpr int NT = D / 8;  // output n-tiles
   constexpr int KS2 = D / 32; // pairs of k-steps of Q K^T
@@ -343,9 +351,10 @@ __global__ void __launch_bounds__(kDecodeThreads, 1) decode_mma_kernel(const Dec
   // ring: [stage][vector][thread] 16-byte slots; after the loop the same memory holds the merge buffers
   const uint32_t ring = (uint32_t)__cvta_generic_to_shared(decode_smem) + threadIdx.x * 16u;
   float *sm_acc = decode_smem;                                 // [warp][row][D]
-  float *sm_m = decode_smem + kDecodeWarps * kMmaRows * D;     // [warp][row]
-  float *sm_l = sm_m + kDecodeWarps * kMmaRows;
+  float *sm_m = decode_smem + kMmaWarps * kMmaRows * D;     // [warp][row]
+  float *sm_l = sm_m + kMmaWarps * kMmaRows;
 
+  pdl_launch_dependents(); // the merge kernel may take free slots once every block of this grid runs
   const int split = blockIdx.x;
   const int chunk = blockIdx.y % p.chunks, hk = blockIdx.y / p.chunks;
   const int b = blockIdx.z;
@@ -396,7 +405,7 @@ __global__ void __launch_bounds__(kDecodeThreads, 1) decode_mma_kernel(const Dec
   // append: the blocks of the first row chunk copy all new rows into the cache, 16 bytes a thread
   if (chunk == 0) {
     const int pieces = (len - cache_len) * (D / 8);
-    for (int idx = split * kDecodeThreads + (int)threadIdx.x; idx < pieces; idx += p.splits * kDecodeThreads) {
+    for (int idx = split * kMmaThreads + (int)threadIdx.x; idx < pieces; idx += p.splits * kMmaThreads) {
       const int jn = idx / (D / 8), e = (idx % (D / 8)) * 8;
       *reinterpret_cast<uint4 *>(kc + (int64_t)(cache_len + jn) * p.k_rs + e) = ld_nc_v4(kn + (int64_t)jn * p.kn_rs + e);
       *reinterpret_cast<uint4 *>(vc + (int64_t)(cache_len + jn) * p.v_rs + e) = ld_nc_v4(vn + (int64_t)jn * p.vn_rs + e);
@@ -404,28 +413,62 @@ __global__ void __launch_bounds__(kDecodeThreads, 1) decode_mma_kernel(const Dec
   }
 
   // vectors of a tile: K of keys j0 + 8 nt + g, head-dim values [32 s2 + 8 c, +8)  (index nt * KS2 + s2);
-  // V of keys j0 + 8 (ki / 2) + 2 c + ki % 2, columns [64 hb + 8 g, +8)  (index 2 KS2 + ki * HB + hb)
-  auto issue_tile = [&](int j0, int stage) {
-    const uint32_t base = ring + (uint32_t)stage * (NV * kDecodeThreads * 16);
+  // V of keys j0 + 8 (ki / 2) + 2 c + ki % 2, columns [64 hb + 8 g, +8)  (index 2 KS2 + ki * HB + hb).
+  // Tiles that lie wholly in the old part of the cache (all but the last few) take their row
+  // addresses from running pointers; the others work them out row by row.
+  const int j_first = j_begin + warp * 16;
+  const T *kp[2], *vp[4];
 #pragma unroll
-    for (int nt = 0; nt < 2; ++nt) {
-      const int j = j0 + 8 * nt + g;
-      const bool real = j < j_end;
-      const T *row = !real ? kc : (j < cache_len ? kc + (int64_t)j * p.k_rs : kn + (int64_t)(j - cache_len) * p.kn_rs);
+  for (int nt = 0; nt < 2; ++nt)
+    kp[nt] = kc + (int64_t)(j_first + 8 * nt + g) * p.k_rs + 8 * c;
 #pragma unroll
-      for (int s2 = 0; s2 < KS2; ++s2)
-        cp_async16(base + (nt * KS2 + s2) * (kDecodeThreads * 16), row + 32 * s2 + 8 * c, real);
+  for (int ki = 0; ki < 4; ++ki)
+    vp[ki] = vc + (int64_t)(j_first + 8 * (ki >> 1) + 2 * c + (ki & 1)) * p.v_rs + 8 * g;
+  const int64_t k_step = (int64_t)kMmaKeysPerStep * p.k_rs, v_step = (int64_t)kMmaKeysPerStep * p.v_rs;
+  const int plain_end = min(cache_len, j_end);
+  auto issue_tile = [&](int j0, int stage) { // tiles are issued in order, one block step apart
+    const uint32_t base = ring + (uint32_t)stage * (NV * kMmaThreads * 16);
+    if (j0 + 16 <= plain_end) {
+#pragma unroll
+      for (int nt = 0; nt < 2; ++nt)
+#pragma unroll
+        for (int s2 = 0; s2 < KS2; ++s2)
+          cp_async16(base + (nt * KS2 + s2) * (kMmaThreads * 16), kp[nt] + 32 * s2, true);
+#pragma unroll
+      for (int ki = 0; ki < 4; ++ki)
+#pragma unroll
+        for (int hb = 0; hb < HB; ++hb)
+          cp_async16(base + (2 * KS2 + ki * HB + hb) * (kMmaThreads * 16), vp[ki] + 64 * hb, true);
+    } else {
+#pragma unroll
+      for (int nt = 0; nt < 2; ++nt) {
+        const int j = j0 + 8 * nt + g;
+        const bool real = j < j_end;
+        const T *row = !real ? kc : (j < cache_len ? kc + (int64_t)j * p.k_rs : kn + (int64_t)(j - cache_len) * p.kn_rs);
+#pragma unroll
+        for (int s2 = 0; s2 < KS2; ++s2)
+          cp_async16(base + (nt * KS2 + s2) * (kMmaThreads * 16), row + 32 * s2 + 8 * c, real);
+      }
+#pragma unroll
+      for (int ki = 0; ki < 4; ++ki) {
+        const int j = j0 + 8 * (ki >> 1) + 2 * c + (ki & 1);
+        const bool real = j < j_end;
+        const T *row = !real ? vc : (j < cache_len ? vc + (int64_t)j * p.v_rs : vn + (int64_t)(j - cache_len) * p.vn_rs);
+#pragma unroll
+        for (int hb = 0; hb < HB; ++hb)
+          cp_async16(base + (2 * KS2 + ki * HB + hb) * (kMmaThreads * 16), row + 64 * hb + 8 * g, real);
+      }
     }
 #pragma unroll
-    for (int ki = 0; ki < 4; ++ki) {
-      const int j = j0 + 8 * (ki >> 1) + 2 * c + (ki & 1);
-      const bool real = j < j_end;
-      const T *row = !real ? vc : (j < cache_len ? vc + (int64_t)j * p.v_rs : vn + (int64_t)(j - cache_len) * p.vn_rs);
+    for (int nt = 0; nt < 2; ++nt)
+      kp[nt] += k_step;
 #pragma unroll
-      for (int hb = 0; hb < HB; ++hb)
-        cp_async16(base + (2 * KS2 + ki * HB + hb) * (kDecodeThreads * 16), row + 64 * hb + 8 * g, real);
-    }
+    for (int ki = 0; ki < 4; ++ki)
+      vp[ki] += v_step;
   };
+  // tiles [j0, j0 + 16) inside [seen_lo, seen_hi) are visible to every row of the block: no masking
+  const int seen_lo = p.window_left >= 0 ? i_max + shift - p.window_left : 0;
+  const int seen_hi = min(j_end, p.window_right >= 0 ? i_min + shift + p.window_right + 1 : j_end);
 
   float o[NT][4];
 #pragma unroll
@@ -433,7 +476,7 @@ __global__ void __launch_bounds__(kDecodeThreads, 1) decode_mma_kernel(const Dec
     o[t][0] = o[t][1] = o[t][2] = o[t][3] = 0.f;
   float m_a = -INFINITY, m_b = -INFINITY, l_a = 0.f, l_b = 0.f;
 
-  int j0 = j_begin + warp * 16;
+  int j0 = j_first;
 #pragma unroll
   for (int st = 0; st < kMmaStages - 1; ++st) { // one group per tile, empty past the end
     if (j0 + st * kMmaKeysPerStep < j_end)
@@ -449,41 +492,46 @@ __global__ void __launch_bounds__(kDecodeThreads, 1) decode_mma_kernel(const Dec
         issue_tile(j_ahead, (it + kMmaStages - 1) % kMmaStages);
       cp_async_commit();
     }
-    const uint32_t base = ring + (uint32_t)(it % kMmaStages) * (NV * kDecodeThreads * 16);
+    const uint32_t base = ring + (uint32_t)(it % kMmaStages) * (NV * kMmaThreads * 16);
     float s[2][4];
 #pragma unroll
     for (int nt = 0; nt < 2; ++nt) {
       s[nt][0] = s[nt][1] = s[nt][2] = s[nt][3] = 0.f;
 #pragma unroll
       for (int s2 = 0; s2 < KS2; ++s2) {
-        const uint4 kv = lds_v4(base + (nt * KS2 + s2) * (kDecodeThreads * 16));
+        const uint4 kv = lds_v4(base + (nt * KS2 + s2) * (kMmaThreads * 16));
         mma16816<kBF16>(s[nt], qa[s2][0], kv.x, kv.y);
         mma16816<kBF16>(s[nt], qa[s2][1], kv.z, kv.w);
       }
     }
 
     // s[nt][e]: key j0 + 8 nt + 2 c + (e & 1), row a for e < 2, row b otherwise
-    float mx_a = -INFINITY, mx_b = -INFINITY;
+    if (j0 >= seen_lo && j0 + 16 <= seen_hi) {
 #pragma unroll
-    for (int nt = 0; nt < 2; ++nt)
+      for (int nt = 0; nt < 2; ++nt)
 #pragma unroll
-      for (int e = 0; e < 4; ++e) {
-        const int j = j0 + 8 * nt + 2 * c + (e & 1);
-        const int qi = e < 2 ? qi_a : qi_b;
-        bool visible = j < j_end && (e < 2 ? valid_a : valid_b);
-        if (p.window_right >= 0 && j > qi + shift + p.window_right)
-          visible = false;
-        if (p.window_left >= 0 && j < qi + shift - p.window_left)
-          visible = false;
-        s[nt][e] = visible ? s[nt][e] * p.scale_log2 : -INFINITY;
-        if (e < 2)
-          mx_a = fmaxf(mx_a, s[nt][e]);
-        else
-          mx_b = fmaxf(mx_b, s[nt][e]);
-      }
+        for (int e = 0; e < 4; ++e)
+          s[nt][e] *= p.scale_log2;
+    } else {
+#pragma unroll
+      for (int nt = 0; nt < 2; ++nt)
+#pragma unroll
+        for (int e = 0; e < 4; ++e) {
+          const int j = j0 + 8 * nt + 2 * c + (e & 1);
+          const int qi = e < 2 ? qi_a : qi_b;
+          bool visible = j < j_end && (e < 2 ? valid_a : valid_b);
+          if (p.window_right >= 0 && j > qi + shift + p.window_right)
+            visible = false;
+          if (p.window_left >= 0 && j < qi + shift - p.window_left)
+            visible = false;
+          s[nt][e] = visible ? s[nt][e] * p.scale_log2 : -INFINITY;
+        }
+    }
+    float mx_a = fmaxf(fmaxf(s[0][0], s[0][1]), fmaxf(s[1][0], s[1][1]));
+    float mx_b = fmaxf(fmaxf(s[0][2], s[0][3]), fmaxf(s[1][2], s[1][3]));
     mx_a = fmaxf(mx_a, __shfl_xor_sync(0xffffffffu, mx_a, 1));
-    mx_a = fmaxf(mx_a, __shfl_xor_sync(0xffffffffu, mx_a, 2));
     mx_b = fmaxf(mx_b, __shfl_xor_sync(0xffffffffu, mx_b, 1));
+    mx_a = fmaxf(mx_a, __shfl_xor_sync(0xffffffffu, mx_a, 2));
     mx_b = fmaxf(mx_b, __shfl_xor_sync(0xffffffffu, mx_b, 2));
     const float new_a = fmaxf(m_a, mx_a), new_b = fmaxf(m_b, mx_b);
     if (__any_sync(0xffffffffu, new_a > m_a || new_b > m_b)) { // some row's maximum grew: rescale
@@ -497,11 +545,13 @@ __global__ void __launch_bounds__(kDecodeThreads, 1) decode_mma_kernel(const Dec
       }
       m_a = new_a, m_b = new_b;
     }
+    // a row that has seen nothing yet has only -inf scores: subtract 0 from them, not -inf
+    const float sub_a = m_a == -INFINITY ? 0.f : m_a, sub_b = m_b == -INFINITY ? 0.f : m_b;
 #pragma unroll
     for (int nt = 0; nt < 2; ++nt)
 #pragma unroll
       for (int e = 0; e < 4; ++e) {
-        const float pr = s[nt][e] == -INFINITY ? 0.f : exp2f(s[nt][e] - (e < 2 ? m_a : m_b));
+        const float pr = ex2_approx(s[nt][e] - (e < 2 ? sub_a : sub_b));
         s[nt][e] = pr;
         if (e < 2)
           l_a += pr;
@@ -515,7 +565,7 @@ __global__ void __launch_bounds__(kDecodeThreads, 1) decode_mma_kernel(const Dec
       uint4 vreg[4];
 #pragma unroll
       for (int ki = 0; ki < 4; ++ki)
-        vreg[ki] = lds_v4(base + (2 * KS2 + ki * HB + hb) * (kDecodeThreads * 16));
+        vreg[ki] = lds_v4(base + (2 * KS2 + ki * HB + hb) * (kMmaThreads * 16));
 #pragma unroll
       for (int e = 0; e < 8; ++e) {
         const uint32_t sel = (e & 1) ? 0x7632u : 0x5410u;
@@ -549,18 +599,18 @@ __global__ void __launch_bounds__(kDecodeThreads, 1) decode_mma_kernel(const Dec
   __syncthreads();
 
   // merge the warps; one thread per (row, element)
-  for (int idx = threadIdx.x; idx < kMmaRows * D; idx += kDecodeThreads) {
+  for (int idx = threadIdx.x; idx < kMmaRows * D; idx += kMmaThreads) {
     const int t = idx / D, e = idx % D;
     const int r = r0 + t;
     if (r >= p.rows_per_kv)
       continue;
     float mx = -INFINITY;
 #pragma unroll
-    for (int w = 0; w < kDecodeWarps; ++w)
+    for (int w = 0; w < kMmaWarps; ++w)
       mx = fmaxf(mx, sm_m[w * kMmaRows + t]);
     float sum = 0.f, val = 0.f;
 #pragma unroll
-    for (int w = 0; w < kDecodeWarps; ++w) {
+    for (int w = 0; w < kMmaWarps; ++w) {
       const float a = scale_of(sm_m[w * kMmaRows + t], mx);
       sum += sm_l[w * kMmaRows + t] * a;
       val += sm_acc[((size_t)w * kMmaRows + t) * D + e] * a;
@@ -583,46 +633,63 @@ __global__ void __launch_bounds__(kDecodeThreads, 1) decode_mma_kernel(const Dec
   }
 }
 
-// one block per query row: merges the partial results of the splits
+// one block per query row: merges the partial results of the splits.  Thread s takes split s's
+// (max, sum), so those loads are one round trip; the output columns then read the splits eight
+// at a time.
 template <bool kBF16>
 __global__ void __launch_bounds__(128) decode_merge_kernel(const DecodeParams p) {
   using T = typename std::conditional<kBF16, __nv_bfloat16, __half>::type;
+  static_assert(kMaxSplits <= 128, "one thread per split");
   __shared__ float weight[kMaxSplits];
-  __shared__ float total;
+  __shared__ float red[2][4];
   const int64_t row = blockIdx.x;
+  const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+  pdl_wait(); // the partial results of the split kernel
   const int i = (int)(row % p.seqlen_q);
   const int head = (int)((row / p.seqlen_q) % p.h);
   const int b = (int)(row / ((int64_t)p.seqlen_q * p.h));
-  const float *ml = p.part_ml + row * p.splits * 2;
-  float mx = -INFINITY;
-  for (int s = 0; s < p.splits; ++s)
-    mx = fmaxf(mx, ml[2 * s]);
-  if (threadIdx.x < 32) {
-    float sum = 0.f;
-    for (int s = threadIdx.x; s < p.splits; s += 32) {
-      const float a = scale_of(ml[2 * s], mx);
-      weight[s] = a;
-      sum += ml[2 * s + 1] * a;
-    }
+  const float2 ml = tid < p.splits ? reinterpret_cast<const float2 *>(p.part_ml)[row * p.splits + tid]
+                                   : make_float2(-INFINITY, 0.f);
+  float mx = ml.x;
 #pragma unroll
-    for (int o = 16; o > 0; o >>= 1)
-      sum += __shfl_xor_sync(0xffffffffu, sum, o);
-    if (threadIdx.x == 0) {
-      total = sum;
-      p.lse[row] = sum > 0.f ? mx * kLn2 + logf(sum) : INFINITY;
-    }
-  }
+  for (int o = 16; o > 0; o >>= 1)
+    mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, o));
+  if (lane == 0)
+    red[0][warp] = mx;
   __syncthreads();
+  mx = fmaxf(fmaxf(red[0][0], red[0][1]), fmaxf(red[0][2], red[0][3]));
+  const float w = scale_of(ml.x, mx);
+  if (tid < p.splits)
+    weight[tid] = w;
+  float sum = ml.y * w;
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1)
+    sum += __shfl_xor_sync(0xffffffffu, sum, o);
+  if (lane == 0)
+    red[1][warp] = sum;
+  __syncthreads();
+  const float total = red[1][0] + red[1][1] + red[1][2] + red[1][3];
+  if (tid == 0)
+    p.lse[row] = total > 0.f ? mx * kLn2 + logf(total) : INFINITY;
   const float inv = total > 0.f ? 1.f / total : 0.f;
   const float *po = p.part_o + row * p.splits * p.d;
   T *op = static_cast<T *>(p.o) + (int64_t)b * p.o_bs + (int64_t)i * p.o_rs + (int64_t)head * p.o_hs;
-  for (int e = threadIdx.x; e < p.d; e += blockDim.x) {
+  for (int e = tid; e < p.d; e += blockDim.x) {
     float val = 0.f;
-    for (int s = 0; s < p.splits; ++s)
-      val = fmaf(po[(int64_t)s * p.d + e], weight[s], val);
+    for (int s0 = 0; s0 < p.splits; s0 += 8) {
+      float part[8];
+#pragma unroll
+      for (int u = 0; u < 8; ++u)
+        part[u] = s0 + u < p.splits ? po[(int64_t)(s0 + u) * p.d + e] : 0.f;
+#pragma unroll
+      for (int u = 0; u < 8; ++u)
+        val = fmaf(part[u], s0 + u < p.splits ? weight[s0 + u] : 0.f, val);
+    }
     op[e] = Elt<T>::from_f32(val * inv);
   }
 }
+
+int g_splits_override = 0; // tuning door: a fixed number of key ranges per (batch, kv head, row chunk)
 
 struct DecodePlan {
   bool mma; // head dim 64 or 128: the tensor-core kernel, 16 query rows a block
@@ -661,11 +728,23 @@ int make_plan(const b200_flash_kvcache_params &p, DecodePlan *plan) {
     return B200_ERR_UNSUPPORTED;
   const int64_t keys_per_step = plan->mma ? kMmaKeysPerStep : (int64_t)kDecodeWarps * 32 / plan->lpk;
   const int64_t base = p.b * p.h_k * plan->chunks;
-  // enough blocks to fill every SM a few times over (the tensor-core kernel has one block per SM,
-  // the scalar one up to four), as long as every split keeps four block steps of keys
-  const int64_t want = ceil_div<int64_t>((int64_t)kNumSMs * (plan->mma ? 2 : 4), base);
+  // enough blocks for about four per SM (more and shorter blocks measured slower: a block's
+  // start and merge are not free), as long as every split keeps four block steps of keys;
+  // among the counts up to twice that, the one whose last wave of blocks is fullest
+  const int64_t slots = (int64_t)kNumSMs * (plan->mma ? 3 : 4); // blocks the GPU holds at a time
   const int64_t room = std::max<int64_t>(1, p.seqlen_k / (4 * keys_per_step));
-  plan->splits = (int)std::max<int64_t>(1, std::min<int64_t>({want, room, (int64_t)kMaxSplits}));
+  const int64_t cap = std::min<int64_t>(room, kMaxSplits);
+  const int64_t want = std::min<int64_t>(cap, ceil_div<int64_t>((int64_t)kNumSMs * 4, base));
+  int64_t best = want;
+  double best_fill = 0.0;
+  for (int64_t n = want; n <= std::min<int64_t>(cap, 2 * want); ++n) {
+    const double fill = (double)(base * n) / (double)(ceil_div<int64_t>(base * n, slots) * slots);
+    if (fill > best_fill + 1e-9)
+      best = n, best_fill = fill;
+  }
+  plan->splits = (int)std::max<int64_t>(1, best);
+  if (g_splits_override > 0)
+    plan->splits = (int)std::min<int64_t>(g_splits_override, cap);
   plan->rows = p.b * p.h * p.seqlen_q;
   plan->workspace_bytes =
       plan->splits > 1 ? (size_t)plan->rows * plan->splits * ((size_t)p.d + 2) * sizeof(float) : 0;
@@ -690,14 +769,14 @@ template <bool kBF16> int launch_decode(const DecodeParams &dp, const DecodePlan
   const dim3 grid((unsigned)plan.splits, (unsigned)(plan.chunks * dp.h_k), (unsigned)dp.b);
   int rc;
   if (plan.mma) {
-    // the cp.async ring (16 bytes x d/8 vectors x 256 threads a stage); the merge buffers reuse it
-    const size_t ring = (size_t)kMmaStages * (dp.d / 8) * kDecodeThreads * 16;
-    const size_t smem = std::max(ring, ((size_t)kDecodeWarps * kMmaRows * (dp.d + 2)) * sizeof(float));
+    // the cp.async ring (16 bytes x d/8 vectors x 128 threads a stage); the merge buffers reuse it
+    const size_t ring = (size_t)kMmaStages * (dp.d / 8) * kMmaThreads * 16;
+    const size_t smem = std::max(ring, ((size_t)kMmaWarps * kMmaRows * (dp.d + 2)) * sizeof(float));
     auto kernel = dp.d == 128 ? decode_mma_kernel<128, kBF16> : decode_mma_kernel<64, kBF16>;
     // the attribute belongs to the current device's context: set it on every call
     if (int e = check_cuda(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem)))
       return e;
-    kernel<<<grid, kDecodeThreads, smem, stream>>>(dp);
+    kernel<<<grid, kMmaThreads, smem, stream>>>(dp);
     rc = check_launch();
   } else
   switch (plan.lpk) {
@@ -715,14 +794,17 @@ template <bool kBF16> int launch_decode(const DecodeParams &dp, const DecodePlan
   }
   if (rc != B200_OK || plan.splits == 1)
     return rc;
-  decode_merge_kernel<kBF16><<<(unsigned)plan.rows, 128, 0, stream>>>(dp);
-  return check_launch();
+  // launched while the split kernel's last wave still runs; it waits for that grid before it reads
+  return launch_pdl(decode_merge_kernel<kBF16>, dim3((unsigned)plan.rows), dim3(128), 0, stream, dp);
 }
 
 } // namespace
 } // namespace b200
 
 using namespace b200;
+
+// not in the header: fixes the number of key ranges (0 = automatic), for tuning runs
+extern "C" void b200_flash_attn_kvcache_tune(int splits) { g_splits_override = splits; }
 
 extern "C" int64_t b200_flash_attn_kvcache_workspace_bytes(const b200_flash_kvcache_params *params) {
   DecodePlan plan;
