@@ -49,6 +49,7 @@ NCU_TRAFFIC = {
     "gather": 62.25e6 + 24.40e6,         # gather_generic_kernel (profiles/gather_ncu_full.md)
     "scatter": 81.86e6 + 5.33e6,         # scatter_chunk_kernel alone (profiles/chunk_ncu_full.md)
     "attn": 16 * (50.40e6 + 0.98e6),     # flash_fwd_kernel<bf16> (profiles/flash_fwd_ncu_full.md)
+    "decode": 452.36e6 + 4.24e6,         # decode_mma_kernel<128, bf16> (profiles/decode_ncu_full.md)
 }
 
 

@@ -13,16 +13,17 @@
 // The work is a stream over the cache: 4*d bytes per key against 4*d flops per key and
 // query row, so with the few query rows of a decode step it is bound by HBM.  The
 // reference runs one block per (batch, head) (num_splits = 1), which leaves most of a
-// B200 idle when batch * heads < 148; here the keys of one (batch, kv head) are split
-// over enough blocks to fill the GPU and a second small kernel merges the partial
-// results.  All query heads that share a kv head are rows of the same block, so a grouped
-// cache is read once per row chunk.
+// B200 idle when batch * heads < 148; here the keys of every (batch entry, kv head) are cut
+// into ranges, enough to fill the GPU, and a second small kernel merges the partial (max,
+// sum, output) of the ranges.  All query heads that share a kv head are rows of the same
+// block, so a grouped cache is read once per row chunk.
 //
-// Thread mapping: a key row of d 16-bit values is read by LPK = pow2(d / 8) lanes, 16
-// bytes each, so a warp takes 32 / LPK keys per step and the 8 warps of a block
-// 8 * 32 / LPK.  Every lane group keeps a running (max, sum, output slice) per query
-// row in registers, rescaled only when the maximum grows; groups are merged by shuffles,
-// warps through shared memory, splits by the merge kernel.
+// Two kernels.  Head dims 64 and 128 (decode_mma_kernel): scores and outputs on tensor-core
+// tiles, 16 query rows a block.  Other head dims (decode_split_kernel): a key row of d 16-bit
+// values is read by LPK = pow2(d / 8) lanes, 16 bytes each, so a warp takes 32 / LPK keys per
+// step; every lane group keeps a running (max, sum, output slice) per query row in registers,
+// rescaled only when the maximum grows; groups are merged by shuffles, warps through shared
+// memory.
 #include "common.cuh"
 
 #include <algorithm>
@@ -728,19 +729,26 @@ int make_plan(const b200_flash_kvcache_params &p, DecodePlan *plan) {
     return B200_ERR_UNSUPPORTED;
   const int64_t keys_per_step = plan->mma ? kMmaKeysPerStep : (int64_t)kDecodeWarps * 32 / plan->lpk;
   const int64_t base = p.b * p.h_k * plan->chunks;
-  // enough blocks for about four per SM (more and shorter blocks measured slower: a block's
-  // start and merge are not free), as long as every split keeps four block steps of keys;
-  // among the counts up to twice that, the one whose last wave of blocks is fullest
+  // Measured: the tensor-core kernel streams fastest as ONE wave of at most two blocks per SM
+  // (a block keeps a fixed number of bytes in flight, and a ragged second wave costs more than
+  // the idle slots of a first one); when (batch, kv head, row chunk) alone exceed that, and for
+  // the scalar kernel, about four blocks per SM, taking among the counts up to twice that the
+  // one whose last wave is fullest.  Every range keeps at least four block steps of keys.
   const int64_t slots = (int64_t)kNumSMs * (plan->mma ? 3 : 4); // blocks the GPU holds at a time
   const int64_t room = std::max<int64_t>(1, p.seqlen_k / (4 * keys_per_step));
   const int64_t cap = std::min<int64_t>(room, kMaxSplits);
-  const int64_t want = std::min<int64_t>(cap, ceil_div<int64_t>((int64_t)kNumSMs * 4, base));
-  int64_t best = want;
-  double best_fill = 0.0;
-  for (int64_t n = want; n <= std::min<int64_t>(cap, 2 * want); ++n) {
-    const double fill = (double)(base * n) / (double)(ceil_div<int64_t>(base * n, slots) * slots);
-    if (fill > best_fill + 1e-9)
-      best = n, best_fill = fill;
+  int64_t best;
+  if (plan->mma && base <= 2 * kNumSMs) {
+    best = std::min<int64_t>(cap, 2 * kNumSMs / base);
+  } else {
+    const int64_t want = std::min<int64_t>(cap, ceil_div<int64_t>((int64_t)kNumSMs * 4, base));
+    best = want;
+    double best_fill = 0.0;
+    for (int64_t n = want; n <= std::min<int64_t>(cap, 2 * want); ++n) {
+      const double fill = (double)(base * n) / (double)(ceil_div<int64_t>(base * n, slots) * slots);
+      if (fill > best_fill + 1e-9)
+        best = n, best_fill = fill;
+    }
   }
   plan->splits = (int)std::max<int64_t>(1, best);
   if (g_splits_override > 0)

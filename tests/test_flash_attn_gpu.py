@@ -183,6 +183,8 @@ KV_CASES = [
     (2, 2, 8, 2, 128, 700, 2, True, (100, 0), [698, 300]),             # sliding window on the tensor-core path
     (2, 2, 8, 2, 64, 700, 2, False, (30, 5), [690, 0]),                # window on both sides, head dim 64
     (3, 7, 4, 4, 128, 50, 7, True, (-1, -1), [43, 0, 20]),             # more new rows than a block step of the append
+    (8, 1, 8, 2, 128, 4096, 1, True, (-1, -1), [4000, 3, 0, 10, 1, 0, 7, 2]),  # one entry holds nearly all the keys
+    (150, 1, 4, 2, 64, 300, 1, True, (-1, -1), "ragged"),              # more batch entries than threads in a block
 ]
 
 
@@ -195,6 +197,8 @@ def test_flash_attn_kvcache(b, sq, h, hk, d, cap, s_new, causal, window, lens, d
     kc, vc = _mk(rng, (b, cap, hk, d), dt), _mk(rng, (b, cap, hk, d), dt)
     kn = _mk(rng, (b, s_new, hk, d), dt) if s_new else None
     vn = _mk(rng, (b, s_new, hk, d), dt) if s_new else None
+    if lens == "ragged":  # from empty to full, a quarter of them empty
+        lens = [0 if i % 4 == 1 else int(v) for i, v in enumerate(rng.integers(0, cap - s_new + 1, b))]
     lens_h = None if lens == "full" else np.array(lens, np.int32)
     scale = 1.0 / np.sqrt(d)
     want_k, want_v = kc.copy(), vc.copy()
