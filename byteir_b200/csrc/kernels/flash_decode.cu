@@ -286,8 +286,7 @@ __global__ void __launch_bounds__(kDecodeThreads) decode_split_kernel(const Deco
 // and a warp reads whole 128-byte lines.  The output column of accumulator (n-tile t, logical
 // column n) is 64 (t / 8) + 8 n + t % 8.  The vectors travel through a ring of cp.async stages
 // in shared memory in which every thread owns the slots it later reads itself, so the ring
-// needs no barrier: it only takes the loads of the next tile off the registers' hands (8 KB in
-// flight per warp, twelve warps per SM).
+// needs no barrier: it only takes the loads of the next one or two tiles off the registers' hands.
 template <bool kBF16>
 __device__ __forceinline__ void mma16816(float (&acc)[4], const uint32_t (&a)[4], uint32_t b0, uint32_t b1) {
   if constexpr (kBF16)
@@ -336,18 +335,21 @@ __device__ __forceinline__ uint4 lds_v4(uint32_t smem_addr) {
 }
 
 constexpr int kMmaRows = 16;                   // query rows of one block
-constexpr int kMmaStages = 2;                  // tiles of the cp.async ring: one in flight, one in use
+// tiles of the cp.async ring: the one in use and one (head dim 128) or two (64) in flight; measured:
+// a third stage slows head dim 128 down (104 -> 117 us on a 512 MiB cache) and speeds 64 up (65 -> 59 us)
+constexpr int mma_stages(int d) { return d == 128 ? 2 : 3; }
 constexpr int kMmaWarps = 4;                   // three such blocks share an SM and overlap each other's ends
 constexpr int kMmaThreads = kMmaWarps * 32;
 constexpr int kMmaKeysPerStep = 16 * kMmaWarps;
 
 template <int D, bool kBF16>
-__global__ void __launch_bounds__(kMmaThreads, 3) decode_mma_kernel(const DecodeParams p) {
+__global__ void __launch_bounds__(kMmaThreads, D == 128 ? 3 : 2) decode_mma_kernel(const DecodeParams p) {
   using T = typename std::conditional<kBF16, __nv_bfloat16, __half>::type;
   constexpr int NT = D / 8;  // output n-tiles
   constexpr int KS2 = D / 32; // pairs of k-steps of Q K^T
   constexpr int HB = D / 64;
   constexpr int NV = 2 * KS2 + 4 * HB; // 16-byte vectors of K and V a thread takes per tile
+  constexpr int kMmaStages = mma_stages(D);
   extern __shared__ __align__(16) float decode_smem[];
   // ring: [stage][vector][thread] 16-byte slots; after the loop the same memory holds the merge buffers
   const uint32_t ring = (uint32_t)__cvta_generic_to_shared(decode_smem) + threadIdx.x * 16u;
@@ -778,7 +780,7 @@ template <bool kBF16> int launch_decode(const DecodeParams &dp, const DecodePlan
   int rc;
   if (plan.mma) {
     // the cp.async ring (16 bytes x d/8 vectors x 128 threads a stage); the merge buffers reuse it
-    const size_t ring = (size_t)kMmaStages * (dp.d / 8) * kMmaThreads * 16;
+    const size_t ring = (size_t)mma_stages(dp.d) * (dp.d / 8) * kMmaThreads * 16;
     const size_t smem = std::max(ring, ((size_t)kMmaWarps * kMmaRows * (dp.d + 2)) * sizeof(float));
     auto kernel = dp.d == 128 ? decode_mma_kernel<128, kBF16> : decode_mma_kernel<64, kBF16>;
     // the attribute belongs to the current device's context: set it on every call
