@@ -429,11 +429,13 @@ private:
     if (TryKeyword("true")) {
       a->dense_i.push_back(1);
       a->dense_f.push_back(1);
+      a->splat = a->splat || depth == 0;
       return;
     }
     if (TryKeyword("false")) {
       a->dense_i.push_back(0);
       a->dense_f.push_back(0);
+      a->splat = a->splat || depth == 0;
       return;
     }
     if (Peek() == '"') { // hex blob: keep the text, values unavailable

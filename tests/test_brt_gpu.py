@@ -179,10 +179,12 @@ def test_host_device_copies_and_fill_through_session():
     three = torch.zeros(3, dtype=torch.float16, device="cuda")
     halves = torch.zeros(1001, dtype=torch.float16, device="cuda")
     sevens = torch.zeros(37, dtype=torch.int64, device="cuda")
+    flags = torch.zeros(3, dtype=torch.bool, device="cuda")
     s = brt.Session("cuda", host_space=True)
     s.load_from_memory(HOST_DEVICE)
     req = s.new_request(torch.cuda.current_stream().cuda_stream)
-    for name, t in (("A", a_host), ("Sum", sum_host), ("Three", three), ("Halves", halves), ("Sevens", sevens)):
+    for name, t in (("A", a_host), ("Sum", sum_host), ("Three", three), ("Halves", halves), ("Sevens", sevens),
+                    ("Flags", flags)):
         info = s.arg_info(s.arg_offset(name))
         assert info.space == ("cpu" if not t.is_cuda else "cuda") and info.nbytes == t.numel() * t.element_size()
         req.bind_arg(info.offset, t.data_ptr())
@@ -194,7 +196,7 @@ def test_host_device_copies_and_fill_through_session():
     want = O.reduce("sum", a_host.numpy(), 1024, 256, 1)
     np.testing.assert_allclose(sum_host.numpy(), want, rtol=1e-5, atol=1e-5)
     assert three.cpu().tolist() == [1.0, 2.0, 3.0]
-    assert torch.all(halves == 0.5) and torch.all(sevens == 7)
+    assert torch.all(halves == 0.5) and torch.all(sevens == 7) and torch.all(flags)
     req.close()
     s.close()
 

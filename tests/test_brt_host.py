@@ -305,7 +305,8 @@ module attributes {byre.container_module} {
                   %arg1: memref<1024xf32, "cpu"> {byre.argname = "Sum", byre.argtype = 2 : i32},
                   %arg2: memref<3xf16, "cuda"> {byre.argname = "Three", byre.argtype = 2 : i32},
                   %arg3: memref<1001xf16, "cuda"> {byre.argname = "Halves", byre.argtype = 2 : i32},
-                  %arg4: memref<37xi64, "cuda"> {byre.argname = "Sevens", byre.argtype = 2 : i32}) attributes {byre.entry_point} {
+                  %arg4: memref<37xi64, "cuda"> {byre.argname = "Sevens", byre.argtype = 2 : i32},
+                  %arg5: memref<3xi1, "cuda"> {byre.argname = "Flags", byre.argtype = 2 : i32}) attributes {byre.entry_point} {
     %0 = memref.alloc() : memref<1024x256xf32, "cuda">
     %1 = memref.alloc() : memref<1024xf32, "cuda">
     byre.compute @cpu2cuda(%arg0, %0) {memory_effects = [1 : i32, 2 : i32]} : memref<1024x256xf32, "cpu">, memref<1024x256xf32, "cuda">
@@ -314,6 +315,7 @@ module attributes {byre.container_module} {
     byre.compute @FillOp(%arg2) {value = dense<[1.000000e+00, 2.000000e+00, 3.000000e+00]> : tensor<3xf16>} : memref<3xf16, "cuda">
     byre.compute @FillOp(%arg3) {value = dense<5.000000e-01> : tensor<1001xf16>} : memref<1001xf16, "cuda">
     byre.compute @FillOp(%arg4) {value = dense<7> : tensor<37xi64>} : memref<37xi64, "cuda">
+    byre.compute @FillOp(%arg5) {value = dense<true> : tensor<3xi1>} : memref<3xi1, "cuda">
     return
   }
 }
@@ -325,10 +327,36 @@ def test_host_device_copies_and_fill_load():
     has the host allocator, and FillOp checks its constant against the tensor"""
     s = brt.Session("cuda", host_space=True)
     s.load_from_memory(HOST_DEVICE)
-    assert [s.arg_info(i).space for i in range(5)] == ["cpu", "cpu", "cuda", "cuda", "cuda"]
+    assert [s.arg_info(i).space for i in range(6)] == ["cpu", "cpu", "cuda", "cuda", "cuda", "cuda"]
+    assert s.arg_info(5).nbytes == 3  # i1 is stored one byte per element
     with pytest.raises(brt.BrtError, match="FillOp"):
         brt.Session("cuda", host_space=True).load_from_memory(
             HOST_DEVICE.replace("dense<[1.000000e+00, 2.000000e+00, 3.000000e+00]> : tensor<3xf16>",
                                 "dense<[1.000000e+00, 2.000000e+00]> : tensor<2xf16>"))
     with pytest.raises(brt.BrtError, match="no allocator registered for memory space \"cpu\""):
         brt.Session("cuda").load_from_memory(HOST_DEVICE)  # a plain CUDA session has no host allocator
+
+
+def test_compiler_written_modules_load_when_a_checkout_is_given():
+    """With BYTEIR_CHECKOUT pointing at a checkout of the reference: its runtime fixtures written by the
+    compiler (resnet18 forward / backward / both, 167 to 265 arguments, one arena with dozens of
+    byre.alias views) and by hand (fill, cpu2cuda) load, once the ops outside this provider
+    (PTX, cuDNN, cuBLAS kernels) are taken out of the text."""
+    import os
+    import re
+    root = os.environ.get("BYTEIR_CHECKOUT")
+    if not root or not (Path(root) / "runtime" / "test" / "test_files").is_dir():
+        pytest.skip("BYTEIR_CHECKOUT is not set")
+    ours = ("ReduceSumOp", "ReduceMaxOp", "IndexSelectOp", "IndexPutOp", "TransposeOp", "FillOp", "cpu2cuda", "cuda2cpu")
+    files = {"resnet18_fw_host_cuda.mlir": 265, "resnet18_bw_host_cuda.mlir": 204, "resnet18_fw_bw_host_cuda.mlir": 167,
+             "fill_cuda.mlir": 5, "custom_add_cpu2cuda.mlir": 3}
+    for name, n_args in files.items():
+        kept = []
+        for line in (Path(root) / "runtime" / "test" / "test_files" / name).read_text().splitlines():
+            m = re.search(r"byre\.compute @(\w+)\(", line)
+            if m and not m.group(1).startswith(ours):
+                continue
+            kept.append(line)
+        s = brt.Session("cuda", host_space=True)
+        s.load_from_memory("\n".join(kept))
+        assert len(s.args()) == n_args, name
