@@ -84,11 +84,13 @@ common::Status ByREHandle::Load(const std::string &url, const std::string &fmt) 
   std::stringstream ss;
   ss << in.rdbuf();
   const std::string text = ss.str();
-  // MLIR bytecode starts with the magic "ML\xefR"
-  if (text.size() >= 4 && text[0] == 'M' && text[1] == 'L' && (unsigned char)text[2] == 0xef && text[3] == 'R')
-    return common::Status(common::BRT, common::NOT_IMPLEMENTED,
-                          "ByRE bytecode (.mlirbc) is not supported by this runtime; print the module as text");
   std::string err;
+  if (IsByREBytecode(text.data(), text.size())) {
+    auto bc = ParseByREBytecode(text.data(), text.size(), &err);
+    if (!bc)
+      return common::Status(common::BRT, common::INVALID_GRAPH, url + ": " + err);
+    return Adopt(std::move(bc));
+  }
   auto m = ParseByRE(text, &err);
   if (!m)
     return common::Status(common::BRT, common::INVALID_GRAPH, url + ": " + err);

@@ -5,7 +5,7 @@
 // object model and a hand-written parser for the textual ByRE subset that
 // byteir-opt emits: a module with one func.func marked byre.entry_point whose
 // body is a flat list of byre.compute / byre.copy / byre.alias / byre.custom /
-// memref.alloc ops.
+// memref.alloc ops; and a reader of the same modules in ByRE bytecode (bytecode.cc).
 #pragma once
 
 #include "brt/core/common/status.h"
@@ -83,6 +83,11 @@ struct Module {
 // "line N: message".
 std::unique_ptr<Module> ParseByRE(const std::string &text, std::string *error);
 
+// Reads ByRE bytecode: MLIR bytecode (container version 5) of the `byre_serial` dialect,
+// version 1.0.0.  On failure returns nullptr and sets *error.
+bool IsByREBytecode(const void *data, size_t size);
+std::unique_ptr<Module> ParseByREBytecode(const void *data, size_t size, std::string *error);
+
 class IRHandle {
 public:
   virtual ~IRHandle() = default;
@@ -93,8 +98,8 @@ public:
 // Holds one loaded ByRE module and its entry function.
 class ByREHandle : public IRHandle {
 public:
-  // fmt "byre": `url` names a text file (.mlir).  Bytecode (.mlirbc) is MLIR's own
-  // serialisation and is rejected with NOT_IMPLEMENTED.
+  // fmt "byre": `url` names a text file (.mlir) or a bytecode file (.mlirbc, told apart by
+  // its magic).
   common::Status Load(const std::string &url, const std::string &fmt) override;
   // fmt "byre": `ptr` is a NUL-terminated ByRE text buffer.  (The reference takes an
   // mlir::ModuleOp here, runtime/lib/core/ir/ir.cc:171-184.)

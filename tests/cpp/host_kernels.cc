@@ -66,7 +66,26 @@ public:
   }
 };
 
+// LLVMJITOp stand-in: checks at construction that the attributes of the reference's bytecode
+// fixture (LLJIT/Case0) arrived, then does nothing
+class HostJitStub final : public OpKernel {
+public:
+  explicit HostJitStub(const OpKernelInfo &info) : OpKernel(info) {
+    OpAccessor a(info_);
+    BRT_ENFORCE(a.GetAttrAsString("device") == "cpu", "device");
+    BRT_ENFORCE(a.GetAttrAsString("llvm_file_name").rfind("host_kernels", 0) == 0, "llvm_file_name");
+    BRT_ENFORCE(a.GetAttrAsString("kernel_name").rfind("Unknown", 0) == 0, "kernel_name");
+    const std::vector<int64_t> want = {1, 1, 1, 1, 2, 2};
+    BRT_ENFORCE(a.GetAttrAsIntArray("memory_effects") == want, "memory_effects");
+    BRT_ENFORCE(a.GetNumArgs() == 6, "operands");
+  }
+  common::Status RunImpl(const ExecutionContext &) override { return common::Status::OK(); }
+};
+
 BRT_STATIC_KERNEL_REGISTRATION(DeviceKind::CPU, ProviderType::BRT, [](KernelRegistry *registry) {
+  registry->Register("LLVMJITOp", [](const OpKernelInfo &info) -> std::shared_ptr<OpKernel> {
+    return std::make_shared<HostJitStub>(info);
+  });
   registry->Register("AddOp_f32f32_f32", [](const OpKernelInfo &info) -> std::shared_ptr<OpKernel> {
     return std::make_shared<HostAdd>(info);
   });

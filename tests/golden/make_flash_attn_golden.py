@@ -13,6 +13,10 @@ go to a second file: b=2, cache of 128 rows with 64 in use, one new row, heads=3
 head_dim=32, fp16, scale 0.5; inputs q/k/v/kcache/vcache/cache_seqlens, outputs out
 and the two updated caches.
 
+It also copies the reference's one ByRE bytecode fixture (runtime/test/test_files/LLJIT/
+Case0_v1_0_0/entry.mlirbc, 447 bytes, byre_serial 1.0.0 in an MLIR 17 container) to
+byre_serial_v1_lljit_case0.mlirbc; its text twin is LLJIT/Case0/entry.mlir.
+
 Run where a checkout of the reference is at hand:
     python tests/golden/make_flash_attn_golden.py <path to the byteir checkout>
 """
@@ -67,6 +71,9 @@ def kvcache(src: Path) -> None:
 def main(ref_root: str) -> None:
     src = Path(ref_root) / "runtime" / "test" / "test_files"
     kvcache(src)
+    bc = (src / "LLJIT" / "Case0_v1_0_0" / "entry.mlirbc").read_bytes()
+    assert bc[:4] == b"ML\xefR"
+    Path(__file__).with_name("byre_serial_v1_lljit_case0.mlirbc").write_bytes(bc)
     arrays = {}
     for key, fname in NAMES.items():
         vals = np.array((src / fname).read_text().split(), dtype=np.float64)

@@ -246,3 +246,36 @@ def test_flash_attn_kvcache_custom_call_through_session():
     assert torch.isfinite(dev["SoftmaxLse"]).all()
     req.close()
     s.close()
+
+
+def test_bytecode_module_runs_on_the_gpu(tmp_path):
+    """a ByRE bytecode file (byre_serial 1.0.0): an arena, two views of it, a transpose into one, a column
+    sum into the other, a max over the rows of the transpose; same results as the oracle"""
+    from byre_bytecode_writer import write_module
+    desc = {"name": "main",
+            "args": [("X", 1, "f32", (64, 256), "cuda"), ("ColSum", 2, "f32", (64,), "cuda"), ("RowMax", 2, "f32", (64,), "cuda")],
+            "ops": [("alloc", "i8", (65536 + 256,), "cuda"),
+                    ("alias", 3, 0, "f32", (256, 64), "cuda"),
+                    ("alias", 3, 65536, "f32", (64,), "cuda"),
+                    ("compute", "TransposeOp_f32_f32", [0, 4], {"permutation": ("dense", "i64", (2,), [1, 0])}, [1, 2]),
+                    ("compute", "ReduceSumOp_f32_f32", [4, 5], {"dimensions": ("dense", "i64", (1,), [0])}, [1, 2]),
+                    ("copy", 5, 1, "cuda2cuda"),
+                    ("compute", "ReduceMaxOp_f32_f32", [4, 2], {"dimensions": ("array", "i64", [0])}, [1, 2])]}
+    path = tmp_path / "m.mlirbc"
+    path.write_bytes(write_module(desc))
+    s = brt.Session("cuda")
+    s.load(str(path))
+    x = np.random.default_rng(3).standard_normal((64, 256)).astype(np.float32)
+    xd = torch.from_numpy(x).cuda()
+    col, row = torch.zeros(64, device="cuda"), torch.zeros(64, device="cuda")
+    req = s.new_request(torch.cuda.current_stream().cuda_stream)
+    for name, t in (("X", xd), ("ColSum", col), ("RowMax", row)):
+        req.bind_arg(s.arg_offset(name), t.data_ptr())
+    req.finish_io_binding()
+    req.run()
+    req.sync()
+    torch.cuda.synchronize()
+    np.testing.assert_allclose(col.cpu().numpy(), x.astype(np.float64).sum(axis=1), rtol=1e-5, atol=1e-4)
+    assert np.array_equal(row.cpu().numpy(), x.max(axis=1))
+    req.close()
+    s.close()

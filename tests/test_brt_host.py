@@ -157,7 +157,7 @@ def test_run_time_failure_is_a_status_and_the_context_stays_usable():
         req.run()  # still answers
 
 
-def test_load_file_and_bytecode_rejection(tmp_path):
+def test_load_file_and_truncated_bytecode(tmp_path):
     p = tmp_path / "add.mlir"
     p.write_text(ADD)
     s = brt.Session("cpu")
