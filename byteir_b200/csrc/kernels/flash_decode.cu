@@ -316,8 +316,10 @@ __device__ __forceinline__ uint32_t word_of(const uint4 &v, int w) {
 }
 
 __device__ __forceinline__ void cp_async16(uint32_t smem_addr, const void *src, bool real) {
-  const int bytes = real ? 16 : 0; // 0: the 16 bytes are filled with zeros and src is not read
-  asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(smem_addr), "l"(src), "r"(bytes) : "memory");
+  // bytes = 0: the 16 bytes are filled with zeros and src is not read.  The L2 hint pulls the rest of
+  // the 256-byte row (or the neighbouring head's 128-byte row) into L2 with the first request.
+  const int bytes = real ? 16 : 0;
+  asm volatile("cp.async.cg.shared.global.L2::256B [%0], [%1], 16, %2;" ::"r"(smem_addr), "l"(src), "r"(bytes) : "memory");
 }
 __device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
 template <int N> __device__ __forceinline__ void cp_async_wait() {
