@@ -24,6 +24,7 @@ SIGNATURES = {
     "brt_session_add_cuda_external": (_int, [_vp, _int, _vp, _vp]),
     "brt_session_load": (_int, [_vp, _cp]),
     "brt_session_load_from_memory": (_int, [_vp, _cp]),
+    "brt_session_load_buffer": (_int, [_vp, _cp, _sz]),
     "brt_session_arg_num": (_i64, [_vp]),
     "brt_session_arg_offset": (_int, [_vp, _cp]),
     "brt_session_arg_info": (_int, [_vp, _i64, C.POINTER(_int), C.POINTER(_int), C.POINTER(_i64), _cp, _sz,
@@ -118,7 +119,11 @@ class Session:
         _check(lib().brt_session_load(self._h, str(path).encode()))
 
     def load_from_memory(self, text):
-        _check(lib().brt_session_load_from_memory(self._h, text.encode()))
+        """ByRE text (str), or ByRE text / bytecode as bytes"""
+        if isinstance(text, (bytes, bytearray)):
+            _check(lib().brt_session_load_buffer(self._h, bytes(text), len(text)))
+        else:
+            _check(lib().brt_session_load_from_memory(self._h, text.encode()))
 
     def arg_num(self):
         return lib().brt_session_arg_num(self._h)

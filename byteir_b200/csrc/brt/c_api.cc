@@ -92,6 +92,10 @@ int brt_session_load_from_memory(brt_session *s, const char *text) {
   return Guard([&] { return s->session.LoadFromMemory(text, "byre"); });
 }
 
+int brt_session_load_buffer(brt_session *s, const void *data, size_t size) {
+  return Guard([&] { return s->session.LoadFromBuffer(data, size); });
+}
+
 int64_t brt_session_arg_num(brt_session *s) { return (int64_t)s->session.GetArgNum(); }
 int brt_session_arg_offset(brt_session *s, const char *name) { return s->session.GetGraphArgOffset(name); }
 

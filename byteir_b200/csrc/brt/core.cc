@@ -97,6 +97,17 @@ common::Status ByREHandle::Load(const std::string &url, const std::string &fmt) 
   return Adopt(std::move(m));
 }
 
+common::Status ByREHandle::LoadFromBuffer(const void *data, size_t size) {
+  if (!data)
+    return common::Status(common::BRT, common::INVALID_ARGUMENT, "null module buffer");
+  std::string err;
+  auto m = IsByREBytecode(data, size) ? ParseByREBytecode(data, size, &err)
+                                      : ParseByRE(std::string(static_cast<const char *>(data), size), &err);
+  if (!m)
+    return common::Status(common::BRT, common::INVALID_GRAPH, err);
+  return Adopt(std::move(m));
+}
+
 common::Status ByREHandle::LoadFromMemory(const void *ptr, const std::string &fmt) {
   if (fmt != "byre")
     return common::Status(common::BRT, common::INVALID_ARGUMENT, "unknown model format: " + fmt);

@@ -296,6 +296,14 @@ Status Session::LoadFromMemory(const void *ptr, const std::string &fmt) {
   return BuildPlan("");
 }
 
+Status Session::LoadFromBuffer(const void *data, size_t size) {
+  auto handle = std::make_unique<ir::ByREHandle>();
+  BRT_RETURN_IF_ERROR(handle->LoadFromBuffer(data, size));
+  execution_plan_.reset();
+  ir_handle_ = std::move(handle);
+  return BuildPlan("");
+}
+
 Status Session::LoadWeights(const std::string &, const std::string &) {
   return Status(common::BRT, common::NOT_IMPLEMENTED, "LoadWeights is not implemented"); // as the reference
 }

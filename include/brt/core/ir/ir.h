@@ -104,6 +104,8 @@ public:
   // fmt "byre": `ptr` is a NUL-terminated ByRE text buffer.  (The reference takes an
   // mlir::ModuleOp here, runtime/lib/core/ir/ir.cc:171-184.)
   common::Status LoadFromMemory(const void *ptr, const std::string &fmt) override;
+  // `size` bytes of ByRE text or ByRE bytecode (a module a host already holds in memory)
+  common::Status LoadFromBuffer(const void *data, size_t size);
 
   const Module &GetModule() const { return *module_; }
   const Function &GetEntryFunc() const { return *entry_; }

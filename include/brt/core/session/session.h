@@ -30,6 +30,8 @@ public:
   common::Status Load(const std::string &url, const std::string &fmt);
   // Load a ByRE model from a NUL-terminated text buffer.  fmt: "byre".
   common::Status LoadFromMemory(const void *ptr, const std::string &fmt);
+  // ByRE text or bytecode held in memory (the reference hands over an mlir::ModuleOp instead)
+  common::Status LoadFromBuffer(const void *data, size_t size);
 
   void *GetWeightAsyncValue(size_t offset);
   common::Status LoadWeights(const std::string &url, const std::string &fmt);

@@ -35,6 +35,8 @@ int brt_session_add_cuda(brt_session *s, int device_id);
 int brt_session_add_cuda_external(brt_session *s, int device_id, void *alloc_fn, void *free_fn);
 int brt_session_load(brt_session *s, const char *path);                 /* Session::Load(path, "byre") */
 int brt_session_load_from_memory(brt_session *s, const char *byre_text); /* Session::LoadFromMemory */
+/* `size` bytes of ByRE text or ByRE bytecode (byre_serial 1.0.0) */
+int brt_session_load_buffer(brt_session *s, const void *data, size_t size);
 
 int64_t brt_session_arg_num(brt_session *s);
 int brt_session_arg_offset(brt_session *s, const char *name); /* -1 if unknown */

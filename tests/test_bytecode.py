@@ -48,6 +48,16 @@ def test_writer_reproduces_the_fixtures_module(tmp_path):
     assert [vars(x) for x in a.args()] == [vars(x) for x in b.args()]
 
 
+def test_bytecode_from_memory():
+    s = brt.Session("cpu")
+    s.load_from_memory(FIXTURE.read_bytes())
+    assert [a.name for a in s.args()][:2] == ["Input0", "Input1"]
+    s.load_from_memory(TEXT.encode())  # text as bytes takes the same door
+    assert s.arg_num() == 4
+    with pytest.raises(brt.BrtError):
+        s.load_from_memory(FIXTURE.read_bytes()[:100])
+
+
 def test_varints_of_every_length():
     assert varint(0) == b"\x01" and varint(127) == b"\xff" and varint(128) == b"\x02\x02"
     assert varint(6400) == bytes([0x02, 0x64])  # (6400 << 2 | 2) little endian
