@@ -340,7 +340,7 @@ constexpr int kMmaRows = 16;                   // query rows of one block
 // tiles of the cp.async ring: the one in use and one (head dim 128) or two (64) in flight; measured:
 // a third stage slows head dim 128 down (104 -> 117 us on a 512 MiB cache) and speeds 64 up (65 -> 59 us)
 constexpr int mma_stages(int d) { return d == 128 ? 2 : 3; }
-constexpr int kMmaWarps = 4;                   // three such blocks share an SM and overlap each other's ends
+constexpr int kMmaWarps = 4;                   // up to three (head dim 128) or two (64) such blocks share an SM
 constexpr int kMmaThreads = kMmaWarps * 32;
 constexpr int kMmaKeysPerStep = 16 * kMmaWarps;
 
