@@ -177,7 +177,7 @@ def section(sid, body):
     return bytes([sid]) + varint(len(body)) + body
 
 
-def write_module(desc, producer="MLIR17.0.0git"):
+def write_module(desc, producer="MLIR17.0.0git", isolated_func=False):
     """The bytes of one module; strings, attributes and types are numbered in the order of first use."""
     w = Writer()
     used_ops = ["module_v1", "func_v1"]
@@ -226,21 +226,23 @@ def write_module(desc, producer="MLIR17.0.0git"):
     loc = len(w.attrs)  # the builtin unknown location comes last
 
     # IR section: top-level block, module, its region, func, its region and block, the body
+    region = varint(1) + varint(n_values) + varint(((len(body_ops) + 1) << 1) | 1)
+    region += varint(len(arg_types)) + b"".join(flagged(t, 0) for t in arg_types) + b"\x00"
+    all_props = [module_prop, func_prop]
+    for name, mask, prop, results, operands in body_ops:
+        region += varint(op_id[name]) + bytes([mask]) + varint(loc) + varint(len(all_props))
+        all_props.append(prop)
+        if results:
+            region += varint(len(results)) + b"".join(varint(t) for t in results)
+        if operands:
+            region += varint(len(operands)) + b"".join(varint(v) for v in operands)
+    region += varint(op_id["return_v1"]) + bytes([0x00]) + varint(loc)
     ir = varint((1 << 1) | 0)
     ir += varint(op_id["module_v1"]) + bytes([0x50]) + varint(loc) + varint(0) + flagged(1, 0)
     ir += varint(1) + varint(0) + varint((1 << 1) | 0)
-    ir += varint(op_id["func_v1"]) + bytes([0x50]) + varint(loc) + varint(1) + flagged(1, 0)
-    ir += varint(1) + varint(n_values) + varint(((len(body_ops) + 1) << 1) | 1)
-    ir += varint(len(arg_types)) + b"".join(flagged(t, 0) for t in arg_types) + b"\x00"
-    all_props = [module_prop, func_prop]
-    for name, mask, prop, results, operands in body_ops:
-        ir += varint(op_id[name]) + bytes([mask]) + varint(loc) + varint(len(all_props))
-        all_props.append(prop)
-        if results:
-            ir += varint(len(results)) + b"".join(varint(t) for t in results)
-        if operands:
-            ir += varint(len(operands)) + b"".join(varint(v) for v in operands)
-    ir += varint(op_id["return_v1"]) + bytes([0x00]) + varint(loc)
+    ir += varint(op_id["func_v1"]) + bytes([0x50]) + varint(loc) + varint(1)
+    # a region marked isolated from above travels in an IR section of its own (lazy loading)
+    ir += flagged(1, 1) + section(4, region) if isolated_func else flagged(1, 0) + region
 
     dialect = (varint(2) + flagged(w.string("byre_serial"), 1) + section(7, varint(0)) + flagged(w.string("builtin"), 0) +
                varint(len(used_ops)) + varint(0) + varint(len(used_ops)) +

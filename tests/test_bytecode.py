@@ -109,10 +109,11 @@ def test_bytecode_and_text_twins_run_alike(tmp_path):
     st = brt.Session("cpu")
     st.load_from_memory(TEXT)
     want_c, want_tail = _run(st, a, b)
-    sb = _load(write_module(DESC), tmp_path)
-    got_c, got_tail = _run(sb, a, b)
-    np.testing.assert_array_equal(got_c, want_c)
-    np.testing.assert_array_equal(got_tail, want_tail)
+    for isolated in (False, True):  # the function body inline, or in a nested IR section
+        sb = _load(write_module(DESC, isolated_func=isolated), tmp_path)
+        got_c, got_tail = _run(sb, a, b)
+        np.testing.assert_array_equal(got_c, want_c)
+        np.testing.assert_array_equal(got_tail, want_tail)
     np.testing.assert_array_equal(got_c, (a + b) * np.float32(-2.5) - 3)
     np.testing.assert_array_equal(got_tail, ((a + b) * np.float32(0.5))[50:])
 
