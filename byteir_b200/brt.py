@@ -86,17 +86,34 @@ class ArgInfo:
         return f"ArgInfo({self.offset}, {self.name!r}, {self.dtype}, {self.shape}, {self.space!r}, type={self.argtype})"
 
 
-class Session:
-    """device: "cuda" (default CUDA provider + CUDA allocators) or "cpu"; host_space=True adds the
-    CPU allocator and provider to a CUDA session, for modules with memrefs in the "cpu" space
-    (cpu2cuda / cuda2cpu copies)."""
+_ALLOC_FN = C.CFUNCTYPE(C.c_void_p, C.c_size_t)
+_FREE_FN = C.CFUNCTYPE(None, C.c_void_p)
 
-    def __init__(self, device="cuda", device_id=0, host_space=False):
+
+class Session:
+    """device: "cuda" (default CUDA provider + CUDA allocators) or "cpu" (any case, as the reference's
+    binding takes "CUDA" / "CPU"); host_space=True adds the CPU allocator and provider to a CUDA session,
+    for modules with memrefs in the "cpu" space (cpu2cuda / cuda2cpu copies).  alloc_func(size) -> address
+    and free_func(address) make the session take its device memory (unbound arguments, intermediates,
+    weights) from the caller, e.g. torch.cuda.caching_allocator_alloc / caching_allocator_delete, as the
+    reference's Session(device, alloc_func, free_func) does (runtime/python/src/module.cc:340-376)."""
+
+    def __init__(self, device="cuda", device_id=0, host_space=False, alloc_func=None, free_func=None):
+        device = device.lower()
         self._h = lib().brt_session_create()
         if not self._h:
             raise BrtError(lib().brt_last_error().decode())
+        if (alloc_func is None) != (free_func is None):
+            raise ValueError("alloc_func and free_func come together")
         if device == "cuda":
-            _check(lib().brt_session_add_cuda(self._h, device_id))
+            if alloc_func is not None:
+                # the C side keeps the two function pointers for the session's life: so must Python
+                self._alloc = _ALLOC_FN(lambda size: int(alloc_func(size)) or None)
+                self._free = _FREE_FN(lambda ptr: free_func(ptr or 0))
+                _check(lib().brt_session_add_cuda_external(self._h, device_id, C.cast(self._alloc, C.c_void_p),
+                                                           C.cast(self._free, C.c_void_p)))
+            else:
+                _check(lib().brt_session_add_cuda(self._h, device_id))
             if host_space:
                 _check(lib().brt_session_add_cpu(self._h))
         elif device == "cpu":
@@ -146,6 +163,31 @@ class Session:
     def new_request(self, cuda_stream=None):
         return Request(self, cuda_stream)
 
+    # ---- the names of the reference's binding (runtime/python/src/module.cc:377-421)
+    new_request_context = new_request
+
+    def get_input_arg_offsets(self):
+        return [a.offset for a in self.args() if a.argtype & 1]
+
+    def get_output_arg_offsets(self):
+        return [a.offset for a in self.args() if a.argtype & 2]
+
+    def get_weight_arg_offsets(self):
+        return [a.offset for a in self.args() if a.argtype & 4]
+
+    def get_static_shape(self, offset):
+        return list(self.arg_info(offset).shape)
+
+    def get_data_type(self, offset):
+        """the element type's name: "f32", "f16", "bf16", "i64", ..."""
+        return self.arg_info(offset).dtype
+
+    def get_input_names(self):
+        return [a.name for a in self.args() if a.argtype & 1]
+
+    def get_output_names(self):
+        return [a.name for a in self.args() if a.argtype & 2]
+
 
 class Request:
     def __init__(self, session, cuda_stream=None):
@@ -164,6 +206,10 @@ class Request:
             self.close()
         except Exception:
             pass
+
+    def bind_args(self, offset_and_ptr):
+        for offset, ptr in offset_and_ptr:
+            self.bind_arg(offset, ptr)
 
     def bind_arg(self, offset, ptr):
         _check(lib().brt_request_bind_arg(self._h, offset, ptr))

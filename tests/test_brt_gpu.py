@@ -279,3 +279,24 @@ def test_bytecode_module_runs_on_the_gpu(tmp_path):
     assert np.array_equal(row.cpu().numpy(), x.max(axis=1))
     req.close()
     s.close()
+
+
+def test_backend_run_and_profile_with_the_torch_allocator(tmp_path):
+    """BRTBackend as the reference's users drive it: device memory from torch's caching allocator, torch's
+    current stream, run / run_with_outputs / profile"""
+    from byteir_b200.backend import BRTBackend
+    path = tmp_path / "reduce.mlir"
+    path.write_text(reduce_mlir("ReduceSumOp_f16_f16", "f16", (64, 512, 1024), (1024,), "dense<[0, 1]> : tensor<2xi64>"))
+    be = BRTBackend("cuda", str(path))
+    assert be.input_shapes == [[64, 512, 1024]] and be.output_dtypes == [torch.float16]
+    x = torch.from_numpy(np.random.default_rng(5).uniform(-1, 1, (64, 512, 1024)).astype(np.float16)).cuda()
+    want = O.reduce("sum", x.cpu().numpy(), 1, 64 * 512, 1024).reshape(-1).astype(np.float32)
+    (out,) = be.run([x])
+    np.testing.assert_allclose(out.float().cpu().numpy(), want, rtol=2e-2, atol=1e-2)
+    out2 = torch.zeros(1024, dtype=torch.float16, device="cuda")
+    be.run_with_outputs([x], [out2])
+    assert torch.equal(out, out2)
+    (out3,), ms = be.profile([x], warmup_trials=2, run_trials=5)
+    assert torch.equal(out, out3) and 0 < ms < 50
+    with pytest.raises(AssertionError):
+        be.run([x.float()])

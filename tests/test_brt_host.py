@@ -360,3 +360,35 @@ def test_compiler_written_modules_load_when_a_checkout_is_given():
         s = brt.Session("cuda", host_space=True)
         s.load_from_memory("\n".join(kept))
         assert len(s.args()) == n_args, name
+
+
+def test_session_takes_device_memory_from_the_callers_functions():
+    """Session(alloc_func, free_func): unbound arguments and intermediates come from the caller's
+    allocator and go back to it (here host memory stands in for the device's); the reference's names
+    of the binding answer too"""
+    import ctypes
+    live, sizes = {}, []
+
+    def alloc(size):
+        buf = ctypes.create_string_buffer(max(size, 1))
+        live[ctypes.addressof(buf)] = buf
+        sizes.append(size)
+        return ctypes.addressof(buf)
+
+    def free(ptr):
+        del live[ptr]
+
+    s = brt.Session("CUDA", alloc_func=alloc, free_func=free)
+    s.load_from_memory(reduce_mlir("ReduceSumOp_f32_f32", "f32", (64, 32), (64,), "dense<1> : tensor<1xi64>"))
+    assert s.get_input_arg_offsets() == [0] and s.get_output_arg_offsets() == [1]
+    assert s.get_static_shape(0) == [64, 32] and s.get_data_type(1) == "f32"
+    assert s.get_input_names() == ["Input0"] and s.get_output_names() == ["Output0"]
+    req = s.new_request_context(0x10)  # any non-null stream: nothing is launched here
+    req.bind_args([(0, 0x1000)])
+    req.finish_io_binding()             # the unbound output is allocated by the caller's function
+    assert 64 * 4 in sizes and len(live) >= 1
+    req.close()
+    s.close()
+    assert not live
+    with pytest.raises(ValueError):
+        brt.Session("cuda", alloc_func=alloc)
