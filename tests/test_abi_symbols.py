@@ -63,3 +63,37 @@ def test_ops_refuse_cpu_tensors():
     from byteir_b200 import ops
     with pytest.raises(ValueError, match="no CPU path"):
         ops.reduce_sum(torch.zeros(4, 4), [1])
+
+
+def test_kvcache_plan_is_a_pure_function_of_the_shapes():
+    """workspace size and argument checks of the decode entry need no device"""
+    import ctypes as C
+    from byteir_b200 import _native as N
+
+    def params(b=16, sq=1, h=32, hk=8, d=128, cap=8192):
+        p = N.FlashKvCacheParams()
+        p.b, p.seqlen_q, p.h, p.h_k, p.d, p.seqlen_k, p.seqlen_knew = b, sq, h, hk, d, cap, 1
+        p.q_row_stride = p.o_row_stride = h * d
+        p.q_batch_stride = p.o_batch_stride = sq * h * d
+        p.k_row_stride = p.v_row_stride = p.knew_row_stride = p.vnew_row_stride = hk * d
+        p.k_batch_stride = p.v_batch_stride = cap * hk * d
+        p.knew_batch_stride = p.vnew_batch_stride = hk * d
+        for n in ("q", "k", "v", "knew", "vnew", "o"):
+            setattr(p, n + "_head_stride", d)
+        p.softmax_scale = 0.1
+        p.window_size_left = p.window_size_right = -1
+        return p
+
+    need = N.lib().b200_flash_attn_kvcache_workspace_bytes
+    big = need(C.byref(params()))
+    assert big > 0 and big % 4 == 0
+    assert need(C.byref(params(b=1, h=1, hk=1, d=32, cap=64))) == 0      # one range: no partial results
+    assert need(C.byref(params(d=12))) == -1 and need(C.byref(params(d=264))) == -1
+    assert need(C.byref(params(h=30))) == -1 and need(C.byref(params(cap=0))) == -1
+    # rows * ranges * (d + 2) floats, with at most 128 ranges
+    rows = 16 * 32
+    assert big % (rows * (128 + 2) * 4) == 0 and big // (rows * (128 + 2) * 4) <= 128
+    # the checks come before any launch: a null tensor is refused without a device
+    rc = N.lib().b200_flash_attn_kvcache(1, None, None, None, None, None, None, None,
+                                         None, C.byref(params()), None, 0, None)
+    assert rc != 0
