@@ -392,3 +392,33 @@ def test_session_takes_device_memory_from_the_callers_functions():
     assert not live
     with pytest.raises(ValueError):
         brt.Session("cuda", alloc_func=alloc)
+
+
+def test_damaged_text_is_an_error_not_a_crash():
+    """400 random edits of valid modules (dropped, doubled and replaced characters, truncations): the
+    loader answers with a Status or a loaded module, never with a fault"""
+    rng = np.random.default_rng(7)
+    alphabet = list('<>(){}[]"%@:,=x-+ \n') + list("0123456789abcdefmrt")
+    sources = [ADD, HOST_DEVICE, reduce_mlir("ReduceSumOp_f32_f32", "f32", (64, 32), (64,), "dense<1> : tensor<1xi64>")]
+    outcomes = {"ok": 0, "error": 0}
+    for trial in range(400):
+        text = list(sources[trial % len(sources)])
+        for _ in range(int(rng.integers(1, 4))):
+            pos = int(rng.integers(0, len(text)))
+            kind = int(rng.integers(0, 4))
+            if kind == 0:
+                del text[pos]
+            elif kind == 1:
+                text.insert(pos, text[pos])
+            elif kind == 2:
+                text[pos] = alphabet[int(rng.integers(0, len(alphabet)))]
+            else:
+                del text[pos:]
+        s = brt.Session("cuda", host_space=True) if trial % len(sources) else brt.Session("cpu")
+        try:
+            s.load_from_memory("".join(text))
+            outcomes["ok"] += 1
+        except brt.BrtError:
+            outcomes["error"] += 1
+        s.close()
+    assert outcomes["error"] > 100  # most edits break the module
