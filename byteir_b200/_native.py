@@ -62,11 +62,14 @@ SIGNATURES = {
     "b200_reduce_no_alloc": (_int, [_int, _int, _vp, _vp, _i64, _i64, _i64, _vp]),
     "b200_index_select": (_int, [_int, _int, _vp, _vp, _vp, _i64, _i64, _i64, _i64, _vp, _vp]),
     "b200_index_put_workspace_bytes": (_sz, [_int, _i64, _i64, _i64]),
+    "b200_index_put_prepare": (_int, [_vp]),
+    "b200_index_put_release": (_int, [_vp]),
     "b200_index_put_add": (_int, [_int, _vp, _vp, _vp, _vp, _i64, _i64, _i64, _vp, _sz, _vp, _vp]),
     "b200_transpose_batched": (_int, [_int, _vp, _vp, _i64, _i64, _i64, _vp]),
     "b200_permute": (_int, [_int, _vp, _vp, _int, C.POINTER(_i64), C.POINTER(_i64), _vp]),
     "b200_flash_attn_fwd": (_int, [_int, _vp, _vp, _vp, _vp, _vp, C.POINTER(FlashAttnParams), _vp]),
     "b200_flash_attn_bwd": (_int, [_int] + [_vp] * 11 + [C.POINTER(FlashAttnParams), _vp]),
+    "b200_flash_attn_take_status": (_int, [C.POINTER(_int)]),
     "b200_flash_attn_kvcache_workspace_bytes": (_i64, [C.POINTER(FlashKvCacheParams)]),
     "b200_flash_attn_kvcache": (_int, [_int] + [_vp] * 8 + [C.POINTER(FlashKvCacheParams), _vp, _sz, _vp]),
 }
@@ -75,6 +78,9 @@ EXTRA = {
     "b200_index_select_path": (_int, [_int, _int, _int, _vp, _vp, _vp, _i64, _i64, _i64, _i64, _vp, _vp]),
     "b200_transpose_batched_path": (_int, [_int, _int, _vp, _vp, _i64, _i64, _i64, _vp]),
     "b200_flash_attn_kvcache_tune": (None, [_int]),
+    "b200_reduce_cols_plan_override": (None, [_int, _int]),
+    "b200_index_put_tune": (None, [_int]),
+    "b200_flash_attn_debug": (None, [_int, C.c_uint]),
 }
 
 _lib = None

@@ -63,9 +63,22 @@ constexpr uint32_t kColS0 = 0, kColS1 = 128, kColP0 = 256, kColP1 = 320, kColO =
 constexpr int kCtrlRegs = 56, kSoftmaxRegs = 224; // 128 * 56 + 256 * 224 <= 64 Ki registers
 constexpr float kRescaleThreshold = 8.0f; // log2 units
 
+// Sticky status of the attention kernels on this device: 0, or the code of the last kernel whose
+// bounded wait ran out (2 forward, 3 backward).  Device code names it directly; the host reads and
+// clears it with b200_flash_attn_take_status.
+static __device__ int g_attn_status;
+
+// Host-side test hook (b200_flash_attn_debug): polls per bounded wait, and whether the elementwise
+// warps leave out the arrival that hands P (forward) or P / dS (backward) to the MMA issuer, so
+// that a wait runs out without anything faulting.
+uint32_t g_wait_polls = 100000u;
+int g_debug_skip_arrive = 0;
+
 struct FwdParams {
   float *lse;
   int *status;
+  uint32_t wait_polls;
+  int debug_skip_arrive;
   int64_t H, Hk, Sq, Sk;
   int n_q_tiles, pairs; // query tiles per (batch, head); pairs of them per work item
   int64_t total_items;  // pairs * H * B
@@ -156,12 +169,13 @@ struct SharedStorage {
   uint64_t mx_ready[2][2];
   uint32_t tmem_base;
   int failed;
+  uint32_t wait_polls;
   float rowmax[2][2][kBM]; // [group][tile parity][row]: scaled row maximum of the group's tile
   float2 xch[2][kBM];      // (reference max, row sum) of each group, for the final merge
 };
 
 __device__ __forceinline__ bool wait_or_flag(uint64_t *bar, uint32_t parity, SharedStorage *ss) {
-  if (mbar_wait(bar, parity))
+  if (mbar_wait(bar, parity, ss->wait_polls))
     return true;
   ss->failed = 1; // some arrival never came: every role gives up at its next wait
   return false;
@@ -184,7 +198,7 @@ __device__ __forceinline__ bool elect_one() {
 // all 32 lanes wait; the verdict is the same in every lane, so a warp gives up as a whole and
 // the warp-wide votes and tensor-memory instructions that follow a wait stay convergent
 __device__ __forceinline__ bool warp_wait_or_flag(uint64_t *bar, uint32_t parity, SharedStorage *ss) {
-  const bool ok = __all_sync(0xffffffffu, mbar_wait(bar, parity));
+  const bool ok = __all_sync(0xffffffffu, mbar_wait(bar, parity, ss->wait_polls));
   if (!ok)
     ss->failed = 1;
   return ok;
@@ -300,6 +314,7 @@ __global__ void __launch_bounds__(kThreads, 1)
       mbar_init(&ss->mx_ready[g][1], 4);
     }
     ss->failed = 0;
+    ss->wait_polls = p.wait_polls;
     mbar_fence_init();
   }
   if (warp == 1) {
@@ -583,7 +598,7 @@ __global__ void __launch_bounds__(kThreads, 1)
         tmem_wait_st();
         tc_fence_before_sync();
         __syncwarp();
-        if (lane == 0)
+        if (lane == 0 && !p.debug_skip_arrive)
           mbar_arrive(&ss->p_full[g]);
       }
 
@@ -655,8 +670,11 @@ __global__ void __launch_bounds__(kThreads, 1)
 
   tc_fence_before_sync();
   __syncthreads();
-  if (threadIdx.x == 0 && ss->failed && p.status)
-    *p.status = 2;
+  if (threadIdx.x == 0 && ss->failed) {
+    g_attn_status = 2;
+    if (p.status)
+      *p.status = 2;
+  }
   if (warp == 1) {
     tc_fence_after_sync();
     tmem_dealloc(tmem, kTmemCols);
@@ -707,6 +725,8 @@ struct BwdParams {
   int64_t H, Hk, Sq, Sk, Sq_rounded;
   float scale, scale_log2;
   int64_t window_left, window_right;
+  uint32_t wait_polls;
+  int debug_skip_arrive;
 };
 
 struct BwdShared {
@@ -718,6 +738,7 @@ struct BwdShared {
   uint64_t all_done;                              // every MMA of the block has completed
   uint32_t tmem_base;
   int failed;
+  uint32_t wait_polls;
   // dK/dV kernel: -lse * log2e and -dsum of the streamed queries [group][parity][row], negated
   // so that pairs of them are addends of packed FMAs / ADDs
   float neg_lse2[2][2][kBwdBN];
@@ -725,13 +746,13 @@ struct BwdShared {
 };
 
 __device__ __forceinline__ bool bwd_wait(uint64_t *bar, uint32_t parity, BwdShared *ss) {
-  if (mbar_wait(bar, parity))
+  if (mbar_wait(bar, parity, ss->wait_polls))
     return true;
   ss->failed = 1;
   return false;
 }
 __device__ __forceinline__ bool bwd_warp_wait(uint64_t *bar, uint32_t parity, BwdShared *ss) {
-  const bool ok = __all_sync(0xffffffffu, mbar_wait(bar, parity));
+  const bool ok = __all_sync(0xffffffffu, mbar_wait(bar, parity, ss->wait_polls));
   if (!ok)
     ss->failed = 1;
   return ok;
@@ -864,6 +885,7 @@ __global__ void __launch_bounds__(kThreads, 1)
     }
     mbar_init(&ss->all_done, 1);
     ss->failed = 0;
+    ss->wait_polls = p.wait_polls;
     mbar_fence_init();
   }
   if (warp == 1) {
@@ -1127,7 +1149,7 @@ __global__ void __launch_bounds__(kThreads, 1)
       tmem_wait_st();
       tc_fence_before_sync();
       __syncwarp();
-      if (lane == 0)
+      if (lane == 0 && !p.debug_skip_arrive)
         mbar_arrive(&ss->pds_full[g]);
     }
 
@@ -1179,6 +1201,8 @@ __global__ void __launch_bounds__(kThreads, 1)
 
   tc_fence_before_sync();
   __syncthreads();
+  if (threadIdx.x == 0 && ss->failed)
+    g_attn_status = 3; // dq / dk / dv of this block were not stored
   if (warp == 1) {
     tc_fence_after_sync();
     tmem_dealloc(tmem, kTmemCols);
@@ -1190,13 +1214,10 @@ int launch_bwd(const CUtensorMap &res0, const CUtensorMap &res1, const CUtensorM
                const CUtensorMap &out0, const CUtensorMap &out1, const BwdParams &p, dim3 grid,
                cudaStream_t stream) {
   const size_t smem = (size_t)2 * kTileBytes + (size_t)kBwdStages * 2 * kStrTileBytes + sizeof(BwdShared) + 1024;
-  static bool attr_set = false;
-  if (!attr_set) {
-    if (int rc = check_cuda(cudaFuncSetAttribute(flash_bwd_kernel<kBF16, kDKDV>,
-                                                 cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem)))
-      return rc;
-    attr_set = true;
-  }
+  // the attribute belongs to the current device's context: set on every call (a host-side table write)
+  if (int rc = check_cuda(cudaFuncSetAttribute(flash_bwd_kernel<kBF16, kDKDV>,
+                                               cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem)))
+    return rc;
   flash_bwd_kernel<kBF16, kDKDV><<<grid, kThreads, smem, stream>>>(res0, res1, str0, str1, out0, out1, p);
   return check_launch();
 }
@@ -1205,6 +1226,25 @@ int launch_bwd(const CUtensorMap &res0, const CUtensorMap &res1, const CUtensorM
 } // namespace b200
 
 using namespace b200;
+
+extern "C" int b200_flash_attn_take_status(int *status) {
+  int v = 0;
+  if (int rc = check_cuda(cudaMemcpyFromSymbol(&v, g_attn_status, sizeof(int))))
+    return rc;
+  if (v != 0) {
+    const int zero = 0;
+    if (int rc = check_cuda(cudaMemcpyToSymbol(g_attn_status, &zero, sizeof(int))))
+      return rc;
+  }
+  if (status)
+    *status = v;
+  return B200_OK;
+}
+
+extern "C" void b200_flash_attn_debug(int skip_arrive, unsigned wait_polls) {
+  g_debug_skip_arrive = skip_arrive;
+  g_wait_polls = wait_polls ? wait_polls : 100000u;
+}
 
 extern "C" int b200_flash_attn_fwd(int dtype, const void *q, const void *k, const void *v, void *out,
                                    float *softmax_lse, const b200_flash_attn_params *pp, cudaStream_t stream) {
@@ -1237,6 +1277,8 @@ extern "C" int b200_flash_attn_fwd(int dtype, const void *q, const void *k, cons
   FwdParams p;
   p.lse = softmax_lse;
   p.status = nullptr;
+  p.wait_polls = g_wait_polls;
+  p.debug_skip_arrive = g_debug_skip_arrive;
   p.H = a.h;
   p.Hk = a.h_k;
   p.Sq = a.seqlen_q;
@@ -1248,13 +1290,11 @@ extern "C" int b200_flash_attn_fwd(int dtype, const void *q, const void *k, cons
   p.pairs = (p.n_q_tiles + 1) / 2;
   p.total_items = (int64_t)p.pairs * a.h * a.b;
   const size_t smem = (size_t)(2 + kFwdKStages + kFwdVStages) * kTileBytes + sizeof(SharedStorage) + 1024;
-  static bool attr_set[2] = {false, false};
-  if (!attr_set[bf16]) {
+  { // the attribute belongs to the current device's context: set on every call (a host-side table write)
     cudaError_t e = bf16 ? cudaFuncSetAttribute(flash_fwd_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem)
                          : cudaFuncSetAttribute(flash_fwd_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
     if (int rc = check_cuda(e))
       return rc;
-    attr_set[bf16] = true;
   }
   const dim3 grid((unsigned)(p.total_items < kNumSMs ? p.total_items : kNumSMs)); // persistent blocks, one per SM
   if (bf16)
@@ -1331,6 +1371,8 @@ extern "C" int b200_flash_attn_bwd(int dtype, const void *dout, const void *q, c
   p.scale_log2 = a.softmax_scale * 1.4426950408889634f;
   p.window_left = a.window_size_left;
   p.window_right = a.window_size_right;
+  p.wait_polls = g_wait_polls;
+  p.debug_skip_arrive = g_debug_skip_arrive;
   const dim3 grid_kv((unsigned)((a.seqlen_k + 127) / 128), (unsigned)a.h_k, (unsigned)a.b);
   const dim3 grid_q((unsigned)((a.seqlen_q + kBM - 1) / kBM), (unsigned)a.h, (unsigned)a.b);
   int rc = bf16 ? launch_bwd<true, true>(k_map, v_map, q64_map, do64_map, dk_map, dv_map, p, grid_kv, stream)

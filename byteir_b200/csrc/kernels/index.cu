@@ -180,6 +180,164 @@ __global__ void __launch_bounds__(256)
   }
 }
 
+// The same gather as a persistent kernel: a block walks over groups of TY * U output rows,
+// keeps U row loads per thread in flight, and reads the indices of its next group before it
+// waits for the rows of the current one, so that the index load never stands between two
+// batches of row loads.
+template <typename V, typename IdxT, int U>
+__global__ void __launch_bounds__(256, U <= 8 ? 3 : 1)
+    gather_rows_vec_kernel(const V *__restrict__ in, const IdxT *__restrict__ idx, V *__restrict__ out,
+                           int64_t A, int64_t IB, int64_t OB, int64_t vpr, int tx_log2, int *status) {
+  const int TX = 1 << tx_log2, TY = 256 >> tx_log2;
+  const int tx = threadIdx.x & (TX - 1), ty = threadIdx.x >> tx_log2;
+  const int64_t group = (int64_t)TY * U;
+  auto load_rows = [&](int64_t ob0, int(&row)[U]) { // IB < 2^31: checked by the launcher
+#pragma unroll
+    for (int u = 0; u < U; ++u) {
+      const int64_t ob = ob0 + u * TY + ty;
+      const int64_t i = ob < OB ? (int64_t)idx[ob] : 0;
+      row[u] = ob < OB ? (int)i : -2; // -2: past the end; -1: out of range
+      if (ob < OB && (i < 0 || i >= IB)) {
+        row[u] = -1;
+        if (status && tx == 0)
+          *status = 1;
+      }
+    }
+  };
+  for (int64_t a = blockIdx.y; a < A; a += gridDim.y) {
+    const V *src = in + a * IB * vpr;
+    V *dst = out + a * OB * vpr;
+    int64_t ob0 = (int64_t)blockIdx.x * group;
+    int row[U], next[U];
+    if (ob0 < OB)
+      load_rows(ob0, row);
+    for (; ob0 < OB; ob0 += (int64_t)gridDim.x * group) {
+      const int64_t ob_next = ob0 + (int64_t)gridDim.x * group;
+      if (ob_next < OB)
+        load_rows(ob_next, next);
+      for (int64_t v = tx; v < vpr; v += TX) {
+        V val[U];
+#pragma unroll
+        for (int u = 0; u < U; ++u) {
+          val[u] = V{};
+          if (row[u] >= 0)
+            val[u] = src[(int64_t)row[u] * vpr + v];
+        }
+#pragma unroll
+        for (int u = 0; u < U; ++u)
+          if (row[u] != -2)
+            dst[(ob0 + u * TY + ty) * vpr + v] = val[u];
+      }
+#pragma unroll
+      for (int u = 0; u < U; ++u)
+        row[u] = next[u];
+    }
+  }
+}
+
+template <typename V, typename IdxT, int U>
+int launch_gather_vec(const void *in, const void *idx, void *out, int64_t A, int64_t IB, int64_t OB,
+                      int64_t row_bytes, int blocks_per_sm, int *status, cudaStream_t stream) {
+  const int64_t vpr = row_bytes / (int64_t)sizeof(V);
+  int tx_log2 = 0;
+  while ((1 << tx_log2) < vpr && tx_log2 < 8)
+    ++tx_log2;
+  const int TY = 256 >> tx_log2;
+  const int64_t groups = ceil_div<int64_t>(OB, (int64_t)TY * U);
+  dim3 grid((unsigned)std::min<int64_t>(groups, (int64_t)kNumSMs * blocks_per_sm), (unsigned)std::min<int64_t>(A, 65535));
+  gather_rows_vec_kernel<V, IdxT, U><<<grid, 256, 0, stream>>>((const V *)in, (const IdxT *)idx, (V *)out, A, IB, OB,
+                                                               vpr, tx_log2, status);
+  return check_launch();
+}
+
+// Rows of 64 .. 1024 bytes through the tensor-map gather: one cp.async.bulk.tensor instruction
+// in the tile::gather4 form fetches four table rows, named by four row coordinates, into four
+// consecutive rows of a shared-memory tile; the tile's mbarrier counts the bytes, and one bulk
+// copy shared -> global writes the tile, which is contiguous in the output.  One warp per block
+// drives a ring of kGatherStages tiles, lane q of it the q-th quad of rows of each tile.  The
+// tensor map is two-dimensional over this GPU's table only, [A * IB rows][row_bytes / 4 32-bit
+// columns], box = one row; a row coordinate past the end reads zeros (an index out of range).
+template <typename IdxT>
+__global__ void __launch_bounds__(32)
+    gather_rows_g4_kernel(const __grid_constant__ CUtensorMap table_map, const IdxT *__restrict__ idx,
+                          char *__restrict__ out, int64_t IB, int64_t OB, int64_t total_rows, uint32_t row_bytes,
+                          int rows_per_tile, int64_t tiles_per_a, int64_t num_tiles, int *status) {
+  extern __shared__ __align__(128) unsigned char smem[];
+  __shared__ uint64_t full[kGatherStages];
+  const int lane = threadIdx.x;
+  const uint32_t stage_bytes = (uint32_t)rows_per_tile * row_bytes;
+  if (lane == 0) {
+    prefetch_tensormap(&table_map);
+    for (int s = 0; s < kGatherStages; ++s)
+      mbar_init(&full[s], 1);
+    mbar_fence_init();
+  }
+  __syncwarp();
+  const int64_t my_tiles = (num_tiles - blockIdx.x + gridDim.x - 1) / gridDim.x;
+
+  auto issue = [&](int64_t k) {
+    const int64_t tile = blockIdx.x + k * gridDim.x;
+    const int stage = (int)(k % kGatherStages);
+    const int64_t a = tile / tiles_per_a;
+    const int64_t ob0 = (tile - a * tiles_per_a) * rows_per_tile;
+    const int nrows = (int)min((int64_t)rows_per_tile, OB - ob0);
+    const int quads = (nrows + 3) >> 2;
+    unsigned char *dst = smem + (size_t)stage * stage_bytes;
+    if (lane == 0)
+      mbar_arrive_expect_tx(&full[stage], (uint32_t)quads * 4u * row_bytes);
+    __syncwarp();
+    if (lane < quads) {
+      int r[4];
+#pragma unroll
+      for (int u = 0; u < 4; ++u) {
+        const int rr = lane * 4 + u;
+        int64_t i = (int64_t)total_rows; // past the end of the map: zeros
+        if (rr < nrows) {
+          const int64_t v = (int64_t)idx[ob0 + rr];
+          if (v < 0 || v >= IB) {
+            if (status)
+              *status = 1;
+          } else {
+            i = a * IB + v;
+          }
+        }
+        r[u] = (int)i;
+      }
+      tma_gather4_2d(dst + (size_t)lane * 4 * row_bytes, &table_map, 0, r[0], r[1], r[2], r[3], &full[stage]);
+    }
+  };
+
+  const int prologue = (int)min((int64_t)(kGatherStages - 1), my_tiles);
+  for (int k = 0; k < prologue; ++k)
+    issue(k);
+  for (int64_t k = 0; k < my_tiles; ++k) {
+    const int stage = (int)(k % kGatherStages);
+    const uint32_t parity = (uint32_t)((k / kGatherStages) & 1);
+    if (!__all_sync(0xffffffffu, mbar_wait(&full[stage], parity))) {
+      if (status)
+        *status = 2; // a copy never arrived: give up instead of spinning
+      break;
+    }
+    if (lane == 0) {
+      const int64_t tile = blockIdx.x + k * gridDim.x;
+      const int64_t a = tile / tiles_per_a;
+      const int64_t ob0 = (tile - a * tiles_per_a) * rows_per_tile;
+      const int nrows = (int)min((int64_t)rows_per_tile, OB - ob0);
+      bulk_s2g(out + ((size_t)a * OB + ob0) * row_bytes, smem + (size_t)stage * stage_bytes,
+               (uint32_t)nrows * row_bytes);
+      bulk_commit();
+    }
+    if (k + kGatherStages - 1 < my_tiles) {
+      if (lane == 0)
+        bulk_wait_read<1>(); // the stage to refill was last read by the store of tile k - 1
+      __syncwarp();
+      issue(k + kGatherStages - 1);
+    }
+  }
+  if (lane == 0)
+    bulk_wait_all<0>();
+}
+
 template <typename V, typename IdxT>
 int launch_gather_generic(const void *in, const void *idx, void *out, int64_t A, int64_t IB,
                           int64_t OB, int64_t row_bytes, int *status, cudaStream_t stream) {
@@ -212,15 +370,12 @@ int launch_gather(int path, const void *in, const void *idx, void *out, int64_t 
     const int64_t tiles_per_a = ceil_div<int64_t>(OB, rows_per_tile);
     const int64_t num_tiles = tiles_per_a * A;
     const size_t smem = (size_t)kGatherStages * rows_per_tile * row_bytes;
-    static bool attr_set[2] = {false, false};
-    constexpr int which = sizeof(IdxT) == 8 ? 1 : 0;
-    if (!attr_set[which]) {
-      if (int rc = check_cuda(cudaFuncSetAttribute(gather_rows_bulk_kernel<IdxT>,
-                                                   cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                                   kGatherStages * 49152)))
-        return rc;
-      attr_set[which] = true;
-    }
+    // the attribute belongs to the current device's context, so it is set on every call (a
+    // host-side table write) rather than once per process
+    if (int rc = check_cuda(cudaFuncSetAttribute(gather_rows_bulk_kernel<IdxT>,
+                                                 cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                                 kGatherStages * 49152)))
+      return rc;
     const int ctas_per_sm = (int)std::max<size_t>(1, std::min<size_t>(8, (200 * 1024) / (smem + 1024)));
     const unsigned grid = (unsigned)std::min<int64_t>(num_tiles, (int64_t)kNumSMs * ctas_per_sm);
     gather_rows_bulk_kernel<IdxT><<<grid, 32, smem, stream>>>(
@@ -230,6 +385,44 @@ int launch_gather(int path, const void *in, const void *idx, void *out, int64_t 
   }
   const uintptr_t both = reinterpret_cast<uintptr_t>(in) | reinterpret_cast<uintptr_t>(out) |
                          (uintptr_t)row_bytes;
+  // paths 3 .. 6 (measurement): the persistent vector kernel with 8 or 16 rows in flight per thread
+  if (path >= 3 && path <= 6) {
+    if (both % 16 != 0 || IB >= 0x7fffffffLL)
+      return B200_ERR_ALIGNMENT;
+    switch (path) {
+    case 3: return launch_gather_vec<uint4, IdxT, 8>(in, idx, out, A, IB, OB, row_bytes, 3, status, stream);
+    case 4: return launch_gather_vec<uint4, IdxT, 8>(in, idx, out, A, IB, OB, row_bytes, 4, status, stream);
+    case 5: return launch_gather_vec<uint4, IdxT, 16>(in, idx, out, A, IB, OB, row_bytes, 2, status, stream);
+    default: return launch_gather_vec<uint4, IdxT, 4>(in, idx, out, A, IB, OB, row_bytes, 6, status, stream);
+    }
+  }
+  // paths 7, 8: the tensor-map gather, 64- and 128-row tiles
+  if (path == 7 || path == 8) {
+    const int64_t total_rows = A * IB;
+    if (!bulk_ok || row_bytes > 1024 || row_bytes < 64 || total_rows >= 0x7fffffffLL)
+      return B200_ERR_ALIGNMENT;
+    CUtensorMap map;
+    const uint64_t dims[2] = {(uint64_t)(row_bytes / 4), (uint64_t)total_rows};
+    const uint64_t strides[1] = {(uint64_t)row_bytes};
+    const uint32_t box[2] = {(uint32_t)(row_bytes / 4), 1};
+    if (int rc = make_tensor_map(&map, CU_TENSOR_MAP_DATA_TYPE_UINT32, 2, const_cast<void *>(in), dims, strides, box,
+                                 CU_TENSOR_MAP_SWIZZLE_NONE))
+      return rc;
+    int rows_per_tile = (int)std::min<int64_t>(path == 7 ? 64 : 128, 32768 / row_bytes);
+    rows_per_tile = std::max(4, rows_per_tile & ~3);
+    const int64_t tiles_per_a = ceil_div<int64_t>(OB, rows_per_tile);
+    const int64_t num_tiles = tiles_per_a * A;
+    const size_t smem = (size_t)kGatherStages * rows_per_tile * row_bytes;
+    if (int rc = check_cuda(cudaFuncSetAttribute(gather_rows_g4_kernel<IdxT>,
+                                                 cudaFuncAttributeMaxDynamicSharedMemorySize, 4 * 32768)))
+      return rc;
+    const int ctas_per_sm = (int)std::max<size_t>(1, std::min<size_t>(8, (200 * 1024) / (smem + 1024)));
+    const unsigned grid = (unsigned)std::min<int64_t>(num_tiles, (int64_t)kNumSMs * ctas_per_sm);
+    gather_rows_g4_kernel<IdxT><<<grid, 32, smem, stream>>>(map, (const IdxT *)idx, (char *)out, IB, OB, total_rows,
+                                                            (uint32_t)row_bytes, rows_per_tile, tiles_per_a,
+                                                            num_tiles, status);
+    return check_launch();
+  }
   if (both % 16 == 0)
     return launch_gather_generic<uint4, IdxT>(in, idx, out, A, IB, OB, row_bytes, status, stream);
   if (both % 8 == 0)
@@ -244,8 +437,14 @@ int launch_gather(int path, const void *in, const void *idx, void *out, int64_t 
 // =============================================================================
 // scatter-add
 // =============================================================================
-constexpr int kRadixBits = 8;
-constexpr int kRadix = 1 << kRadixBits;
+// Stable LSD radix sort of (row index, position).  Digits are up to 10 bits wide (a table of
+// a million rows sorts in two passes); a pass is a scan kernel and a scatter kernel, and the
+// scatter kernel of one pass counts the digits of the next pass on the fly (per destination
+// tile, with global atomics: the counts are exact whatever the order), so that only the first
+// pass needs a histogram kernel of its own.  Every kernel of the chain is launched with
+// programmatic dependent launch: its blocks are resident and waiting when its predecessor ends.
+constexpr int kMaxRadixBits = 10;
+constexpr int kMaxRadix = 1 << kMaxRadixBits;
 constexpr int kSortTile = 2048; // keys per block: 8 warps x 8 rounds x 32 lanes
 constexpr int kChunk = 32;      // sorted entries per warp in the accumulate pass
 
@@ -258,50 +457,95 @@ __device__ __forceinline__ uint32_t key_of_index(int64_t i, int64_t rows, int *s
   return (uint32_t)i;
 }
 
-// per-block digit histogram; the first pass also turns int64 indices into keys
-template <bool FIRST>
+// First pass only: int64 indices -> keys, and the per-tile histogram of the first digit.
+// hist: [digit][tile].
 __global__ void __launch_bounds__(256)
-    radix_hist_kernel(const int64_t *__restrict__ idx, const uint32_t *__restrict__ keys_in,
-                      uint32_t *__restrict__ keys_first, uint32_t *__restrict__ block_hist, int64_t n,
-                      int64_t rows, int shift, int nblocks, int *status, uint32_t *leader_count) {
-  __shared__ uint32_t hist[kRadix];
-  if (FIRST && blockIdx.x == 0 && threadIdx.x == 0) {
+    radix_first_hist_kernel(const int64_t *__restrict__ idx, uint32_t *__restrict__ keys,
+                            uint32_t *__restrict__ hist, int64_t n, int64_t rows, int radix, int ntiles,
+                            int *status, uint32_t *leader_count) {
+  __shared__ uint32_t sh[kMaxRadix];
+  pdl_wait();
+  pdl_launch_dependents();
+  if (blockIdx.x == 0 && threadIdx.x == 0) {
     leader_count[0] = 0; // work-list counters of the accumulate passes, which run
     leader_count[1] = 0; // after the whole sort
   }
-  hist[threadIdx.x] = 0;
+  for (int d = threadIdx.x; d < radix; d += 256)
+    sh[d] = 0;
   __syncthreads();
   const int64_t base = (int64_t)blockIdx.x * kSortTile;
   for (int k = 0; k < kSortTile / 256; ++k) {
     const int64_t i = base + k * 256 + threadIdx.x;
     if (i < n) {
-      uint32_t key;
-      if (FIRST) {
-        key = key_of_index(idx[i], rows, status);
-        keys_first[i] = key;
-      } else {
-        key = keys_in[i];
-      }
-      atomicAdd(&hist[(key >> shift) & (kRadix - 1)], 1u);
+      const uint32_t key = key_of_index(idx[i], rows, status);
+      keys[i] = key;
+      atomicAdd(&sh[key & (radix - 1)], 1u);
     }
   }
   __syncthreads();
-  block_hist[(size_t)threadIdx.x * nblocks + blockIdx.x] = hist[threadIdx.x];
+  for (int d = threadIdx.x; d < radix; d += 256)
+    hist[(size_t)d * ntiles + blockIdx.x] = sh[d];
 }
 
-// exclusive scan of the (digit-major, block-minor) histogram, one block;
-// m is a multiple of 4 (256 digits x blocks), 4096 entries per sweep
-__global__ void __launch_bounds__(1024) radix_scan_kernel(uint32_t *__restrict__ hist, int64_t m) {
-  __shared__ uint32_t warp_sums[32];
-  __shared__ uint32_t sweep_total;
-  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+// One warp per digit: exclusive prefix of the digit's counts over the tiles, in place, and the
+// digit's total.  The same warp clears the digit's row of the other histogram, which the
+// scatter kernel of this pass fills for the next pass.
+__global__ void __launch_bounds__(256)
+    radix_scan_kernel(uint32_t *__restrict__ hist, uint32_t *__restrict__ totals,
+                      uint32_t *__restrict__ hist_next, int radix, int next_radix, int ntiles) {
+  pdl_wait();
+  pdl_launch_dependents();
+  const int lane = threadIdx.x & 31;
+  const int d = blockIdx.x * 8 + (threadIdx.x >> 5);
+  if (d < next_radix && hist_next)
+    for (int t = lane; t < ntiles; t += 32)
+      hist_next[(size_t)d * ntiles + t] = 0;
+  if (d >= radix)
+    return;
+  uint32_t *row = hist + (size_t)d * ntiles;
   uint32_t carry = 0;
-  for (int64_t base = 0; base < m; base += 4096) {
-    const int64_t i = base + (int64_t)threadIdx.x * 4;
-    uint4 v = make_uint4(0, 0, 0, 0);
-    if (i < m)
-      v = *reinterpret_cast<const uint4 *>(hist + i);
-    const uint32_t local = v.x + v.y + v.z + v.w;
+  for (int t0 = 0; t0 < ntiles; t0 += 32) {
+    const int t = t0 + lane;
+    const uint32_t v = t < ntiles ? row[t] : 0u;
+    uint32_t incl = v;
+    for (int off = 1; off < 32; off <<= 1) {
+      const uint32_t u = __shfl_up_sync(0xffffffffu, incl, off);
+      if (lane >= off)
+        incl += u;
+    }
+    if (t < ntiles)
+      row[t] = carry + incl - v;
+    carry += __shfl_sync(0xffffffffu, incl, 31);
+  }
+  if (lane == 0)
+    totals[d] = carry;
+}
+
+// stable scatter of one digit; FIRST: the value of entry i is i itself
+template <bool FIRST>
+__global__ void __launch_bounds__(256)
+    radix_scatter_kernel(const uint32_t *__restrict__ keys_in, const uint32_t *__restrict__ vals_in,
+                         uint32_t *__restrict__ keys_out, uint32_t *__restrict__ vals_out,
+                         const uint32_t *__restrict__ hist, const uint32_t *__restrict__ totals,
+                         uint32_t *__restrict__ hist_next, int64_t n, int shift, int radix, int next_shift,
+                         int next_radix, int ntiles) {
+  __shared__ uint32_t whist[8][kMaxRadix];
+  __shared__ uint32_t digit_base[kMaxRadix];
+  __shared__ uint32_t warp_tot[8];
+  pdl_wait();
+  pdl_launch_dependents();
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  for (int i = threadIdx.x; i < 8 * kMaxRadix; i += 256)
+    (&whist[0][0])[i] = 0;
+  // digit_base[d] = number of keys whose digit is below d: block-wide exclusive scan of the totals
+  {
+    uint32_t t[kMaxRadix / 256], local = 0;
+#pragma unroll
+    for (int k = 0; k < kMaxRadix / 256; ++k) {
+      const int d = threadIdx.x * (kMaxRadix / 256) + k;
+      t[k] = d < radix ? totals[d] : 0u;
+      local += t[k];
+    }
     uint32_t incl = local;
     for (int off = 1; off < 32; off <<= 1) {
       const uint32_t u = __shfl_up_sync(0xffffffffu, incl, off);
@@ -309,45 +553,17 @@ __global__ void __launch_bounds__(1024) radix_scan_kernel(uint32_t *__restrict__
         incl += u;
     }
     if (lane == 31)
-      warp_sums[warp] = incl;
+      warp_tot[warp] = incl;
     __syncthreads();
-    if (warp == 0) {
-      const uint32_t w = warp_sums[lane];
-      uint32_t wi = w;
-      for (int off = 1; off < 32; off <<= 1) {
-        const uint32_t u = __shfl_up_sync(0xffffffffu, wi, off);
-        if (lane >= off)
-          wi += u;
-      }
-      warp_sums[lane] = wi - w;
-      if (lane == 31)
-        sweep_total = wi;
+    uint32_t run = incl - local;
+    for (int w = 0; w < warp; ++w)
+      run += warp_tot[w];
+#pragma unroll
+    for (int k = 0; k < kMaxRadix / 256; ++k) {
+      digit_base[threadIdx.x * (kMaxRadix / 256) + k] = run;
+      run += t[k];
     }
-    __syncthreads();
-    uint32_t run = carry + warp_sums[warp] + incl - local;
-    if (i < m) {
-      uint4 o;
-      o.x = run;
-      o.y = run + v.x;
-      o.z = o.y + v.y;
-      o.w = o.z + v.z;
-      *reinterpret_cast<uint4 *>(hist + i) = o;
-    }
-    carry += sweep_total;
-    __syncthreads();
   }
-}
-
-// stable scatter of one digit
-template <bool FIRST>
-__global__ void __launch_bounds__(256)
-    radix_scatter_kernel(const uint32_t *__restrict__ keys_in, const uint32_t *__restrict__ vals_in,
-                         uint32_t *__restrict__ keys_out, uint32_t *__restrict__ vals_out,
-                         const uint32_t *__restrict__ block_hist, int64_t n, int shift, int nblocks) {
-  __shared__ uint32_t whist[8][kRadix];
-  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  for (int i = threadIdx.x; i < 8 * kRadix; i += 256)
-    (&whist[0][0])[i] = 0;
   __syncthreads();
   const int64_t base = (int64_t)blockIdx.x * kSortTile + warp * 256;
   uint32_t key[8], val[8], rank[8];
@@ -358,7 +574,7 @@ __global__ void __launch_bounds__(256)
     const bool ok = i < n;
     key[r] = ok ? keys_in[i] : 0u;
     val[r] = ok ? (FIRST ? (uint32_t)i : vals_in[i]) : 0u;
-    const uint32_t d = ok ? ((key[r] >> shift) & (kRadix - 1)) : 0xffffffffu;
+    const uint32_t d = ok ? ((key[r] >> shift) & (radix - 1)) : 0xffffffffu;
     const uint32_t peers = __match_any_sync(0xffffffffu, d);
     uint32_t prefix = 0;
     if (ok)
@@ -370,9 +586,8 @@ __global__ void __launch_bounds__(256)
     rank[r] = prefix + __popc(peers & lt);
   }
   __syncthreads();
-  {
-    const int d = threadIdx.x;
-    uint32_t run = block_hist[(size_t)d * nblocks + blockIdx.x];
+  for (int d = threadIdx.x; d < radix; d += 256) {
+    uint32_t run = hist[(size_t)d * ntiles + blockIdx.x] + digit_base[d];
 #pragma unroll
     for (int w = 0; w < 8; ++w) {
       const uint32_t c = whist[w][d];
@@ -385,10 +600,12 @@ __global__ void __launch_bounds__(256)
   for (int r = 0; r < 8; ++r) {
     const int64_t i = base + r * 32 + lane;
     if (i < n) {
-      const uint32_t d = (key[r] >> shift) & (kRadix - 1);
+      const uint32_t d = (key[r] >> shift) & (radix - 1);
       const uint32_t dst = whist[warp][d] + rank[r];
       keys_out[dst] = key[r];
       vals_out[dst] = val[r];
+      if (hist_next)
+        atomicAdd(&hist_next[(size_t)((key[r] >> next_shift) & (next_radix - 1)) * ntiles + dst / kSortTile], 1u);
     }
   }
 }
@@ -469,6 +686,8 @@ __global__ void __launch_bounds__(256)
                          const uint32_t *__restrict__ keys, const uint32_t *__restrict__ vals,
                          float *__restrict__ part, uint32_t *__restrict__ leaders, int64_t n,
                          int64_t rows, int64_t feature) {
+  pdl_wait();
+  pdl_launch_dependents();
   const int lane = threadIdx.x & 31;
   const int64_t chunk = (int64_t)blockIdx.x * 8 + (threadIdx.x >> 5);
   const int64_t e0 = chunk * kChunk;
@@ -560,6 +779,126 @@ __global__ void __launch_bounds__(256)
   }
 }
 
+// The same pass for rows that are multiples of 16 bytes (every pointer 16-byte aligned): the 32
+// update rows of a chunk, and the table rows of the runs that end inside it, are first copied
+// into the warp's shared-memory buffers with 16-byte asynchronous copies, all of them in flight
+// at once and none of them held in registers; the warp then adds the rows up from shared memory,
+// in the order of the sorted list.  A row is handled in tiles of 256 bytes (8 bytes per lane).
+// Shared memory: [warp][update rows | table rows][32 rows][256 B] = 16 KiB per warp.
+constexpr int kStagedWarps = 4;
+constexpr int kStagedTileBytes = 256;
+constexpr size_t kStagedSmemPerWarp = 2 * kChunk * kStagedTileBytes;
+
+__device__ __forceinline__ void cp_async_16(void *smem_dst, const void *gmem_src) {
+  asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(smem_addr(smem_dst)), "l"(gmem_src) : "memory");
+}
+__device__ __forceinline__ void cp_async_wait_all() {
+  asm volatile("cp.async.commit_group;\ncp.async.wait_group 0;" ::: "memory");
+}
+
+template <typename T>
+__global__ void __launch_bounds__(kStagedWarps * 32)
+    scatter_chunk_staged_kernel(const T *in, const T *__restrict__ upd, T *out,
+                                const uint32_t *__restrict__ keys, const uint32_t *__restrict__ vals,
+                                float *__restrict__ part, uint32_t *__restrict__ leaders, int64_t n,
+                                int64_t rows, int64_t feature) {
+  constexpr int LV = 8 / (int)sizeof(T); // elements per lane per tile
+  extern __shared__ __align__(128) unsigned char staged_smem[];
+  pdl_wait();
+  pdl_launch_dependents();
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  const int64_t chunk = (int64_t)blockIdx.x * kStagedWarps + warp;
+  const int64_t e0 = chunk * kChunk;
+  if (e0 >= n)
+    return;
+  unsigned char *upd_s = staged_smem + (size_t)warp * kStagedSmemPerWarp;
+  unsigned char *base_s = upd_s + kChunk * kStagedTileBytes;
+  const int cnt = (int)min((int64_t)kChunk, n - e0);
+  const uint32_t invalid = (uint32_t)rows;
+  const uint32_t my_key = lane < cnt ? keys[e0 + lane] : 0xffffffffu;
+  const uint32_t my_pos = lane < cnt ? vals[e0 + lane] : 0u;
+  const uint32_t prev_key = e0 > 0 ? keys[e0 - 1] : 0xffffffffu;
+  const uint32_t next_key = e0 + kChunk < n ? keys[e0 + kChunk] : 0xffffffffu;
+  const uint32_t first_key = __shfl_sync(0xffffffffu, my_key, 0);
+  const uint32_t last_key = __shfl_sync(0xffffffffu, my_key, cnt - 1);
+  const uint32_t key_after = __shfl_down_sync(0xffffffffu, my_key, 1);
+  const bool my_end = lane < cnt && (lane == cnt - 1 || key_after != my_key);
+  const bool my_open = (my_key == first_key && first_key == prev_key) ||
+                       (my_key == last_key && last_key == next_key);
+  const bool my_live = lane < cnt && my_key != invalid;
+  const uint32_t end_mask = __ballot_sync(0xffffffffu, my_end);
+  const uint32_t closed_mask = __ballot_sync(0xffffffffu, my_end && !my_open && my_key != invalid);
+  const uint32_t live_mask = __ballot_sync(0xffffffffu, my_live);
+  float *part0 = part + (size_t)chunk * 2 * feature;
+  float *part1 = part0 + feature;
+  if (lane == 0 && last_key != invalid && last_key == next_key &&
+      !(first_key == last_key && first_key == prev_key))
+    leaders[64 + atomicAdd(&leaders[0], 1u)] = (uint32_t)chunk;
+
+  const int64_t row_bytes = feature * (int64_t)sizeof(T);
+  const char *upd_b = reinterpret_cast<const char *>(upd);
+  const char *in_b = reinterpret_cast<const char *>(in);
+  for (int64_t tb = 0; tb < row_bytes; tb += kStagedTileBytes) {
+    const int tile_bytes = (int)min((int64_t)kStagedTileBytes, row_bytes - tb);
+    const int c16 = tile_bytes >> 4; // 16-byte pieces of a row in this tile, 1..16
+    if (tb > 0)
+      __syncwarp(); // the previous tile has been read out of the buffers
+    // stage: piece p of the chunk = (entry p / c16, 16-byte column p % c16)
+    const int pieces = cnt * c16;
+    for (int p0 = 0; p0 < pieces; p0 += 32) {
+      const int pc = p0 + lane;
+      const int r = min(pc / c16, kChunk - 1), c = pc % c16;
+      const uint32_t k = __shfl_sync(0xffffffffu, my_key, r);
+      const uint32_t pos = __shfl_sync(0xffffffffu, my_pos, r);
+      if (pc < pieces && ((live_mask >> r) & 1u)) {
+        cp_async_16(upd_s + r * kStagedTileBytes + c * 16, upd_b + (size_t)pos * row_bytes + tb + c * 16);
+        if ((closed_mask >> r) & 1u)
+          cp_async_16(base_s + r * kStagedTileBytes + c * 16, in_b + (size_t)k * row_bytes + tb + c * 16);
+      }
+    }
+    cp_async_wait_all();
+    __syncwarp();
+    const bool lane_on = lane * 8 < tile_bytes;
+    const int64_t f0 = tb / (int64_t)sizeof(T) + (int64_t)lane * LV;
+    float acc[LV];
+#pragma unroll
+    for (int j = 0; j < LV; ++j)
+      acc[j] = 0.f;
+    for (int i = 0; i < cnt; ++i) {
+      if (!((live_mask >> i) & 1u))
+        continue;
+      const uint32_t k = __shfl_sync(0xffffffffu, my_key, i);
+      if (lane_on) {
+        float xf[LV];
+        unpack_raw<T, LV>(*reinterpret_cast<const uint2 *>(upd_s + i * kStagedTileBytes + lane * 8), xf);
+#pragma unroll
+        for (int j = 0; j < LV; ++j)
+          acc[j] += xf[j];
+      }
+      if ((end_mask >> i) & 1u) {
+        if (lane_on) {
+          if ((closed_mask >> i) & 1u) {
+            float bf[LV];
+            unpack_raw<T, LV>(*reinterpret_cast<const uint2 *>(base_s + i * kStagedTileBytes + lane * 8), bf);
+#pragma unroll
+            for (int j = 0; j < LV; ++j)
+              bf[j] += acc[j];
+            store_lane<T, LV>(out + (size_t)k * feature + f0, bf);
+          } else {
+            float *dst = (k == first_key ? part0 : part1) + f0;
+#pragma unroll
+            for (int j = 0; j < LV; ++j)
+              dst[j] = acc[j];
+          }
+        }
+#pragma unroll
+        for (int j = 0; j < LV; ++j)
+          acc[j] = 0.f;
+      }
+    }
+  }
+}
+
 // Finishes the runs that cross chunk borders; work list written by the chunk pass.
 // leaders[0] = number of entries, leaders[1] = number of long entries (second
 // list, filled here), leaders[64 + i] = chunk where run i starts,
@@ -573,6 +912,8 @@ __global__ void __launch_bounds__(256)
     scatter_span_short_kernel(const T *in, T *out, const uint32_t *__restrict__ keys,
                               const float *__restrict__ part, uint32_t *__restrict__ leaders,
                               int64_t n, int64_t feature) {
+  pdl_wait();
+  pdl_launch_dependents();
   const int lane = threadIdx.x & 31;
   const int64_t nchunks = ceil_div<int64_t>(n, kChunk);
   const uint32_t nlead = leaders[0];
@@ -600,11 +941,23 @@ __global__ void __launch_bounds__(256)
 #pragma unroll
       for (int j = 0; j < LV; ++j)
         sum[j] = p[j];
-      for (int c = 1; c <= extra; ++c) {
-        const float *q = part + (size_t)(chunk + c) * 2 * feature + f0;
+      for (int c0 = 1; c0 <= extra; c0 += 8) { // eight chunks' partials in flight, added in chunk order
+        float q[8][LV];
 #pragma unroll
-        for (int j = 0; j < LV; ++j)
-          sum[j] += q[j];
+        for (int u = 0; u < 8; ++u)
+          if (c0 + u <= extra) {
+            const float *qp = part + (size_t)(chunk + c0 + u) * 2 * feature + f0;
+#pragma unroll
+            for (int j = 0; j < LV; ++j)
+              q[u][j] = qp[j];
+          }
+#pragma unroll
+        for (int u = 0; u < 8; ++u)
+          if (c0 + u <= extra) {
+#pragma unroll
+            for (int j = 0; j < LV; ++j)
+              sum[j] += q[u][j];
+          }
       }
 #pragma unroll
       for (int j = 0; j < LV; ++j)
@@ -625,6 +978,8 @@ __global__ void __launch_bounds__(1024)
                              const float *__restrict__ part, const uint32_t *__restrict__ leaders,
                              int64_t n, int64_t feature) {
   __shared__ float sm[32][32 * LV];
+  pdl_wait();
+  pdl_launch_dependents();
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
   const int64_t nchunks = ceil_div<int64_t>(n, kChunk);
   const uint32_t nlead = leaders[1];
@@ -704,8 +1059,8 @@ __global__ void __launch_bounds__(1024)
 
 struct ScatterPlan {
   int64_t nblocks, nchunks;
-  int passes;
-  size_t off_keys[2], off_vals[2], off_hist, off_part, off_leaders, total;
+  int passes, digit_bits;
+  size_t off_keys[2], off_vals[2], off_hist[2], off_totals, off_part, off_leaders, total;
 };
 
 inline size_t align256(size_t v) { return (v + 255) & ~(size_t)255; }
@@ -714,10 +1069,11 @@ ScatterPlan make_scatter_plan(int64_t rows, int64_t n, int64_t feature) {
   ScatterPlan p{};
   p.nblocks = ceil_div<int64_t>(n, kSortTile);
   p.nchunks = ceil_div<int64_t>(n, kChunk);
-  int bits = 1;
+  int bits = 1; // of the largest key, which is `rows` itself (the key of an index out of range)
   while (bits < 32 && ((uint64_t)rows >> bits) != 0)
     ++bits;
-  p.passes = (bits + kRadixBits - 1) / kRadixBits;
+  p.passes = (bits + kMaxRadixBits - 1) / kMaxRadixBits;
+  p.digit_bits = (bits + p.passes - 1) / p.passes;
   size_t off = 0;
   for (int i = 0; i < 2; ++i) {
     p.off_keys[i] = off;
@@ -725,8 +1081,12 @@ ScatterPlan make_scatter_plan(int64_t rows, int64_t n, int64_t feature) {
     p.off_vals[i] = off;
     off += align256((size_t)n * 4);
   }
-  p.off_hist = off;
-  off += align256((size_t)kRadix * p.nblocks * 4);
+  for (int i = 0; i < 2; ++i) {
+    p.off_hist[i] = off;
+    off += align256((size_t)kMaxRadix * p.nblocks * 4);
+  }
+  p.off_totals = off;
+  off += align256((size_t)kMaxRadix * 4);
   p.off_part = off;
   off += align256((size_t)p.nchunks * 2 * feature * 4);
   p.off_leaders = off; // two counters, then two lists of chunk ids (see the span kernels)
@@ -735,45 +1095,62 @@ ScatterPlan make_scatter_plan(int64_t rows, int64_t n, int64_t feature) {
   return p;
 }
 
+// measurement override of the accumulate pass (b200_index_put_tune): 0 = rule, 1 = rows through
+// registers, 2 = rows staged in shared memory
+int g_chunk_path_override = 0;
+
 template <typename T, int LV>
-int launch_scatter_tail(const T *in, const T *upd, T *out, const uint32_t *keys, const uint32_t *vals,
+int launch_scatter_tail(bool staged, const T *in, const T *upd, T *out, const uint32_t *keys, const uint32_t *vals,
                         float *part, uint32_t *leaders, int64_t n, int64_t rows, int64_t feature,
                         cudaStream_t stream) {
   const int64_t nchunks = ceil_div<int64_t>(n, kChunk);
-  scatter_chunk_kernel<T, LV><<<(unsigned)ceil_div<int64_t>(nchunks, 8), 256, 0, stream>>>(
-      in, upd, out, keys, vals, part, leaders, n, rows, feature);
-  if (int rc = check_launch())
-    return rc;
+  if (staged) {
+    const size_t smem = kStagedWarps * kStagedSmemPerWarp;
+    // the attribute belongs to the current device's context: set on every call (a host-side table write)
+    if (int rc = check_cuda(cudaFuncSetAttribute(scatter_chunk_staged_kernel<T>,
+                                                 cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem)))
+      return rc;
+    if (int rc = launch_pdl(scatter_chunk_staged_kernel<T>, dim3((unsigned)ceil_div<int64_t>(nchunks, kStagedWarps)),
+                            dim3(kStagedWarps * 32), smem, stream, in, upd, out, keys, vals, part, leaders, n, rows,
+                            feature))
+      return rc;
+  } else {
+    if (int rc = launch_pdl(scatter_chunk_kernel<T, LV>, dim3((unsigned)ceil_div<int64_t>(nchunks, 8)), dim3(256), 0,
+                            stream, in, upd, out, keys, vals, part, leaders, n, rows, feature))
+      return rc;
+  }
   const unsigned short_grid = (unsigned)std::min<int64_t>(ceil_div<int64_t>(nchunks, 8), kNumSMs * 8);
-  scatter_span_short_kernel<T, LV><<<short_grid, 256, 0, stream>>>(in, out, keys, part, leaders, n, feature);
-  if (int rc = check_launch())
+  if (int rc = launch_pdl(scatter_span_short_kernel<T, LV>, dim3(short_grid), dim3(256), 0, stream, in, out, keys,
+                          (const float *)part, leaders, n, feature))
     return rc;
   const unsigned long_grid = (unsigned)std::min<int64_t>(ceil_div<int64_t>(nchunks, 32), kNumSMs);
-  scatter_span_long_kernel<T, LV><<<long_grid, 1024, 0, stream>>>(in, out, keys, part, leaders, n, feature);
-  return check_launch();
+  return launch_pdl(scatter_span_long_kernel<T, LV>, dim3(long_grid), dim3(1024), 0, stream, in, out, keys,
+                    (const float *)part, (const uint32_t *)leaders, n, feature);
 }
 
 // The index sort does not depend on the table copy, so the two run side by side:
 // the sort is forked onto a helper stream and joined before the accumulate pass.
-// One helper stream (and its two events) is kept per (device, caller stream); they
-// are created the first time that caller stream is seen and live until exit.
+// One helper stream (and its two events) is kept per (device, caller stream): created
+// by b200_index_put_prepare, or by the first call that needs them, and destroyed by
+// b200_index_put_release.
 struct SideStream {
   cudaStream_t stream = nullptr;
   cudaEvent_t fork = nullptr, join = nullptr;
 };
 
+std::mutex g_side_mu;
+std::map<std::pair<int, cudaStream_t>, SideStream> g_side_pool;
+
 int get_side_stream(cudaStream_t user, SideStream *out) {
-  static std::mutex mu;
-  static std::map<std::pair<int, cudaStream_t>, SideStream> pool;
   int dev = 0;
   if (int rc = check_cuda(cudaGetDevice(&dev)))
     return rc;
-  std::lock_guard<std::mutex> lock(mu);
-  auto it = pool.find({dev, user});
-  if (it == pool.end()) {
+  std::lock_guard<std::mutex> lock(g_side_mu);
+  auto it = g_side_pool.find({dev, user});
+  if (it == g_side_pool.end()) {
     SideStream s;
-    // Highest priority: the helper stream carries the sort, a chain of nine small kernels, beside
-    // the table copy, whose sixteen thousand blocks would otherwise sit in front of every one of
+    // Highest priority: the helper stream carries the sort, a chain of small kernels, beside the
+    // table copy, whose sixteen thousand blocks would otherwise sit in front of every one of
     // them in the block scheduler's queue.
     int least = 0, greatest = 0;
     if (int rc = check_cuda(cudaDeviceGetStreamPriorityRange(&least, &greatest)))
@@ -784,10 +1161,29 @@ int get_side_stream(cudaStream_t user, SideStream *out) {
       return rc;
     if (int rc = check_cuda(cudaEventCreateWithFlags(&s.join, cudaEventDisableTiming)))
       return rc;
-    it = pool.emplace(std::make_pair(dev, user), s).first;
+    it = g_side_pool.emplace(std::make_pair(dev, user), s).first;
   }
-  *out = it->second;
+  if (out)
+    *out = it->second;
   return B200_OK;
+}
+
+int release_side_stream(cudaStream_t user) {
+  int dev = 0;
+  if (int rc = check_cuda(cudaGetDevice(&dev)))
+    return rc;
+  SideStream s;
+  {
+    std::lock_guard<std::mutex> lock(g_side_mu);
+    auto it = g_side_pool.find({dev, user});
+    if (it == g_side_pool.end())
+      return B200_OK;
+    s = it->second;
+    g_side_pool.erase(it);
+  }
+  (void)cudaEventDestroy(s.fork);
+  (void)cudaEventDestroy(s.join);
+  return check_cuda(cudaStreamDestroy(s.stream)); // work already queued on it still completes
 }
 
 template <typename T>
@@ -828,23 +1224,33 @@ int scatter_add(const T *in, const int64_t *idx, const T *upd, T *out, int64_t r
   char *w = static_cast<char *>(ws);
   uint32_t *keys[2] = {(uint32_t *)(w + p.off_keys[0]), (uint32_t *)(w + p.off_keys[1])};
   uint32_t *vals[2] = {(uint32_t *)(w + p.off_vals[0]), (uint32_t *)(w + p.off_vals[1])};
-  uint32_t *hist = (uint32_t *)(w + p.off_hist);
+  uint32_t *hist[2] = {(uint32_t *)(w + p.off_hist[0]), (uint32_t *)(w + p.off_hist[1])};
+  uint32_t *totals = (uint32_t *)(w + p.off_totals);
   float *part = (float *)(w + p.off_part);
   uint32_t *leaders = (uint32_t *)(w + p.off_leaders);
   const int nb = (int)p.nblocks;
+  const int radix = 1 << p.digit_bits;
+  if (int rc = launch_pdl(radix_first_hist_kernel, dim3(nb), dim3(256), 0, stream, idx, keys[0], hist[0], n, rows,
+                          radix, nb, status, leaders))
+    return rc;
   int cur = 0;
   for (int pass = 0; pass < p.passes; ++pass) {
-    const int shift = pass * kRadixBits;
+    const int shift = pass * p.digit_bits;
+    const bool has_next = pass + 1 < p.passes;
+    uint32_t *h = hist[pass & 1], *h_next = has_next ? hist[(pass + 1) & 1] : nullptr;
+    if (int rc = launch_pdl(radix_scan_kernel, dim3((unsigned)ceil_div<int64_t>(radix, 8)), dim3(256), 0, stream, h,
+                            totals, h_next, radix, radix, nb))
+      return rc;
+    int rc;
     if (pass == 0)
-      radix_hist_kernel<true><<<nb, 256, 0, stream>>>(idx, nullptr, keys[0], hist, n, rows, shift, nb, status, leaders);
+      rc = launch_pdl(radix_scatter_kernel<true>, dim3(nb), dim3(256), 0, stream, (const uint32_t *)keys[cur],
+                      (const uint32_t *)nullptr, keys[cur ^ 1], vals[cur ^ 1], (const uint32_t *)h,
+                      (const uint32_t *)totals, h_next, n, shift, radix, shift + p.digit_bits, radix, nb);
     else
-      radix_hist_kernel<false><<<nb, 256, 0, stream>>>(nullptr, keys[cur], nullptr, hist, n, rows, shift, nb, nullptr, nullptr);
-    radix_scan_kernel<<<1, 1024, 0, stream>>>(hist, (int64_t)kRadix * nb);
-    if (pass == 0)
-      radix_scatter_kernel<true><<<nb, 256, 0, stream>>>(keys[cur], nullptr, keys[cur ^ 1], vals[cur ^ 1], hist, n, shift, nb);
-    else
-      radix_scatter_kernel<false><<<nb, 256, 0, stream>>>(keys[cur], vals[cur], keys[cur ^ 1], vals[cur ^ 1], hist, n, shift, nb);
-    if (int rc = check_launch())
+      rc = launch_pdl(radix_scatter_kernel<false>, dim3(nb), dim3(256), 0, stream, (const uint32_t *)keys[cur],
+                      (const uint32_t *)vals[cur], keys[cur ^ 1], vals[cur ^ 1], (const uint32_t *)h,
+                      (const uint32_t *)totals, h_next, n, shift, radix, shift + p.digit_bits, radix, nb);
+    if (rc)
       return rc;
     cur ^= 1;
   }
@@ -862,17 +1268,21 @@ int scatter_add(const T *in, const int64_t *idx, const T *upd, T *out, int64_t r
   while (lane_bytes > (int)sizeof(T) && (mis % lane_bytes != 0 || feature * (int64_t)sizeof(T) < 32LL * lane_bytes))
     lane_bytes >>= 1;
   const int lv = lane_bytes / (int)sizeof(T);
+  // rows staged through shared memory whenever whole rows can be copied in 16-byte pieces
+  bool staged = mis % 16 == 0 && feature * (int64_t)sizeof(T) >= 64;
+  if (g_chunk_path_override == 1)
+    staged = false;
   switch (lv) {
   case 8:
     if constexpr (sizeof(T) == 2)
-      return launch_scatter_tail<T, 8>(in, upd, out, keys[cur], vals[cur], part, leaders, n, rows, feature, stream);
+      return launch_scatter_tail<T, 8>(staged, in, upd, out, keys[cur], vals[cur], part, leaders, n, rows, feature, stream);
     return B200_ERR_UNSUPPORTED;
   case 4:
-    return launch_scatter_tail<T, 4>(in, upd, out, keys[cur], vals[cur], part, leaders, n, rows, feature, stream);
+    return launch_scatter_tail<T, 4>(staged, in, upd, out, keys[cur], vals[cur], part, leaders, n, rows, feature, stream);
   case 2:
-    return launch_scatter_tail<T, 2>(in, upd, out, keys[cur], vals[cur], part, leaders, n, rows, feature, stream);
+    return launch_scatter_tail<T, 2>(staged, in, upd, out, keys[cur], vals[cur], part, leaders, n, rows, feature, stream);
   default:
-    return launch_scatter_tail<T, 1>(in, upd, out, keys[cur], vals[cur], part, leaders, n, rows, feature, stream);
+    return launch_scatter_tail<T, 1>(staged, in, upd, out, keys[cur], vals[cur], part, leaders, n, rows, feature, stream);
   }
 }
 
@@ -901,6 +1311,12 @@ extern "C" int b200_index_select(int elt_bytes, int idx_bytes, const void *in, c
                                  cudaStream_t stream) {
   return b200_index_select_path(0, elt_bytes, idx_bytes, in, idx, out, A, IB, OB, C, status, stream);
 }
+
+extern "C" void b200_index_put_tune(int chunk_path) { g_chunk_path_override = chunk_path; }
+
+extern "C" int b200_index_put_prepare(cudaStream_t stream) { return get_side_stream(stream, nullptr); }
+
+extern "C" int b200_index_put_release(cudaStream_t stream) { return release_side_stream(stream); }
 
 extern "C" size_t b200_index_put_workspace_bytes(int dtype, int64_t rows, int64_t index_count,
                                                  int64_t feature) {

@@ -16,8 +16,12 @@
 //                        column slab per step, 8 warps stride over the B rows,
 //                        and B is split over enough blocks to fill 148 SMs
 //                        (split-K); the f32 partials of the splits are combined in
-//                        split order by a second pass, so the result does not
-//                        depend on scheduling.
+//                        split order, so the result does not depend on scheduling.
+//                        When the fold is small it happens in the same launch: each
+//                        block takes a ticket after writing its partials and the
+//                        block that draws the last ticket of a column slab folds
+//                        that slab (nobody waits for anybody).  Otherwise a second
+//                        pass does it.
 //
 // Max semantics (reduction_helper.h:159-180 folded in ascending index order):
 // NaN wins; otherwise the largest value; between +0 and -0, which compare equal,
@@ -26,7 +30,10 @@
 // backward scan for the last zero of the range to fix the sign.
 #include <cooperative_groups.h>
 
+#include <algorithm>
+#include <map>
 #include <mutex>
+#include <utility>
 
 #include "common.cuh"
 
@@ -336,12 +343,21 @@ __global__ void __launch_bounds__(kBlock)
 // NV = elements per lane per load (16 / sizeof(T) when 16-byte loads are
 // possible, else 1).  A warp covers `rpw = 32 / lpr` rows of a slab of
 // lpr * NV columns per step; 8 warps stride over the rows of this block's split.
-template <typename T, int OP, int NV, typename OutT>
+//
+// kFused: after writing its partials a block takes a ticket of its (a, slab); the block
+// that draws the last one folds the `splits` partials of the slab's columns in split order.
+// The ticket words live in g_cols_tickets (zero when the library is loaded; atomicInc wraps
+// the last ticket back to zero, so every launch leaves its words as it found them).
+constexpr int kTicketWords = 1 << 14;
+static __device__ unsigned g_cols_tickets[kTicketWords];
+
+template <typename T, int OP, int NV, bool kFused, typename OutT>
 __global__ void __launch_bounds__(kBlock, 4)
-    reduce_cols_kernel(const T *__restrict__ in, OutT *__restrict__ out, float *__restrict__ partial,
+    reduce_cols_kernel(const T *__restrict__ in, OutT *__restrict__ out, float *partial,
                        int64_t A, int64_t B, int64_t C, int lpr, int slabs, int splits,
-                       int64_t rows_per_split) {
-  __shared__ float smem[kBlock * NV]; // [row lane][column of the slab]
+                       int64_t rows_per_split, int ticket_base) {
+  __shared__ float smem[kBlock * (NV > 4 ? NV : 4)]; // [row lane][column of the slab]; the fold: [slice][column]
+  __shared__ int is_last;
   pdl_wait();              // inputs may come from the kernel launched just before this one
   pdl_launch_dependents(); // lets the next kernel (the second pass) be scheduled while this one runs
 
@@ -447,6 +463,82 @@ __global__ void __launch_bounds__(kBlock, 4)
     else
       partial[((int64_t)split * A + a) * C + col] = r;
   }
+  if (!kFused || splits == 1)
+    return;
+
+  // ---- the last block of this (a, slab) folds the slab's partials --------------------------
+  __threadfence(); // this thread's partials are visible before the ticket is
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    const unsigned old = atomicInc(&g_cols_tickets[ticket_base + a * slabs + slab], (unsigned)splits - 1u);
+    is_last = old == (unsigned)splits - 1u;
+    __threadfence();
+  }
+  __syncthreads();
+  if (!is_last)
+    return;
+  const int live_cols = (int)min((int64_t)ncols, C - slab_col0);
+  const float *pbase = partial + a * C + slab_col0; // + s * A * C
+  const int64_t pstride = A * C;
+  // V floats per load: 4 when every row of partials starts 16-byte aligned
+  const bool v4 = NV > 1 && (C % 4 == 0) && (live_cols % 4 == 0) && (reinterpret_cast<uintptr_t>(partial) & 15u) == 0;
+  const int groups = v4 ? live_cols / 4 : live_cols; // column groups
+  const int slices = max(1, min(kBlock / groups, splits));
+  const int per = (splits + slices - 1) / slices;
+  {
+    const int cg = threadIdx.x % groups, slice = threadIdx.x / groups;
+    if (slice < slices) {
+      const int s0 = slice * per, s1 = min(splits, s0 + per);
+      if (v4) {
+        float4 r = make_float4(0.f, 0.f, 0.f, 0.f);
+        if (s0 < s1) {
+          const float *p = pbase + cg * 4;
+          r = __ldcg(reinterpret_cast<const float4 *>(p + s0 * pstride));
+          for (int s = s0 + 1; s < s1; s += 8) {
+            float4 v[8];
+#pragma unroll
+            for (int u = 0; u < 8; ++u)
+              if (s + u < s1)
+                v[u] = __ldcg(reinterpret_cast<const float4 *>(p + (s + u) * pstride));
+#pragma unroll
+            for (int u = 0; u < 8; ++u)
+              if (s + u < s1) {
+                r.x = op_apply_ordered<OP>(r.x, v[u].x);
+                r.y = op_apply_ordered<OP>(r.y, v[u].y);
+                r.z = op_apply_ordered<OP>(r.z, v[u].z);
+                r.w = op_apply_ordered<OP>(r.w, v[u].w);
+              }
+          }
+        }
+        *reinterpret_cast<float4 *>(&smem[slice * live_cols + cg * 4]) = r;
+      } else {
+        float r = 0.f;
+        if (s0 < s1) {
+          const float *p = pbase + cg;
+          r = __ldcg(p + s0 * pstride);
+          for (int s = s0 + 1; s < s1; s += 8) {
+            float v[8];
+#pragma unroll
+            for (int u = 0; u < 8; ++u)
+              if (s + u < s1)
+                v[u] = __ldcg(p + (s + u) * pstride);
+#pragma unroll
+            for (int u = 0; u < 8; ++u)
+              if (s + u < s1)
+                r = op_apply_ordered<OP>(r, v[u]);
+          }
+        }
+        smem[slice * live_cols + cg] = r;
+      }
+    }
+  }
+  __syncthreads();
+  for (int j = threadIdx.x; j < live_cols; j += kBlock) {
+    float r = smem[j];
+    for (int w = 1; w < slices && w * per < splits; ++w)
+      r = op_apply_ordered<OP>(r, smem[w * live_cols + j]);
+    store_out(out + a * C + slab_col0 + j, r);
+  }
 }
 
 // second pass: out[i] = fold over s of partial[i * stride_i + s * stride_s].
@@ -504,6 +596,15 @@ __global__ void __launch_bounds__(kBlock)
 // plan constants of the column path (threads that cover one row of a slab; blocks per SM aimed at)
 constexpr int kColsThreadsPerRow = 32;
 constexpr int kColsBlocksPerSm = 4;
+// The last block of a slab folds splits x columns f32 partials out of L2 on its own: above this
+// many bytes the slab is made narrower (more slabs fold side by side) or the fold is left to a
+// second launch that spreads it over many blocks.
+constexpr int64_t kFusedFoldMaxBytes = 64 * 1024;
+
+// Measurement override of the column plan (b200_reduce_cols_plan_override): threads per slab
+// row (0 = rule above) and fused fold (-1 = rule, 0 = never, 1 = whenever tickets are available).
+int g_cols_lpr_override = 0;
+int g_cols_fused_override = -1;
 
 // ---- launch plan: a pure function of the shape -----------------------------
 struct Plan {
@@ -515,6 +616,7 @@ struct Plan {
   // columns
   int lpr, slabs, splits;
   int64_t rows_per_split;
+  bool fused; // columns: the fold of the splits happens in the same launch
   size_t ws_bytes;
 };
 
@@ -544,17 +646,62 @@ Plan make_plan(int esize, int64_t A, int64_t B, int64_t C, bool vec_cols) {
   } else {
     p.rows = false;
     const int NV = vec_cols ? N : 1;
-    p.lpr = (int)std::min<int64_t>(kColsThreadsPerRow, pow2_ceil(ceil_div<int64_t>(C, NV)));
-    p.slabs = (int)ceil_div<int64_t>(C, (int64_t)p.lpr * NV);
-    const int64_t rows_per_step = kBlock / p.lpr;
-    const int64_t blocks = A * p.slabs;
-    int64_t splits = std::max<int64_t>(1, ceil_div<int64_t>((int64_t)kColsBlocksPerSm * kNumSMs, blocks));
-    splits = std::min<int64_t>(splits, std::max<int64_t>(1, B / (rows_per_step * 4)));
-    p.rows_per_split = ceil_div<int64_t>(B, splits);
-    p.splits = (int)ceil_div<int64_t>(B, p.rows_per_split);
+    auto split_for = [&](int lpr) {
+      p.lpr = lpr;
+      p.slabs = (int)ceil_div<int64_t>(C, (int64_t)p.lpr * NV);
+      const int64_t rows_per_step = kBlock / p.lpr;
+      const int64_t blocks = A * p.slabs;
+      int64_t splits = std::max<int64_t>(1, ceil_div<int64_t>((int64_t)kColsBlocksPerSm * kNumSMs, blocks));
+      splits = std::min<int64_t>(splits, std::max<int64_t>(1, B / (rows_per_step * 4)));
+      p.rows_per_split = ceil_div<int64_t>(B, splits);
+      p.splits = (int)ceil_div<int64_t>(B, p.rows_per_split);
+    };
+    auto fold_bytes = [&] { return (int64_t)p.splits * std::min<int64_t>((int64_t)p.lpr * NV, C) * 4; };
+    int lpr = (int)std::min<int64_t>(kColsThreadsPerRow, pow2_ceil(ceil_div<int64_t>(C, NV)));
+    if (g_cols_lpr_override > 0)
+      lpr = std::min(lpr, g_cols_lpr_override);
+    split_for(lpr);
+    // narrower slabs while a slab's fold is too large for one block and a warp still reads
+    // 256 contiguous bytes of a row
+    while (g_cols_lpr_override == 0 && vec_cols && p.splits > 1 && fold_bytes() > kFusedFoldMaxBytes && p.lpr > 16)
+      split_for(p.lpr / 2);
+    p.fused = p.splits > 1 && fold_bytes() <= kFusedFoldMaxBytes && A * p.slabs <= 1024;
+    if (g_cols_fused_override >= 0)
+      p.fused = p.splits > 1 && g_cols_fused_override == 1 && A * p.slabs <= 1024;
     p.ws_bytes = p.splits > 1 ? (size_t)p.splits * A * C * sizeof(float) : 0;
   }
   return p;
+}
+
+// A fused launch needs A * slabs ticket words of g_cols_tickets that no other launch in flight
+// uses.  Two launches that may overlap on the GPU have different workspaces (they would race on
+// the partials otherwise), so a range is bound to (device, workspace address) the first time
+// that workspace is seen and kept for the life of the process; the words are zero whenever no
+// launch is in flight.  Returns -1 when the pool is used up: the caller then folds in a second
+// launch instead.
+int ticket_range(const void *ws, int words) {
+  struct Range {
+    int base, words;
+  };
+  static std::mutex mu;
+  static std::map<std::pair<int, const void *>, Range> bound;
+  static std::map<int, int> next_free; // per device
+  int dev = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess) {
+    (void)cudaGetLastError();
+    return -1;
+  }
+  std::lock_guard<std::mutex> lock(mu);
+  auto it = bound.find({dev, ws});
+  if (it != bound.end() && it->second.words >= words)
+    return it->second.base;
+  int &next = next_free[dev];
+  if (next + words > kTicketWords)
+    return -1;
+  const Range r{next, words};
+  next += words;
+  bound[{dev, ws}] = r;
+  return r.base;
 }
 
 // Whether 16-byte loads are possible for the column kernel is a property of the
@@ -631,20 +778,31 @@ int launch(const T *in, OutT *out, int64_t A, int64_t B, int64_t C, void *ws,
   if (!vec && cols_vec_by_shape(sizeof(T), C)) {
     q.lpr = (int)std::min<int64_t>(kColsThreadsPerRow, pow2_ceil(C));
     q.slabs = (int)ceil_div<int64_t>(C, q.lpr);
+    q.fused = false;
   }
   const int64_t grid = A * q.slabs * q.splits;
   if (grid > 0x7fffffffLL)
     return B200_ERR_UNSUPPORTED;
+  int ticket_base = -1;
+  if (q.fused)
+    ticket_base = ticket_range(ws, (int)(A * q.slabs));
+  const bool fused = q.fused && ticket_base >= 0;
   int rc;
-  if (vec)
-    rc = launch_pdl(reduce_cols_kernel<T, OP, N, OutT>, dim3((unsigned)grid), dim3(kBlock), 0, stream, in, out,
-                    partial, A, B, C, q.lpr, q.slabs, q.splits, q.rows_per_split);
+  if (vec && fused)
+    rc = launch_pdl(reduce_cols_kernel<T, OP, N, true, OutT>, dim3((unsigned)grid), dim3(kBlock), 0, stream, in, out,
+                    partial, A, B, C, q.lpr, q.slabs, q.splits, q.rows_per_split, ticket_base);
+  else if (vec)
+    rc = launch_pdl(reduce_cols_kernel<T, OP, N, false, OutT>, dim3((unsigned)grid), dim3(kBlock), 0, stream, in, out,
+                    partial, A, B, C, q.lpr, q.slabs, q.splits, q.rows_per_split, 0);
+  else if (fused)
+    rc = launch_pdl(reduce_cols_kernel<T, OP, 1, true, OutT>, dim3((unsigned)grid), dim3(kBlock), 0, stream, in, out,
+                    partial, A, B, C, q.lpr, q.slabs, q.splits, q.rows_per_split, ticket_base);
   else
-    rc = launch_pdl(reduce_cols_kernel<T, OP, 1, OutT>, dim3((unsigned)grid), dim3(kBlock), 0, stream, in, out,
-                    partial, A, B, C, q.lpr, q.slabs, q.splits, q.rows_per_split);
+    rc = launch_pdl(reduce_cols_kernel<T, OP, 1, false, OutT>, dim3((unsigned)grid), dim3(kBlock), 0, stream, in, out,
+                    partial, A, B, C, q.lpr, q.slabs, q.splits, q.rows_per_split, 0);
   if (rc)
     return rc;
-  if (q.splits > 1) {
+  if (q.splits > 1 && !fused) {
     const int64_t n = A * C;
     return launch_pdl(reduce_finalize_kernel<OP, OutT>, dim3((unsigned)ceil_div<int64_t>(n, 32)),
                       dim3(kFinalizeBlock), 0, stream, (const float *)partial, out, n, q.splits, (int64_t)1, n);
@@ -670,6 +828,14 @@ int esize_of(int dtype) {
 } // namespace b200
 
 using namespace b200;
+
+// Measurement hook (not part of the drop-in ABI): pins the column plan's threads per slab row
+// (0 = the shape rule) and whether the fold is fused into the first launch (-1 = the rule).
+// Workspace sizes follow the pinned plan, so ask for them after calling this.
+extern "C" void b200_reduce_cols_plan_override(int threads_per_row, int fused) {
+  g_cols_lpr_override = threads_per_row;
+  g_cols_fused_override = fused;
+}
 
 extern "C" size_t b200_reduce_workspace_bytes(int op, int dtype, int64_t A, int64_t B, int64_t C) {
   (void)op;

@@ -111,6 +111,15 @@ __device__ __forceinline__ void tma_load_4d(void *smem_dst, const CUtensorMap *m
                "l"(map), "r"(x), "r"(y), "r"(z), "r"(w), "r"(smem_addr(bar))
                : "memory");
 }
+// four rows of a two-dimensional tensor, named by their row coordinates, into four consecutive
+// rows of shared memory (box = one row of the map); x is the first column, a multiple of 16 bytes
+__device__ __forceinline__ void tma_gather4_2d(void *smem_dst, const CUtensorMap *map, int x, int r0, int r1,
+                                               int r2, int r3, uint64_t *bar) {
+  asm volatile("cp.async.bulk.tensor.2d.shared::cluster.global.tile::gather4.mbarrier::complete_tx::bytes "
+               "[%0], [%1, {%2, %3, %4, %5, %6}], [%7];" ::"r"(smem_addr(smem_dst)),
+               "l"(map), "r"(x), "r"(r0), "r"(r1), "r"(r2), "r"(r3), "r"(smem_addr(bar))
+               : "memory");
+}
 __device__ __forceinline__ void tma_store_3d(const CUtensorMap *map, const void *smem_src, int x,
                                              int y, int z) {
   asm volatile("cp.async.bulk.tensor.3d.global.shared::cta.tile.bulk_group [%0, {%2, %3, %4}], [%1];" ::

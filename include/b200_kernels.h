@@ -52,7 +52,11 @@ const char *b200_error_string(int code);
  * f32 (reduce_impl.h:63-69).  Max follows reduction_helper.h:159-180 folded in
  * ascending index order: any NaN gives NaN, equal values keep the later one.
  * Workspace bytes depend only on (op, dtype, A, B, C); the workspace may be
- * uninitialised.
+ * uninitialised.  Two calls that may overlap on the GPU need different
+ * workspaces.  (A column reduction split over many blocks folds its partial
+ * sums in the same launch: the last block of a column slab to finish does it.
+ * The tickets that tell which block is last are library-owned words bound to
+ * the workspace address, zero between launches.)
  */
 size_t b200_reduce_workspace_bytes(int op, int dtype, int64_t A, int64_t B,
                                    int64_t C);
@@ -142,6 +146,16 @@ int b200_index_select(int elt_bytes, int idx_bytes, const void *in,
  */
 size_t b200_index_put_workspace_bytes(int dtype, int64_t rows,
                                       int64_t index_count, int64_t feature);
+/* Out of place, the index sort runs on a helper stream beside the table copy.  The
+ * helper stream and its two events belong to the pair (current device, caller
+ * stream): b200_index_put_prepare creates them ahead of time (a host-side call,
+ * no device work); otherwise the first b200_index_put_add on that pair does, so
+ * make one of the two before a stream capture begins.  b200_index_put_release
+ * destroys them; call it before destroying `stream`, whose handle value the
+ * runtime may give to a later stream.  (No counterpart in the reference, whose
+ * IndexPut is a copy and one atomicAdd kernel on the caller's stream.) */
+int b200_index_put_prepare(cudaStream_t stream);
+int b200_index_put_release(cudaStream_t stream);
 int b200_index_put_add(int dtype, const void *in, const int64_t *idx,
                        const void *upd, void *out, int64_t rows,
                        int64_t index_count, int64_t feature, void *workspace,
@@ -201,6 +215,14 @@ int b200_flash_attn_bwd(int dtype, const void *dout, const void *q,
                         float *d_softmax_sum, float *dq_accum,
                         const b200_flash_attn_params *params,
                         cudaStream_t stream);
+
+/* Every wait inside the forward and backward kernels is bounded (about 2 s).  If one
+ * runs out, the block stops, stores nothing more (its part of out / dq / dk / dv
+ * stays unwritten) and sets a sticky per-device status word: 2 = forward, 3 =
+ * backward.  This call copies the word to *status and clears it.  It is a
+ * synchronous device read: call it after synchronising the streams that ran
+ * attention.  (No counterpart in the reference, whose kernels have no waits.) */
+int b200_flash_attn_take_status(int *status);
 
 /* Attention over a key/value cache (decode): the typed door behind
  * run_flash_attn_kvcache (flash_api.h:75-82, unpacking flash_api.cu:727-811, setup

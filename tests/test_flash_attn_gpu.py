@@ -89,6 +89,41 @@ def test_flash_attn_bwd(b, sq, sk, h, hk, causal, dt):
         assert torch.equal(a.view(torch.int16), b_.view(torch.int16)), "backward is not deterministic"
 
 
+# The configuration the benchmark times: S = 4096, D = 128, causal, bf16 (32 x 32 tiles per (batch, head), every
+# ring of the forward and of both backward passes wraps many times), on slices the oracle finishes in seconds.
+FULL_SEQ_CASES = [
+    # b, sq, sk, h, hk, causal
+    (1, 4096, 4096, 2, 2, True),
+    (1, 4096, 4096, 4, 1, True),     # grouped heads: four query heads on one key/value head
+    (1, 4096, 4224, 2, 2, False),    # no mask, Sk > Sq: 33 key tiles for every query tile
+]
+
+
+@pytest.mark.parametrize("b,sq,sk,h,hk,causal", FULL_SEQ_CASES)
+def test_flash_attn_fwd_bwd_at_benchmark_sequence_length(b, sq, sk, h, hk, causal):
+    from byteir_b200 import ops
+    dt = "bf16"
+    rng = np.random.default_rng(sq + sk + h * 13)
+    q, k, v = _mk(rng, (b, sq, h, 128), dt), _mk(rng, (b, sk, hk, 128), dt), _mk(rng, (b, sk, hk, 128), dt)
+    do = _mk(rng, (b, sq, h, 128), dt)
+    scale = 1.0 / np.sqrt(128.0)
+    qd, kd, vd, dod = _dev(q), _dev(k), _dev(v), _dev(do)
+    want_o, want_lse = O.flash_attn_fwd(q, k, v, scale, causal)
+    o, lse = ops.flash_attn_fwd(qd, kd, vd, scale, causal)
+    dq, dk, dv = ops.flash_attn_bwd(dod, qd, kd, vd, o, lse, scale, causal)
+    torch.cuda.synchronize()
+    np.testing.assert_allclose(lse.cpu().numpy(), want_lse, rtol=1e-3, atol=1e-3)
+    np.testing.assert_allclose(O.to_f32(_host(o)), O.to_f32(want_o), rtol=2e-2, atol=1e-2)
+    wq, wk, wv = O.flash_attn_bwd(do, q, k, v, _host(o), lse.cpu().numpy(), scale, causal)
+    for name, got, want in (("dq", dq, wq), ("dk", dk, wk), ("dv", dv, wv)):
+        np.testing.assert_allclose(O.to_f32(_host(got)), O.to_f32(want), rtol=2e-2, atol=1e-2, err_msg=name)
+    o2, lse2 = ops.flash_attn_fwd(qd, kd, vd, scale, causal)
+    again = ops.flash_attn_bwd(dod, qd, kd, vd, o, lse, scale, causal)
+    assert torch.equal(o2.view(torch.int16), o.view(torch.int16)) and torch.equal(lse2, lse)
+    for a, b_ in zip(again, (dq, dk, dv)):
+        assert torch.equal(a.view(torch.int16), b_.view(torch.int16)), "backward is not deterministic"
+
+
 def _fwd_bwd_check(q, k, v, do, causal, window, check_bwd=True, grad_atol_of_max=0.0):
     """grad_atol_of_max: extra absolute tolerance for the gradients as a fraction of the largest
     gradient magnitude, for inputs whose gradients are sums of large cancelling 16-bit products
@@ -248,3 +283,64 @@ def test_flash_attn_kvcache_caller_workspace_and_strided_cache():
     np.testing.assert_allclose(O.to_f32(_host(o)), O.to_f32(want_o), rtol=2e-2, atol=1e-2)
     with pytest.raises(Exception):
         ops.flash_attn_kvcache(qd, kd, vd, None, None, None, 0.09, True, workspace=ws[:64])
+
+
+# ---- bounded waits and the status word -------------------------------------------------------------
+@pytest.mark.parametrize("which", ["fwd", "bwd"])
+def test_flash_attn_wait_that_runs_out_sets_the_status_word(which):
+    """The elementwise warps leave out one arrival (a flag that nothing sets) and the waits get a short
+    limit: the kernel must end by itself, report 2 (forward) or 3 (backward) through the sticky status
+    word, and the next call on the same context must work and leave the word at zero."""
+    import ctypes as C
+    from byteir_b200 import ops, _native as N
+    lib = N.lib()
+    rng = np.random.default_rng(5)
+    q, k, v, do = (_mk(rng, (1, 256, 2, 128), "bf16") for _ in range(4))
+    scale = 1.0 / np.sqrt(128.0)
+    qd, kd, vd, dod = _dev(q), _dev(k), _dev(v), _dev(do)
+    o, lse = ops.flash_attn_fwd(qd, kd, vd, scale, True)
+    torch.cuda.synchronize()
+    st = C.c_int(-1)
+    assert lib.b200_flash_attn_take_status(C.byref(st)) == 0 and st.value == 0
+    try:
+        lib.b200_flash_attn_debug(1, 50)  # 50 polls of at most 20 us per wait
+        if which == "fwd":
+            ops.flash_attn_fwd(qd, kd, vd, scale, True)
+        else:
+            ops.flash_attn_bwd(dod, qd, kd, vd, o, lse, scale, True)
+        torch.cuda.synchronize()
+    finally:
+        lib.b200_flash_attn_debug(0, 0)
+    assert lib.b200_flash_attn_take_status(C.byref(st)) == 0
+    assert st.value == (2 if which == "fwd" else 3)
+    # the context is intact and the word was cleared by the read
+    o2, lse2 = ops.flash_attn_fwd(qd, kd, vd, scale, True)
+    dq, dk, dv = ops.flash_attn_bwd(dod, qd, kd, vd, o2, lse2, scale, True)
+    torch.cuda.synchronize()
+    assert torch.equal(o2.view(torch.int16), o.view(torch.int16))
+    wq, wk, wv = O.flash_attn_bwd(do, q, k, v, _host(o2), lse2.cpu().numpy(), scale, True)
+    np.testing.assert_allclose(O.to_f32(_host(dq)), O.to_f32(wq), rtol=2e-2, atol=1e-2)
+    assert lib.b200_flash_attn_take_status(C.byref(st)) == 0 and st.value == 0
+
+
+def test_kernels_with_large_shared_memory_on_a_second_device():
+    """The dynamic shared-memory limit of a kernel is a per-device attribute: every entry point that needs
+    more than 48 KiB must work with any device current, not only the first one a process used."""
+    if torch.cuda.device_count() < 2:
+        pytest.skip("needs two visible GPUs")
+    from byteir_b200 import ops
+    rng = np.random.default_rng(6)
+    q, k, v, do = (_mk(rng, (1, 256, 2, 128), "bf16") for _ in range(4))
+    scale = 1.0 / np.sqrt(128.0)
+    want_o, _ = O.flash_attn_fwd(q, k, v, scale, True)
+    table = rng.standard_normal((4096, 512), dtype=np.float32)
+    idx = rng.integers(0, 4096, 3000).astype(np.int64)
+    for dev in (0, 1):
+        with torch.cuda.device(dev):
+            to = lambda a: _dev(a).to(f"cuda:{dev}")
+            o, lse = ops.flash_attn_fwd(to(q), to(k), to(v), scale, True)
+            dq, dk, dv = ops.flash_attn_bwd(to(do), to(q), to(k), to(v), o, lse, scale, True)
+            g = ops.index_select(torch.from_numpy(table).to(f"cuda:{dev}"), torch.from_numpy(idx).to(f"cuda:{dev}"), 0)
+            torch.cuda.synchronize()
+            np.testing.assert_allclose(O.to_f32(_host(o)), O.to_f32(want_o), rtol=2e-2, atol=1e-2)
+            assert np.array_equal(g.cpu().numpy(), table[idx])

@@ -137,6 +137,40 @@ def test_reduce_config2_f16_multi_axis(ops):
     assert np.array_equal(_bits(gm), _bits(wm))
 
 
+@pytest.mark.parametrize("dt", ["f32", "f16", "bf16"])
+@pytest.mark.parametrize("op", ["sum", "max"])
+@pytest.mark.parametrize("shape", [(64 * 512, 1024), (20000, 96), (3, 9000, 40), (100000, 7)])
+def test_reduce_columns_fold_in_the_same_launch_equals_the_second_pass(ops, shape, op, dt):
+    """The split partials are folded in split order either by the last block of a slab (one launch) or
+    by a second launch: same bits, for every slab width the plan may choose."""
+    from byteir_b200 import _native as N
+    rng = np.random.default_rng(31)
+    x = _make(rng, shape, dt, "normal")
+    dims = [len(shape) - 2]
+    fn = ops.reduce_sum if op == "sum" else ops.reduce_max
+    xd = _to_dev(x)
+    outs = {}
+    try:
+        for lpr in (0, 32, 16, 8):
+            for fused in (0, 1):
+                N.lib().b200_reduce_cols_plan_override(lpr, fused)
+                outs[(lpr, fused)] = _to_host(fn(xd, dims)).reshape(-1)
+    finally:
+        N.lib().b200_reduce_cols_plan_override(0, -1)
+    auto = _to_host(fn(xd, dims)).reshape(-1)
+    A, B, C = O.reduce_abc(shape, dims)
+    want = O.reduce(op, x, A, B, C)
+    if op == "max":
+        _assert_max_equal(auto, want)
+    else:
+        np.testing.assert_allclose(O.to_f32(auto).astype(np.float64), O.to_f32(want).astype(np.float64),
+                                   rtol=2e-2 if dt != "f32" else 1e-5, atol=1e-2 if dt != "f32" else 2e-4)
+    for lpr in (0, 32, 16, 8):
+        a, b = outs[(lpr, 0)], outs[(lpr, 1)]
+        nan = np.isnan(O.to_f32(a))
+        assert np.array_equal(_bits(a)[~nan], _bits(b)[~nan]), (lpr, "fused and two-pass differ")
+
+
 def test_reduce_sum_sharded_partials_then_single_rounding(ops):
     """dim-0 sharding: f32 partials of the shards, summed, rounded once == unsharded result."""
     rng = np.random.default_rng(9)
@@ -177,6 +211,67 @@ def test_index_select(ops, shape, dim, n, dt, idt, path):
     assert np.array_equal(_bits(got), _bits(want))
 
 
+VARIANT_CASES = [((1000, 128), 0, 5000), ((30522, 128), 0, 128), ((256, 64, 128), 1, 100),
+                 ((4, 100, 40), 1, 1001), ((777, 32), 0, 3), ((50, 256), 0, 77)]
+
+
+def _check_gather_variant(ops, shape, dim, n, dt, idt, path):
+    """the persistent vector kernel (paths 3-6) and the tensor-map gather (paths 7, 8), bit for bit,
+    including an index out of range (zero row, status 1)"""
+    from byteir_b200 import _native as N
+    rng = np.random.default_rng(n + path)
+    x = _make(rng, shape, dt, "normal")
+    idx = rng.integers(0, shape[dim], n).astype(idt)
+    inner = int(np.prod(shape[dim + 1:])) * x.itemsize
+    ok = inner % 16 == 0 and (path < 7 or 64 <= inner <= 1024)
+    status = torch.zeros(1, dtype=torch.int32, device="cuda")
+    if not ok:
+        with pytest.raises(N.B200Error):
+            ops.index_select(_to_dev(x), _to_dev(idx), dim, status=status, path=path)
+        return
+    want, _ = O.index_select(x, idx, dim)
+    got = _to_host(ops.index_select(_to_dev(x), _to_dev(idx), dim, status=status, path=path))
+    assert int(status.item()) == 0
+    assert np.array_equal(_bits(got), _bits(want))
+    if idt == np.int64:
+        bad = idx.copy()
+        bad[n // 2] = shape[dim] + 5
+        bad[0] = -1
+        got = _to_host(ops.index_select(_to_dev(x), _to_dev(bad), dim, status=status, path=path))
+        assert int(status.item()) == 1
+        g = np.moveaxis(got, dim, 0)
+        w = np.moveaxis(want, dim, 0).copy()
+        w[n // 2] = 0
+        w[0] = 0
+        assert np.array_equal(_bits(np.ascontiguousarray(g)), _bits(np.ascontiguousarray(w)))
+
+
+
+@pytest.mark.parametrize("path", [3, 4, 5, 6])
+@pytest.mark.parametrize("dt,idt", [("f32", np.uint32), ("f16", np.int64)])
+@pytest.mark.parametrize("shape,dim,n", VARIANT_CASES)
+def test_index_select_persistent_vector_variants(ops, shape, dim, n, dt, idt, path):
+    _check_gather_variant(ops, shape, dim, n, dt, idt, path)
+
+
+@pytest.mark.parametrize("path", [7, 8])
+@pytest.mark.parametrize("dt,idt", [("f32", np.uint32), ("f16", np.int64)])
+@pytest.mark.parametrize("shape,dim,n", VARIANT_CASES)
+def test_index_select_tensor_map_gather(ops, shape, dim, n, dt, idt, path):
+    _check_gather_variant(ops, shape, dim, n, dt, idt, path)
+
+
+def test_index_select_tensor_map_gather_full_size_table(ops):
+    rng = np.random.default_rng(1234 + 2)
+    table = (rng.standard_normal((1_000_000, 128), dtype=np.float32) * 0.02).astype(np.float16)
+    idx = rng.integers(0, 1_000_000, 262_144).astype(np.int64)
+    want, _ = O.index_select(table, idx, 0)
+    td, idd = _to_dev(table), _to_dev(idx)
+    for path in (7, 8):
+        got = _to_host(ops.index_select(td, idd, 0, path=path))
+        assert np.array_equal(_bits(got), _bits(want))
+
+
 def test_index_select_config3_shape(ops):
     rng = np.random.default_rng(1234 + 2)
     table = (rng.standard_normal((200000, 128), dtype=np.float32) * 0.02).astype(np.float16)
@@ -184,6 +279,18 @@ def test_index_select_config3_shape(ops):
     want, _ = O.index_select(table, idx, 0)
     for path in (1, 2):
         got = _to_host(ops.index_select(_to_dev(table), _to_dev(idx), 0, path=path))
+        assert np.array_equal(_bits(got), _bits(want))
+
+
+def test_index_select_full_size_table(ops):
+    """the benchmark's own gather: f16 table [1,000,000 x 128] N(0, 0.02), 262,144 uniform int64 indices"""
+    rng = np.random.default_rng(1234 + 2)
+    table = (rng.standard_normal((1_000_000, 128), dtype=np.float32) * 0.02).astype(np.float16)
+    idx = rng.integers(0, 1_000_000, 262_144).astype(np.int64)
+    want, _ = O.index_select(table, idx, 0)
+    td, idd = _to_dev(table), _to_dev(idx)
+    for path in (0, 1, 2, 3, 5):
+        got = _to_host(ops.index_select(td, idd, 0, path=path))
         assert np.array_equal(_bits(got), _bits(want))
 
 
@@ -255,6 +362,86 @@ def test_index_put_add_zipf_duplicates_f16(ops):
     inplace = td.clone()
     ops.index_put_add(inplace, idd, ud, out=inplace)
     assert np.array_equal(_bits(_to_host(inplace)), _bits(got))
+
+
+def test_index_put_add_full_size_table_zipf(ops):
+    """the benchmark's own scatter-add: f16 table [1,000,000 x 128], 262,144 updates N(0,1), Zipf(1.1) indices;
+    deterministic, within rel 1e-3 of the oracle, untouched rows copied bit for bit"""
+    rng = np.random.default_rng(1234 + 3)
+    rows, n, feat = 1_000_000, 262_144, 128
+    table = (rng.standard_normal((rows, feat), dtype=np.float32) * 0.02).astype(np.float16)
+    upd = rng.standard_normal((n, feat), dtype=np.float32).astype(np.float16)
+    idx = _zipf_indices(rng, n, rows)
+    want, _ = O.index_put_add(table, idx, upd)
+    td, ud, idd = _to_dev(table), _to_dev(upd), _to_dev(idx)
+    got = _to_host(ops.index_put_add(td, idd, ud))
+    again = _to_host(ops.index_put_add(td, idd, ud))
+    assert np.array_equal(_bits(got), _bits(again)), "not deterministic"
+    touched = np.zeros(rows, bool)
+    touched[idx] = True
+    assert np.array_equal(_bits(got)[~touched], _bits(table)[~touched])
+    g, w = got[touched].astype(np.float64), want[touched].astype(np.float64)
+    assert np.all(np.abs(g - w) <= 1e-3 * np.abs(w) + 1e-4)
+
+
+def test_index_put_add_three_radix_passes_and_staged_tiles(ops):
+    """a table of more than 2^20 rows (three digits of the radix sort) with 1 KiB rows (four shared-memory
+    tiles per row in the accumulate pass), f32: against the sequential f32 oracle"""
+    rng = np.random.default_rng(21)
+    rows, n, feat = 3_000_000, 50_000, 16
+    x = rng.standard_normal((rows, feat), dtype=np.float32)
+    upd = rng.standard_normal((n, feat), dtype=np.float32)
+    idx = np.concatenate([rng.integers(0, rows, n - 5000), np.full(5000, rows - 1)]).astype(np.int64)
+    rng.shuffle(idx)
+    want, _ = O.index_put_add(x, idx, upd)
+    got = _to_host(ops.index_put_add(_to_dev(x), _to_dev(idx), _to_dev(upd)))
+    np.testing.assert_allclose(got, want, rtol=1e-5, atol=1e-5)
+    rows, n, feat = 3000, 40_000, 256
+    x = rng.standard_normal((rows, feat), dtype=np.float32)
+    upd = rng.standard_normal((n, feat), dtype=np.float32)
+    idx = rng.integers(0, rows, n).astype(np.int64)
+    want, _ = O.index_put_add(x, idx, upd)
+    got = _to_host(ops.index_put_add(_to_dev(x), _to_dev(idx), _to_dev(upd)))
+    np.testing.assert_allclose(got, want, rtol=1e-5, atol=2e-5)
+
+
+@pytest.mark.parametrize("chunk_path", [1, 2])
+def test_index_put_add_both_accumulate_kernels_agree_bit_for_bit(ops, chunk_path):
+    """rows through registers and rows staged in shared memory add in the same order"""
+    from byteir_b200 import _native as N
+    rng = np.random.default_rng(22)
+    rows, n, feat = 20_000, 100_000, 128
+    x = (rng.standard_normal((rows, feat), dtype=np.float32) * 0.02).astype(np.float16)
+    upd = rng.standard_normal((n, feat), dtype=np.float32).astype(np.float16)
+    idx = _zipf_indices(rng, n, rows)
+    ref = _to_host(ops.index_put_add(_to_dev(x), _to_dev(idx), _to_dev(upd)))
+    try:
+        N.lib().b200_index_put_tune(chunk_path)
+        got = _to_host(ops.index_put_add(_to_dev(x), _to_dev(idx), _to_dev(upd)))
+    finally:
+        N.lib().b200_index_put_tune(0)
+    assert np.array_equal(_bits(got), _bits(ref))
+
+
+def test_index_put_helper_stream_prepare_and_release(ops):
+    import ctypes as C
+    from byteir_b200 import _native as N
+    s = torch.cuda.Stream()
+    h = C.c_void_p(s.cuda_stream)
+    assert N.lib().b200_index_put_prepare(h) == 0
+    assert N.lib().b200_index_put_prepare(h) == 0  # idempotent
+    rng = np.random.default_rng(23)
+    x = rng.standard_normal((40_000, 64), dtype=np.float32)  # 10 MB: large enough to fork the sort
+    upd = rng.standard_normal((5000, 64), dtype=np.float32)
+    idx = rng.integers(0, 40_000, 5000).astype(np.int64)
+    want, _ = O.index_put_add(x, idx, upd)
+    xd, idd, ud = _to_dev(x), _to_dev(idx), _to_dev(upd)
+    with torch.cuda.stream(s):
+        got = ops.index_put_add(xd, idd, ud)
+    s.synchronize()
+    np.testing.assert_allclose(_to_host(got), want, rtol=1e-5, atol=1e-5)
+    assert N.lib().b200_index_put_release(h) == 0
+    assert N.lib().b200_index_put_release(h) == 0  # nothing left to release
 
 
 def test_index_put_add_out_of_range_skipped_and_flagged(ops):
