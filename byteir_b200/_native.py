@@ -78,8 +78,9 @@ EXTRA = {
     "b200_index_select_path": (_int, [_int, _int, _int, _vp, _vp, _vp, _i64, _i64, _i64, _i64, _vp, _vp]),
     "b200_transpose_batched_path": (_int, [_int, _int, _vp, _vp, _i64, _i64, _i64, _vp]),
     "b200_flash_attn_kvcache_tune": (None, [_int]),
-    "b200_reduce_cols_plan_override": (None, [_int, _int]),
+    "b200_reduce_cols_plan_override": (None, [_int]),
     "b200_index_put_tune": (None, [_int]),
+    "b200_reduce_tune": (None, [_int]),
     "b200_flash_attn_debug": (None, [_int, C.c_uint]),
 }
 

@@ -87,6 +87,14 @@ __device__ __forceinline__ void st_cs_v4(void *p, uint4 v) {
                : "memory");
 }
 
+// Hint that brings the line holding *p into L2 and returns nothing.  L2 is the point of coherence
+// of global memory, so the hint is harmless even for a line that a kernel still running is about
+// to write: a kernel launched with programmatic dependent launch may issue it BEFORE pdl_wait(),
+// which overlaps the DRAM fetch of its first loads with the tail of its predecessor.
+__device__ __forceinline__ void prefetch_l2(const void *p) {
+  asm volatile("prefetch.global.L2 [%0];" ::"l"(p));
+}
+
 // Programmatic dependent launch: a kernel launched with the programmatic stream
 // serialization attribute may start while its predecessor still runs; it must call
 // pdl_wait() before touching the predecessor's output.  The predecessor calls

@@ -170,7 +170,7 @@ struct SharedStorage {
   uint32_t tmem_base;
   int failed;
   uint32_t wait_polls;
-  float rowmax[2][2][kBM]; // [group][tile parity][row]: scaled row maximum of the group's tile
+  alignas(16) float rowmax[2][2][kBM]; // [group][tile parity][row]: scaled row maximum of the group's tile
   float2 xch[2][kBM];      // (reference max, row sum) of each group, for the final merge
 };
 
@@ -740,9 +740,9 @@ struct BwdShared {
   int failed;
   uint32_t wait_polls;
   // dK/dV kernel: -lse * log2e and -dsum of the streamed queries [group][parity][row], negated
-  // so that pairs of them are addends of packed FMAs / ADDs
-  float neg_lse2[2][2][kBwdBN];
-  float neg_dsum[2][2][kBwdBN];
+  // so that pairs of them are addends of packed FMAs / ADDs (read four at a time: 16-byte aligned)
+  alignas(16) float neg_lse2[2][2][kBwdBN];
+  alignas(16) float neg_dsum[2][2][kBwdBN];
 };
 
 __device__ __forceinline__ bool bwd_wait(uint64_t *bar, uint32_t parity, BwdShared *ss) {

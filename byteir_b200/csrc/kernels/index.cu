@@ -359,10 +359,15 @@ int launch_gather(int path, const void *in, const void *idx, void *out, int64_t 
   const bool bulk_ok = row_bytes % 16 == 0 && aligned16(in) && aligned16(out) && row_bytes <= 49152;
   if (path == 1 && !bulk_ok)
     return B200_ERR_ALIGNMENT;
-  // Measured on 64 MB of gathered rows from a 256 MB table: rows of 64 .. 256 bytes run at
-  // 3.3 .. 3.7 TB/s through vector loads and 2.0 .. 3.3 TB/s through the bulk-copy ring (a
-  // bulk copy per 64-byte row is mostly descriptor overhead); rows of 1 KiB and more run at
-  // 5.7 .. 6.4 TB/s through the ring and 4.4 .. 4.9 TB/s through vector loads.
+  // Measured on 64 MB of gathered rows out of a 256 MB table.  The tensor-map gather with 8 KiB
+  // tiles beats both other forms for rows of 64 bytes .. 1 KiB: 3.9 TB/s at 64 B, 5.1 at 128 B,
+  // 6.1 at 256 B, 6.3 at 512 B, 6.5 at 1 KiB, against 3.2 .. 4.4 through vector loads and
+  // 2.0 .. 5.7 with one bulk copy per row (a bulk copy per small row is mostly descriptor
+  // overhead).  Longer rows (a box holds at most 256 columns) run at 5.7 .. 6.4 TB/s through the
+  // ring of per-row bulk copies and 4.4 .. 4.9 TB/s through vector loads.
+  const bool g4_ok = bulk_ok && row_bytes % 32 == 0 && row_bytes >= 64 && row_bytes <= 1024 && A * IB < 0x7fffffffLL;
+  if (path == 0 && g4_ok)
+    path = 10;
   if ((path == 0 && bulk_ok && row_bytes >= 512) || path == 1) {
     int rows_per_tile =
         (int)std::max<int64_t>(1, std::min<int64_t>(kGatherMaxRowsPerTile, 16384 / row_bytes));
@@ -396,10 +401,11 @@ int launch_gather(int path, const void *in, const void *idx, void *out, int64_t 
     default: return launch_gather_vec<uint4, IdxT, 4>(in, idx, out, A, IB, OB, row_bytes, 6, status, stream);
     }
   }
-  // paths 7, 8: the tensor-map gather, 64- and 128-row tiles
-  if (path == 7 || path == 8) {
+  // paths 7 .. 10: the tensor-map gather, 64-, 128- and 32-row tiles, and tiles of 8 KiB
+  if (path >= 7 && path <= 10) {
     const int64_t total_rows = A * IB;
-    if (!bulk_ok || row_bytes > 1024 || row_bytes < 64 || total_rows >= 0x7fffffffLL)
+    // a tensor copy lands on a 128-byte boundary of shared memory: four rows must be a multiple of that
+    if (!bulk_ok || row_bytes % 32 != 0 || row_bytes > 1024 || row_bytes < 64 || total_rows >= 0x7fffffffLL)
       return B200_ERR_ALIGNMENT;
     CUtensorMap map;
     const uint64_t dims[2] = {(uint64_t)(row_bytes / 4), (uint64_t)total_rows};
@@ -408,7 +414,7 @@ int launch_gather(int path, const void *in, const void *idx, void *out, int64_t 
     if (int rc = make_tensor_map(&map, CU_TENSOR_MAP_DATA_TYPE_UINT32, 2, const_cast<void *>(in), dims, strides, box,
                                  CU_TENSOR_MAP_SWIZZLE_NONE))
       return rc;
-    int rows_per_tile = (int)std::min<int64_t>(path == 7 ? 64 : 128, 32768 / row_bytes);
+    int rows_per_tile = (int)std::min<int64_t>(path == 7 ? 64 : path == 8 ? 128 : path == 9 ? 32 : std::max<int64_t>(8, 8192 / row_bytes), 32768 / row_bytes);
     rows_per_tile = std::max(4, rows_per_tile & ~3);
     const int64_t tiles_per_a = ceil_div<int64_t>(OB, rows_per_tile);
     const int64_t num_tiles = tiles_per_a * A;
@@ -599,29 +605,61 @@ __global__ void __launch_bounds__(256)
 #pragma unroll
   for (int r = 0; r < 8; ++r) {
     const int64_t i = base + r * 32 + lane;
-    if (i < n) {
+    const bool ok = i < n;
+    uint32_t tag = 0xffffffffu; // counter of the next pass this entry adds to: (digit, destination tile)
+    if (ok) {
       const uint32_t d = (key[r] >> shift) & (radix - 1);
       const uint32_t dst = whist[warp][d] + rank[r];
       keys_out[dst] = key[r];
       vals_out[dst] = val[r];
-      if (hist_next)
-        atomicAdd(&hist_next[(size_t)((key[r] >> next_shift) & (next_radix - 1)) * ntiles + dst / kSortTile], 1u);
+      tag = ((key[r] >> next_shift) & (next_radix - 1)) * (uint32_t)ntiles + dst / kSortTile;
+    }
+    if (hist_next) {
+      // one atomic per distinct counter of the warp: thousands of equal keys (a hot row) would
+      // otherwise queue up on one address
+      const uint32_t peers = __match_any_sync(0xffffffffu, tag);
+      if (ok && (peers & lt) == 0)
+        atomicAdd(&hist_next[tag], (uint32_t)__popc(peers));
     }
   }
 }
 
+// The table copy runs beside the index sort.  It moves 32 bytes per load and marks its lines
+// first to go in L2 on both sides: the table streams through L2 once and should not push out
+// the few megabytes the sort kernels beside it keep going back to.  (Measured alternatives: a
+// persistent copy grid that keeps only the bandwidth-delay product in flight, 2 .. 16 blocks per
+// SM, made the whole op slower, 147 .. 165 us against 139 us: a kernel without shared memory
+// that never leaves its SMs also keeps kernels with another shared-memory carve-out from
+// starting on them until it ends.)
+struct alignas(32) Vec32 {
+  uint64_t a, b, c, d;
+};
+__device__ __forceinline__ Vec32 ld_stream_v32(const Vec32 *p) {
+  Vec32 v;
+  asm volatile("ld.global.nc.L1::no_allocate.L2::evict_first.v4.b64 {%0,%1,%2,%3}, [%4];"
+               : "=l"(v.a), "=l"(v.b), "=l"(v.c), "=l"(v.d)
+               : "l"(p));
+  return v;
+}
+__device__ __forceinline__ void st_stream_v32(Vec32 *p, const Vec32 &v) {
+  asm volatile("st.global.L1::no_allocate.L2::evict_first.v4.b64 [%0], {%1,%2,%3,%4};" ::"l"(p), "l"(v.a), "l"(v.b),
+               "l"(v.c), "l"(v.d)
+               : "memory");
+}
+
+// 256 threads, four 32-byte vectors each
 __global__ void __launch_bounds__(256)
-    copy_table_kernel(const uint4 *__restrict__ in, uint4 *__restrict__ out, int64_t nvec) {
-  int64_t i = (int64_t)blockIdx.x * 256 * 4 + threadIdx.x;
+    copy_table_kernel(const Vec32 *__restrict__ in, Vec32 *__restrict__ out, int64_t nvec) {
+  const int64_t i = (int64_t)blockIdx.x * 1024 + threadIdx.x;
   if (i + 3 * 256 < nvec) {
-    uint4 a = ld_nc_v4(in + i), b = ld_nc_v4(in + i + 256), c = ld_nc_v4(in + i + 512),
-          d = ld_nc_v4(in + i + 768);
-    st_cs_v4(out + i, a), st_cs_v4(out + i + 256, b), st_cs_v4(out + i + 512, c),
-        st_cs_v4(out + i + 768, d);
+    const Vec32 a = ld_stream_v32(in + i), b = ld_stream_v32(in + i + 256), c = ld_stream_v32(in + i + 512),
+                d = ld_stream_v32(in + i + 768);
+    st_stream_v32(out + i, a), st_stream_v32(out + i + 256, b), st_stream_v32(out + i + 512, c),
+        st_stream_v32(out + i + 768, d);
   } else {
-    for (int k = 0; k < 4; ++k, i += 256)
-      if (i < nvec)
-        out[i] = in[i];
+    for (int64_t k = 0, j = i; k < 4; ++k, j += 256)
+      if (j < nvec)
+        out[j] = in[j];
   }
 }
 
@@ -676,6 +714,25 @@ __device__ __forceinline__ void store_lane(T *p, const float (&f)[LV]) {
   *reinterpret_cast<Raw *>(p) = raw;
 }
 
+// A run that starts in a chunk and continues into the next one is finished by the span pass: the
+// chunk goes on one of its two work lists.  leaders[0] / leaders[1] = lengths of the short and the
+// long list, leaders[64 + i] = short entries (the run goes on into at most 31 further chunks),
+// leaders[64 + nchunks + i] = long entries.  All lanes of the warp call this.
+__device__ __forceinline__ void register_leader(const uint32_t *__restrict__ keys, uint32_t *__restrict__ leaders,
+                                                int64_t chunk, int64_t nchunks, uint32_t first_key, uint32_t last_key,
+                                                uint32_t prev_key, uint32_t next_key, uint32_t invalid, int lane) {
+  if (last_key == invalid || last_key != next_key || (first_key == last_key && first_key == prev_key))
+    return; // uniform over the warp
+  const int64_t probe = chunk + 1 + lane;
+  const unsigned hits = __ballot_sync(0xffffffffu, probe < nchunks && keys[probe * kChunk] == last_key);
+  if (lane == 0) {
+    if (hits == 0xffffffffu)
+      leaders[64 + nchunks + atomicAdd(&leaders[1], 1u)] = (uint32_t)chunk;
+    else
+      leaders[64 + atomicAdd(&leaders[0], 1u)] = (uint32_t)chunk;
+  }
+}
+
 // One warp per chunk of kChunk sorted entries.  part: [nchunks][2][feature] f32.
 // Entries are handled 8 at a time: the 8 update rows, and the table rows of the
 // runs that end (and are complete) inside those 8 entries, are all loaded before
@@ -710,11 +767,8 @@ __global__ void __launch_bounds__(256)
   const uint32_t closed_mask = __ballot_sync(0xffffffffu, my_end && !my_open && my_key != invalid);
   float *part0 = part + (size_t)chunk * 2 * feature;
   float *part1 = part0 + feature;
-  // a run that starts in this chunk and continues into the next one is finished by
-  // the span pass: put this chunk on its work list
-  if (lane == 0 && last_key != invalid && last_key == next_key &&
-      !(first_key == last_key && first_key == prev_key))
-    leaders[64 + atomicAdd(&leaders[0], 1u)] = (uint32_t)chunk;
+  register_leader(keys, leaders, chunk, ceil_div<int64_t>(n, kChunk), first_key, last_key, prev_key, next_key, invalid,
+                  lane);
 
   // uniform over the warp (it contains shuffles); lanes past the end of a short
   // row only skip their loads and stores
@@ -779,40 +833,42 @@ __global__ void __launch_bounds__(256)
   }
 }
 
-// The same pass for rows that are multiples of 16 bytes (every pointer 16-byte aligned): the 32
-// update rows of a chunk, and the table rows of the runs that end inside it, are first copied
-// into the warp's shared-memory buffers with 16-byte asynchronous copies, all of them in flight
-// at once and none of them held in registers; the warp then adds the rows up from shared memory,
-// in the order of the sorted list.  A row is handled in tiles of 256 bytes (8 bytes per lane).
-// Shared memory: [warp][update rows | table rows][32 rows][256 B] = 16 KiB per warp.
+// The same pass for rows that are multiples of 32 bytes: the 32 update rows of a chunk, and the
+// table rows of the runs that end inside it, are fetched into the warp's shared-memory buffers by
+// the tensor-map gather (cp.async.bulk.tensor, tile::gather4: four rows per instruction, named by
+// their row coordinates), all of them in flight at once and none of them held in registers; the
+// warp then adds the rows up from shared memory, in the order of the sorted list.  A row is
+// handled in tiles of 256 bytes (8 bytes per lane).  Rows that are not needed (an entry out of
+// range, a run that does not end here) are named by a coordinate past the end of the map, which
+// reads zeros and costs no memory traffic.
+// Shared memory: [warp][update rows | table rows][32 rows][tile] = 16 KiB per warp.
 constexpr int kStagedWarps = 4;
 constexpr int kStagedTileBytes = 256;
 constexpr size_t kStagedSmemPerWarp = 2 * kChunk * kStagedTileBytes;
 
-__device__ __forceinline__ void cp_async_16(void *smem_dst, const void *gmem_src) {
-  asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(smem_addr(smem_dst)), "l"(gmem_src) : "memory");
-}
-__device__ __forceinline__ void cp_async_wait_all() {
-  asm volatile("cp.async.commit_group;\ncp.async.wait_group 0;" ::: "memory");
-}
-
 template <typename T>
 __global__ void __launch_bounds__(kStagedWarps * 32)
-    scatter_chunk_staged_kernel(const T *in, const T *__restrict__ upd, T *out,
+    scatter_chunk_staged_kernel(const __grid_constant__ CUtensorMap upd_map,
+                                const __grid_constant__ CUtensorMap in_map, T *out,
                                 const uint32_t *__restrict__ keys, const uint32_t *__restrict__ vals,
                                 float *__restrict__ part, uint32_t *__restrict__ leaders, int64_t n,
-                                int64_t rows, int64_t feature) {
+                                int64_t rows, int64_t feature, int *status) {
   constexpr int LV = 8 / (int)sizeof(T); // elements per lane per tile
-  extern __shared__ __align__(128) unsigned char staged_smem[];
+  extern __shared__ __align__(1024) unsigned char staged_smem[];
+  __shared__ uint64_t bars[kStagedWarps];
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  if (lane == 0) {
+    mbar_init(&bars[warp], 1);
+    mbar_fence_init();
+  }
+  __syncwarp();
   pdl_wait();
   pdl_launch_dependents();
-  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
   const int64_t chunk = (int64_t)blockIdx.x * kStagedWarps + warp;
   const int64_t e0 = chunk * kChunk;
   if (e0 >= n)
     return;
   unsigned char *upd_s = staged_smem + (size_t)warp * kStagedSmemPerWarp;
-  unsigned char *base_s = upd_s + kChunk * kStagedTileBytes;
   const int cnt = (int)min((int64_t)kChunk, n - e0);
   const uint32_t invalid = (uint32_t)rows;
   const uint32_t my_key = lane < cnt ? keys[e0 + lane] : 0xffffffffu;
@@ -826,60 +882,86 @@ __global__ void __launch_bounds__(kStagedWarps * 32)
   const bool my_open = (my_key == first_key && first_key == prev_key) ||
                        (my_key == last_key && last_key == next_key);
   const bool my_live = lane < cnt && my_key != invalid;
+  const bool my_closed = my_end && !my_open && my_live;
   const uint32_t end_mask = __ballot_sync(0xffffffffu, my_end);
-  const uint32_t closed_mask = __ballot_sync(0xffffffffu, my_end && !my_open && my_key != invalid);
+  const uint32_t closed_mask = __ballot_sync(0xffffffffu, my_closed);
   const uint32_t live_mask = __ballot_sync(0xffffffffu, my_live);
   float *part0 = part + (size_t)chunk * 2 * feature;
   float *part1 = part0 + feature;
-  if (lane == 0 && last_key != invalid && last_key == next_key &&
-      !(first_key == last_key && first_key == prev_key))
-    leaders[64 + atomicAdd(&leaders[0], 1u)] = (uint32_t)chunk;
+  register_leader(keys, leaders, chunk, ceil_div<int64_t>(n, kChunk), first_key, last_key, prev_key, next_key, invalid,
+                  lane);
 
+  // row coordinates of the two gathers; a row that is not needed lies past the end of its map
+  const int upd_row = my_live ? (int)my_pos : (int)min(n, (int64_t)0x7fffffff);
+  const int in_row = my_closed ? (int)my_key : (int)rows;
   const int64_t row_bytes = feature * (int64_t)sizeof(T);
-  const char *upd_b = reinterpret_cast<const char *>(upd);
-  const char *in_b = reinterpret_cast<const char *>(in);
-  for (int64_t tb = 0; tb < row_bytes; tb += kStagedTileBytes) {
+  const int live_quads = (32 - __clz(live_mask | 1u) + 3) >> 2; // quads of entries holding a live one
+  // the box of both maps is one row of `pitch` bytes, which is also the row pitch in shared memory;
+  // the last tile of a row may be narrower: its columns past the end of the row read zeros
+  const int pitch = (int)min((int64_t)kStagedTileBytes, row_bytes);
+  unsigned char *base_s = upd_s + kChunk * pitch;
+  uint32_t phase = 0;
+  for (int64_t tb = 0; tb < row_bytes; tb += kStagedTileBytes, phase ^= 1u) {
     const int tile_bytes = (int)min((int64_t)kStagedTileBytes, row_bytes - tb);
-    const int c16 = tile_bytes >> 4; // 16-byte pieces of a row in this tile, 1..16
-    if (tb > 0)
-      __syncwarp(); // the previous tile has been read out of the buffers
-    // stage: piece p of the chunk = (entry p / c16, 16-byte column p % c16)
-    const int pieces = cnt * c16;
-    for (int p0 = 0; p0 < pieces; p0 += 32) {
-      const int pc = p0 + lane;
-      const int r = min(pc / c16, kChunk - 1), c = pc % c16;
-      const uint32_t k = __shfl_sync(0xffffffffu, my_key, r);
-      const uint32_t pos = __shfl_sync(0xffffffffu, my_pos, r);
-      if (pc < pieces && ((live_mask >> r) & 1u)) {
-        cp_async_16(upd_s + r * kStagedTileBytes + c * 16, upd_b + (size_t)pos * row_bytes + tb + c * 16);
-        if ((closed_mask >> r) & 1u)
-          cp_async_16(base_s + r * kStagedTileBytes + c * 16, in_b + (size_t)k * row_bytes + tb + c * 16);
-      }
+    if (tb > 0) { // the previous tile has been read out of the buffers by every lane
+      __syncwarp();
+      fence_proxy_async_smem();
     }
-    cp_async_wait_all();
+    // lanes 0 .. 7 fetch the update rows of their quad, lanes 8 .. 15 the table rows of theirs
+    const int q = lane & 7;
+    int r[4];
+#pragma unroll
+    for (int u = 0; u < 4; ++u) { // what is exchanged is the SOURCE lane's value: both are sent, the receiver picks
+      const int ru = __shfl_sync(0xffffffffu, upd_row, 4 * q + u);
+      const int ri = __shfl_sync(0xffffffffu, in_row, 4 * q + u);
+      r[u] = lane < 8 ? ru : ri;
+    }
+    const int r0 = r[0], r1 = r[1], r2 = r[2], r3 = r[3];
+    const bool quad_closed = ((closed_mask >> (4 * q)) & 0xfu) != 0;
+    const bool issue_upd = lane < 8 && q < live_quads;
+    const bool issue_in = lane >= 8 && lane < 16 && quad_closed;
+    const int nq = __popc(__ballot_sync(0xffffffffu, issue_upd || issue_in));
+    if (lane == 0)
+      mbar_arrive_expect_tx(&bars[warp], (uint32_t)nq * 4u * (uint32_t)pitch);
     __syncwarp();
+    if (issue_upd)
+      tma_gather4_2d(upd_s + q * 4 * pitch, &upd_map, (int)(tb >> 2), r0, r1, r2, r3, &bars[warp]);
+    if (issue_in)
+      tma_gather4_2d(base_s + q * 4 * pitch, &in_map, (int)(tb >> 2), r0, r1, r2, r3, &bars[warp]);
+    if (!__all_sync(0xffffffffu, mbar_wait(&bars[warp], phase))) {
+      if (status && lane == 0)
+        *status = 2; // a copy never arrived: give up instead of spinning
+      return;
+    }
     const bool lane_on = lane * 8 < tile_bytes;
     const int64_t f0 = tb / (int64_t)sizeof(T) + (int64_t)lane * LV;
     float acc[LV];
 #pragma unroll
     for (int j = 0; j < LV; ++j)
       acc[j] = 0.f;
-    for (int i = 0; i < cnt; ++i) {
-      if (!((live_mask >> i) & 1u))
+    // this lane's piece of all 32 update rows, read before any of them is used: the additions below
+    // then wait on no shared-memory latency
+    uint2 xr[kChunk];
+#pragma unroll
+    for (int i = 0; i < kChunk; ++i)
+      xr[i] = lane_on ? *reinterpret_cast<const uint2 *>(upd_s + i * pitch + lane * 8) : make_uint2(0u, 0u);
+#pragma unroll
+    for (int i = 0; i < kChunk; ++i) {
+      if (i >= cnt || !((live_mask >> i) & 1u))
         continue;
-      const uint32_t k = __shfl_sync(0xffffffffu, my_key, i);
-      if (lane_on) {
+      {
         float xf[LV];
-        unpack_raw<T, LV>(*reinterpret_cast<const uint2 *>(upd_s + i * kStagedTileBytes + lane * 8), xf);
+        unpack_raw<T, LV>(xr[i], xf);
 #pragma unroll
         for (int j = 0; j < LV; ++j)
           acc[j] += xf[j];
       }
       if ((end_mask >> i) & 1u) {
+        const uint32_t k = __shfl_sync(0xffffffffu, my_key, i);
         if (lane_on) {
           if ((closed_mask >> i) & 1u) {
             float bf[LV];
-            unpack_raw<T, LV>(*reinterpret_cast<const uint2 *>(base_s + i * kStagedTileBytes + lane * 8), bf);
+            unpack_raw<T, LV>(*reinterpret_cast<const uint2 *>(base_s + i * pitch + lane * 8), bf);
 #pragma unroll
             for (int j = 0; j < LV; ++j)
               bf[j] += acc[j];
@@ -899,91 +981,73 @@ __global__ void __launch_bounds__(kStagedWarps * 32)
   }
 }
 
-// Finishes the runs that cross chunk borders; work list written by the chunk pass.
-// leaders[0] = number of entries, leaders[1] = number of long entries (second
-// list, filled here), leaders[64 + i] = chunk where run i starts,
-// leaders[64 + nchunks + i] = long entries.
-//
-// Short pass: one warp per entry.  The lanes probe the next 32 chunks at once; a
-// run that continues into at most 32 chunks is finished by the warp (partials
-// added in chunk order), a longer one is handed to the long pass.
-template <typename T, int LV>
-__global__ void __launch_bounds__(256)
-    scatter_span_short_kernel(const T *in, T *out, const uint32_t *__restrict__ keys,
-                              const float *__restrict__ part, uint32_t *__restrict__ leaders,
-                              int64_t n, int64_t feature) {
-  pdl_wait();
-  pdl_launch_dependents();
-  const int lane = threadIdx.x & 31;
-  const int64_t nchunks = ceil_div<int64_t>(n, kChunk);
-  const uint32_t nlead = leaders[0];
-  const int64_t warps = (int64_t)gridDim.x * 8;
-  for (int64_t l = (int64_t)blockIdx.x * 8 + (threadIdx.x >> 5); l < nlead; l += warps) {
-    const int64_t chunk = leaders[64 + l];
-    const int64_t e0 = chunk * kChunk;
-    const uint32_t key = keys[min(n, e0 + kChunk) - 1];
-    const int first_slot = keys[e0] == key ? 0 : 1;
-    const int64_t probe = chunk + 1 + lane;
-    const unsigned hits = __ballot_sync(0xffffffffu, probe < nchunks && keys[probe * kChunk] == key);
-    if (hits == 0xffffffffu) { // may go on beyond 32 chunks
-      if (lane == 0)
-        leaders[64 + nchunks + atomicAdd(&leaders[1], 1u)] = (uint32_t)chunk;
-      continue;
-    }
-    const int extra = __popc(hits); // keys are sorted: the hits are the low bits
-    for (int64_t fbase = 0; fbase < feature; fbase += 32 * LV) {
-      const int64_t f0 = fbase + (int64_t)lane * LV;
-      if (f0 >= feature)
-        continue;
-      float base[LV], sum[LV];
-      load_lane<T, LV>(in + (size_t)key * feature + f0, base);
-      const float *p = part + ((size_t)chunk * 2 + first_slot) * feature + f0;
-#pragma unroll
-      for (int j = 0; j < LV; ++j)
-        sum[j] = p[j];
-      for (int c0 = 1; c0 <= extra; c0 += 8) { // eight chunks' partials in flight, added in chunk order
-        float q[8][LV];
-#pragma unroll
-        for (int u = 0; u < 8; ++u)
-          if (c0 + u <= extra) {
-            const float *qp = part + (size_t)(chunk + c0 + u) * 2 * feature + f0;
-#pragma unroll
-            for (int j = 0; j < LV; ++j)
-              q[u][j] = qp[j];
-          }
-#pragma unroll
-        for (int u = 0; u < 8; ++u)
-          if (c0 + u <= extra) {
-#pragma unroll
-            for (int j = 0; j < LV; ++j)
-              sum[j] += q[u][j];
-          }
-      }
-#pragma unroll
-      for (int j = 0; j < LV; ++j)
-        base[j] += sum[j];
-      store_lane<T, LV>(out + (size_t)key * feature + f0, base);
-    }
-  }
-}
-
-// Long pass: blocks of 32 warps walk over the long entries.  The block counts how
-// many following chunks the run continues into, each warp adds the slot-0 partials
-// of a contiguous slice of those chunks, and warp 0 adds the 32 slice sums in
-// order to the run's own partial and the table row.  Which block handles which
-// entry does not affect the result.
+// Finishes the runs that cross chunk borders, from the two work lists the chunk pass wrote
+// (register_leader).  One launch, blocks of 32 warps: the first `short_blocks` blocks give a
+// warp to every short entry (the partials of up to 31 following chunks added in chunk order, eight
+// loads in flight); the other blocks take one long entry at a time: the block counts how many
+// following chunks the run continues into, each warp adds the slot-0 partials of a contiguous
+// slice of those chunks, and warp 0 adds the 32 slice sums in order to the run's own partial
+// and the table row.  Which warp or block handles which entry does not affect the result.
 template <typename T, int LV>
 __global__ void __launch_bounds__(1024)
-    scatter_span_long_kernel(const T *in, T *out, const uint32_t *__restrict__ keys,
-                             const float *__restrict__ part, const uint32_t *__restrict__ leaders,
-                             int64_t n, int64_t feature) {
+    scatter_span_kernel(const T *in, T *out, const uint32_t *__restrict__ keys, const float *__restrict__ part,
+                        const uint32_t *__restrict__ leaders, int64_t n, int64_t feature, int short_blocks) {
   __shared__ float sm[32][32 * LV];
+  constexpr int U = LV > 4 ? 4 : 8; // rows of partials in flight per lane: 32 floats
   pdl_wait();
   pdl_launch_dependents();
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
   const int64_t nchunks = ceil_div<int64_t>(n, kChunk);
+  if ((int)blockIdx.x < short_blocks) {
+    const uint32_t nlead = leaders[0];
+    const int64_t warps = (int64_t)short_blocks * 32;
+    for (int64_t l = (int64_t)blockIdx.x * 32 + warp; l < nlead; l += warps) {
+      const int64_t chunk = leaders[64 + l];
+      const int64_t e0 = chunk * kChunk;
+      const uint32_t key = keys[min(n, e0 + kChunk) - 1];
+      const int first_slot = keys[e0] == key ? 0 : 1;
+      const int64_t probe = chunk + 1 + lane;
+      const unsigned hits = __ballot_sync(0xffffffffu, probe < nchunks && keys[probe * kChunk] == key);
+      const int extra = __popc(hits); // keys are sorted: the hits are the low bits; at most 31 here
+      for (int64_t fbase = 0; fbase < feature; fbase += 32 * LV) {
+        const int64_t f0 = fbase + (int64_t)lane * LV;
+        if (f0 >= feature)
+          continue;
+        float base[LV], sum[LV];
+        load_lane<T, LV>(in + (size_t)key * feature + f0, base);
+        const float *p = part + ((size_t)chunk * 2 + first_slot) * feature + f0;
+#pragma unroll
+        for (int j = 0; j < LV; ++j)
+          sum[j] = p[j];
+        for (int c0 = 1; c0 <= extra; c0 += U) {
+          float q[U][LV];
+#pragma unroll
+          for (int u = 0; u < U; ++u)
+            if (c0 + u <= extra) {
+              const float *qp = part + (size_t)(chunk + c0 + u) * 2 * feature + f0;
+#pragma unroll
+              for (int j = 0; j < LV; ++j)
+                q[u][j] = qp[j];
+            }
+#pragma unroll
+          for (int u = 0; u < U; ++u)
+            if (c0 + u <= extra) {
+#pragma unroll
+              for (int j = 0; j < LV; ++j)
+                sum[j] += q[u][j];
+            }
+        }
+#pragma unroll
+        for (int j = 0; j < LV; ++j)
+          base[j] += sum[j];
+        store_lane<T, LV>(out + (size_t)key * feature + f0, base);
+      }
+    }
+    return;
+  }
   const uint32_t nlead = leaders[1];
-  for (uint32_t l = blockIdx.x; l < nlead; l += gridDim.x) {
+  const uint32_t long_blocks = gridDim.x - short_blocks;
+  for (uint32_t l = blockIdx.x - short_blocks; l < nlead; l += long_blocks) {
     const int64_t chunk = leaders[64 + nchunks + l];
     const int64_t e0 = chunk * kChunk;
     const uint32_t key = keys[min(n, e0 + kChunk) - 1];
@@ -1009,27 +1073,23 @@ __global__ void __launch_bounds__(1024)
       for (int j = 0; j < LV; ++j)
         total[j] = 0.f;
       if (lane_on) {
-        int64_t c = c0;
-        for (; c + 3 < c1; c += 4) {
-          float q[4][LV];
+        for (int64_t c = c0; c < c1; c += U) { // U rows of partials in flight, the last batch predicated
+          float q[U][LV];
 #pragma unroll
-          for (int u = 0; u < 4; ++u) {
-            const float *p = part + (size_t)(c + u) * 2 * feature + f0;
+          for (int u = 0; u < U; ++u)
+            if (c + u < c1) {
+              const float *p = part + (size_t)(c + u) * 2 * feature + f0;
 #pragma unroll
-            for (int j = 0; j < LV; ++j)
-              q[u][j] = p[j];
-          }
+              for (int j = 0; j < LV; ++j)
+                q[u][j] = p[j];
+            }
 #pragma unroll
-          for (int u = 0; u < 4; ++u)
+          for (int u = 0; u < U; ++u)
+            if (c + u < c1) {
 #pragma unroll
-            for (int j = 0; j < LV; ++j)
-              total[j] += q[u][j];
-        }
-        for (; c < c1; ++c) {
-          const float *p = part + (size_t)c * 2 * feature + f0;
-#pragma unroll
-          for (int j = 0; j < LV; ++j)
-            total[j] += p[j];
+              for (int j = 0; j < LV; ++j)
+                total[j] += q[u][j];
+            }
         }
       }
 #pragma unroll
@@ -1101,31 +1161,43 @@ int g_chunk_path_override = 0;
 
 template <typename T, int LV>
 int launch_scatter_tail(bool staged, const T *in, const T *upd, T *out, const uint32_t *keys, const uint32_t *vals,
-                        float *part, uint32_t *leaders, int64_t n, int64_t rows, int64_t feature,
+                        float *part, uint32_t *leaders, int64_t n, int64_t rows, int64_t feature, int *status,
                         cudaStream_t stream) {
   const int64_t nchunks = ceil_div<int64_t>(n, kChunk);
   if (staged) {
-    const size_t smem = kStagedWarps * kStagedSmemPerWarp;
+    // two-dimensional maps over the update rows and the table rows, 32-bit columns, box = one
+    // tile of one row
+    const int64_t row_bytes = feature * (int64_t)sizeof(T);
+    const uint32_t box_cols = (uint32_t)(std::min<int64_t>(row_bytes, kStagedTileBytes) / 4);
+    CUtensorMap upd_map, in_map;
+    const uint64_t strides[1] = {(uint64_t)row_bytes};
+    const uint32_t box[2] = {box_cols, 1};
+    const uint64_t upd_dims[2] = {(uint64_t)(row_bytes / 4), (uint64_t)n};
+    const uint64_t in_dims[2] = {(uint64_t)(row_bytes / 4), (uint64_t)rows};
+    if (int rc = make_tensor_map(&upd_map, CU_TENSOR_MAP_DATA_TYPE_UINT32, 2, const_cast<T *>(upd), upd_dims, strides,
+                                 box, CU_TENSOR_MAP_SWIZZLE_NONE))
+      return rc;
+    if (int rc = make_tensor_map(&in_map, CU_TENSOR_MAP_DATA_TYPE_UINT32, 2, const_cast<T *>(in), in_dims, strides, box,
+                                 CU_TENSOR_MAP_SWIZZLE_NONE))
+      return rc;
+    const size_t smem = kStagedWarps * kStagedSmemPerWarp + 1024;
     // the attribute belongs to the current device's context: set on every call (a host-side table write)
     if (int rc = check_cuda(cudaFuncSetAttribute(scatter_chunk_staged_kernel<T>,
                                                  cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem)))
       return rc;
     if (int rc = launch_pdl(scatter_chunk_staged_kernel<T>, dim3((unsigned)ceil_div<int64_t>(nchunks, kStagedWarps)),
-                            dim3(kStagedWarps * 32), smem, stream, in, upd, out, keys, vals, part, leaders, n, rows,
-                            feature))
+                            dim3(kStagedWarps * 32), smem, stream, upd_map, in_map, out, keys, vals, part, leaders, n,
+                            rows, feature, status))
       return rc;
   } else {
     if (int rc = launch_pdl(scatter_chunk_kernel<T, LV>, dim3((unsigned)ceil_div<int64_t>(nchunks, 8)), dim3(256), 0,
                             stream, in, upd, out, keys, vals, part, leaders, n, rows, feature))
       return rc;
   }
-  const unsigned short_grid = (unsigned)std::min<int64_t>(ceil_div<int64_t>(nchunks, 8), kNumSMs * 8);
-  if (int rc = launch_pdl(scatter_span_short_kernel<T, LV>, dim3(short_grid), dim3(256), 0, stream, in, out, keys,
-                          (const float *)part, leaders, n, feature))
-    return rc;
-  const unsigned long_grid = (unsigned)std::min<int64_t>(ceil_div<int64_t>(nchunks, 32), kNumSMs);
-  return launch_pdl(scatter_span_long_kernel<T, LV>, dim3(long_grid), dim3(1024), 0, stream, in, out, keys,
-                    (const float *)part, (const uint32_t *)leaders, n, feature);
+  const int short_blocks = (int)std::min<int64_t>(ceil_div<int64_t>(nchunks, 32), kNumSMs);
+  const int long_blocks = (int)std::min<int64_t>(ceil_div<int64_t>(nchunks, 32), kNumSMs);
+  return launch_pdl(scatter_span_kernel<T, LV>, dim3((unsigned)(short_blocks + long_blocks)), dim3(1024), 0, stream, in,
+                    out, keys, (const float *)part, (const uint32_t *)leaders, n, feature, short_blocks);
 }
 
 // The index sort does not depend on the table copy, so the two run side by side:
@@ -1208,10 +1280,10 @@ int scatter_add(const T *in, const int64_t *idx, const T *upd, T *out, int64_t r
   }
   if (in != out) {
     cudaStream_t stream = user_stream; // the copy always runs on the caller's stream
-    if (table_bytes % 16 == 0 && aligned16(in) && aligned16(out)) {
-      const int64_t nvec = (int64_t)(table_bytes / 16);
+    if (table_bytes % 32 == 0 && ((reinterpret_cast<uintptr_t>(in) | reinterpret_cast<uintptr_t>(out)) & 31u) == 0) {
+      const int64_t nvec = (int64_t)(table_bytes / 32);
       copy_table_kernel<<<(unsigned)ceil_div<int64_t>(nvec, 1024), 256, 0, stream>>>(
-          (const uint4 *)in, (uint4 *)out, nvec);
+          (const Vec32 *)in, (Vec32 *)out, nvec);
       if (int rc = check_launch())
         return rc;
     } else if (int rc = check_cuda(
@@ -1269,20 +1341,22 @@ int scatter_add(const T *in, const int64_t *idx, const T *upd, T *out, int64_t r
     lane_bytes >>= 1;
   const int lv = lane_bytes / (int)sizeof(T);
   // rows staged through shared memory whenever whole rows can be copied in 16-byte pieces
-  bool staged = mis % 16 == 0 && feature * (int64_t)sizeof(T) >= 64;
+  // (four rows of a tile land on a 128-byte boundary of shared memory: rows are multiples of 32 bytes;
+  // row coordinates are 32-bit)
+  bool staged = mis % 16 == 0 && (feature * (int64_t)sizeof(T)) % 32 == 0 && rows < 0x7fffffffLL && n < 0x7fffffffLL;
   if (g_chunk_path_override == 1)
     staged = false;
   switch (lv) {
   case 8:
     if constexpr (sizeof(T) == 2)
-      return launch_scatter_tail<T, 8>(staged, in, upd, out, keys[cur], vals[cur], part, leaders, n, rows, feature, stream);
+      return launch_scatter_tail<T, 8>(staged, in, upd, out, keys[cur], vals[cur], part, leaders, n, rows, feature, status, stream);
     return B200_ERR_UNSUPPORTED;
   case 4:
-    return launch_scatter_tail<T, 4>(staged, in, upd, out, keys[cur], vals[cur], part, leaders, n, rows, feature, stream);
+    return launch_scatter_tail<T, 4>(staged, in, upd, out, keys[cur], vals[cur], part, leaders, n, rows, feature, status, stream);
   case 2:
-    return launch_scatter_tail<T, 2>(staged, in, upd, out, keys[cur], vals[cur], part, leaders, n, rows, feature, stream);
+    return launch_scatter_tail<T, 2>(staged, in, upd, out, keys[cur], vals[cur], part, leaders, n, rows, feature, status, stream);
   default:
-    return launch_scatter_tail<T, 1>(staged, in, upd, out, keys[cur], vals[cur], part, leaders, n, rows, feature, stream);
+    return launch_scatter_tail<T, 1>(staged, in, upd, out, keys[cur], vals[cur], part, leaders, n, rows, feature, status, stream);
   }
 }
 

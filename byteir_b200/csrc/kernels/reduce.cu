@@ -16,12 +16,13 @@
 //                        column slab per step, 8 warps stride over the B rows,
 //                        and B is split over enough blocks to fill 148 SMs
 //                        (split-K); the f32 partials of the splits are combined in
-//                        split order, so the result does not depend on scheduling.
-//                        When the fold is small it happens in the same launch: each
-//                        block takes a ticket after writing its partials and the
-//                        block that draws the last ticket of a column slab folds
-//                        that slab (nobody waits for anybody).  Otherwise a second
-//                        pass does it.
+//                        split order by a second pass, so the result does not
+//                        depend on scheduling.  (Folding in the first launch - the
+//                        last block of a slab to finish, found by a ticket, folds
+//                        it - was measured slower: 14.4 against 13.6 us on f16
+//                        [32768, 1024], because the fence, the ticket and the fold
+//                        are one more latency chain after the last load, while
+//                        the second pass is already resident and waiting.)
 //
 // Max semantics (reduction_helper.h:159-180 folded in ascending index order):
 // NaN wins; otherwise the largest value; between +0 and -0, which compare equal,
@@ -31,9 +32,7 @@
 #include <cooperative_groups.h>
 
 #include <algorithm>
-#include <map>
 #include <mutex>
-#include <utility>
 
 #include "common.cuh"
 
@@ -262,10 +261,9 @@ __global__ void __launch_bounds__(kBlock)
 template <typename T, int OP, int VPT, typename OutT>
 __global__ void __launch_bounds__(kBlock)
     reduce_short_rows_kernel(const T *__restrict__ in, OutT *__restrict__ out, int64_t A, int64_t B,
-                             int tpr) {
+                             int tpr, int prefetch) {
   constexpr int N = 16 / sizeof(T);
   __shared__ float warp_part[2][kBlock / 32];
-  pdl_wait();
   pdl_launch_dependents();
   const int groups_per_block = kBlock / tpr;
   const int t = threadIdx.x % tpr;
@@ -286,6 +284,14 @@ __global__ void __launch_bounds__(kBlock)
     }
   };
   int64_t a = (int64_t)blockIdx.x * block_rows + gib;
+  if (prefetch && a < A) { // the first row's loads, on their way into L2 during the wait
+    const uint4 *vp = reinterpret_cast<const uint4 *>(in + a * B);
+#pragma unroll
+    for (int k = 0; k < VPT; ++k)
+      if (t + k * tpr < nvec)
+        prefetch_l2(vp + t + k * tpr);
+  }
+  pdl_wait();
   load_row(a, cur);
   for (int64_t it = 0; it < iters; ++it) {
     const int64_t a_next = a + (int64_t)gridDim.x * block_rows;
@@ -343,22 +349,12 @@ __global__ void __launch_bounds__(kBlock)
 // NV = elements per lane per load (16 / sizeof(T) when 16-byte loads are
 // possible, else 1).  A warp covers `rpw = 32 / lpr` rows of a slab of
 // lpr * NV columns per step; 8 warps stride over the rows of this block's split.
-//
-// kFused: after writing its partials a block takes a ticket of its (a, slab); the block
-// that draws the last one folds the `splits` partials of the slab's columns in split order.
-// The ticket words live in g_cols_tickets (zero when the library is loaded; atomicInc wraps
-// the last ticket back to zero, so every launch leaves its words as it found them).
-constexpr int kTicketWords = 1 << 14;
-static __device__ unsigned g_cols_tickets[kTicketWords];
-
-template <typename T, int OP, int NV, bool kFused, typename OutT>
+template <typename T, int OP, int NV, typename OutT>
 __global__ void __launch_bounds__(kBlock, 4)
     reduce_cols_kernel(const T *__restrict__ in, OutT *__restrict__ out, float *partial,
                        int64_t A, int64_t B, int64_t C, int lpr, int slabs, int splits,
-                       int64_t rows_per_split, int ticket_base) {
-  __shared__ float smem[kBlock * (NV > 4 ? NV : 4)]; // [row lane][column of the slab]; the fold: [slice][column]
-  __shared__ int is_last;
-  pdl_wait();              // inputs may come from the kernel launched just before this one
+                       int64_t rows_per_split, int prefetch) {
+  __shared__ float smem[kBlock * NV]; // [row lane][column of the slab]
   pdl_launch_dependents(); // lets the next kernel (the second pass) be scheduled while this one runs
 
   const int64_t bid = blockIdx.x;
@@ -376,6 +372,13 @@ __global__ void __launch_bounds__(kBlock, 4)
   const int64_t r1 = min(B, r0 + rows_per_split);
   const T *base = in + a * B * C + col0;
   const int64_t step = row_lanes;
+  if (prefetch && col_ok) { // the first batch of this thread's loads, on its way into L2 during the wait
+#pragma unroll
+    for (int u = 0; u < 8; ++u)
+      if (r0 + lane_row + u * step < r1)
+        prefetch_l2(base + (r0 + lane_row + u * step) * C);
+  }
+  pdl_wait(); // inputs may come from the kernel launched just before this one
 
   float acc[NV];
 #pragma unroll
@@ -463,82 +466,6 @@ __global__ void __launch_bounds__(kBlock, 4)
     else
       partial[((int64_t)split * A + a) * C + col] = r;
   }
-  if (!kFused || splits == 1)
-    return;
-
-  // ---- the last block of this (a, slab) folds the slab's partials --------------------------
-  __threadfence(); // this thread's partials are visible before the ticket is
-  __syncthreads();
-  if (threadIdx.x == 0) {
-    const unsigned old = atomicInc(&g_cols_tickets[ticket_base + a * slabs + slab], (unsigned)splits - 1u);
-    is_last = old == (unsigned)splits - 1u;
-    __threadfence();
-  }
-  __syncthreads();
-  if (!is_last)
-    return;
-  const int live_cols = (int)min((int64_t)ncols, C - slab_col0);
-  const float *pbase = partial + a * C + slab_col0; // + s * A * C
-  const int64_t pstride = A * C;
-  // V floats per load: 4 when every row of partials starts 16-byte aligned
-  const bool v4 = NV > 1 && (C % 4 == 0) && (live_cols % 4 == 0) && (reinterpret_cast<uintptr_t>(partial) & 15u) == 0;
-  const int groups = v4 ? live_cols / 4 : live_cols; // column groups
-  const int slices = max(1, min(kBlock / groups, splits));
-  const int per = (splits + slices - 1) / slices;
-  {
-    const int cg = threadIdx.x % groups, slice = threadIdx.x / groups;
-    if (slice < slices) {
-      const int s0 = slice * per, s1 = min(splits, s0 + per);
-      if (v4) {
-        float4 r = make_float4(0.f, 0.f, 0.f, 0.f);
-        if (s0 < s1) {
-          const float *p = pbase + cg * 4;
-          r = __ldcg(reinterpret_cast<const float4 *>(p + s0 * pstride));
-          for (int s = s0 + 1; s < s1; s += 8) {
-            float4 v[8];
-#pragma unroll
-            for (int u = 0; u < 8; ++u)
-              if (s + u < s1)
-                v[u] = __ldcg(reinterpret_cast<const float4 *>(p + (s + u) * pstride));
-#pragma unroll
-            for (int u = 0; u < 8; ++u)
-              if (s + u < s1) {
-                r.x = op_apply_ordered<OP>(r.x, v[u].x);
-                r.y = op_apply_ordered<OP>(r.y, v[u].y);
-                r.z = op_apply_ordered<OP>(r.z, v[u].z);
-                r.w = op_apply_ordered<OP>(r.w, v[u].w);
-              }
-          }
-        }
-        *reinterpret_cast<float4 *>(&smem[slice * live_cols + cg * 4]) = r;
-      } else {
-        float r = 0.f;
-        if (s0 < s1) {
-          const float *p = pbase + cg;
-          r = __ldcg(p + s0 * pstride);
-          for (int s = s0 + 1; s < s1; s += 8) {
-            float v[8];
-#pragma unroll
-            for (int u = 0; u < 8; ++u)
-              if (s + u < s1)
-                v[u] = __ldcg(p + (s + u) * pstride);
-#pragma unroll
-            for (int u = 0; u < 8; ++u)
-              if (s + u < s1)
-                r = op_apply_ordered<OP>(r, v[u]);
-          }
-        }
-        smem[slice * live_cols + cg] = r;
-      }
-    }
-  }
-  __syncthreads();
-  for (int j = threadIdx.x; j < live_cols; j += kBlock) {
-    float r = smem[j];
-    for (int w = 1; w < slices && w * per < splits; ++w)
-      r = op_apply_ordered<OP>(r, smem[w * live_cols + j]);
-    store_out(out + a * C + slab_col0 + j, r);
-  }
 }
 
 // second pass: out[i] = fold over s of partial[i * stride_i + s * stride_s].
@@ -562,18 +489,18 @@ __global__ void __launch_bounds__(kFinalizeBlock)
   if (i < n && s0 < s1) {
     const float *p = partial + i * stride_i;
     r = p[s0 * stride_s];
-    int s = s0 + 1;
-    for (; s + 7 < s1; s += 8) {
+    // batches of eight loads in flight, the last one predicated: one memory latency per batch
+    for (int s = s0 + 1; s < s1; s += 8) {
       float v[8];
 #pragma unroll
       for (int u = 0; u < 8; ++u)
-        v[u] = p[(s + u) * stride_s];
+        if (s + u < s1)
+          v[u] = p[(s + u) * stride_s];
 #pragma unroll
       for (int u = 0; u < 8; ++u)
-        r = op_apply_ordered<OP>(r, v[u]);
+        if (s + u < s1)
+          r = op_apply_ordered<OP>(r, v[u]);
     }
-    for (; s < s1; ++s)
-      r = op_apply_ordered<OP>(r, p[s * stride_s]);
   }
   sm[slice][lane] = r;
   __syncthreads();
@@ -596,15 +523,12 @@ __global__ void __launch_bounds__(kBlock)
 // plan constants of the column path (threads that cover one row of a slab; blocks per SM aimed at)
 constexpr int kColsThreadsPerRow = 32;
 constexpr int kColsBlocksPerSm = 4;
-// The last block of a slab folds splits x columns f32 partials out of L2 on its own: above this
-// many bytes the slab is made narrower (more slabs fold side by side) or the fold is left to a
-// second launch that spreads it over many blocks.
-constexpr int64_t kFusedFoldMaxBytes = 64 * 1024;
-
 // Measurement override of the column plan (b200_reduce_cols_plan_override): threads per slab
-// row (0 = rule above) and fused fold (-1 = rule, 0 = never, 1 = whenever tickets are available).
+// row (0 = the rule above).
 int g_cols_lpr_override = 0;
-int g_cols_fused_override = -1;
+// b200_reduce_tune: whether kernels hint their first loads into L2 before waiting for the kernel in
+// front of them (1, default) or not (0)
+int g_prefetch_before_wait = 1;
 
 // ---- launch plan: a pure function of the shape -----------------------------
 struct Plan {
@@ -616,7 +540,6 @@ struct Plan {
   // columns
   int lpr, slabs, splits;
   int64_t rows_per_split;
-  bool fused; // columns: the fold of the splits happens in the same launch
   size_t ws_bytes;
 };
 
@@ -656,52 +579,13 @@ Plan make_plan(int esize, int64_t A, int64_t B, int64_t C, bool vec_cols) {
       p.rows_per_split = ceil_div<int64_t>(B, splits);
       p.splits = (int)ceil_div<int64_t>(B, p.rows_per_split);
     };
-    auto fold_bytes = [&] { return (int64_t)p.splits * std::min<int64_t>((int64_t)p.lpr * NV, C) * 4; };
     int lpr = (int)std::min<int64_t>(kColsThreadsPerRow, pow2_ceil(ceil_div<int64_t>(C, NV)));
     if (g_cols_lpr_override > 0)
       lpr = std::min(lpr, g_cols_lpr_override);
     split_for(lpr);
-    // narrower slabs while a slab's fold is too large for one block and a warp still reads
-    // 256 contiguous bytes of a row
-    while (g_cols_lpr_override == 0 && vec_cols && p.splits > 1 && fold_bytes() > kFusedFoldMaxBytes && p.lpr > 16)
-      split_for(p.lpr / 2);
-    p.fused = p.splits > 1 && fold_bytes() <= kFusedFoldMaxBytes && A * p.slabs <= 1024;
-    if (g_cols_fused_override >= 0)
-      p.fused = p.splits > 1 && g_cols_fused_override == 1 && A * p.slabs <= 1024;
     p.ws_bytes = p.splits > 1 ? (size_t)p.splits * A * C * sizeof(float) : 0;
   }
   return p;
-}
-
-// A fused launch needs A * slabs ticket words of g_cols_tickets that no other launch in flight
-// uses.  Two launches that may overlap on the GPU have different workspaces (they would race on
-// the partials otherwise), so a range is bound to (device, workspace address) the first time
-// that workspace is seen and kept for the life of the process; the words are zero whenever no
-// launch is in flight.  Returns -1 when the pool is used up: the caller then folds in a second
-// launch instead.
-int ticket_range(const void *ws, int words) {
-  struct Range {
-    int base, words;
-  };
-  static std::mutex mu;
-  static std::map<std::pair<int, const void *>, Range> bound;
-  static std::map<int, int> next_free; // per device
-  int dev = 0;
-  if (cudaGetDevice(&dev) != cudaSuccess) {
-    (void)cudaGetLastError();
-    return -1;
-  }
-  std::lock_guard<std::mutex> lock(mu);
-  auto it = bound.find({dev, ws});
-  if (it != bound.end() && it->second.words >= words)
-    return it->second.base;
-  int &next = next_free[dev];
-  if (next + words > kTicketWords)
-    return -1;
-  const Range r{next, words};
-  next += words;
-  bound[{dev, ws}] = r;
-  return r.base;
 }
 
 // Whether 16-byte loads are possible for the column kernel is a property of the
@@ -751,11 +635,11 @@ int launch(const T *in, OutT *out, int64_t A, int64_t B, int64_t C, void *ws,
       const int64_t row_blocks = ceil_div<int64_t>(A, groups_per_block);
       const unsigned pgrid = (unsigned)std::min<int64_t>(row_blocks, (int64_t)kNumSMs * (2048 / kBlock));
       if (vpt <= 1)
-        return launch_pdl(reduce_short_rows_kernel<T, OP, 1, OutT>, dim3(pgrid), dim3(kBlock), 0, stream, in, out, A, B, p.tpr);
+        return launch_pdl(reduce_short_rows_kernel<T, OP, 1, OutT>, dim3(pgrid), dim3(kBlock), 0, stream, in, out, A, B, p.tpr, g_prefetch_before_wait);
       else if (vpt == 2)
-        return launch_pdl(reduce_short_rows_kernel<T, OP, 2, OutT>, dim3(pgrid), dim3(kBlock), 0, stream, in, out, A, B, p.tpr);
+        return launch_pdl(reduce_short_rows_kernel<T, OP, 2, OutT>, dim3(pgrid), dim3(kBlock), 0, stream, in, out, A, B, p.tpr, g_prefetch_before_wait);
       else
-        return launch_pdl(reduce_short_rows_kernel<T, OP, 4, OutT>, dim3(pgrid), dim3(kBlock), 0, stream, in, out, A, B, p.tpr);
+        return launch_pdl(reduce_short_rows_kernel<T, OP, 4, OutT>, dim3(pgrid), dim3(kBlock), 0, stream, in, out, A, B, p.tpr, g_prefetch_before_wait);
     }
     if (vec)
       reduce_rows_kernel<T, OP, true, false, OutT><<<(unsigned)grid, kBlock, 0, stream>>>(
@@ -778,31 +662,20 @@ int launch(const T *in, OutT *out, int64_t A, int64_t B, int64_t C, void *ws,
   if (!vec && cols_vec_by_shape(sizeof(T), C)) {
     q.lpr = (int)std::min<int64_t>(kColsThreadsPerRow, pow2_ceil(C));
     q.slabs = (int)ceil_div<int64_t>(C, q.lpr);
-    q.fused = false;
   }
   const int64_t grid = A * q.slabs * q.splits;
   if (grid > 0x7fffffffLL)
     return B200_ERR_UNSUPPORTED;
-  int ticket_base = -1;
-  if (q.fused)
-    ticket_base = ticket_range(ws, (int)(A * q.slabs));
-  const bool fused = q.fused && ticket_base >= 0;
   int rc;
-  if (vec && fused)
-    rc = launch_pdl(reduce_cols_kernel<T, OP, N, true, OutT>, dim3((unsigned)grid), dim3(kBlock), 0, stream, in, out,
-                    partial, A, B, C, q.lpr, q.slabs, q.splits, q.rows_per_split, ticket_base);
-  else if (vec)
-    rc = launch_pdl(reduce_cols_kernel<T, OP, N, false, OutT>, dim3((unsigned)grid), dim3(kBlock), 0, stream, in, out,
-                    partial, A, B, C, q.lpr, q.slabs, q.splits, q.rows_per_split, 0);
-  else if (fused)
-    rc = launch_pdl(reduce_cols_kernel<T, OP, 1, true, OutT>, dim3((unsigned)grid), dim3(kBlock), 0, stream, in, out,
-                    partial, A, B, C, q.lpr, q.slabs, q.splits, q.rows_per_split, ticket_base);
+  if (vec)
+    rc = launch_pdl(reduce_cols_kernel<T, OP, N, OutT>, dim3((unsigned)grid), dim3(kBlock), 0, stream, in, out,
+                    partial, A, B, C, q.lpr, q.slabs, q.splits, q.rows_per_split, g_prefetch_before_wait);
   else
-    rc = launch_pdl(reduce_cols_kernel<T, OP, 1, false, OutT>, dim3((unsigned)grid), dim3(kBlock), 0, stream, in, out,
-                    partial, A, B, C, q.lpr, q.slabs, q.splits, q.rows_per_split, 0);
+    rc = launch_pdl(reduce_cols_kernel<T, OP, 1, OutT>, dim3((unsigned)grid), dim3(kBlock), 0, stream, in, out,
+                    partial, A, B, C, q.lpr, q.slabs, q.splits, q.rows_per_split, g_prefetch_before_wait);
   if (rc)
     return rc;
-  if (q.splits > 1 && !fused) {
+  if (q.splits > 1) {
     const int64_t n = A * C;
     return launch_pdl(reduce_finalize_kernel<OP, OutT>, dim3((unsigned)ceil_div<int64_t>(n, 32)),
                       dim3(kFinalizeBlock), 0, stream, (const float *)partial, out, n, q.splits, (int64_t)1, n);
@@ -830,12 +703,10 @@ int esize_of(int dtype) {
 using namespace b200;
 
 // Measurement hook (not part of the drop-in ABI): pins the column plan's threads per slab row
-// (0 = the shape rule) and whether the fold is fused into the first launch (-1 = the rule).
-// Workspace sizes follow the pinned plan, so ask for them after calling this.
-extern "C" void b200_reduce_cols_plan_override(int threads_per_row, int fused) {
-  g_cols_lpr_override = threads_per_row;
-  g_cols_fused_override = fused;
-}
+// (0 = the shape rule).  Workspace sizes follow the pinned plan, so ask for them after calling this.
+extern "C" void b200_reduce_cols_plan_override(int threads_per_row) { g_cols_lpr_override = threads_per_row; }
+
+extern "C" void b200_reduce_tune(int prefetch_before_wait) { g_prefetch_before_wait = prefetch_before_wait; }
 
 extern "C" size_t b200_reduce_workspace_bytes(int op, int dtype, int64_t A, int64_t B, int64_t C) {
   (void)op;

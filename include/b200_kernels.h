@@ -53,10 +53,7 @@ const char *b200_error_string(int code);
  * ascending index order: any NaN gives NaN, equal values keep the later one.
  * Workspace bytes depend only on (op, dtype, A, B, C); the workspace may be
  * uninitialised.  Two calls that may overlap on the GPU need different
- * workspaces.  (A column reduction split over many blocks folds its partial
- * sums in the same launch: the last block of a column slab to finish does it.
- * The tickets that tell which block is last are library-owned words bound to
- * the workspace address, zero between launches.)
+ * workspaces.
  */
 size_t b200_reduce_workspace_bytes(int op, int dtype, int64_t A, int64_t B,
                                    int64_t C);
