@@ -169,13 +169,12 @@ struct SharedStorage {
   uint64_t mx_ready[2][2];
   uint32_t tmem_base;
   int failed;
-  uint32_t wait_polls;
   alignas(16) float rowmax[2][2][kBM]; // [group][tile parity][row]: scaled row maximum of the group's tile
   float2 xch[2][kBM];      // (reference max, row sum) of each group, for the final merge
 };
 
-__device__ __forceinline__ bool wait_or_flag(uint64_t *bar, uint32_t parity, SharedStorage *ss) {
-  if (mbar_wait(bar, parity, ss->wait_polls))
+__device__ __forceinline__ bool wait_or_flag(uint64_t *bar, uint32_t parity, SharedStorage *ss, uint32_t polls) {
+  if (mbar_wait(bar, parity, polls))
     return true;
   ss->failed = 1; // some arrival never came: every role gives up at its next wait
   return false;
@@ -197,8 +196,8 @@ __device__ __forceinline__ bool elect_one() {
 }
 // all 32 lanes wait; the verdict is the same in every lane, so a warp gives up as a whole and
 // the warp-wide votes and tensor-memory instructions that follow a wait stay convergent
-__device__ __forceinline__ bool warp_wait_or_flag(uint64_t *bar, uint32_t parity, SharedStorage *ss) {
-  const bool ok = __all_sync(0xffffffffu, mbar_wait(bar, parity, ss->wait_polls));
+__device__ __forceinline__ bool warp_wait_or_flag(uint64_t *bar, uint32_t parity, SharedStorage *ss, uint32_t polls) {
+  const bool ok = __all_sync(0xffffffffu, mbar_wait(bar, parity, polls));
   if (!ok)
     ss->failed = 1;
   return ok;
@@ -314,7 +313,6 @@ __global__ void __launch_bounds__(kThreads, 1)
       mbar_init(&ss->mx_ready[g][1], 4);
     }
     ss->failed = 0;
-    ss->wait_polls = p.wait_polls;
     mbar_fence_init();
   }
   if (warp == 1) {
@@ -341,7 +339,7 @@ __global__ void __launch_bounds__(kThreads, 1)
         if (w.n == 0)
           continue;
         // Q's buffer is free once the last Q K^T of the previous query tile has completed
-        if (qc > 0 && !wait_or_flag(&ss->q_empty, (qc - 1) & 1, ss))
+        if (qc > 0 && !wait_or_flag(&ss->q_empty, (qc - 1) & 1, ss, p.wait_polls))
           break;
         mbar_arrive_expect_tx(&ss->bar_q, kTileBytes);
         tma_load_4d(sQ, &q_map, 0, w.h, (int)w.q0, w.b, &ss->bar_q);
@@ -349,7 +347,7 @@ __global__ void __launch_bounds__(kThreads, 1)
         ++qc;
         for (int j = 0; j < w.n; ++j, ++kc) {
           const int st = kc % kFwdKStages;
-          if (!wait_or_flag(&ss->k_empty[st], ((kc / kFwdKStages) & 1) ^ 1, ss)) {
+          if (!wait_or_flag(&ss->k_empty[st], ((kc / kFwdKStages) & 1) ^ 1, ss, p.wait_polls)) {
             ok = false;
             break;
           }
@@ -370,7 +368,7 @@ __global__ void __launch_bounds__(kThreads, 1)
       while (ok && next_work(idx, w)) {
         for (int j = 0; j < w.n; ++j, ++vc) {
           const int st = vc % kFwdVStages;
-          if (!wait_or_flag(&ss->v_empty[st], ((vc / kFwdVStages) & 1) ^ 1, ss)) {
+          if (!wait_or_flag(&ss->v_empty[st], ((vc / kFwdVStages) & 1) ^ 1, ss, p.wait_polls)) {
             ok = false;
             break;
           }
@@ -394,12 +392,12 @@ __global__ void __launch_bounds__(kThreads, 1)
     while (ok && next_work(idx, w)) {
       if (w.n == 0)
         continue;
-      ok = warp_wait_or_flag(&ss->bar_q, qc & 1, ss);
+      ok = warp_wait_or_flag(&ss->bar_q, qc & 1, ss, p.wait_polls);
       ++qc;
       for (int j = 0; ok && j < w.n; ++j, ++kc) {
         const int g = j & 1, st = kc % kFwdKStages;
-        ok = warp_wait_or_flag(&ss->k_full[st], (kc / kFwdKStages) & 1, ss) &&
-             warp_wait_or_flag(&ss->s_empty[g], (tc[g] & 1) ^ 1, ss);
+        ok = warp_wait_or_flag(&ss->k_full[st], (kc / kFwdKStages) & 1, ss, p.wait_polls) &&
+             warp_wait_or_flag(&ss->s_empty[g], (tc[g] & 1) ^ 1, ss, p.wait_polls);
         if (!ok)
           break;
         ++tc[g];
@@ -433,8 +431,8 @@ __global__ void __launch_bounds__(kThreads, 1)
     while (ok && next_work(idx, w)) {
       for (int j = 0; ok && j < w.n; ++j, ++vc) {
         const int g = j & 1, st = vc % kFwdVStages;
-        ok = warp_wait_or_flag(&ss->v_full[st], (vc / kFwdVStages) & 1, ss) &&
-             warp_wait_or_flag(&ss->p_full[g], tc[g] & 1, ss);
+        ok = warp_wait_or_flag(&ss->v_full[st], (vc / kFwdVStages) & 1, ss, p.wait_polls) &&
+             warp_wait_or_flag(&ss->p_full[g], tc[g] & 1, ss, p.wait_polls);
         if (!ok)
           break;
         ++tc[g];
@@ -481,13 +479,13 @@ __global__ void __launch_bounds__(kThreads, 1)
         float m_other = -INFINITY;
         if (j > 0) {
           const uint32_t to = tc[1] + ((j - 1) >> 1); // tile j - 1 among the other group's tiles
-          if (!warp_wait_or_flag(&ss->mx_ready[g ^ 1][to & 1], (to >> 1) & 1, ss)) {
+          if (!warp_wait_or_flag(&ss->mx_ready[g ^ 1][to & 1], (to >> 1) & 1, ss, p.wait_polls)) {
             ok = false;
             break;
           }
           m_other = ss->rowmax[g ^ 1][to & 1][row];
         }
-        if (!warp_wait_or_flag(&ss->s_full[g], ti & 1, ss)) {
+        if (!warp_wait_or_flag(&ss->s_full[g], ti & 1, ss, p.wait_polls)) {
           ok = false;
           break;
         }
@@ -573,7 +571,7 @@ __global__ void __launch_bounds__(kThreads, 1)
         // previous one, which read the P columns, and O holds every tile up to j - 1
         if (j > 0) {
           const uint32_t to = tc[1] + ((j - 1) >> 1);
-          if (!warp_wait_or_flag(&ss->pv_done[g ^ 1], to & 1, ss)) {
+          if (!warp_wait_or_flag(&ss->pv_done[g ^ 1], to & 1, ss, p.wait_polls)) {
             ok = false;
             break;
           }
@@ -607,7 +605,7 @@ __global__ void __launch_bounds__(kThreads, 1)
       if (ok && n > 0) {
         const int gl = (n - 1) & 1; // group of the last key tile
         const uint32_t tl = (gl == g ? tc[0] : tc[1]) + ((n - 1) >> 1);
-        ok = warp_wait_or_flag(&ss->pv_done[gl], tl & 1, ss);
+        ok = warp_wait_or_flag(&ss->pv_done[gl], tl & 1, ss, p.wait_polls);
       }
       tc[0] += n_mine;
       tc[1] += n_other;
@@ -738,21 +736,20 @@ struct BwdShared {
   uint64_t all_done;                              // every MMA of the block has completed
   uint32_t tmem_base;
   int failed;
-  uint32_t wait_polls;
   // dK/dV kernel: -lse * log2e and -dsum of the streamed queries [group][parity][row], negated
   // so that pairs of them are addends of packed FMAs / ADDs (read four at a time: 16-byte aligned)
   alignas(16) float neg_lse2[2][2][kBwdBN];
   alignas(16) float neg_dsum[2][2][kBwdBN];
 };
 
-__device__ __forceinline__ bool bwd_wait(uint64_t *bar, uint32_t parity, BwdShared *ss) {
-  if (mbar_wait(bar, parity, ss->wait_polls))
+__device__ __forceinline__ bool bwd_wait(uint64_t *bar, uint32_t parity, BwdShared *ss, uint32_t polls) {
+  if (mbar_wait(bar, parity, polls))
     return true;
   ss->failed = 1;
   return false;
 }
-__device__ __forceinline__ bool bwd_warp_wait(uint64_t *bar, uint32_t parity, BwdShared *ss) {
-  const bool ok = __all_sync(0xffffffffu, mbar_wait(bar, parity, ss->wait_polls));
+__device__ __forceinline__ bool bwd_warp_wait(uint64_t *bar, uint32_t parity, BwdShared *ss, uint32_t polls) {
+  const bool ok = __all_sync(0xffffffffu, mbar_wait(bar, parity, polls));
   if (!ok)
     ss->failed = 1;
   return ok;
@@ -885,7 +882,6 @@ __global__ void __launch_bounds__(kThreads, 1)
     }
     mbar_init(&ss->all_done, 1);
     ss->failed = 0;
-    ss->wait_polls = p.wait_polls;
     mbar_fence_init();
   }
   if (warp == 1) {
@@ -917,7 +913,7 @@ __global__ void __launch_bounds__(kThreads, 1)
       tma_load_4d(sRes1 + kHalfTile, &res1_map, 64, res_head, (int)own0, b, &ss->bar_resident);
       for (int it = 0; it < T; ++it) {
         const int st = it % kBwdStages;
-        if (!bwd_wait(&ss->empty[st], (uint32_t)(((it / kBwdStages) & 1) ^ 1), ss))
+        if (!bwd_wait(&ss->empty[st], (uint32_t)(((it / kBwdStages) & 1) ^ 1), ss, p.wait_polls))
           break;
         mbar_arrive_expect_tx(&ss->full[st], 2 * kStrTileBytes);
         unsigned char *t0 = sStr + st * 2 * kStrTileBytes, *t1 = t0 + kStrTileBytes;
@@ -960,9 +956,9 @@ __global__ void __launch_bounds__(kThreads, 1)
         if (elect_one())
           umma_commit(&ss->sdp_full[g]);
       };
-      bool ok = kDKDV ? bwd_warp_wait(&ss->bar_resident, 0, ss) : bwd_warp_wait(&ss->res_ready, 0, ss);
+      bool ok = kDKDV ? bwd_warp_wait(&ss->bar_resident, 0, ss, p.wait_polls) : bwd_warp_wait(&ss->res_ready, 0, ss, p.wait_polls);
       for (int it = 0; ok && it < 2 && it < T; ++it) {
-        ok = bwd_warp_wait(&ss->full[it % kBwdStages], 0, ss);
+        ok = bwd_warp_wait(&ss->full[it % kBwdStages], 0, ss, p.wait_polls);
         if (ok) {
           tc_fence_after_sync();
           issue_sdp(it);
@@ -974,8 +970,8 @@ __global__ void __launch_bounds__(kThreads, 1)
         // the streamed tile after next arrived long ago (the ring is four deep): look at its
         // barrier while the group still computes, not between the two batches of products
         if (it + 2 < T)
-          ok = bwd_warp_wait(&ss->full[(it + 2) % kBwdStages], (uint32_t)(((it + 2) / kBwdStages) & 1), ss);
-        ok = ok && bwd_warp_wait(&ss->pds_full[g], (uint32_t)((it >> 1) & 1), ss);
+          ok = bwd_warp_wait(&ss->full[(it + 2) % kBwdStages], (uint32_t)(((it + 2) / kBwdStages) & 1), ss, p.wait_polls);
+        ok = ok && bwd_warp_wait(&ss->pds_full[g], (uint32_t)((it >> 1) & 1), ss, p.wait_polls);
         if (!ok)
           break;
         tc_fence_after_sync();
@@ -1022,7 +1018,7 @@ __global__ void __launch_bounds__(kThreads, 1)
     bool ok = T > 0;
     if (!kDKDV && T > 0) {
       // own Q (group 0) / dO (group 1) row -> tensor memory, the A operands of S and dP
-      ok = bwd_wait(&ss->bar_resident, 0, ss);
+      ok = bwd_wait(&ss->bar_resident, 0, ss, p.wait_polls);
       const unsigned char *src = g == 0 ? sRes0 : sRes1;
 #pragma unroll
       for (int db = 0; db < 2; ++db) {
@@ -1073,7 +1069,7 @@ __global__ void __launch_bounds__(kThreads, 1)
         }
         load_stats(i + 1, next_l2, next_dd); // in flight during this tile
       }
-      const bool waited = bwd_wait(&ss->sdp_full[g], (uint32_t)(i & 1), ss);
+      const bool waited = bwd_wait(&ss->sdp_full[g], (uint32_t)(i & 1), ss, p.wait_polls);
       // one barrier per tile and group: publishes the statistics and makes giving up unanimous
       if (named_bar_or_id(1 + g, !waited)) {
         ok = false;
@@ -1155,7 +1151,7 @@ __global__ void __launch_bounds__(kThreads, 1)
 
     // ---- epilogue: accumulators -> 16 bit -> shared -> TMA store
     if (ok && T > 0)
-      ok = bwd_wait(&ss->all_done, 0, ss);
+      ok = bwd_wait(&ss->all_done, 0, ss, p.wait_polls);
     tc_fence_after_sync();
     const bool have = ok && T > 0;
     // kDKDV: group 0 takes dV (unscaled) -> V's tile, group 1 dK (* scale) -> K's tile;

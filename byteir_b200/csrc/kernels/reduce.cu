@@ -160,7 +160,6 @@ __global__ void __launch_bounds__(kBlock)
   constexpr int N = 16 / sizeof(T);
   __shared__ float warp_part[kBlock / 32];
   __shared__ float cluster_part;
-  pdl_wait();
   pdl_launch_dependents();
 
   const int groups_per_block = kBlock / tpr;
@@ -173,6 +172,15 @@ __global__ void __launch_bounds__(kBlock)
   const int64_t e1 = active ? min(B, e0 + seg_len) : e0;
   const T *row = in + (active ? a : 0) * B;
 
+  if (VEC) { // the first loads, on their way into L2 while the kernel in front of this one ends
+    const uint4 *vp = reinterpret_cast<const uint4 *>(row + e0);
+    const int64_t nvec = (e1 - e0) / N;
+#pragma unroll
+    for (int k = 0; k < 4; ++k)
+      if (t + (int64_t)k * tpr < nvec)
+        prefetch_l2(vp + t + (int64_t)k * tpr);
+  }
+  pdl_wait();
   Acc<T, OP> acc;
   if (VEC) {
     const uint4 *vp = reinterpret_cast<const uint4 *>(row + e0);
@@ -284,12 +292,13 @@ __global__ void __launch_bounds__(kBlock)
     }
   };
   int64_t a = (int64_t)blockIdx.x * block_rows + gib;
-  if (prefetch && a < A) { // the first row's loads, on their way into L2 during the wait
-    const uint4 *vp = reinterpret_cast<const uint4 *>(in + a * B);
+  // the loads of the first `prefetch` rows of this group, on their way into L2 during the wait
+  for (int64_t ap = a, k = 0; k < prefetch && ap < A; ++k, ap += (int64_t)gridDim.x * block_rows) {
+    const uint4 *vp = reinterpret_cast<const uint4 *>(in + ap * B);
 #pragma unroll
-    for (int k = 0; k < VPT; ++k)
-      if (t + k * tpr < nvec)
-        prefetch_l2(vp + t + k * tpr);
+    for (int k2 = 0; k2 < VPT; ++k2)
+      if (t + k2 * tpr < nvec)
+        prefetch_l2(vp + t + k2 * tpr);
   }
   pdl_wait();
   load_row(a, cur);
@@ -372,11 +381,13 @@ __global__ void __launch_bounds__(kBlock, 4)
   const int64_t r1 = min(B, r0 + rows_per_split);
   const T *base = in + a * B * C + col0;
   const int64_t step = row_lanes;
-  if (prefetch && col_ok) { // the first batch of this thread's loads, on its way into L2 during the wait
+  if (col_ok) { // the first `prefetch` batches of this thread's loads, on their way into L2 during the wait
+    for (int64_t r = r0 + lane_row, k = 0; k < prefetch && r < r1; ++k, r += 8 * step) {
 #pragma unroll
-    for (int u = 0; u < 8; ++u)
-      if (r0 + lane_row + u * step < r1)
-        prefetch_l2(base + (r0 + lane_row + u * step) * C);
+      for (int u = 0; u < 8; ++u)
+        if (r + u * step < r1)
+          prefetch_l2(base + (r + u * step) * C);
+    }
   }
   pdl_wait(); // inputs may come from the kernel launched just before this one
 
@@ -522,13 +533,20 @@ __global__ void __launch_bounds__(kBlock)
 
 // plan constants of the column path (threads that cover one row of a slab; blocks per SM aimed at)
 constexpr int kColsThreadsPerRow = 32;
-constexpr int kColsBlocksPerSm = 4;
 // Measurement override of the column plan (b200_reduce_cols_plan_override): threads per slab
 // row (0 = the rule above).
 int g_cols_lpr_override = 0;
-// b200_reduce_tune: whether kernels hint their first loads into L2 before waiting for the kernel in
-// front of them (1, default) or not (0)
-int g_prefetch_before_wait = 1;
+// How many batches of eight loads (column kernel) and rows (short-row kernel) a thread hints into L2
+// before it waits for the kernel in front of it, and how many blocks per SM the two kernels aim at
+// (both use 64 registers per thread, so four blocks of 256 threads fill an SM: more would be a
+// second wave).  Measured on f16 [64, 512, 1024] (us per op, graph replay): column sum 13.6 with one
+// batch hinted, 14.1 with two, 15.3 with four, 14.4 with none; row max 12.5 with nothing hinted,
+// 10.5 with one row, 10.2 with four; two or three column blocks per SM 16.4 / 15.5 against 13.6.
+// b200_reduce_tune changes them for such measurements.
+int g_prefetch_cols = 1;
+int g_prefetch_rows = 4;
+int g_cols_blocks_per_sm = 4;
+int g_rows_blocks_per_sm = 4;
 
 // ---- launch plan: a pure function of the shape -----------------------------
 struct Plan {
@@ -574,7 +592,7 @@ Plan make_plan(int esize, int64_t A, int64_t B, int64_t C, bool vec_cols) {
       p.slabs = (int)ceil_div<int64_t>(C, (int64_t)p.lpr * NV);
       const int64_t rows_per_step = kBlock / p.lpr;
       const int64_t blocks = A * p.slabs;
-      int64_t splits = std::max<int64_t>(1, ceil_div<int64_t>((int64_t)kColsBlocksPerSm * kNumSMs, blocks));
+      int64_t splits = std::max<int64_t>(1, ceil_div<int64_t>((int64_t)g_cols_blocks_per_sm * kNumSMs, blocks));
       splits = std::min<int64_t>(splits, std::max<int64_t>(1, B / (rows_per_step * 4)));
       p.rows_per_split = ceil_div<int64_t>(B, splits);
       p.splits = (int)ceil_div<int64_t>(B, p.rows_per_split);
@@ -633,21 +651,22 @@ int launch(const T *in, OutT *out, int64_t A, int64_t B, int64_t C, void *ws,
     if (vec && p.segs == 1 && nvec <= 4LL * p.tpr) {
       const int vpt = (int)ceil_div<int64_t>(nvec, p.tpr);
       const int64_t row_blocks = ceil_div<int64_t>(A, groups_per_block);
-      const unsigned pgrid = (unsigned)std::min<int64_t>(row_blocks, (int64_t)kNumSMs * (2048 / kBlock));
+      const unsigned pgrid = (unsigned)std::min<int64_t>(row_blocks, (int64_t)kNumSMs * g_rows_blocks_per_sm);
       if (vpt <= 1)
-        return launch_pdl(reduce_short_rows_kernel<T, OP, 1, OutT>, dim3(pgrid), dim3(kBlock), 0, stream, in, out, A, B, p.tpr, g_prefetch_before_wait);
+        return launch_pdl(reduce_short_rows_kernel<T, OP, 1, OutT>, dim3(pgrid), dim3(kBlock), 0, stream, in, out, A, B, p.tpr, g_prefetch_rows);
       else if (vpt == 2)
-        return launch_pdl(reduce_short_rows_kernel<T, OP, 2, OutT>, dim3(pgrid), dim3(kBlock), 0, stream, in, out, A, B, p.tpr, g_prefetch_before_wait);
+        return launch_pdl(reduce_short_rows_kernel<T, OP, 2, OutT>, dim3(pgrid), dim3(kBlock), 0, stream, in, out, A, B, p.tpr, g_prefetch_rows);
       else
-        return launch_pdl(reduce_short_rows_kernel<T, OP, 4, OutT>, dim3(pgrid), dim3(kBlock), 0, stream, in, out, A, B, p.tpr, g_prefetch_before_wait);
+        return launch_pdl(reduce_short_rows_kernel<T, OP, 4, OutT>, dim3(pgrid), dim3(kBlock), 0, stream, in, out, A, B, p.tpr, g_prefetch_rows);
     }
+    int rc;
     if (vec)
-      reduce_rows_kernel<T, OP, true, false, OutT><<<(unsigned)grid, kBlock, 0, stream>>>(
-          in, out, partial, A, B, p.tpr, p.segs, p.seg_len);
+      rc = launch_pdl(reduce_rows_kernel<T, OP, true, false, OutT>, dim3((unsigned)grid), dim3(kBlock), 0, stream, in,
+                      out, partial, A, B, p.tpr, p.segs, p.seg_len);
     else
-      reduce_rows_kernel<T, OP, false, false, OutT><<<(unsigned)grid, kBlock, 0, stream>>>(
-          in, out, partial, A, B, p.tpr, p.segs, p.seg_len);
-    if (int rc = check_launch())
+      rc = launch_pdl(reduce_rows_kernel<T, OP, false, false, OutT>, dim3((unsigned)grid), dim3(kBlock), 0, stream, in,
+                      out, partial, A, B, p.tpr, p.segs, p.seg_len);
+    if (rc)
       return rc;
     if (p.segs > 1) {
       return launch_pdl(reduce_finalize_kernel<OP, OutT>, dim3((unsigned)ceil_div<int64_t>(A, 32)),
@@ -669,10 +688,10 @@ int launch(const T *in, OutT *out, int64_t A, int64_t B, int64_t C, void *ws,
   int rc;
   if (vec)
     rc = launch_pdl(reduce_cols_kernel<T, OP, N, OutT>, dim3((unsigned)grid), dim3(kBlock), 0, stream, in, out,
-                    partial, A, B, C, q.lpr, q.slabs, q.splits, q.rows_per_split, g_prefetch_before_wait);
+                    partial, A, B, C, q.lpr, q.slabs, q.splits, q.rows_per_split, g_prefetch_cols);
   else
     rc = launch_pdl(reduce_cols_kernel<T, OP, 1, OutT>, dim3((unsigned)grid), dim3(kBlock), 0, stream, in, out,
-                    partial, A, B, C, q.lpr, q.slabs, q.splits, q.rows_per_split, g_prefetch_before_wait);
+                    partial, A, B, C, q.lpr, q.slabs, q.splits, q.rows_per_split, g_prefetch_cols);
   if (rc)
     return rc;
   if (q.splits > 1) {
@@ -706,7 +725,12 @@ using namespace b200;
 // (0 = the shape rule).  Workspace sizes follow the pinned plan, so ask for them after calling this.
 extern "C" void b200_reduce_cols_plan_override(int threads_per_row) { g_cols_lpr_override = threads_per_row; }
 
-extern "C" void b200_reduce_tune(int prefetch_before_wait) { g_prefetch_before_wait = prefetch_before_wait; }
+extern "C" void b200_reduce_tune(int prefetch_cols, int prefetch_rows, int cols_blocks_per_sm, int rows_blocks_per_sm) {
+  g_prefetch_cols = prefetch_cols;
+  g_prefetch_rows = prefetch_rows;
+  g_cols_blocks_per_sm = cols_blocks_per_sm > 0 ? cols_blocks_per_sm : 4;
+  g_rows_blocks_per_sm = rows_blocks_per_sm > 0 ? rows_blocks_per_sm : 4;
+}
 
 extern "C" size_t b200_reduce_workspace_bytes(int op, int dtype, int64_t A, int64_t B, int64_t C) {
   (void)op;

@@ -182,6 +182,17 @@ inline void store_from_f64(void *p, int dt, int64_t i, double v) {
 
 extern "C" {
 
+// A launcher may have exported OMP_NUM_THREADS=1 for its ranks: the benchmark's CPU legs set the
+// thread count to the cores the process may run on.
+void oracle_set_num_threads(int n) {
+#ifdef _OPENMP
+  if (n > 0)
+    omp_set_num_threads(n);
+#else
+  (void)n;
+#endif
+}
+
 int oracle_num_threads() {
 #ifdef _OPENMP
   return omp_get_max_threads();
