@@ -19,6 +19,9 @@ SIGNATURES = {
     "brt_register_kernels_from_dynlib": (_int, [_cp]),
     "brt_session_create": (_vp, []),
     "brt_session_destroy": (None, [_vp]),
+    "brt_session_create_distributed": (_vp, [_int, _int]),
+    "brt_session_set_allreduce_callback": (_int, [_vp, _vp, _vp]),
+    "brt_session_set_allreduce_peer": (_int, [_vp, C.c_uint64, C.POINTER(_vp), C.POINTER(_vp), _vp, _vp]),
     "brt_session_add_cpu": (_int, [_vp]),
     "brt_session_add_cuda": (_int, [_vp, _int]),
     "brt_session_add_cuda_external": (_int, [_vp, _int, _vp, _vp]),
@@ -100,7 +103,7 @@ class Session:
 
     def __init__(self, device="cuda", device_id=0, host_space=False, alloc_func=None, free_func=None):
         device = device.lower()
-        self._h = lib().brt_session_create()
+        self._h = self._create()
         if not self._h:
             raise BrtError(lib().brt_last_error().decode())
         if (alloc_func is None) != (free_func is None):
@@ -120,6 +123,9 @@ class Session:
             _check(lib().brt_session_add_cpu(self._h))
         else:
             raise ValueError(device)
+
+    def _create(self):
+        return lib().brt_session_create()
 
     def close(self):
         if self._h:
@@ -187,6 +193,51 @@ class Session:
 
     def get_output_names(self):
         return [a.name for a in self.args() if a.argtype & 2]
+
+
+REDUCE_OP_NAMES = {0: "sum", 1: "max", 2: "min"}
+_ALLREDUCE_FN = C.CFUNCTYPE(C.c_int, C.c_void_p, C.c_void_p, C.c_void_p, C.c_uint64, C.c_int, C.c_int,
+                            C.POINTER(C.c_int64), C.c_uint64, C.c_void_p)
+
+
+class DistributedSession(Session):
+    """One rank of `nranks` (the reference's DistributedSession, runtime/include/brt/core/distributed/
+    distributed_session.h:44-82): every rank loads its own module; `nccl.AllReduce` ops run on the
+    communicator given with set_allreduce (a function of this program that runs one all-reduce on the
+    process group it created once) or set_allreduce_peer (the one-kernel sum over NVLink peer memory)."""
+
+    def __init__(self, rank, nranks, device="cuda", device_id=None, host_space=False, alloc_func=None, free_func=None):
+        self.rank, self.nranks = rank, nranks
+        super().__init__(device, rank if device_id is None else device_id, host_space, alloc_func, free_func)
+
+    def _create(self):
+        return lib().brt_session_create_distributed(self.rank, self.nranks)
+
+    def load_config(self, config):
+        """config[rank] is this rank's module file"""
+        self.load(config[self.rank])
+
+    def set_allreduce(self, fn):
+        """fn(send, recv, length, dtype, op, group, stream): addresses as int, dtype as "f32" / "f16" / ...,
+        op "sum" / "max" / "min", group a list of ranks (empty: all), stream a CUDA stream handle or None for
+        host buffers.  It enqueues (device) or completes (host) one all-reduce; an exception fails the run."""
+        def thunk(_user, send, recv, length, dtype, op, group, group_len, stream):
+            try:
+                fn(send, recv, int(length), DTYPE_NAMES.get(dtype, str(dtype)), REDUCE_OP_NAMES.get(op, str(op)),
+                   [int(group[i]) for i in range(group_len)], stream)
+                return 0
+            except Exception as e:  # the C side turns the code into a failed Status
+                self.allreduce_error = e
+                return 1
+        self._allreduce = _ALLREDUCE_FN(thunk)  # kept alive as long as the session
+        _check(lib().brt_session_set_allreduce_callback(self._h, C.cast(self._allreduce, C.c_void_p), None))
+
+    def set_allreduce_peer(self, capacity, peer_inbox, peer_flags, epoch_counter, status=None):
+        """peer_inbox / peer_flags: device addresses per rank (memory every rank has mapped, zeroed once);
+        epoch_counter: address of a zeroed device uint32; status: address of a device int, or None"""
+        inbox = (C.c_void_p * self.nranks)(*peer_inbox)
+        flags = (C.c_void_p * self.nranks)(*peer_flags)
+        _check(lib().brt_session_set_allreduce_peer(self._h, capacity, inbox, flags, epoch_counter, status))
 
 
 class Request:

@@ -5,7 +5,9 @@
 #include "brt/backends/cuda/device/cuda_allocator.h"
 #include "brt/backends/cuda/device/cuda_work_queue.h"
 #include "brt/backends/cuda/providers/default/cuda_provider.h"
+#include "brt/backends/nccl/device/distributed_backend_b200.h"
 #include "brt/core/common/common.h"
+#include "brt/core/distributed/distributed_session.h"
 #include "brt/core/framework/execution_provider.h"
 #include "brt/core/session/request_context.h"
 #include "brt/core/session/session.h"
@@ -16,7 +18,11 @@
 using namespace brt;
 
 struct brt_session {
-  Session session;
+  brt_session() : owned(new Session()), session(*owned) {}
+  brt_session(int rank, int nranks) : owned(new DistributedSession(rank, nranks)), session(*owned) {}
+  std::unique_ptr<DistributedBackend> backend; // destroyed after the session
+  std::unique_ptr<Session> owned;
+  Session &session;
 };
 struct brt_request {
   std::unique_ptr<RequestContext> ctx;
@@ -69,6 +75,52 @@ brt_session *brt_session_create(void) {
   }
 }
 void brt_session_destroy(brt_session *s) { delete s; }
+
+brt_session *brt_session_create_distributed(int rank, int nranks) {
+  try {
+    return new brt_session(rank, nranks);
+  } catch (const std::exception &e) {
+    g_error = e.what();
+    return nullptr;
+  }
+}
+
+namespace {
+common::Status AsDistributed(brt_session *s, DistributedSession **out) {
+  *out = dynamic_cast<DistributedSession *>(s->owned.get());
+  if (!*out)
+    return common::Status(common::BRT, common::INVALID_ARGUMENT,
+                          "not a distributed session (brt_session_create_distributed)");
+  return common::Status::OK();
+}
+} // namespace
+
+int brt_session_set_allreduce_callback(brt_session *s, brt_allreduce_fn fn, void *user) {
+  return Guard([&]() -> common::Status {
+    DistributedSession *ds = nullptr;
+    BRT_RETURN_IF_ERROR(AsDistributed(s, &ds));
+    s->backend.reset(new DistributedBackendCallback((uint32_t)ds->GetNRanks(), (uint32_t)ds->GetRank(),
+                                                    reinterpret_cast<BrtAllReduceFn>(fn), user));
+    ds->SetDistributedBackend(s->backend.get());
+    return common::Status::OK();
+  });
+}
+
+int brt_session_set_allreduce_peer(brt_session *s, uint64_t capacity, void *const *peer_inbox, void *const *peer_flags,
+                                   void *epoch_counter, void *status) {
+  return Guard([&]() -> common::Status {
+    DistributedSession *ds = nullptr;
+    BRT_RETURN_IF_ERROR(AsDistributed(s, &ds));
+    if (!peer_inbox || !peer_flags || !epoch_counter || capacity == 0)
+      return common::Status(common::BRT, common::INVALID_ARGUMENT, "peer tables, counter and capacity are required");
+    std::vector<void *> inbox(peer_inbox, peer_inbox + ds->GetNRanks()), flags(peer_flags, peer_flags + ds->GetNRanks());
+    s->backend.reset(new DistributedBackendPeer((uint32_t)ds->GetNRanks(), (uint32_t)ds->GetRank(), (size_t)capacity,
+                                                inbox, flags, static_cast<uint32_t *>(epoch_counter),
+                                                static_cast<int *>(status)));
+    ds->SetDistributedBackend(s->backend.get());
+    return common::Status::OK();
+  });
+}
 
 int brt_session_add_cpu(brt_session *s) {
   return Guard([&] { return NaiveCPUExecutionProviderFactory(&s->session); });

@@ -55,6 +55,12 @@ std::vector<int64_t> DeduceReduceShape(const std::vector<int64_t> &shape, std::v
   return out;
 }
 
+// Dimensions of size 1 reduce nothing; the rest form groups of consecutive dimensions.  One group is one
+// A x B x C reduction, as in the reference, which stops there ("Only consecutive dimensions ..."
+// reduce_impl.h:40-42).  Several groups are reduced one after the other, last group first, through f32
+// intermediates in the workspace (for a sum of 16-bit values, so that the result is rounded once).
+// The target may also be f32 for a 16-bit source (ReduceSumOp_f16_f32): the unrounded sum, which is what a
+// device contributes when the reduced axis is sharded over devices and an all-reduce follows.
 template <int OP> class ReduceImpl {
 public:
   explicit ReduceImpl(const OpAccessor &accessor) {
@@ -64,40 +70,99 @@ public:
     for (auto d : dimensions)
       BRT_ENFORCE(d >= 0 && d < (int64_t)shape.size(), "reduce dimension out of range");
     BRT_ENFORCE(tshape == DeduceReduceShape(shape, dimensions), "output shape does not match input minus dimensions");
-    BRT_ENFORCE(accessor.GetArgDTypeEnum(0) == accessor.GetArgDTypeEnum(1), "input and output types differ");
-    dtype_ = KernelDType(accessor.GetArgDTypeEnum(0));
+    in_dtype_ = KernelDType(accessor.GetArgDTypeEnum(0));
+    out_dtype_ = KernelDType(accessor.GetArgDTypeEnum(1));
+    BRT_ENFORCE(in_dtype_ == out_dtype_ || (OP == B200_REDUCE_SUM && out_dtype_ == B200_F32),
+                "input and output types differ (only a sum may be delivered as f32)");
     // dims of size 1 reduce nothing (reduce_impl.h:81-90)
     dimensions.erase(std::remove_if(dimensions.begin(), dimensions.end(), [&](int64_t d) { return shape[d] == 1; }),
                      dimensions.end());
-    if (!dimensions.empty()) {
-      std::sort(dimensions.begin(), dimensions.end());
-      for (size_t i = 0; i + 1 < dimensions.size(); ++i)
-        BRT_ENFORCE(dimensions[i + 1] - dimensions[i] == 1,
-                    "Only consecutive dimensions reductino were supported now.");
-      A = B = C = 1;
-      for (int64_t i = 0; i < dimensions.front(); ++i)
-        A *= shape[i];
-      for (auto d : dimensions)
-        B *= shape[d];
-      for (size_t i = dimensions.back() + 1; i < shape.size(); ++i)
-        C *= shape[i];
-    } else {
-      A = B = 0;
-      C = OpAccessor::GetNumElementsOfShape(shape);
+    std::sort(dimensions.begin(), dimensions.end());
+    dimensions.erase(std::unique(dimensions.begin(), dimensions.end()), dimensions.end());
+    total_ = OpAccessor::GetNumElementsOfShape(shape);
+    std::vector<int64_t> cur(shape.begin(), shape.end());
+    // groups of consecutive dimensions, taken from the back so that the indices in front stay valid
+    for (size_t hi = dimensions.size(); hi > 0;) {
+      size_t lo = hi - 1;
+      while (lo > 0 && dimensions[lo] - dimensions[lo - 1] == 1)
+        --lo;
+      Pass p{1, 1, 1};
+      for (int64_t i = 0; i < dimensions[lo]; ++i)
+        p.A *= cur[i];
+      for (size_t k = lo; k < hi; ++k)
+        p.B *= cur[dimensions[k]];
+      for (size_t i = dimensions[hi - 1] + 1; i < cur.size(); ++i)
+        p.C *= cur[i];
+      passes_.push_back(p);
+      cur.erase(cur.begin() + dimensions[lo], cur.begin() + dimensions[hi - 1] + 1);
+      hi = lo;
     }
+    // bytes: [kernel workspace, the largest any pass needs][two intermediates of the first pass's output]
+    const int mid = MidDType();
+    kernel_ws_ = 0;
+    for (size_t i = 0; i < passes_.size(); ++i) {
+      const Pass &p = passes_[i];
+      if (p.A && p.B && p.C)
+        kernel_ws_ = std::max(kernel_ws_, b200_reduce_workspace_bytes(OP, i == 0 ? in_dtype_ : mid, p.A, p.B, p.C));
+    }
+    kernel_ws_ = (kernel_ws_ + 255) & ~(size_t)255;
+    mid_bytes_ = 0;
+    const bool cast_at_end = passes_.size() > 1 && mid != out_dtype_;
+    if (passes_.size() > 1 || cast_at_end)
+      mid_bytes_ = ((size_t)(passes_[0].A * passes_[0].C) * ElemBytes(mid) + 255) & ~(size_t)255;
   }
 
   common::Status Execute(const void *input, void *output, void *workspace, cudaStream_t stream) {
-    return FromRc(b200_reduce(OP, dtype_, input, output, A, B, C, workspace, GetWorkspaceBytes(), stream),
-                  "b200_reduce");
+    if (passes_.empty()) { // nothing to reduce: a copy (reduce_impl.h:70-73)
+      return FromRc(b200_reduce(OP, in_dtype_, input, output, 0, 0, total_, nullptr, 0, stream), "b200_reduce");
+    }
+    char *ws = static_cast<char *>(workspace);
+    if (passes_.size() == 1) {
+      const Pass &p = passes_[0];
+      if (out_dtype_ == in_dtype_)
+        return FromRc(b200_reduce(OP, in_dtype_, input, output, p.A, p.B, p.C, ws, kernel_ws_, stream), "b200_reduce");
+      return FromRc(b200_reduce_sum_to_f32(in_dtype_, input, static_cast<float *>(output), p.A, p.B, p.C, ws, kernel_ws_,
+                                           stream),
+                    "b200_reduce_sum_to_f32");
+    }
+    // several groups: in -> mid[0] -> mid[1] -> ... -> out, the intermediates in f32 for a sum
+    const int mid = MidDType();
+    void *bufs[2] = {ws + kernel_ws_, ws + kernel_ws_ + mid_bytes_};
+    const void *src = input;
+    for (size_t i = 0; i < passes_.size(); ++i) {
+      const Pass &p = passes_[i];
+      const bool last = i + 1 == passes_.size();
+      void *dst = (last && mid == out_dtype_) ? output : bufs[i & 1];
+      int rc;
+      if (i == 0 && mid != in_dtype_)
+        rc = b200_reduce_sum_to_f32(in_dtype_, src, static_cast<float *>(dst), p.A, p.B, p.C, ws, kernel_ws_, stream);
+      else
+        rc = b200_reduce(OP, i == 0 ? in_dtype_ : mid, src, dst, p.A, p.B, p.C, ws, kernel_ws_, stream);
+      if (rc)
+        return FromRc(rc, "b200_reduce");
+      src = dst;
+    }
+    if (mid != out_dtype_) {
+      const Pass &p = passes_.back();
+      return FromRc(b200_cast_from_f32(out_dtype_, static_cast<const float *>(src), output, p.A * p.C, stream),
+                    "b200_cast_from_f32");
+    }
+    return common::Status::OK();
   }
 
-  size_t GetWorkspaceSize(const ExecutionContext &) const { return GetWorkspaceBytes(); }
+  size_t GetWorkspaceSize(const ExecutionContext &) const { return kernel_ws_ + 2 * mid_bytes_; }
 
 private:
-  size_t GetWorkspaceBytes() const { return (A && B && C) ? b200_reduce_workspace_bytes(OP, dtype_, A, B, C) : 0; }
-  int64_t A, B, C;
-  int dtype_;
+  struct Pass {
+    int64_t A, B, C;
+  };
+  static size_t ElemBytes(int dt) { return dt == B200_F32 ? 4 : 2; }
+  // element type between the passes of a multi-group reduction
+  int MidDType() const { return (OP == B200_REDUCE_SUM && in_dtype_ != B200_F32) ? B200_F32 : in_dtype_; }
+  std::vector<Pass> passes_; // in execution order
+  int64_t total_;
+  int in_dtype_, out_dtype_;
+  size_t kernel_ws_, mid_bytes_;
 };
 
 template <int OP>
@@ -430,6 +495,9 @@ void RegisterReductionOps(KernelRegistry *registry) {
     registry->Register(std::string("ReduceSumOp_") + t, Creator<Reduce<B200_REDUCE_SUM>>());
     registry->Register(std::string("ReduceMaxOp_") + t, Creator<Reduce<B200_REDUCE_MAX>>());
   }
+  // the unrounded sum of 16-bit values, for a sum that an all-reduce over devices continues
+  for (const char *t : {"f16_f32", "bf16_f32"})
+    registry->Register(std::string("ReduceSumOp_") + t, Creator<Reduce<B200_REDUCE_SUM>>());
 }
 
 void RegisterIndexingOps(KernelRegistry *registry) {

@@ -334,7 +334,8 @@ Status Session::NewRequestContext(std::unique_ptr<RequestContext> *request_ctx, 
 Status Session::Run(RequestContext &request) {
   if (!execution_plan_)
     return Status(common::BRT, common::NO_MODEL, "Run before a model is loaded");
-  ExecutionContext ctx(request.frame_.get(), request.wq_.get(), &request.frame_->GetStateInfo(), request.events_.get());
+  ExecutionContext ctx(request.frame_.get(), request.wq_.get(), &request.frame_->GetStateInfo(), request.events_.get(),
+                       distributed_backend_);
   try {
     request.frame_->FinishIOBinding();
     if (!request.frame_->IsPrologued()) {
@@ -352,7 +353,7 @@ void Session::Cleanup(RequestContext &request) noexcept {
     return;
   try {
     ExecutionContext ctx(request.frame_.get(), request.wq_.get(), &request.frame_->GetStateInfo(),
-                         request.events_.get());
+                         request.events_.get(), distributed_backend_);
     (void)execution_plan_->EpiloguePerFrame(ctx);
   } catch (...) {
   }

@@ -43,7 +43,7 @@ template <typename OutT>
 __global__ void __launch_bounds__(1024)
     sharded_sum_finish_kernel(const float *__restrict__ partial, PeerTable peers, int rank, int world,
                               int64_t n, uint32_t *epoch_counter, OutT *__restrict__ out, int *status,
-                              uint64_t timeout_ns) {
+                              uint64_t timeout_ns, int vec4) {
   __shared__ uint32_t s_epoch;
   __shared__ int s_timed_out;
   if (threadIdx.x == 0) {
@@ -53,11 +53,24 @@ __global__ void __launch_bounds__(1024)
   __syncthreads();
   const uint32_t epoch = s_epoch;
   const int slot = (int)(epoch & 1u);
-  // 1. push my partials into slot [slot][rank] of every inbox (mine included)
-  for (int p = 0; p < world; ++p) {
-    float *dst = peers.inbox[p] + ((size_t)slot * world + rank) * n;
-    for (int64_t i = threadIdx.x; i < n; i += blockDim.x)
-      dst[i] = partial[i];
+  // 1. push my partials into slot [slot][rank] of every inbox (mine included): the world x n
+  //    elements are spread over all threads, so that the stores to all peers are in flight together
+  //    (16 bytes each when the vector allows it)
+  const size_t slot_off = ((size_t)slot * world + rank) * n;
+  if (vec4) {
+    const int64_t nv = n >> 2;
+    const float4 *src = reinterpret_cast<const float4 *>(partial);
+    for (int64_t idx = threadIdx.x; idx < nv * world; idx += blockDim.x) {
+      const int p = (int)(idx / nv);
+      const int64_t i = idx - (int64_t)p * nv;
+      reinterpret_cast<float4 *>(peers.inbox[p] + slot_off)[i] = src[i];
+    }
+  } else {
+    for (int64_t idx = threadIdx.x; idx < n * world; idx += blockDim.x) {
+      const int p = (int)(idx / n);
+      const int64_t i = idx - (int64_t)p * n;
+      (peers.inbox[p] + slot_off)[i] = partial[i];
+    }
   }
   __threadfence_system();
   __syncthreads();
@@ -76,8 +89,12 @@ __global__ void __launch_bounds__(1024)
   }
   __syncthreads();
   if (s_timed_out) {
+    // `out` stays as it was and the epoch does not advance: the caller reads *status before it
+    // trusts `out`, and must re-establish the protocol (zeroed flags and counters on every rank)
+    // before the next call
     if (threadIdx.x == 0 && status)
       *status = 3;
+    return;
   }
   // 4. fold the world's partials in rank order; the inbox was written by other GPUs, read it past L1
   const float *inbox = peers.inbox[rank] + (size_t)slot * world * n;
@@ -116,18 +133,22 @@ extern "C" int b200_sharded_sum_finish(int dtype, const float *partial, void *co
     t.flags[p] = static_cast<uint32_t *>(peer_flags[p]);
   }
   const uint64_t timeout_ns = 2000000000ull; // 2 s
+  bool vec = n % 4 == 0 && aligned16(partial);
+  for (int p = 0; p < world; ++p)
+    vec = vec && aligned16(peer_inbox[p]);
+  const int vec4 = vec ? 1 : 0;
   switch (dtype) {
   case B200_F32:
     sharded_sum_finish_kernel<float><<<1, 1024, 0, stream>>>(partial, t, rank, world, n, epoch_counter,
-                                                              (float *)out, status, timeout_ns);
+                                                              (float *)out, status, timeout_ns, vec4);
     break;
   case B200_F16:
     sharded_sum_finish_kernel<__half><<<1, 1024, 0, stream>>>(partial, t, rank, world, n, epoch_counter,
-                                                               (__half *)out, status, timeout_ns);
+                                                               (__half *)out, status, timeout_ns, vec4);
     break;
   case B200_BF16:
     sharded_sum_finish_kernel<__nv_bfloat16><<<1, 1024, 0, stream>>>(partial, t, rank, world, n, epoch_counter,
-                                                                      (__nv_bfloat16 *)out, status, timeout_ns);
+                                                                      (__nv_bfloat16 *)out, status, timeout_ns, vec4);
     break;
   default:
     return B200_ERR_INVALID_ARG;

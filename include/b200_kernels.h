@@ -85,9 +85,14 @@ int b200_cast_from_f32(int dtype, const float *in, void *out, int64_t n,
  *   epoch_counter a device uint32 of this rank, zeroed once, owned by this call chain
  *   out           n elements of `dtype`, identical on every rank afterwards
  * The wait for the peers is bounded (2 s); on expiry *status (device int, may be
- * NULL) is set to 3 and the kernel ends.  Ranks must not run ahead of each other by
- * more than this call enforces itself (a rank needs every peer's epoch to finish
- * one), so no other synchronisation is needed between steps.
+ * NULL) is set to 3, `out` is left as it was, the epoch does not advance, and the
+ * kernel ends: check *status before trusting `out` (a caller that passes NULL
+ * cannot tell), and zero the flags and counters of every rank again before the
+ * next call.  Ranks must not run ahead of each other by more than this call
+ * enforces itself (a rank needs every peer's epoch to finish one), so no other
+ * synchronisation is needed between steps.  One block does the whole exchange: it
+ * is meant for vectors of up to a few thousand elements (the partial sums of a
+ * reduction); world <= 16.
  */
 size_t b200_sharded_sum_inbox_bytes(int world, int64_t n);
 int b200_sharded_sum_finish(int dtype, const float *partial, void *const *peer_inbox,

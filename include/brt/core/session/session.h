@@ -17,6 +17,7 @@ class ExecutionProvider;
 class IAllocator;
 class RequestContext;
 class WorkQueue;
+class DistributedBackend;
 namespace ir {
 class ByREHandle;
 }
@@ -66,6 +67,9 @@ protected:
   std::unordered_map<std::string, std::unique_ptr<IAllocator>> allocators_;
   std::unique_ptr<StaticBRTExecutionPlan> execution_plan_;
   std::unique_ptr<ir::ByREHandle> ir_handle_;
+
+  // the communicator Run hands to the kernels; set by a DistributedSession, null otherwise
+  DistributedBackend *distributed_backend_ = nullptr;
 
   std::vector<std::string> weight_names_, input_names_, output_names_;
   std::vector<size_t> weight_offsets_, input_offsets_, output_offsets_;

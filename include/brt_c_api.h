@@ -27,6 +27,21 @@ int brt_register_kernels_from_dynlib(const char *path);
 
 brt_session *brt_session_create(void);
 void brt_session_destroy(brt_session *s);
+/* DistributedSession(rank, nranks): one rank of several, each loading its own module.  The
+ * communicator its nccl.* ops run on is one of:
+ *  - a function of the host program that runs one all-reduce on the process group it created once
+ *    (DistributedBackendCallback): fn(user, send, recv, len, dtype (brt::DTypeEnum), op (0 sum, 1 max,
+ *    2 min), group, group_len, stream (NULL for host buffers)) returns 0 on success;
+ *  - the one-kernel sum over NVLink peer memory (DistributedBackendPeer): peer_inbox / peer_flags are
+ *    nranks device addresses each (memory every rank has mapped, zeroed once), epoch_counter a zeroed
+ *    device uint32, status a device int or NULL; sums f32 vectors of exactly `capacity` elements over
+ *    all ranks. */
+brt_session *brt_session_create_distributed(int rank, int nranks);
+typedef int (*brt_allreduce_fn)(void *user, const void *send, void *recv, uint64_t len, int dtype, int op,
+                                const int64_t *group, uint64_t group_len, void *stream);
+int brt_session_set_allreduce_callback(brt_session *s, brt_allreduce_fn fn, void *user);
+int brt_session_set_allreduce_peer(brt_session *s, uint64_t capacity, void *const *peer_inbox, void *const *peer_flags,
+                                   void *epoch_counter, void *status);
 /* NaiveCPUExecutionProviderFactory: "cpu" allocator + host provider */
 int brt_session_add_cpu(brt_session *s);
 /* CUDAAllocatorFactory(device) + DefaultCUDAExecutionProviderFactory */

@@ -300,3 +300,85 @@ def test_backend_run_and_profile_with_the_torch_allocator(tmp_path):
     assert torch.equal(out, out3) and 0 < ms < 50
     with pytest.raises(AssertionError):
         be.run([x.float()])
+
+
+# ---- the exchange step and multi-group reductions through the boundary ---------------------------------------
+SHARDED_SUM = """
+module attributes {byre.container_module} {
+  func.func @main(%arg0: memref<8x64x256xf16, "cuda"> {byre.argname = "X", byre.argtype = 1 : i32},
+                  %arg1: memref<256xf16, "cuda"> {byre.argname = "Sum", byre.argtype = 2 : i32}) attributes {byre.entry_point} {
+    %0 = memref.alloc() : memref<256xf32, "cuda">
+    byre.compute @ReduceSumOp_f16_f32(%arg0, %0) {dimensions = dense<[0, 1]> : tensor<2xi64>, memory_effects = [1 : i32, 2 : i32]} : memref<8x64x256xf16, "cuda">, memref<256xf32, "cuda">
+    byre.compute @nccl.AllReduce(%0, %arg1) {reduction = "sum", replica_group = [0], memory_effects = [1 : i32, 2 : i32]} : memref<256xf32, "cuda">, memref<256xf16, "cuda">
+    return
+  }
+}
+"""
+
+
+@pytest.mark.parametrize("backend", ["peer", "callback"])
+def test_sharded_sum_module_on_one_rank(backend):
+    """a rank's module of the sum whose reduced axis is sharded: unrounded f32 partial sums, then nccl.AllReduce
+    into an f16 target (rounded once).  World of one rank: the peer-memory kernel talks to its own inbox; the
+    callback communicator copies send to recv on the request's stream and the op casts afterwards.  Either way the
+    bits equal the unsharded ReduceSumOp_f16_f16."""
+    from byteir_b200 import ops, _native as N
+    rng = np.random.default_rng(41)
+    x = rng.standard_normal((8, 64, 256), dtype=np.float32).astype(np.float16)
+    xd = torch.from_numpy(x).cuda()
+    out = torch.zeros(256, dtype=torch.float16, device="cuda")
+    s = brt.DistributedSession(0, 1, device="cuda", device_id=0)
+    s.load_from_memory(SHARDED_SUM)
+    stream = torch.cuda.Stream()
+    calls = []
+    if backend == "peer":
+        n = 256
+        inbox = torch.zeros(N.lib().b200_sharded_sum_inbox_bytes(1, n) // 4, dtype=torch.float32, device="cuda")
+        flags = torch.zeros(64, dtype=torch.int32, device="cuda")
+        counter = torch.zeros(1, dtype=torch.int32, device="cuda")
+        status = torch.zeros(1, dtype=torch.int32, device="cuda")
+        s.set_allreduce_peer(n, [inbox.data_ptr()], [flags.data_ptr()], counter.data_ptr(), status.data_ptr())
+    else:
+        import ctypes as C
+        cudart = C.CDLL("libcudart.so")
+        cudart.cudaMemcpyAsync.argtypes = [C.c_void_p, C.c_void_p, C.c_size_t, C.c_int, C.c_void_p]
+
+        def all_reduce(send, recv, n, dtype, op, group, st):
+            calls.append((n, dtype, op, tuple(group), st))
+            assert cudart.cudaMemcpyAsync(recv, send, n * 4, 3, st) == 0  # one rank: the sum is the vector itself
+        s.set_allreduce(all_reduce)
+    torch.cuda.synchronize()
+    req = s.new_request(stream.cuda_stream)
+    req.bind_arg(s.arg_offset("X"), xd.data_ptr())
+    req.bind_arg(s.arg_offset("Sum"), out.data_ptr())
+    req.finish_io_binding()
+    for _ in range(3):
+        req.run()
+        req.sync()
+    torch.cuda.synchronize()
+    want = ops.reduce_sum(xd, [0, 1])
+    assert torch.equal(out, want)
+    np.testing.assert_allclose(out.float().cpu().numpy(), x.astype(np.float64).sum(axis=(0, 1)), rtol=2e-2, atol=1e-2)
+    if backend == "peer":
+        assert int(status.item()) == 0 and int(counter.item()) == 3
+    else:
+        assert calls[0] == (256, "f32", "sum", (0,), stream.cuda_stream)
+    req.close()
+    s.close()
+
+
+@pytest.mark.parametrize("t,npdt", [("f32", np.float32), ("f16", np.float16)])
+@pytest.mark.parametrize("shape,dims", [((6, 50, 36), (0, 2)), ((3, 4, 5, 16, 7), (0, 2, 3)), ((9, 1, 8, 20), (0, 1, 3))])
+def test_reduce_over_dimensions_that_are_not_consecutive(shape, dims, t, npdt):
+    """the reference refuses these at load time (reduce_impl.h:40-42); here the groups of consecutive dimensions
+    are reduced one after the other, a 16-bit sum through f32 intermediates so that it is rounded once"""
+    rng = np.random.default_rng(sum(shape))
+    x = rng.standard_normal(shape).astype(npdt)
+    out_shape = tuple(s for i, s in enumerate(shape) if i not in dims)
+    dims_s = "dense<[" + ", ".join(map(str, dims)) + f"]> : tensor<{len(dims)}xi64>"
+    s = _run(reduce_mlir(f"ReduceSumOp_{t}_{t}", t, shape, out_shape, dims_s), {"Input0": x})["Output0"]
+    want = x.astype(np.float64).sum(axis=dims)
+    tol = dict(rtol=1e-5, atol=1e-4) if t == "f32" else dict(rtol=2e-3, atol=2e-2)
+    np.testing.assert_allclose(s.astype(np.float64), want, **tol)
+    m = _run(reduce_mlir(f"ReduceMaxOp_{t}_{t}", t, shape, out_shape, dims_s), {"Input0": x})["Output0"]
+    assert np.array_equal(m, x.max(axis=dims))

@@ -185,17 +185,17 @@ def _cuda_session():
 REDUCE = """
 module attributes {byre.container_module} {
   func.func @reduce(%arg0: memref<%INx%T, "cuda"> {byre.argname = "Input0", byre.argtype = 1 : i32},
-                    %arg1: memref<%OUTx%T, "cuda"> {byre.argname = "Output0", byre.argtype = 2 : i32}) attributes {byre.entry_point} {
-    byre.compute @%KEY(%arg0, %arg1) {device = "cuda", dimensions = %DIMS, memory_effects = [1 : i32, 2 : i32]} : memref<%INx%T, "cuda">, memref<%OUTx%T, "cuda">
+                    %arg1: memref<%OUTx%OT, "cuda"> {byre.argname = "Output0", byre.argtype = 2 : i32}) attributes {byre.entry_point} {
+    byre.compute @%KEY(%arg0, %arg1) {device = "cuda", dimensions = %DIMS, memory_effects = [1 : i32, 2 : i32]} : memref<%INx%T, "cuda">, memref<%OUTx%OT, "cuda">
     return
   }
 }
 """
 
 
-def reduce_mlir(key, t, in_shape, out_shape, dims):
+def reduce_mlir(key, t, in_shape, out_shape, dims, out_t=None):
     f = lambda sh: "x".join(str(d) for d in sh)
-    return (REDUCE.replace("%IN", f(in_shape)).replace("%OUT", f(out_shape)).replace("%T", t)
+    return (REDUCE.replace("%IN", f(in_shape)).replace("%OUT", f(out_shape)).replace("%OT", out_t or t).replace("%T", t)
             .replace("%KEY", key).replace("%DIMS", dims))
 
 
@@ -210,8 +210,14 @@ def test_cuda_reduce_op_validates_shapes_and_consecutive_dims():
     s = _cuda_session()
     with pytest.raises(brt.BrtError, match="output shape"):
         s.load_from_memory(reduce_mlir("ReduceSumOp_f32_f32", "f32", (1024, 4096), (4096,), "dense<1> : tensor<1xi64>"))
-    with pytest.raises(brt.BrtError, match="consecutive"):
-        s.load_from_memory(reduce_mlir("ReduceMaxOp_f16_f16", "f16", (4, 5, 6), (5,), "dense<[0, 2]> : tensor<2xi64>"))
+    # dimensions that are not consecutive are reduced group by group (the reference stops at load time:
+    # "Only consecutive dimensions ...", reduce_impl.h:40-42)
+    s.load_from_memory(reduce_mlir("ReduceMaxOp_f16_f16", "f16", (4, 5, 6), (5,), "dense<[0, 2]> : tensor<2xi64>"))
+    # a 16-bit sum may be delivered unrounded as f32; a max may not change the element type
+    s.load_from_memory(reduce_mlir("ReduceSumOp_f16_f32", "f16", (4, 5, 6), (6,), "dense<[0, 1]> : tensor<2xi64>", "f32"))
+    assert s.arg_info(1).dtype == "f32"
+    with pytest.raises(brt.BrtError):
+        s.load_from_memory(reduce_mlir("ReduceMaxOp_f16_f32", "f16", (4, 5, 6), (6,), "dense<[0, 1]> : tensor<2xi64>", "f32"))
     # unsorted dims are fine (resnet18_fw_bw_host_cuda.mlir:178 has dense<[3, 2]>)
     s.load_from_memory(reduce_mlir("ReduceSumOp_f16_f16", "f16", (2, 3, 4, 5), (2, 3), "dense<[3, 2]> : tensor<2xi64>"))
 

@@ -523,11 +523,12 @@ def test_sharded_sum_finish_times_out_instead_of_hanging(ops):
     status = torch.zeros(1, dtype=torch.int32, device="cuda")
     ss = ops.ShardedSum(0, 2, n, [inbox0.data_ptr(), inbox1.data_ptr()], [flags0.data_ptr(), flags1.data_ptr()],
                         counter, status)
-    out = torch.empty(n, dtype=torch.float32, device="cuda")
+    out = torch.full((n,), -7.0, dtype=torch.float32, device="cuda")
     ss(torch.ones(n, device="cuda"), out)
     torch.cuda.synchronize()  # returns after the 2 s limit
     assert int(status.item()) == 3
     assert int(flags1[0].item()) == 1  # rank 0 did publish to its peer
+    assert torch.all(out == -7.0) and int(counter.item()) == 0  # no stale sum written, the epoch did not advance
     assert float(torch.ones(4, device="cuda").sum().item()) == 4.0
 
 
