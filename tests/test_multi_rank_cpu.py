@@ -201,7 +201,7 @@ def _gloo_worker(rank, world, port, q):
 
 def _write(text, rank, tag):
     import tempfile
-    d = Path(tempfile.gettempdir()) / f"byre_all_reduce_{os.getppid()}"
+    d = Path(tempfile.gettempdir()) / f"byre_all_reduce_{os.getpid()}"  # a directory per rank process
     d.mkdir(exist_ok=True)
     p = d / f"rank{rank}_{tag}.mlir"
     p.write_text(text)
