@@ -788,6 +788,25 @@ private:
       op.callee = op.attrs["callee"].s;
       if (op.operands.size() != 2)
         throw Fail("copy_v1 takes a source and a target");
+    } else if (h.name == "group_copy_v1") { // callee; operands: the sources, then as many targets
+      // (compiler/include/byteir/Dialect/Byre/Serialization/ByreSerial.td:407-413, SameVariadicOperandSize:
+      // no segment sizes are stored).  A group copy is its copies, source i -> target i, in order.
+      const std::vector<int> p = ReadProps(h, {false});
+      const std::string callee = Plain((uint64_t)p[0]).s;
+      if (op.operands.empty() || op.operands.size() % 2 != 0)
+        throw Fail("group_copy_v1 takes as many targets as sources");
+      const size_t pairs = op.operands.size() / 2;
+      for (size_t i = 0; i < pairs; ++i) {
+        Operation one;
+        one.name = "byre.copy";
+        one.index = (int)fn->ops.size();
+        one.line = one.index + 1;
+        one.operands = {op.operands[i], op.operands[pairs + i]};
+        one.attrs["callee"] = Plain((uint64_t)p[0]);
+        one.callee = callee;
+        fn->ops.push_back(std::move(one));
+      }
+      return;
     } else {
       throw Fail("byre_serial op " + h.name + " is not supported");
     }

@@ -115,9 +115,14 @@ Status StaticBRTExecutionPlan::ProloguePerSession(const AllocatorMap &allocators
       auto it = def.attrs.find("offset");
       if (it != def.attrs.end())
         offset = it->second.i;
-      // the offset counts elements of the SOURCE memref (runtime/lib/core/ir/op_helper.cc:43-52)
-      loc = {ExecutionFrame::ConstructInfo::TensorLoc::kAlias, src.id,
-             (size_t)offset * GetDTypeByte(src.type.dtype)};
+      // the offset counts elements of the SOURCE memref (runtime/lib/core/ir/op_helper.cc:43-52); a view
+      // that would start before its source or end behind it is a broken module, not a kernel's problem
+      const size_t src_elt = GetDTypeByte(src.type.dtype);
+      if (offset < 0 || (size_t)offset * src_elt + v.type.SizeInBytes() > src.type.SizeInBytes())
+        return Fail(common::INVALID_GRAPH, "byre.alias " + v.name + " (offset " + std::to_string(offset) + ", " +
+                                               std::to_string(v.type.SizeInBytes()) + " bytes) does not fit its source " +
+                                               src.name + " (" + std::to_string(src.type.SizeInBytes()) + " bytes)");
+      loc = {ExecutionFrame::ConstructInfo::TensorLoc::kAlias, src.id, (size_t)offset * src_elt};
     } else {
       return Fail(common::INVALID_GRAPH, "op " + def.name + " defines a value; only memref.alloc and byre.alias may");
     }

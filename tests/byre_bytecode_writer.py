@@ -9,7 +9,7 @@ A module is described as
     {"name": "main", "args": [(argname, argtype, dtype, shape, space), ...],
      "ops": [("alloc", dtype, shape, space) | ("alias", src, offset, dtype, shape, space)
              | ("compute", callee, [operands], {attr: value}, [memory effects] | None)
-             | ("copy", src, dst, callee)]}
+             | ("copy", src, dst, callee) | ("group_copy", [srcs], [dsts], callee)]}
 where operands are value numbers (arguments first, then results in order) and attribute values are
 str, bool, int (i64), ("i32", int), float (f32), ("f64", float), ("dense", dtype, shape, [values]),
 ("array", dtype, [values]), or a list of those.
@@ -182,7 +182,8 @@ def write_module(desc, producer="MLIR17.0.0git", isolated_func=False):
     w = Writer()
     used_ops = ["module_v1", "func_v1"]
     for op in desc["ops"]:
-        name = {"alloc": "alloc_v1", "alias": "alias", "compute": "compute_v1", "copy": "copy_v1"}[op[0]]
+        name = {"alloc": "alloc_v1", "alias": "alias", "compute": "compute_v1", "copy": "copy_v1",
+                "group_copy": "group_copy_v1"}[op[0]]
         if name not in used_ops:
             used_ops.append(name)
     used_ops.append("return_v1")
@@ -223,6 +224,9 @@ def write_module(desc, producer="MLIR17.0.0git", isolated_func=False):
         elif op[0] == "copy":
             _, src, dst, callee = op
             body_ops.append(("copy_v1", 0x44, varint(w.str_attr(callee)), (), (src, dst)))
+        elif op[0] == "group_copy":
+            _, srcs, dsts, callee = op
+            body_ops.append(("group_copy_v1", 0x44, varint(w.str_attr(callee)), (), tuple(srcs) + tuple(dsts)))
     loc = len(w.attrs)  # the builtin unknown location comes last
 
     # IR section: top-level block, module, its region, func, its region and block, the body

@@ -382,3 +382,28 @@ def test_reduce_over_dimensions_that_are_not_consecutive(shape, dims, t, npdt):
     np.testing.assert_allclose(s.astype(np.float64), want, **tol)
     m = _run(reduce_mlir(f"ReduceMaxOp_{t}_{t}", t, shape, out_shape, dims_s), {"Input0": x})["Output0"]
     assert np.array_equal(m, x.max(axis=dims))
+
+
+def test_group_copy_from_bytecode_runs_on_the_gpu(tmp_path):
+    from byre_bytecode_writer import write_module
+    desc = {"name": "main",
+            "args": [("A", 1, "f32", (1000,), "cuda"), ("B", 1, "f16", (33, 7), "cuda"), ("OutA", 2, "f32", (1000,), "cuda"),
+                     ("OutB", 2, "f16", (33, 7), "cuda")],
+            "ops": [("group_copy", [0, 1], [2, 3], "cuda2cuda")]}
+    s = brt.Session("cuda")
+    s.load_from_memory(write_module(desc))
+    a = torch.randn(1000, device="cuda")
+    b = torch.randn(33, 7, device="cuda").half()
+    oa, ob = torch.zeros_like(a), torch.zeros_like(b)
+    req = s.new_request(torch.cuda.current_stream().cuda_stream)
+    for name, t in (("A", a), ("B", b), ("OutA", oa), ("OutB", ob)):
+        req.bind_arg(s.arg_offset(name), t.data_ptr())
+    req.finish_io_binding()
+    req.enable_op_trace()
+    req.run()
+    req.sync()
+    torch.cuda.synchronize()
+    assert torch.equal(oa, a) and torch.equal(ob, b)
+    assert req.op_trace() == ["cuda2cuda", "cuda2cuda"]
+    req.close()
+    s.close()

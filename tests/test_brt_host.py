@@ -117,6 +117,16 @@ def test_alias_offsets_count_source_elements_and_generic_form():
     np.testing.assert_array_equal(out, x[4:8] * 2 + (x[0:4] * 10 + 1))
 
 
+@pytest.mark.parametrize("bad", ["offset = 52 : i64}> {device = \"cpu\"}",  # 52 + 16 bytes > the 64-byte block
+                                 "offset = -1 : i64}> {device = \"cpu\"}"])
+def test_alias_that_does_not_fit_its_source_is_refused_at_load_time(bad):
+    s = brt.Session("cpu")
+    with pytest.raises(brt.BrtError, match="does not fit its source"):
+        s.load_from_memory(ALIAS.replace("offset = 0 : i64}> {device = \"cpu\"}", bad))
+    with pytest.raises(brt.BrtError, match="does not fit its source"):
+        s.load_from_memory(ALIAS.replace("(%arg0) <{offset = 4 : i64}>", "(%arg0) <{offset = 5 : i64}>"))  # 5 + 4 > 8 elements
+
+
 def test_unknown_op_is_reported_like_the_reference():
     s = brt.Session("cpu")
     with pytest.raises(brt.BrtError, match="No providers support Op NoSuchOp_f32"):

@@ -165,3 +165,19 @@ def test_damaged_bytecode_is_an_error_not_a_crash(tmp_path):
             pass
     with pytest.raises(brt.BrtError, match="version"):
         _load(b"ML\xefR" + varint(6) + good[5:], tmp_path, name="v6.mlirbc")
+
+
+def test_group_copy_is_its_copies_in_order(tmp_path):
+    """group_copy_v1 (ByreSerial.td:407-413): sources first, then as many targets; decoded as one byre.copy per
+    pair with the group's callee.  Loaded into a CUDA session (no device needed to load), the plan holds the two
+    cuda2cuda kernels; an odd operand count is an error."""
+    desc = {"name": "main",
+            "args": [("A", 1, "f32", (64,), "cuda"), ("B", 1, "f16", (8, 4), "cuda"), ("OutA", 2, "f32", (64,), "cuda"),
+                     ("OutB", 2, "f16", (8, 4), "cuda")],
+            "ops": [("group_copy", [0, 1], [2, 3], "cuda2cuda")]}
+    s = brt.Session("cuda")
+    s.load_from_memory(write_module(desc))
+    assert [a.name for a in s.args()] == ["A", "B", "OutA", "OutB"]
+    bad = dict(desc, ops=[("group_copy", [0, 1], [2], "cuda2cuda")])
+    with pytest.raises(brt.BrtError, match="as many targets as sources"):
+        brt.Session("cuda").load_from_memory(write_module(bad))
