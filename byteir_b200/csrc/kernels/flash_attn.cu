@@ -1,4 +1,7 @@
-// Flash-attention forward for sm_100a (head dim 128, f16 / bf16, f32 accumulate).
+// Flash-attention forward for sm_100a (head dim up to 128, f16 / bf16, f32 accumulate).  The tiles are
+// 128 head dims wide; a narrower head (a multiple of 8: 32, 64, 96 ...) is the same computation with
+// the missing columns read as zeros and never written, which the tensor maps do by themselves: their
+// innermost extent is the head dim, loads past it fill zeros, stores past it are clipped.
 //
 // Persistent blocks, one per SM.  A block takes query tiles (128 query rows of one (batch,
 // head)) from a static list and, for each, walks over the key/value tiles of 128 rows that
@@ -79,6 +82,7 @@ struct FwdParams {
   int *status;
   uint32_t wait_polls;
   int debug_skip_arrive;
+  int d; // head dim, <= 128
   int64_t H, Hk, Sq, Sk;
   int n_q_tiles, pairs; // query tiles per (batch, head); pairs of them per work item
   int64_t total_items;  // pairs * H * B
@@ -656,7 +660,8 @@ __global__ void __launch_bounds__(kThreads, 1)
       tc_fence_after_sync();
       if (warp == 4 && lane == 0 && !give_up) {
         tma_store_4d(&o_map, sO, 0, w.h, (int)q0, w.b);
-        tma_store_4d(&o_map, sO + kHalfTile, 64, w.h, (int)q0, w.b);
+        if (p.d > 64) // a store that would start past the end of the head is left out
+          tma_store_4d(&o_map, sO + kHalfTile, 64, w.h, (int)q0, w.b);
         bulk_commit();
       }
       if (give_up)
@@ -725,6 +730,7 @@ struct BwdParams {
   int64_t window_left, window_right;
   uint32_t wait_polls;
   int debug_skip_arrive;
+  int d; // head dim, <= 128
 };
 
 struct BwdShared {
@@ -769,13 +775,13 @@ __device__ __forceinline__ uint4 load_tile_chunk(const unsigned char *tile, int 
 __global__ void __launch_bounds__(256)
     bwd_dot_do_o_kernel(const void *__restrict__ dout, const void *__restrict__ out, float *__restrict__ dsum,
                         int64_t B, int64_t H, int64_t Sq, int64_t Sq_rounded, int64_t o_batch_stride,
-                        int64_t o_row_stride, int64_t o_head_stride, bool bf16) {
-  // 16 threads per (b, h, row): 8 elements each of the 128-wide row
+                        int64_t o_row_stride, int64_t o_head_stride, int d, bool bf16) {
+  // 16 threads per (b, h, row): 8 elements each of the row of d <= 128 elements
   const int64_t gid = (int64_t)blockIdx.x * 16 + (threadIdx.x >> 4);
   const int sub = threadIdx.x & 15;
   const int64_t total = B * H * Sq;
   float acc = 0.f;
-  if (gid < total) {
+  if (gid < total && sub * 8 < d) {
     const int64_t row = gid % Sq, h = (gid / Sq) % H, b = gid / (Sq * H);
     const int64_t off = b * o_batch_stride + row * o_row_stride + h * o_head_stride + sub * 8;
     const uint4 a = ld_nc_v4(static_cast<const uint16_t *>(dout) + off);
@@ -1186,10 +1192,12 @@ __global__ void __launch_bounds__(kThreads, 1)
     if (warp == 4 && lane == 0 && ss->failed == 0) {
       if (kDKDV) {
         tma_store_4d(&out1_map, sRes1, 0, head, (int)own0, b);
-        tma_store_4d(&out1_map, sRes1 + kHalfTile, 64, head, (int)own0, b);
+        if (p.d > 64)
+          tma_store_4d(&out1_map, sRes1 + kHalfTile, 64, head, (int)own0, b);
       }
       tma_store_4d(&out0_map, sRes0, 0, head, (int)own0, b);
-      tma_store_4d(&out0_map, sRes0 + kHalfTile, 64, head, (int)own0, b);
+      if (p.d > 64)
+        tma_store_4d(&out0_map, sRes0 + kHalfTile, 64, head, (int)own0, b);
       bulk_commit();
       bulk_wait_all<0>();
     }
@@ -1249,9 +1257,9 @@ extern "C" int b200_flash_attn_fwd(int dtype, const void *q, const void *k, cons
   const b200_flash_attn_params &a = *pp;
   if (dtype != B200_F16 && dtype != B200_BF16)
     return B200_ERR_UNSUPPORTED;
-  if (a.d != kD || a.p_dropout != 0.f || a.h_k <= 0 || a.h % a.h_k != 0 || a.b <= 0 || a.seqlen_q <= 0 ||
+  if (a.d <= 0 || a.d > kD || a.d % 8 != 0 || a.p_dropout != 0.f || a.h_k <= 0 || a.h % a.h_k != 0 || a.b <= 0 || a.seqlen_q <= 0 ||
       a.seqlen_k <= 0)
-    return B200_ERR_UNSUPPORTED; // head dim 128, no dropout
+    return B200_ERR_UNSUPPORTED; // head dim a multiple of 8 up to 128, no dropout
   const int64_t strides[] = {a.q_batch_stride, a.k_batch_stride, a.v_batch_stride, a.o_batch_stride,
                              a.q_row_stride,   a.k_row_stride,   a.v_row_stride,   a.o_row_stride,
                              a.q_head_stride,  a.k_head_stride,  a.v_head_stride,  a.o_head_stride};
@@ -1275,6 +1283,7 @@ extern "C" int b200_flash_attn_fwd(int dtype, const void *q, const void *k, cons
   p.status = nullptr;
   p.wait_polls = g_wait_polls;
   p.debug_skip_arrive = g_debug_skip_arrive;
+  p.d = (int)a.d;
   p.H = a.h;
   p.Hk = a.h_k;
   p.Sq = a.seqlen_q;
@@ -1310,7 +1319,7 @@ extern "C" int b200_flash_attn_bwd(int dtype, const void *dout, const void *q, c
   const b200_flash_attn_params &a = *pp;
   if (dtype != B200_F16 && dtype != B200_BF16)
     return B200_ERR_UNSUPPORTED;
-  if (a.d != kD || a.p_dropout != 0.f || a.h_k <= 0 || a.h % a.h_k != 0 || a.b <= 0 || a.seqlen_q <= 0 ||
+  if (a.d <= 0 || a.d > kD || a.d % 8 != 0 || a.p_dropout != 0.f || a.h_k <= 0 || a.h % a.h_k != 0 || a.b <= 0 || a.seqlen_q <= 0 ||
       a.seqlen_k <= 0 || a.seqlen_q_rounded < a.seqlen_q)
     return B200_ERR_UNSUPPORTED;
   const int64_t strides[] = {a.q_batch_stride, a.k_batch_stride, a.v_batch_stride, a.o_batch_stride,
@@ -1351,7 +1360,7 @@ extern "C" int b200_flash_attn_bwd(int dtype, const void *dout, const void *q, c
   const int64_t rows = a.b * a.h * a.seqlen_q;
   bwd_dot_do_o_kernel<<<(unsigned)ceil_div<int64_t>(rows, 16), 256, 0, stream>>>(
       dout, out, d_softmax_sum, a.b, a.h, a.seqlen_q, a.seqlen_q_rounded, a.o_batch_stride, a.o_row_stride,
-      a.o_head_stride, bf16);
+      a.o_head_stride, (int)a.d, bf16);
   if (int rc = check_launch())
     return rc;
 
@@ -1369,6 +1378,7 @@ extern "C" int b200_flash_attn_bwd(int dtype, const void *dout, const void *q, c
   p.window_right = a.window_size_right;
   p.wait_polls = g_wait_polls;
   p.debug_skip_arrive = g_debug_skip_arrive;
+  p.d = (int)a.d;
   const dim3 grid_kv((unsigned)((a.seqlen_k + 127) / 128), (unsigned)a.h_k, (unsigned)a.b);
   const dim3 grid_q((unsigned)((a.seqlen_q + kBM - 1) / kBM), (unsigned)a.h, (unsigned)a.b);
   int rc = bf16 ? launch_bwd<true, true>(k_map, v_map, q64_map, do64_map, dk_map, dv_map, p, grid_kv, stream)

@@ -17,6 +17,11 @@ It also copies the reference's one ByRE bytecode fixture (runtime/test/test_file
 Case0_v1_0_0/entry.mlirbc, 447 bytes, byre_serial 1.0.0 in an MLIR 17 container) to
 byre_serial_v1_lljit_case0.mlirbc; its text twin is LLJIT/Case0/entry.mlir.
 
+The reference's three flash-attention test modules (runtime/test/test_files/flash_attn_fwd.mlir,
+flash_attn_bwd.mlir, flash_attn_kvcache.mlir: a few lines of ByRE text each, with the packed
+`extra_args` the compiler writes for the custom call) are copied as fixtures too, so that the GPU
+tests run the reference's own modules, not restatements of them.
+
 Run where a checkout of the reference is at hand:
     python tests/golden/make_flash_attn_golden.py <path to the byteir checkout>
 """
@@ -71,6 +76,11 @@ def kvcache(src: Path) -> None:
 def main(ref_root: str) -> None:
     src = Path(ref_root) / "runtime" / "test" / "test_files"
     kvcache(src)
+    for name in ("flash_attn_fwd.mlir", "flash_attn_bwd.mlir", "flash_attn_kvcache.mlir"):
+        text = (src / name).read_text()
+        assert "byre.custom" in text and "libflash_attn.so" in text, name
+        Path(__file__).with_name(name).write_text(text)
+        print("copied", name, len(text), "bytes")
     bc = (src / "LLJIT" / "Case0_v1_0_0" / "entry.mlirbc").read_bytes()
     assert bc[:4] == b"ML\xefR"
     Path(__file__).with_name("byre_serial_v1_lljit_case0.mlirbc").write_bytes(bc)

@@ -407,3 +407,44 @@ def test_group_copy_from_bytecode_runs_on_the_gpu(tmp_path):
     assert req.op_trace() == ["cuda2cuda", "cuda2cuda"]
     req.close()
     s.close()
+
+
+def test_the_references_own_attention_modules_run_unchanged(tmp_path, monkeypatch):
+    """runtime/test/test_files/flash_attn_fwd.mlir and flash_attn_bwd.mlir, byte for byte (head dim 32, fp16, the
+    library named by a path relative to the working directory, as the compiler writes it), with the reference's
+    vectors: what flash_attn_fwd_test.cc and flash_attn_bwd_test.cc do"""
+    from pathlib import Path
+    golden = Path(__file__).resolve().parent / "golden"
+    libdir = tmp_path / "test" / "test_files" / "external_libs"
+    libdir.mkdir(parents=True)
+    (libdir / "libflash_attn.so").symlink_to(golden.parent.parent / "byteir_b200" / "_lib" / "libflash_attn.so")
+    monkeypatch.chdir(tmp_path)
+    g = np.load(golden / "flash_attn_b1_s128_h3_d32_f16.npz")
+    names = {"Q": "q", "K": "k", "V": "v", "d_Out": "dout"}
+    for module in ("flash_attn_fwd.mlir", "flash_attn_bwd.mlir"):
+        s = brt.Session("cuda")
+        s.load(str(golden / module))
+        req = s.new_request(torch.cuda.current_stream().cuda_stream)
+        held = {}
+        for a in s.args():
+            if a.name in names:
+                t = torch.from_numpy(g[names[a.name]]).cuda()
+            else:
+                t = torch.zeros(a.nbytes, dtype=torch.uint8, device="cuda")
+            assert t.numel() * t.element_size() == a.nbytes
+            held[a.name] = t
+            req.bind_arg(a.offset, t.data_ptr())
+        req.finish_io_binding()
+        req.run()
+        req.sync()
+        torch.cuda.synchronize()
+        view = lambda n: held[n].view(torch.float16).reshape(1, 128, 3, 32).cpu().numpy()
+        key = lambda x: np.where(x.view(np.uint16) & 0x8000, -(x.view(np.uint16).astype(np.int32) & 0x7fff),
+                                 x.view(np.uint16).astype(np.int32))
+        assert np.abs(key(view("Out")) - key(g["out"])).max() <= 1
+        if module == "flash_attn_bwd.mlir":
+            for arg, name in (("d_Q", "dq"), ("d_K", "dk"), ("d_V", "dv")):
+                np.testing.assert_allclose(view(arg).astype(np.float32), g[name].astype(np.float32), rtol=2e-2, atol=1e-2,
+                                           err_msg=name)
+        req.close()
+        s.close()

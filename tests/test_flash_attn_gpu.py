@@ -344,3 +344,53 @@ def test_kernels_with_large_shared_memory_on_a_second_device():
             torch.cuda.synchronize()
             np.testing.assert_allclose(O.to_f32(_host(o)), O.to_f32(want_o), rtol=2e-2, atol=1e-2)
             assert np.array_equal(g.cpu().numpy(), table[idx])
+
+
+# ---- head dims below 128, and the reference's own vectors on the training kernels ---------------------------
+GOLDEN = __import__("pathlib").Path(__file__).parent / "golden" / "flash_attn_b1_s128_h3_d32_f16.npz"
+
+
+def _ulp_f16(a, b):
+    key = lambda x: np.where(x.view(np.uint16) & 0x8000, -(x.view(np.uint16).astype(np.int32) & 0x7fff),
+                             x.view(np.uint16).astype(np.int32))
+    return np.abs(key(a) - key(b))
+
+
+def test_flash_attn_training_kernels_on_the_reference_golden_vectors():
+    """b1 s128 h3 d32 fp16 causal scale 0.5 (flash_attn_fwd_test.cc / flash_attn_bwd_test.cc): the forward within one
+    fp16 step of the reference's output, the gradients within the 16-bit tolerance and a median distance of at most
+    one fp16 step"""
+    from byteir_b200 import ops
+    g = np.load(GOLDEN)
+    q, k, v, do = (_dev(g[n]) for n in ("q", "k", "v", "dout"))
+    o, lse = ops.flash_attn_fwd(q, k, v, 0.5, True)
+    torch.cuda.synchronize()
+    ulp = _ulp_f16(_host(o), g["out"])
+    assert ulp.max() <= 1 and (ulp == 0).mean() > 0.95, (ulp.max(), (ulp == 0).mean())
+    dq, dk, dv = ops.flash_attn_bwd(do, q, k, v, _dev(g["out"]), lse, 0.5, True)
+    torch.cuda.synchronize()
+    for name, got in (("dq", dq), ("dk", dk), ("dv", dv)):
+        np.testing.assert_allclose(_host(got).astype(np.float32), g[name].astype(np.float32), rtol=2e-2, atol=1e-2,
+                                   err_msg=name)
+        assert np.median(_ulp_f16(_host(got), g[name])) <= 1, name
+
+
+@pytest.mark.parametrize("dt", ["bf16", "f16"])
+@pytest.mark.parametrize("d", [32, 64, 96, 8, 120])
+@pytest.mark.parametrize("b,sq,sk,h,hk,causal", [(2, 300, 300, 4, 2, True), (1, 384, 640, 2, 2, False)])
+def test_flash_attn_head_dims_below_128(b, sq, sk, h, hk, causal, d, dt):
+    from byteir_b200 import ops
+    rng = np.random.default_rng(d + sq)
+    q, k, v = _mk(rng, (b, sq, h, d), dt), _mk(rng, (b, sk, hk, d), dt), _mk(rng, (b, sk, hk, d), dt)
+    do = _mk(rng, (b, sq, h, d), dt)
+    scale = 1.0 / np.sqrt(d)
+    want_o, want_lse = O.flash_attn_fwd(q, k, v, scale, causal)
+    qd, kd, vd, dod = _dev(q), _dev(k), _dev(v), _dev(do)
+    o, lse = ops.flash_attn_fwd(qd, kd, vd, scale, causal)
+    dq, dk, dv = ops.flash_attn_bwd(dod, qd, kd, vd, o, lse, scale, causal)
+    torch.cuda.synchronize()
+    np.testing.assert_allclose(lse.cpu().numpy(), want_lse, rtol=1e-3, atol=1e-3)
+    np.testing.assert_allclose(O.to_f32(_host(o)), O.to_f32(want_o), rtol=2e-2, atol=1e-2)
+    wq, wk, wv = O.flash_attn_bwd(do, q, k, v, _host(o), lse.cpu().numpy(), scale, causal)
+    for name, got, want in (("dq", dq, wq), ("dk", dk, wk), ("dv", dv, wv)):
+        np.testing.assert_allclose(O.to_f32(_host(got)), O.to_f32(want), rtol=2e-2, atol=1e-2, err_msg=name)
