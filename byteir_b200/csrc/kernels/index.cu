@@ -274,6 +274,15 @@ __global__ void __launch_bounds__(32)
   }
   __syncwarp();
   const int64_t my_tiles = (num_tiles - blockIdx.x + gridDim.x - 1) / gridDim.x;
+  // the index words of the first tiles, on their way into L2 while the kernel in front of this one ends
+  pdl_launch_dependents();
+  for (int64_t k = 0; k < my_tiles && k < kGatherStages - 1; ++k) {
+    const int64_t tile = blockIdx.x + k * gridDim.x;
+    const int64_t ob0 = (tile % tiles_per_a) * rows_per_tile;
+    if (lane * 16 < rows_per_tile * (int)sizeof(IdxT) && ob0 + lane * (16 / (int)sizeof(IdxT)) < OB)
+      prefetch_l2(reinterpret_cast<const char *>(idx + ob0) + lane * 16);
+  }
+  pdl_wait();
 
   auto issue = [&](int64_t k) {
     const int64_t tile = blockIdx.x + k * gridDim.x;
@@ -424,10 +433,8 @@ int launch_gather(int path, const void *in, const void *idx, void *out, int64_t 
       return rc;
     const int ctas_per_sm = (int)std::max<size_t>(1, std::min<size_t>(8, (200 * 1024) / (smem + 1024)));
     const unsigned grid = (unsigned)std::min<int64_t>(num_tiles, (int64_t)kNumSMs * ctas_per_sm);
-    gather_rows_g4_kernel<IdxT><<<grid, 32, smem, stream>>>(map, (const IdxT *)idx, (char *)out, IB, OB, total_rows,
-                                                            (uint32_t)row_bytes, rows_per_tile, tiles_per_a,
-                                                            num_tiles, status);
-    return check_launch();
+    return launch_pdl(gather_rows_g4_kernel<IdxT>, dim3(grid), dim3(32), smem, stream, map, (const IdxT *)idx, (char *)out,
+                      IB, OB, total_rows, (uint32_t)row_bytes, rows_per_tile, tiles_per_a, num_tiles, status);
   }
   if (both % 16 == 0)
     return launch_gather_generic<uint4, IdxT>(in, idx, out, A, IB, OB, row_bytes, status, stream);

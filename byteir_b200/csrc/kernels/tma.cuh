@@ -120,6 +120,11 @@ __device__ __forceinline__ void tma_gather4_2d(void *smem_dst, const CUtensorMap
                "l"(map), "r"(x), "r"(r0), "r"(r1), "r"(r2), "r"(r3), "r"(smem_addr(bar))
                : "memory");
 }
+// the tile's lines into L2, nothing into shared memory, nothing to wait for
+__device__ __forceinline__ void tma_prefetch_3d(const CUtensorMap *map, int x, int y, int z) {
+  asm volatile("cp.async.bulk.prefetch.tensor.3d.L2.global.tile [%0, {%1, %2, %3}];" ::"l"(map), "r"(x), "r"(y), "r"(z)
+               : "memory");
+}
 __device__ __forceinline__ void tma_store_3d(const CUtensorMap *map, const void *smem_src, int x,
                                              int y, int z) {
   asm volatile("cp.async.bulk.tensor.3d.global.shared::cta.tile.bulk_group [%0, {%2, %3, %4}], [%1];" ::

@@ -78,6 +78,18 @@ __global__ void __launch_bounds__(256)
     tma_load_3d(in_tile + s * kInBytes, &in_map, tc * TC, tr * TR, b, &full[s]);
   };
 
+  // The first tiles of this block are hinted into L2 before the wait for the kernel in front of this
+  // one (a hint returns nothing, and L2 is the point of coherence, so it is harmless even if that kernel
+  // is still writing the input): the DRAM fetch then overlaps the other kernel's tail.
+  pdl_launch_dependents();
+  if (threadIdx.x == 0) {
+    for (int64_t k = 0; k < my_tiles && k < 2; ++k) {
+      int b, tr, tc;
+      coords(k, b, tr, tc);
+      tma_prefetch_3d(&in_map, tc * TC, tr * TR, b);
+    }
+  }
+  pdl_wait();
   if (threadIdx.x == 0 && my_tiles > 0)
     issue_load(0);
 
@@ -174,9 +186,8 @@ int launch_tma(const void *in, void *out, int64_t batch, int64_t rows, int64_t c
   const int64_t num_tiles = (int64_t)tiles_c * tiles_r * batch;
   const size_t smem = (size_t)kInStages * TR * 128 + (size_t)kOutStages * TC * TR * ES + 1024;
   const unsigned grid = (unsigned)std::min<int64_t>(num_tiles, (int64_t)kNumSMs * 6);
-  transpose_tma_kernel<ES><<<grid, 256, smem, stream>>>(in_map, out_map, tiles_c, tiles_r, num_tiles,
-                                                        nullptr);
-  return check_launch();
+  return launch_pdl(transpose_tma_kernel<ES>, dim3(grid), dim3(256), smem, stream, in_map, out_map, tiles_c, tiles_r,
+                    num_tiles, (int *)nullptr);
 }
 
 // =============================================================================
