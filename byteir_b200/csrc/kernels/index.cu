@@ -487,13 +487,24 @@ __global__ void __launch_bounds__(256)
     sh[d] = 0;
   __syncthreads();
   const int64_t base = (int64_t)blockIdx.x * kSortTile;
-  for (int k = 0; k < kSortTile / 256; ++k) {
+  const uint32_t lt = (1u << (threadIdx.x & 31)) - 1u;
+  uint32_t digit[kSortTile / 256];
+#pragma unroll
+  for (int k = 0; k < kSortTile / 256; ++k) { // all loads first
     const int64_t i = base + k * 256 + threadIdx.x;
+    digit[k] = 0xffffffffu;
     if (i < n) {
       const uint32_t key = key_of_index(idx[i], rows, status);
       keys[i] = key;
-      atomicAdd(&sh[key & (radix - 1)], 1u);
+      digit[k] = key & (uint32_t)(radix - 1);
     }
+  }
+#pragma unroll
+  for (int k = 0; k < kSortTile / 256; ++k) {
+    // one atomic per distinct digit of the warp: a hot row would otherwise queue up on one counter
+    const uint32_t peers = __match_any_sync(0xffffffffu, digit[k]);
+    if (digit[k] != 0xffffffffu && (peers & lt) == 0)
+      atomicAdd(&sh[digit[k]], (uint32_t)__popc(peers));
   }
   __syncthreads();
   for (int d = threadIdx.x; d < radix; d += 256)
@@ -637,7 +648,12 @@ __global__ void __launch_bounds__(256)
 // persistent copy grid that keeps only the bandwidth-delay product in flight, 2 .. 16 blocks per
 // SM, made the whole op slower, 147 .. 165 us against 139 us: a kernel without shared memory
 // that never leaves its SMs also keeps kernels with another shared-memory carve-out from
-// starting on them until it ends.)
+// starting on them until it ends.  What slows the sort beside the copy is queueing: the copy keeps
+// about 37 MB in flight, which at the copy's own bandwidth is 5 .. 6 us in front of every access of the
+// sort's chain of dependent accesses.  Also measured and not kept: the accumulate passes beside the copy
+// with the copy leaving out the rows that some index names, 144 .. 165 us against 141 .. 145 us; the sort
+// as one kernel in a cluster of 16 blocks that keeps the list in distributed shared memory, 80 .. 90 us
+// alone against 50 us for the chain of kernels: scattered 8-byte stores from 16 SMs only.)
 struct alignas(32) Vec32 {
   uint64_t a, b, c, d;
 };
@@ -654,17 +670,18 @@ __device__ __forceinline__ void st_stream_v32(Vec32 *p, const Vec32 &v) {
                : "memory");
 }
 
-// 256 threads, four 32-byte vectors each
-__global__ void __launch_bounds__(256)
+// 1024 threads, four 32-byte vectors each (blocks of 256 threads measured 3 % slower on the whole op)
+constexpr int kCopyThreads = 1024;
+__global__ void __launch_bounds__(kCopyThreads)
     copy_table_kernel(const Vec32 *__restrict__ in, Vec32 *__restrict__ out, int64_t nvec) {
-  const int64_t i = (int64_t)blockIdx.x * 1024 + threadIdx.x;
-  if (i + 3 * 256 < nvec) {
-    const Vec32 a = ld_stream_v32(in + i), b = ld_stream_v32(in + i + 256), c = ld_stream_v32(in + i + 512),
-                d = ld_stream_v32(in + i + 768);
-    st_stream_v32(out + i, a), st_stream_v32(out + i + 256, b), st_stream_v32(out + i + 512, c),
-        st_stream_v32(out + i + 768, d);
+  const int64_t i = (int64_t)blockIdx.x * (4 * kCopyThreads) + threadIdx.x;
+  if (i + 3 * kCopyThreads < nvec) {
+    const Vec32 a = ld_stream_v32(in + i), b = ld_stream_v32(in + i + kCopyThreads),
+                c = ld_stream_v32(in + i + 2 * kCopyThreads), d = ld_stream_v32(in + i + 3 * kCopyThreads);
+    st_stream_v32(out + i, a), st_stream_v32(out + i + kCopyThreads, b), st_stream_v32(out + i + 2 * kCopyThreads, c),
+        st_stream_v32(out + i + 3 * kCopyThreads, d);
   } else {
-    for (int64_t k = 0, j = i; k < 4; ++k, j += 256)
+    for (int64_t k = 0, j = i; k < 4; ++k, j += kCopyThreads)
       if (j < nvec)
         out[j] = in[j];
   }
@@ -1289,7 +1306,7 @@ int scatter_add(const T *in, const int64_t *idx, const T *upd, T *out, int64_t r
     cudaStream_t stream = user_stream; // the copy always runs on the caller's stream
     if (table_bytes % 32 == 0 && ((reinterpret_cast<uintptr_t>(in) | reinterpret_cast<uintptr_t>(out)) & 31u) == 0) {
       const int64_t nvec = (int64_t)(table_bytes / 32);
-      copy_table_kernel<<<(unsigned)ceil_div<int64_t>(nvec, 1024), 256, 0, stream>>>(
+      copy_table_kernel<<<(unsigned)ceil_div<int64_t>(nvec, 4 * kCopyThreads), kCopyThreads, 0, stream>>>(
           (const Vec32 *)in, (Vec32 *)out, nvec);
       if (int rc = check_launch())
         return rc;

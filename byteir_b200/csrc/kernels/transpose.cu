@@ -25,8 +25,15 @@ namespace {
 // =============================================================================
 // TMA path
 // =============================================================================
-constexpr int kInStages = 2;
+constexpr int kMaxInStages = 6;
 constexpr int kOutStages = 2;
+// Input tiles a block keeps in its ring (loads run in_stages - 1 tiles ahead), blocks per SM of the
+// persistent grid, and the width of a panel of the tile order; 0 = the rule in launch_tma.
+// b200_transpose_tune sets them for measurements.  Measured (TB/s of bytes read + written; ring depth /
+// blocks per SM): bf16 8192 x 8192: 2/6 4.3, 3/5 5.2, 4/4 5.4; f16 [32] x 128 x 4096: 2/6 4.2, 3/5 6.4,
+// 4/4 6.2; f32 4096 x 4096: 2/6 3.1, 3/5 4.9, 4/4 4.0; f16 1000 x 30000 (panels of 16): 3/5 5.6, 4/4 5.9,
+// row-major order 4.5 / 4.8.
+int g_in_stages = 0, g_blocks_per_sm = 0, g_panel = 0;
 
 // byte offset of 16-byte chunk `chunk` (0..7) of tile row `row` in the 128-byte
 // swizzled layout the TMA unit reads and writes
@@ -38,7 +45,7 @@ template <int ES> // element size: 2 or 4
 __global__ void __launch_bounds__(256)
     transpose_tma_kernel(const __grid_constant__ CUtensorMap in_map,
                          const __grid_constant__ CUtensorMap out_map, int tiles_c, int tiles_r,
-                         int64_t num_tiles, int *error) {
+                         int64_t num_tiles, int in_stages, int panel, int *error) {
   constexpr int TC = 128 / ES; // tile columns = elements per 128-byte row
   constexpr int TR = ES == 2 ? 64 : 32;
   constexpr uint32_t kInBytes = TR * 128;  // TR rows of 128 bytes
@@ -49,33 +56,49 @@ __global__ void __launch_bounds__(256)
   unsigned char *smem = reinterpret_cast<unsigned char *>(
       (reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
   unsigned char *in_tile = smem;
-  unsigned char *out_tile = smem + kInStages * kInBytes;
-  __shared__ uint64_t full[kInStages];
+  unsigned char *out_tile = smem + in_stages * kInBytes;
+  __shared__ uint64_t full[kMaxInStages];
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   if (threadIdx.x == 0) {
     prefetch_tensormap(&in_map);
     prefetch_tensormap(&out_map);
-    for (int s = 0; s < kInStages; ++s)
+    for (int s = 0; s < in_stages; ++s)
       mbar_init(&full[s], 1);
     mbar_fence_init();
   }
   __syncthreads();
 
   const int64_t my_tiles = (num_tiles - blockIdx.x + gridDim.x - 1) / gridDim.x;
+  // Tile order inside one matrix: panels of `panel` tile columns, row-major inside a panel.  The tiles
+  // in flight at one time (a contiguous range of the order) then cover a roughly square region, so that
+  // the loads AND the stores fall on a few kilobytes of every memory row they touch; in plain row-major
+  // order the stores of the tiles in flight are 128-byte pieces of thousands of output rows.
+  const int per_matrix = tiles_c * tiles_r;
+  const int full_panels = tiles_c / panel;
   auto coords = [&](int64_t k, int &b, int &tr, int &tc) {
     const int64_t tile = blockIdx.x + k * gridDim.x;
-    tc = (int)(tile % tiles_c);
-    const int64_t rest = tile / tiles_c;
-    tr = (int)(rest % tiles_r);
-    b = (int)(rest / tiles_r);
+    b = (int)(tile / per_matrix);
+    const int t = (int)(tile - (int64_t)b * per_matrix);
+    const int p = min(t / (panel * tiles_r), full_panels);
+    const int width = p < full_panels ? panel : tiles_c - full_panels * panel;
+    const int u = t - p * panel * tiles_r;
+    tr = u / width;
+    tc = p * panel + u - tr * width;
   };
-  auto issue_load = [&](int64_t k) {
-    int b, tr, tc;
-    coords(k, b, tr, tc);
-    const int s = (int)(k % kInStages);
-    mbar_arrive_expect_tx(&full[s], kInBytes);
-    tma_load_3d(in_tile + s * kInBytes, &in_map, tc * TC, tr * TR, b, &full[s]);
+  // Thread 0 issues the loads and thread 32 the stores.  Each works out the coordinates of its next
+  // tile (a few integer divisions) while it would otherwise wait, so that no division sits between the
+  // arrival of a tile and the issue of the next load.
+  int nb = 0, ntr = 0, ntc = 0; // thread 0: coordinates of the next tile to load
+  int64_t next_load = 0;
+  int load_stage = 0; // stage of the next load (counted, not divided: the ring depth is a run-time value)
+  auto issue_next = [&]() {
+    mbar_arrive_expect_tx(&full[load_stage], kInBytes);
+    tma_load_3d(in_tile + load_stage * kInBytes, &in_map, ntc * TC, ntr * TR, nb, &full[load_stage]);
+    load_stage = load_stage + 1 == in_stages ? 0 : load_stage + 1;
+    ++next_load;
+    if (next_load < my_tiles)
+      coords(next_load, nb, ntr, ntc);
   };
 
   // The first tiles of this block are hinted into L2 before the wait for the kernel in front of this
@@ -88,26 +111,35 @@ __global__ void __launch_bounds__(256)
       coords(k, b, tr, tc);
       tma_prefetch_3d(&in_map, tc * TC, tr * TR, b);
     }
+    if (my_tiles > 0)
+      coords(0, nb, ntr, ntc);
   }
   pdl_wait();
-  if (threadIdx.x == 0 && my_tiles > 0)
-    issue_load(0);
+  const int ahead = in_stages - 1;
+  if (threadIdx.x == 0)
+    for (int64_t k = 0; k < my_tiles && k < ahead; ++k)
+      issue_next();
 
+  int s = 0;          // stage of tile k
+  uint32_t phase = 0; // parity of its barrier
   for (int64_t k = 0; k < my_tiles; ++k) {
-    const int s = (int)(k % kInStages);
     const int so = (int)(k % kOutStages);
-    if (threadIdx.x == 0)
+    int sb = 0, str = 0, stc = 0; // thread 32: where tile k goes
+    if (threadIdx.x == 32) {
       bulk_wait_read<kOutStages - 1>(); // the store that last read out_tile[so] is done
-    const bool arrived = mbar_wait(&full[s], (uint32_t)((k / kInStages) & 1));
+      coords(k, sb, str, stc);
+    }
+    const bool arrived = mbar_wait(&full[s], phase);
     // block-wide agreement (and the barrier after which tile k-1's input stage
-    // may be refilled): if the tile never arrived, all threads leave together
+    // may be refilled, which is where tile k + ahead goes): if the tile never arrived,
+    // all threads leave together
     if (!__syncthreads_and(arrived)) {
       if (error)
         *error = 2;
       break;
     }
-    if (threadIdx.x == 0 && k + 1 < my_tiles)
-      issue_load(k + 1);
+    if (threadIdx.x == 0 && next_load < my_tiles)
+      issue_next();
 
     const unsigned char *src = in_tile + s * kInBytes;
     unsigned char *dst = out_tile + so * kOutBytes;
@@ -148,14 +180,16 @@ __global__ void __launch_bounds__(256)
     }
     fence_proxy_async_smem();
     __syncthreads();
-    if (threadIdx.x == 0) {
-      int b, tr, tc;
-      coords(k, b, tr, tc);
-      tma_store_3d(&out_map, dst, tr * TR, tc * TC, b);
+    if (threadIdx.x == 32) {
+      tma_store_3d(&out_map, dst, str * TR, stc * TC, sb);
       bulk_commit();
     }
+    if (++s == in_stages) {
+      s = 0;
+      phase ^= 1u;
+    }
   }
-  if (threadIdx.x == 0)
+  if (threadIdx.x == 32)
     bulk_wait_all<0>();
 }
 
@@ -184,10 +218,20 @@ int launch_tma(const void *in, void *out, int64_t batch, int64_t rows, int64_t c
   const int tiles_c = (int)ceil_div<int64_t>(cols, TC);
   const int tiles_r = (int)ceil_div<int64_t>(rows, TR);
   const int64_t num_tiles = (int64_t)tiles_c * tiles_r * batch;
-  const size_t smem = (size_t)kInStages * TR * 128 + (size_t)kOutStages * TC * TR * ES + 1024;
-  const unsigned grid = (unsigned)std::min<int64_t>(num_tiles, (int64_t)kNumSMs * 6);
+  // large matrices of 2-byte elements: four tiles in the ring and four blocks per SM; everything else
+  // three and five
+  const bool deep = ES == 2 && (int64_t)tiles_c * tiles_r >= 4096;
+  const int in_stages = g_in_stages > 0 ? std::max(2, std::min(g_in_stages, kMaxInStages)) : (deep ? 4 : 3);
+  const int blocks_per_sm = g_blocks_per_sm > 0 ? g_blocks_per_sm : (deep ? 4 : 5);
+  const int panel = std::max(1, std::min(g_panel > 0 ? g_panel : 16, tiles_c));
+  const size_t smem = (size_t)in_stages * TR * 128 + (size_t)kOutStages * TC * TR * ES + 1024;
+  // the attribute belongs to the current device's context: set on every call (a host-side table write)
+  if (int rc = check_cuda(cudaFuncSetAttribute(transpose_tma_kernel<ES>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                               (int)smem)))
+    return rc;
+  const unsigned grid = (unsigned)std::min<int64_t>(num_tiles, (int64_t)kNumSMs * blocks_per_sm);
   return launch_pdl(transpose_tma_kernel<ES>, dim3(grid), dim3(256), smem, stream, in_map, out_map, tiles_c, tiles_r,
-                    num_tiles, (int *)nullptr);
+                    num_tiles, in_stages, panel, (int *)nullptr);
 }
 
 // =============================================================================
@@ -269,6 +313,12 @@ int launch_permute_plain(const void *in, void *out, const PermuteDims &d, int64_
 } // namespace b200
 
 using namespace b200;
+
+extern "C" void b200_transpose_tune(int in_stages, int blocks_per_sm, int panel) {
+  g_panel = panel;
+  g_in_stages = in_stages;
+  g_blocks_per_sm = blocks_per_sm;
+}
 
 extern "C" int b200_transpose_batched_path(int path, int elt_bytes, const void *in, void *out,
                                            int64_t batch, int64_t rows, int64_t cols,
