@@ -378,10 +378,19 @@ class ReduceC2(Workload):
         self.sharded = None
         if self.world > 1:
             self.exchange = "nccl all-reduce + cast"
-            if os.environ.get("B200_EXCHANGE", "peer") == "peer":
+            if os.environ.get("B200_EXCHANGE", "peer") in ("peer", "switch"):
                 try:
                     self._setup_peer_exchange(torch, ops, N)
                     self.exchange = "b200_sharded_sum_finish (one kernel over NVLink peer memory)"
+                    if os.environ.get("B200_EXCHANGE") == "switch":  # measurement: the sum taken inside the NVSwitch
+                        buf, hdl = self._symm
+                        mc = int(hdl.multicast_ptr)
+                        if not mc:
+                            raise RuntimeError("no multicast mapping of the symmetric buffer")
+                        ptrs = [int(p) for p in hdl.buffer_ptrs]
+                        self.sharded = ops.ShardedSumSwitch(self.rank, self.world, 1024, ptrs[self.rank], mc,
+                                                            [p + self._flag_off for p in ptrs], self.counter, self.status)
+                        self.exchange = "b200_sharded_sum_finish_nvls (multimem.ld_reduce through the NVSwitch)"
                 except Exception as e:  # symmetric memory unavailable: keep NCCL
                     print(f"peer-memory exchange unavailable ({type(e).__name__}: {e}); using NCCL", file=sys.stderr)
 

@@ -80,6 +80,7 @@ EXTRA = {
     "b200_flash_attn_kvcache_tune": (None, [_int]),
     "b200_reduce_cols_plan_override": (None, [_int]),
     "b200_index_put_tune": (None, [_int]),
+    "b200_sharded_sum_finish_nvls": (_int, [_int, _vp, _vp, _vp, C.POINTER(_vp), _int, _int, _i64, _vp, _vp, _vp, _vp]),
     "b200_transpose_tune": (None, [_int, _int, _int]),
     "b200_reduce_tune": (None, [_int, _int, _int, _int]),
     "b200_flash_attn_debug": (None, [_int, C.c_uint]),

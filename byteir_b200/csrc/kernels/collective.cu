@@ -108,6 +108,65 @@ __global__ void __launch_bounds__(1024)
     *epoch_counter = epoch;
 }
 
+
+// The same exchange with the sum taken inside the NVSwitch: every device stores its partials into its
+// OWN slot of symmetric memory, publishes its epoch to the peers and waits for theirs as above, and
+// then reads the slot through the multicast address with multimem.ld_reduce, which returns the sum of
+// all devices' copies.  One flag round and one switch round trip instead of world pushes and a fold;
+// the order of the additions is the switch's, the same for every device and every call.
+//   own_slots: this device's float[2][n] in symmetric memory; mc_slots: the multicast address of the
+//   same range (bound to all `world` devices).
+template <typename OutT>
+__global__ void __launch_bounds__(1024)
+    sharded_sum_finish_nvls_kernel(const float *__restrict__ partial, float *own_slots, const float *mc_slots,
+                                   PeerTable peers, int rank, int world, int64_t n, uint32_t *epoch_counter,
+                                   OutT *__restrict__ out, int *status, uint64_t timeout_ns) {
+  __shared__ uint32_t s_epoch;
+  __shared__ int s_timed_out;
+  if (threadIdx.x == 0) {
+    s_epoch = *epoch_counter + 1;
+    s_timed_out = 0;
+  }
+  __syncthreads();
+  const uint32_t epoch = s_epoch;
+  const size_t slot_off = (size_t)(epoch & 1u) * n;
+  const int64_t nv = n >> 2; // n % 4 == 0, checked by the caller
+  for (int64_t i = threadIdx.x; i < nv; i += blockDim.x)
+    reinterpret_cast<float4 *>(own_slots + slot_off)[i] = reinterpret_cast<const float4 *>(partial)[i];
+  __threadfence_system();
+  __syncthreads();
+  if (threadIdx.x < world) {
+    st_release_sys(peers.flags[threadIdx.x] + rank, epoch);
+    const uint32_t *mine = peers.flags[rank] + threadIdx.x;
+    const uint64_t t0 = global_timer_ns();
+    while ((int32_t)(ld_acquire_sys(mine) - epoch) < 0) {
+      if (global_timer_ns() - t0 > timeout_ns) {
+        s_timed_out = 1;
+        break;
+      }
+    }
+  }
+  __syncthreads();
+  if (s_timed_out) {
+    if (threadIdx.x == 0 && status)
+      *status = 3;
+    return;
+  }
+  for (int64_t i = threadIdx.x; i < nv; i += blockDim.x) {
+    float4 v;
+    asm volatile("multimem.ld_reduce.relaxed.sys.global.add.v4.f32 {%0,%1,%2,%3}, [%4];"
+                 : "=f"(v.x), "=f"(v.y), "=f"(v.z), "=f"(v.w)
+                 : "l"(mc_slots + slot_off + 4 * i)
+                 : "memory");
+    out[4 * i + 0] = Elt<OutT>::from_f32(v.x);
+    out[4 * i + 1] = Elt<OutT>::from_f32(v.y);
+    out[4 * i + 2] = Elt<OutT>::from_f32(v.z);
+    out[4 * i + 3] = Elt<OutT>::from_f32(v.w);
+  }
+  if (threadIdx.x == 0)
+    *epoch_counter = epoch;
+}
+
 } // namespace
 } // namespace b200
 
@@ -149,6 +208,41 @@ extern "C" int b200_sharded_sum_finish(int dtype, const float *partial, void *co
   case B200_BF16:
     sharded_sum_finish_kernel<__nv_bfloat16><<<1, 1024, 0, stream>>>(partial, t, rank, world, n, epoch_counter,
                                                                       (__nv_bfloat16 *)out, status, timeout_ns, vec4);
+    break;
+  default:
+    return B200_ERR_INVALID_ARG;
+  }
+  return check_launch();
+}
+
+
+extern "C" int b200_sharded_sum_finish_nvls(int dtype, const float *partial, float *own_slots,
+                                            const float *multicast_slots, void *const *peer_flags, int rank,
+                                            int world, int64_t n, uint32_t *epoch_counter, void *out, int *status,
+                                            cudaStream_t stream) {
+  if (world <= 0 || world > kMaxWorld || rank < 0 || rank >= world || n <= 0 || n % 4 != 0 || !partial ||
+      !own_slots || !multicast_slots || !peer_flags || !epoch_counter || !out || !aligned16(partial) ||
+      !aligned16(own_slots) || !aligned16(multicast_slots))
+    return B200_ERR_INVALID_ARG;
+  PeerTable t{};
+  for (int p = 0; p < world; ++p) {
+    if (!peer_flags[p])
+      return B200_ERR_INVALID_ARG;
+    t.flags[p] = static_cast<uint32_t *>(peer_flags[p]);
+  }
+  const uint64_t timeout_ns = 2000000000ull; // 2 s
+  switch (dtype) {
+  case B200_F32:
+    sharded_sum_finish_nvls_kernel<float><<<1, 1024, 0, stream>>>(partial, own_slots, multicast_slots, t, rank, world, n,
+                                                                   epoch_counter, (float *)out, status, timeout_ns);
+    break;
+  case B200_F16:
+    sharded_sum_finish_nvls_kernel<__half><<<1, 1024, 0, stream>>>(partial, own_slots, multicast_slots, t, rank, world,
+                                                                    n, epoch_counter, (__half *)out, status, timeout_ns);
+    break;
+  case B200_BF16:
+    sharded_sum_finish_nvls_kernel<__nv_bfloat16><<<1, 1024, 0, stream>>>(
+        partial, own_slots, multicast_slots, t, rank, world, n, epoch_counter, (__nv_bfloat16 *)out, status, timeout_ns);
     break;
   default:
     return B200_ERR_INVALID_ARG;

@@ -310,3 +310,23 @@ class ShardedSum:
             self._status.data_ptr() if self._status is not None else None, _stream())
         N.check(rc, "b200_sharded_sum_finish")
         return out
+
+
+class ShardedSumSwitch:
+    """The same exchange with the sum taken inside the NVSwitch (multimem.ld_reduce over a multicast
+    mapping of symmetric memory).  `own_slots`: this rank's float[2][n] in symmetric memory;
+    `multicast_slots`: the multicast address of the same range; `peer_flags`, `counter` as above."""
+
+    def __init__(self, rank, world, n, own_slots, multicast_slots, peer_flags, counter, status=None):
+        self.rank, self.world, self.n = rank, world, n
+        self._own, self._mc = own_slots, multicast_slots
+        self._flags = (C.c_void_p * world)(*peer_flags)
+        self._counter, self._status = counter, status
+
+    def __call__(self, partial, out):
+        rc = N.lib().b200_sharded_sum_finish_nvls(
+            _dt(out), partial.data_ptr(), self._own, self._mc, self._flags, self.rank, self.world, self.n,
+            self._counter.data_ptr(), out.data_ptr(),
+            self._status.data_ptr() if self._status is not None else None, _stream())
+        N.check(rc, "b200_sharded_sum_finish_nvls")
+        return out
