@@ -10,6 +10,9 @@ from byre_bytecode_writer import write_module, varint
 from test_brt_host import plugin  # noqa: F401  (registers the host kernels)
 
 FIXTURE = Path(__file__).parent / "golden" / "byre_serial_v1_lljit_case0.mlirbc"
+# compiler/test/E2E/Host/Case0_Bytecode/Output.mlirbc: the same module as the compiler's own end-to-end test
+# writes it, with the producer string the dialect's writer puts in ("BYRE_1_0_0" instead of the MLIR version)
+FIXTURE_E2E = Path(__file__).parent / "golden" / "byre_serial_v1_host_case0_bytecode.mlirbc"
 
 
 def _load(data, tmp_path, device="cpu", name="m.mlirbc"):
@@ -20,10 +23,12 @@ def _load(data, tmp_path, device="cpu", name="m.mlirbc"):
     return s
 
 
-def test_reference_fixture_loads(tmp_path):
-    """runtime/test/test_files/LLJIT/Case0_v1_0_0/entry.mlirbc: six host memrefs, one compute op whose
-    attributes came through the extra_args dictionary (checked by the stub kernel's constructor)"""
-    s = _load(FIXTURE.read_bytes(), tmp_path)
+@pytest.mark.parametrize("fixture", [FIXTURE, FIXTURE_E2E], ids=["runtime_lljit_case0", "compiler_e2e_case0_bytecode"])
+def test_reference_fixture_loads(tmp_path, fixture):
+    """runtime/test/test_files/LLJIT/Case0_v1_0_0/entry.mlirbc and compiler/test/E2E/Host/Case0_Bytecode/
+    Output.mlirbc: six host memrefs, one compute op whose attributes came through the extra_args
+    dictionary (checked by the stub kernel's constructor)"""
+    s = _load(fixture.read_bytes(), tmp_path)
     got = [(a.name, a.argtype, a.dtype, tuple(a.shape), a.space) for a in s.args()]
     assert got == [("Input0", 1, "i64", (1,), "cpu"), ("Input1", 1, "i64", (1,), "cpu"), ("Input2", 1, "i64", (1,), "cpu"),
                    ("Input3", 1, "i32", (1, 128), "cpu"), ("Output0", 2, "i32", (1, 128), "cpu"),
