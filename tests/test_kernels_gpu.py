@@ -471,6 +471,16 @@ def test_transpose(ops, shape, perm, dt):
     assert np.array_equal(_bits(got), _bits(want))
 
 
+def test_transpose_matches_the_references_compiled_cpu_code(ops):
+    """the vector made by the reference's own CPU code (its compiler's LLVM IR for f32 [1, 32, 64, 64] -> (0, 2, 3, 1))"""
+    from test_oracle import transpose_golden
+    x, perm, want = transpose_golden()
+    got = _to_host(ops.transpose(_to_dev(x), perm))
+    assert np.array_equal(got.view(np.uint32), want.view(np.uint32))
+    x16 = (x % 2048).astype(np.float16)  # the same permutation through the 2-byte kernel, values exact in f16
+    assert np.array_equal(_bits(_to_host(ops.transpose(_to_dev(x16), perm))), _bits((want % 2048).astype(np.float16)))
+
+
 @pytest.mark.parametrize("path", [1, 2])
 @pytest.mark.parametrize("dt", ["f32", "f16"])
 @pytest.mark.parametrize("b,r,c", [(1, 64, 64), (3, 200, 136), (2, 72, 1000), (1, 8, 8), (4, 4096, 128)])

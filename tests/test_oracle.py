@@ -219,6 +219,24 @@ def test_transpose(shape, perm, dt):
     assert np.array_equal(O.transpose(x, perm), np.transpose(x, perm))
 
 
+TRANSPOSE_GOLDEN = Path(__file__).parent / "golden" / "transpose_f32_1x32x64x64_perm0231.npz"
+
+
+def transpose_golden():
+    """input and output of the reference's own CPU code for f32 [1, 32, 64, 64] -> (0, 2, 3, 1): its compiler's
+    LLVM IR (runtime/test/test_files/LLJIT/transpose_32_64_64.ll) run by tests/golden/make_transpose_llvm_golden.py"""
+    g = np.load(TRANSPOSE_GOLDEN)
+    shape, perm = tuple(int(v) for v in g["shape"]), tuple(int(v) for v in g["perm"])
+    x = np.arange(int(np.prod(shape)), dtype=np.float32).reshape(shape)
+    out = np.cumsum(g["delta"].astype(np.int64)).astype(np.float32).reshape([shape[p] for p in perm])
+    return x, perm, out
+
+
+def test_transpose_matches_the_references_compiled_cpu_code():
+    x, perm, want = transpose_golden()
+    assert np.array_equal(O.transpose(x, perm).view(np.uint32), want.view(np.uint32))
+
+
 def test_bf16_conversion_round_trip():
     x = np.random.default_rng(8).standard_normal(10000).astype(np.float32)
     b = O.f32_to_bf16(x)
