@@ -471,10 +471,11 @@ def test_transpose(ops, shape, perm, dt):
     assert np.array_equal(_bits(got), _bits(want))
 
 
-def test_transpose_matches_the_references_compiled_cpu_code(ops):
-    """the vector made by the reference's own CPU code (its compiler's LLVM IR for f32 [1, 32, 64, 64] -> (0, 2, 3, 1))"""
+@pytest.mark.parametrize("name", ["transpose_f32_1x32x64x64_perm0231.npz", "transpose_f32_1x3x224x224_perm0231.npz"])
+def test_transpose_matches_the_references_compiled_cpu_code(ops, name):
+    """the vectors made by the reference's own CPU code (its compiler's LLVM IR for f32 [1, C, H, W] -> (0, 2, 3, 1))"""
     from test_oracle import transpose_golden
-    x, perm, want = transpose_golden()
+    x, perm, want = transpose_golden(name)
     got = _to_host(ops.transpose(_to_dev(x), perm))
     assert np.array_equal(got.view(np.uint32), want.view(np.uint32))
     x16 = (x % 2048).astype(np.float16)  # the same permutation through the 2-byte kernel, values exact in f16

@@ -219,21 +219,23 @@ def test_transpose(shape, perm, dt):
     assert np.array_equal(O.transpose(x, perm), np.transpose(x, perm))
 
 
-TRANSPOSE_GOLDEN = Path(__file__).parent / "golden" / "transpose_f32_1x32x64x64_perm0231.npz"
+TRANSPOSE_GOLDENS = ["transpose_f32_1x32x64x64_perm0231.npz", "transpose_f32_1x3x224x224_perm0231.npz"]
 
 
-def transpose_golden():
-    """input and output of the reference's own CPU code for f32 [1, 32, 64, 64] -> (0, 2, 3, 1): its compiler's
-    LLVM IR (runtime/test/test_files/LLJIT/transpose_32_64_64.ll) run by tests/golden/make_transpose_llvm_golden.py"""
-    g = np.load(TRANSPOSE_GOLDEN)
+def transpose_golden(name):
+    """input and output of the reference's own CPU code for f32 [1, C, H, W] -> (0, 2, 3, 1): its compiler's
+    LLVM IR (runtime/test/test_files/LLJIT/transpose_{32_64_64,3_224_224}.ll) run by
+    tests/golden/make_transpose_llvm_golden.py"""
+    g = np.load(Path(__file__).parent / "golden" / name)
     shape, perm = tuple(int(v) for v in g["shape"]), tuple(int(v) for v in g["perm"])
     x = np.arange(int(np.prod(shape)), dtype=np.float32).reshape(shape)
     out = np.cumsum(g["delta"].astype(np.int64)).astype(np.float32).reshape([shape[p] for p in perm])
     return x, perm, out
 
 
-def test_transpose_matches_the_references_compiled_cpu_code():
-    x, perm, want = transpose_golden()
+@pytest.mark.parametrize("name", TRANSPOSE_GOLDENS)
+def test_transpose_matches_the_references_compiled_cpu_code(name):
+    x, perm, want = transpose_golden(name)
     assert np.array_equal(O.transpose(x, perm).view(np.uint32), want.view(np.uint32))
 
 
