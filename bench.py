@@ -21,6 +21,8 @@ measures one of them alone (used for profiling).  One JSON line is printed by ra
             oracle/_ref/libref_kernels.so), timed the same way on the same inputs
   cpu_baseline  the CPU oracle (a restatement of the reference's op semantics) on this host's
             cores, on a bounded sample of the same workload
+  in_place  (scatter only) the op with in == out: no table copy, against the bytes of the rows
+            that some index names
 
 Multi-GPU: one process per GPU (torchrun); every rank processes its own batch (weak scaling),
 no exchange, except the sum whose reduced axis is itself sharded: one kernel over NVLink peer
@@ -215,6 +217,9 @@ class Workload:
 
     def ref_gpu(self, ref, torch):  # (kernel name, callable(x) launching the reference kernel) or None
         return None
+
+    def variants(self, torch):  # {key: (callable(x), algorithmic bytes or flops, note)}: the op in another form
+        return {}
 
     def make_session(self, brt, local_rank):  # the session the plug-in leg loads the module into
         return brt.Session("cuda", device_id=local_rank, host_space=True)
@@ -624,6 +629,7 @@ class ScatterC3(Workload):
 
     def setup_gpu(self, torch, ops, xs):
         self.ops = ops
+        self._idx_dev = [x[0] for x in xs]
         self.table_d = torch.from_numpy(self.table).cuda()
         self.upd_d = torch.from_numpy(self.upd).cuda()
         self.out = torch.empty_like(self.table_d)
@@ -657,6 +663,18 @@ class ScatterC3(Workload):
                          ("%1", memref(t, "f16", "cuda"))], "dim = 0 : i32", [1, 1, 1, 2]),
              copy_op("cuda2cpu", "%1", "%arg3", t, "f16")])
         return text, {"Table": ("dev", self.table_d), "Idx": ("in", 0), "Upd": ("dev", self.upd_d), "Out": ("out", 0)}
+
+    def variants(self, torch):
+        # in place (in == out): no table copy; the algorithmic bytes are the rows some index names, read and
+        # written once, the updates and the indices
+        inplace = self.table_d.clone()
+        rows_named = [int(torch.unique(x).numel()) for x in self._idx_dev]
+        u = int(np.median(rows_named))
+        work = 2 * u * self.FEAT * 2 + self.N * self.FEAT * 2 + self.N * 8
+
+        def run(x):
+            self.ops.index_put_add(inplace, x[0], self.upd_d, out=inplace, workspace=self.ws)
+        return {"in_place": (run, work, f"in == out; {u} distinct rows named (median over the index lists)")}
 
     def ref_gpu(self, ref, torch):
         # the reference's IndexPut is f32 only (index_put.cu:57-59): both sides are timed on an f32 copy of the
@@ -1231,6 +1249,16 @@ class Bench:
             entry["ref_gpu"] = {"kernel": ref_name, "ms_per_step": ref_ms, "ours_ms_per_step": ours_ms,
                                 "x_over_ref_gpu": ref_ms / ours_ms}
 
+        # the same op in another form (the in-place scatter-add), timed the same way
+        for vkey, (vrun, vwork, vnote) in wl.variants(torch).items():
+            for i in range(2):
+                vrun(xs[i % n_buf])
+            v_all, _ = self.timed_replays(lambda i: vrun(xs[i % n_buf]), max(3, min(steps, 10)), 3)
+            v_ms = float(np.median(v_all))
+            v_rate = rate(wl, vwork, v_ms * 1e-3)
+            entry[vkey] = {"ms_per_step": v_ms, "value": v_rate, "unit": wl.unit, "frac": v_rate / peak, "work": vwork,
+                           "note": vnote}
+
         entry["e2e"] = self.e2e(wl, xs_host, xs, outs)
 
         entry["cpu_baseline"] = None
@@ -1434,6 +1462,8 @@ def main():
         "e2e": top["e2e"], "gpu_launches": top["gpu_launches"], "clocks": top["clocks"],
         "strong": strong, "workloads": others,
     }
+    if "in_place" in top:
+        line["in_place"] = top["in_place"]
     json_out.write(json.dumps(line) + "\n")
     json_out.flush()
     finish()
