@@ -516,37 +516,39 @@ class ReduceC2(Workload):
         return s
 
     def plugin(self, torch):
+        # Configuration 2 is two ops on the SAME tensor x (sum over dims {0,1}, max over dim 2), so the module
+        # takes x once: one upload, two ops, two results.  (The device-timed step above reads two different
+        # buffers only so that its number does not ride on x still sitting in L2.)
         ins = self.shape
         if self.world > 1:
             group = ", ".join(str(r) for r in range(self.world))
             text = byre_module(
-                [("Xs", 1, ins, "f16", "cpu"), ("Xm", 1, ins, "f16", "cpu"), ("Sum", 2, (1024,), "f16", "cpu"),
-                 ("Max", 2, (self.rows0, 512), "f16", "cpu")],
-                [(ins, "f16"), (ins, "f16"), ((1024,), "f32"), ((1024,), "f16"), ((self.rows0, 512), "f16")],
+                [("X", 1, ins, "f16", "cpu"), ("Sum", 2, (1024,), "f16", "cpu"), ("Max", 2, (self.rows0, 512), "f16", "cpu")],
+                [(ins, "f16"), ((1024,), "f32"), ((1024,), "f16"), ((self.rows0, 512), "f16")],
                 [copy_op("cpu2cuda", "%arg0", "%0", ins, "f16"),
-                 copy_op("cpu2cuda", "%arg1", "%1", ins, "f16"),
-                 compute_op("ReduceSumOp_f16_f32", [("%0", memref(ins, "f16", "cuda")), ("%2", memref((1024,), "f32", "cuda"))],
+                 compute_op("ReduceSumOp_f16_f32", [("%0", memref(ins, "f16", "cuda")), ("%1", memref((1024,), "f32", "cuda"))],
                             "dimensions = dense<[0, 1]> : tensor<2xi64>", [1, 2]),
-                 compute_op("nccl.AllReduce", [("%2", memref((1024,), "f32", "cuda")), ("%3", memref((1024,), "f16", "cuda"))],
+                 compute_op("nccl.AllReduce", [("%1", memref((1024,), "f32", "cuda")), ("%2", memref((1024,), "f16", "cuda"))],
                             f'reduction = "sum", replica_group = [{group}]', [1, 2]),
-                 compute_op("ReduceMaxOp_f16_f16", [("%1", memref(ins, "f16", "cuda")), ("%4", memref((self.rows0, 512), "f16", "cuda"))],
+                 compute_op("ReduceMaxOp_f16_f16", [("%0", memref(ins, "f16", "cuda")), ("%3", memref((self.rows0, 512), "f16", "cuda"))],
                             "dimensions = dense<[2]> : tensor<1xi64>", [1, 2]),
-                 copy_op("cuda2cpu", "%3", "%arg2", (1024,), "f16"),
-                 copy_op("cuda2cpu", "%4", "%arg3", (self.rows0, 512), "f16")])
-            return text, {"Xs": ("in", 0), "Xm": ("in", 1), "Sum": ("out", 0), "Max": ("out", 1)}
+                 copy_op("cuda2cpu", "%2", "%arg1", (1024,), "f16"),
+                 copy_op("cuda2cpu", "%3", "%arg2", (self.rows0, 512), "f16")])
+            return text, {"X": ("in", 0), "Sum": ("out", 0), "Max": ("out", 1)}
         text = byre_module(
-            [("Xs", 1, ins, "f16", "cpu"), ("Xm", 1, ins, "f16", "cpu"), ("Sum", 2, (1024,), "f16", "cpu"),
-             ("Max", 2, (self.rows0, 512), "f16", "cpu")],
-            [(ins, "f16"), (ins, "f16"), ((1024,), "f16"), ((self.rows0, 512), "f16")],
+            [("X", 1, ins, "f16", "cpu"), ("Sum", 2, (1024,), "f16", "cpu"), ("Max", 2, (self.rows0, 512), "f16", "cpu")],
+            [(ins, "f16"), ((1024,), "f16"), ((self.rows0, 512), "f16")],
             [copy_op("cpu2cuda", "%arg0", "%0", ins, "f16"),
-             copy_op("cpu2cuda", "%arg1", "%1", ins, "f16"),
-             compute_op("ReduceSumOp_f16_f16", [("%0", memref(ins, "f16", "cuda")), ("%2", memref((1024,), "f16", "cuda"))],
+             compute_op("ReduceSumOp_f16_f16", [("%0", memref(ins, "f16", "cuda")), ("%1", memref((1024,), "f16", "cuda"))],
                         "dimensions = dense<[0, 1]> : tensor<2xi64>", [1, 2]),
-             compute_op("ReduceMaxOp_f16_f16", [("%1", memref(ins, "f16", "cuda")), ("%3", memref((self.rows0, 512), "f16", "cuda"))],
+             compute_op("ReduceMaxOp_f16_f16", [("%0", memref(ins, "f16", "cuda")), ("%2", memref((self.rows0, 512), "f16", "cuda"))],
                         "dimensions = dense<[2]> : tensor<1xi64>", [1, 2]),
-             copy_op("cuda2cpu", "%2", "%arg2", (1024,), "f16"),
-             copy_op("cuda2cpu", "%3", "%arg3", (self.rows0, 512), "f16")])
-        return text, {"Xs": ("in", 0), "Xm": ("in", 1), "Sum": ("out", 0), "Max": ("out", 1)}
+             copy_op("cuda2cpu", "%1", "%arg1", (1024,), "f16"),
+             copy_op("cuda2cpu", "%2", "%arg2", (self.rows0, 512), "f16")])
+        return text, {"X": ("in", 0), "Sum": ("out", 0), "Max": ("out", 1)}
+
+    def e2e_want(self, x):  # what the typed path computes when both ops read the module's one input
+        return self.step_gpu((x[0], x[0]))
 
 
 def c3_table(rank):
@@ -1341,7 +1343,7 @@ class Bench:
             # what comes back through the boundary is what the typed path computes on the same input
             reqs[0].run()
             reqs[0].sync()
-            want = wl.step_gpu(xs[0])
+            want = wl.e2e_want(xs[0]) if hasattr(wl, "e2e_want") else wl.step_gpu(xs[0])
             torch.cuda.synchronize()
             for kind, w in binding.values():
                 if kind == "out":
@@ -1353,8 +1355,11 @@ class Bench:
             for r in reqs:
                 r.close()
             session.close()
-        return {"value": rate(wl, wl.work() * world, ms * 1e-3), "unit": wl.unit, "h2d_bytes_per_step": h2d,
-                "d2h_bytes_per_step": d2h, "ms_per_step": ms, "steps": steps, "path": path}
+        out = {"value": rate(wl, wl.work() * world, ms * 1e-3), "unit": wl.unit, "h2d_bytes_per_step": h2d,
+               "d2h_bytes_per_step": d2h, "ms_per_step": ms, "steps": steps, "path": path}
+        if isinstance(wl, ReduceC2):
+            out["note"] = "the module takes x once and runs both ops of the configuration on it (one upload per step)"
+        return out
 
 
 def main():
