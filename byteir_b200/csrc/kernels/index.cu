@@ -559,17 +559,34 @@ __global__ void __launch_bounds__(256)
   pdl_wait();
   pdl_launch_dependents();
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  // Everything the block reads from global memory is requested here, in one go: the digit totals, the
+  // block's keys (and positions) and its column of the scanned histogram do not depend on one another, and
+  // beside the table copy every round trip to memory waits behind the copy's queue.
+  const int64_t base = (int64_t)blockIdx.x * kSortTile + warp * 256;
+  uint32_t key[8], val[8], rank[8];
+  uint32_t t[kMaxRadix / 256], hcol[kMaxRadix / 256];
+#pragma unroll
+  for (int k = 0; k < kMaxRadix / 256; ++k) {
+    const int d = threadIdx.x * (kMaxRadix / 256) + k;
+    t[k] = d < radix ? totals[d] : 0u;
+    const int dc = threadIdx.x + k * 256;
+    hcol[k] = dc < radix ? hist[(size_t)dc * ntiles + blockIdx.x] : 0u;
+  }
+#pragma unroll
+  for (int r = 0; r < 8; ++r) {
+    const int64_t i = base + r * 32 + lane;
+    const bool ok = i < n;
+    key[r] = ok ? keys_in[i] : 0u;
+    val[r] = ok ? (FIRST ? (uint32_t)i : vals_in[i]) : 0u;
+  }
   for (int i = threadIdx.x; i < 8 * kMaxRadix; i += 256)
     (&whist[0][0])[i] = 0;
   // digit_base[d] = number of keys whose digit is below d: block-wide exclusive scan of the totals
   {
-    uint32_t t[kMaxRadix / 256], local = 0;
+    uint32_t local = 0;
 #pragma unroll
-    for (int k = 0; k < kMaxRadix / 256; ++k) {
-      const int d = threadIdx.x * (kMaxRadix / 256) + k;
-      t[k] = d < radix ? totals[d] : 0u;
+    for (int k = 0; k < kMaxRadix / 256; ++k)
       local += t[k];
-    }
     uint32_t incl = local;
     for (int off = 1; off < 32; off <<= 1) {
       const uint32_t u = __shfl_up_sync(0xffffffffu, incl, off);
@@ -589,15 +606,11 @@ __global__ void __launch_bounds__(256)
     }
   }
   __syncthreads();
-  const int64_t base = (int64_t)blockIdx.x * kSortTile + warp * 256;
-  uint32_t key[8], val[8], rank[8];
   const uint32_t lt = (1u << lane) - 1u;
 #pragma unroll
   for (int r = 0; r < 8; ++r) {
     const int64_t i = base + r * 32 + lane;
     const bool ok = i < n;
-    key[r] = ok ? keys_in[i] : 0u;
-    val[r] = ok ? (FIRST ? (uint32_t)i : vals_in[i]) : 0u;
     const uint32_t d = ok ? ((key[r] >> shift) & (radix - 1)) : 0xffffffffu;
     const uint32_t peers = __match_any_sync(0xffffffffu, d);
     uint32_t prefix = 0;
@@ -610,8 +623,12 @@ __global__ void __launch_bounds__(256)
     rank[r] = prefix + __popc(peers & lt);
   }
   __syncthreads();
-  for (int d = threadIdx.x; d < radix; d += 256) {
-    uint32_t run = hist[(size_t)d * ntiles + blockIdx.x] + digit_base[d];
+#pragma unroll
+  for (int k = 0; k < kMaxRadix / 256; ++k) {
+    const int d = threadIdx.x + k * 256;
+    if (d >= radix)
+      break;
+    uint32_t run = hcol[k] + digit_base[d];
 #pragma unroll
     for (int w = 0; w < 8; ++w) {
       const uint32_t c = whist[w][d];
