@@ -418,6 +418,9 @@ class ReduceC2(Workload):
         self.status = torch.zeros(1, dtype=torch.int32, device="cuda")
         self.sharded = ops.ShardedSum(self.rank, self.world, n, ptrs, [p + flag_off for p in ptrs],
                                       self.counter, self.status)
+        # the reductions leave two block slots of their wave to the exchange kernels that run beside them (in a
+        # batch of back-to-back steps the exchange of one step is still waiting for its peers when the next one starts)
+        N.lib().b200_reduce_reserve_blocks(int(os.environ.get("B200_RESERVE_BLOCKS", "2")))
         # the exchange is one small block beside grids that fill the GPU: highest priority, so that it
         # never queues behind their blocks
         self.side = torch.cuda.Stream(priority=-1)
@@ -622,7 +625,8 @@ class ScatterC3(Workload):
         self.table = c3_table(self.rank)
         rng = np.random.default_rng(1234 + 3 + 1000 * self.rank)
         self.upd = rng.standard_normal((self.N, self.FEAT), dtype=np.float32).astype(np.float16)
-        return [(zipf_indices(rng, self.N, self.ROWS),) for _ in range(n)]
+        self._idx_host = [zipf_indices(rng, self.N, self.ROWS) for _ in range(n)]
+        return [(x,) for x in self._idx_host]
 
     N_BUF = 2
 
@@ -631,7 +635,6 @@ class ScatterC3(Workload):
 
     def setup_gpu(self, torch, ops, xs):
         self.ops = ops
-        self._idx_dev = [x[0] for x in xs]
         self.table_d = torch.from_numpy(self.table).cuda()
         self.upd_d = torch.from_numpy(self.upd).cuda()
         self.out = torch.empty_like(self.table_d)
@@ -670,7 +673,7 @@ class ScatterC3(Workload):
         # in place (in == out): no table copy; the algorithmic bytes are the rows some index names, read and
         # written once, the updates and the indices
         inplace = self.table_d.clone()
-        rows_named = [int(torch.unique(x).numel()) for x in self._idx_dev]
+        rows_named = [int(np.unique(x).size) for x in self._idx_host]  # counted on the host
         u = int(np.median(rows_named))
         work = 2 * u * self.FEAT * 2 + self.N * self.FEAT * 2 + self.N * 8
 

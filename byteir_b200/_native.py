@@ -57,6 +57,7 @@ SIGNATURES = {
     "b200_cast_from_f32": (_int, [_int, _vp, _vp, _i64, _vp]),
     "b200_fill": (_int, [_int, _vp, _i64, C.c_uint64, _vp]),
     "b200_sharded_sum_inbox_bytes": (_sz, [_int, _i64]),
+    "b200_reduce_reserve_blocks": (None, [_int]),
     "b200_sharded_sum_finish": (_int, [_int, _vp, C.POINTER(_vp), C.POINTER(_vp), _int, _int, _i64, _vp, _vp, _vp, _vp]),
     "b200_reduce_no_alloc_max_bytes": (_sz, []),
     "b200_reduce_no_alloc": (_int, [_int, _int, _vp, _vp, _i64, _i64, _i64, _vp]),

@@ -19,6 +19,9 @@ namespace b200 {
 namespace {
 
 constexpr int kMaxWorld = 16;
+// One block of 256 threads (at most 64 registers each): it fits into the room of ONE block of the
+// reductions it runs beside, whose grids fill every SM exactly (see b200_reduce_reserve_blocks).
+constexpr int kExchangeThreads = 256;
 
 struct PeerTable {
   float *inbox[kMaxWorld];      // rank p's inbox: float[2][world][n]
@@ -40,7 +43,7 @@ __device__ __forceinline__ uint64_t global_timer_ns() {
 }
 
 template <typename OutT>
-__global__ void __launch_bounds__(1024)
+__global__ void __launch_bounds__(kExchangeThreads)
     sharded_sum_finish_kernel(const float *__restrict__ partial, PeerTable peers, int rank, int world,
                               int64_t n, uint32_t *epoch_counter, OutT *__restrict__ out, int *status,
                               uint64_t timeout_ns, int vec4) {
@@ -117,7 +120,7 @@ __global__ void __launch_bounds__(1024)
 //   own_slots: this device's float[2][n] in symmetric memory; mc_slots: the multicast address of the
 //   same range (bound to all `world` devices).
 template <typename OutT>
-__global__ void __launch_bounds__(1024)
+__global__ void __launch_bounds__(kExchangeThreads)
     sharded_sum_finish_nvls_kernel(const float *__restrict__ partial, float *own_slots, const float *mc_slots,
                                    PeerTable peers, int rank, int world, int64_t n, uint32_t *epoch_counter,
                                    OutT *__restrict__ out, int *status, uint64_t timeout_ns) {
@@ -198,15 +201,15 @@ extern "C" int b200_sharded_sum_finish(int dtype, const float *partial, void *co
   const int vec4 = vec ? 1 : 0;
   switch (dtype) {
   case B200_F32:
-    sharded_sum_finish_kernel<float><<<1, 1024, 0, stream>>>(partial, t, rank, world, n, epoch_counter,
+    sharded_sum_finish_kernel<float><<<1, kExchangeThreads, 0, stream>>>(partial, t, rank, world, n, epoch_counter,
                                                               (float *)out, status, timeout_ns, vec4);
     break;
   case B200_F16:
-    sharded_sum_finish_kernel<__half><<<1, 1024, 0, stream>>>(partial, t, rank, world, n, epoch_counter,
+    sharded_sum_finish_kernel<__half><<<1, kExchangeThreads, 0, stream>>>(partial, t, rank, world, n, epoch_counter,
                                                                (__half *)out, status, timeout_ns, vec4);
     break;
   case B200_BF16:
-    sharded_sum_finish_kernel<__nv_bfloat16><<<1, 1024, 0, stream>>>(partial, t, rank, world, n, epoch_counter,
+    sharded_sum_finish_kernel<__nv_bfloat16><<<1, kExchangeThreads, 0, stream>>>(partial, t, rank, world, n, epoch_counter,
                                                                       (__nv_bfloat16 *)out, status, timeout_ns, vec4);
     break;
   default:
@@ -233,15 +236,15 @@ extern "C" int b200_sharded_sum_finish_nvls(int dtype, const float *partial, flo
   const uint64_t timeout_ns = 2000000000ull; // 2 s
   switch (dtype) {
   case B200_F32:
-    sharded_sum_finish_nvls_kernel<float><<<1, 1024, 0, stream>>>(partial, own_slots, multicast_slots, t, rank, world, n,
+    sharded_sum_finish_nvls_kernel<float><<<1, kExchangeThreads, 0, stream>>>(partial, own_slots, multicast_slots, t, rank, world, n,
                                                                    epoch_counter, (float *)out, status, timeout_ns);
     break;
   case B200_F16:
-    sharded_sum_finish_nvls_kernel<__half><<<1, 1024, 0, stream>>>(partial, own_slots, multicast_slots, t, rank, world,
+    sharded_sum_finish_nvls_kernel<__half><<<1, kExchangeThreads, 0, stream>>>(partial, own_slots, multicast_slots, t, rank, world,
                                                                     n, epoch_counter, (__half *)out, status, timeout_ns);
     break;
   case B200_BF16:
-    sharded_sum_finish_nvls_kernel<__nv_bfloat16><<<1, 1024, 0, stream>>>(
+    sharded_sum_finish_nvls_kernel<__nv_bfloat16><<<1, kExchangeThreads, 0, stream>>>(
         partial, own_slots, multicast_slots, t, rank, world, n, epoch_counter, (__nv_bfloat16 *)out, status, timeout_ns);
     break;
   default:

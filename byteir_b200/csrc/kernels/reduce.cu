@@ -547,6 +547,10 @@ int g_prefetch_cols = 1;
 int g_prefetch_rows = 4;
 int g_cols_blocks_per_sm = 4;
 int g_rows_blocks_per_sm = 4;
+// Block slots of a one-wave grid that are left free (b200_reduce_reserve_blocks).  The column and the
+// short-row kernels fill every SM exactly (4 blocks of 256 threads x 64 registers), so a small kernel
+// that runs beside them, like the exchange of a sharded sum, would push blocks into a second wave.
+int g_reserved_blocks = 0;
 
 // ---- launch plan: a pure function of the shape -----------------------------
 struct Plan {
@@ -592,7 +596,8 @@ Plan make_plan(int esize, int64_t A, int64_t B, int64_t C, bool vec_cols) {
       p.slabs = (int)ceil_div<int64_t>(C, (int64_t)p.lpr * NV);
       const int64_t rows_per_step = kBlock / p.lpr;
       const int64_t blocks = A * p.slabs;
-      int64_t splits = std::max<int64_t>(1, ceil_div<int64_t>((int64_t)g_cols_blocks_per_sm * kNumSMs, blocks));
+      const int64_t wave = (int64_t)g_cols_blocks_per_sm * kNumSMs - g_reserved_blocks;
+      int64_t splits = std::max<int64_t>(1, g_reserved_blocks > 0 ? wave / blocks : ceil_div<int64_t>(wave, blocks));
       splits = std::min<int64_t>(splits, std::max<int64_t>(1, B / (rows_per_step * 4)));
       p.rows_per_split = ceil_div<int64_t>(B, splits);
       p.splits = (int)ceil_div<int64_t>(B, p.rows_per_split);
@@ -651,7 +656,8 @@ int launch(const T *in, OutT *out, int64_t A, int64_t B, int64_t C, void *ws,
     if (vec && p.segs == 1 && nvec <= 4LL * p.tpr) {
       const int vpt = (int)ceil_div<int64_t>(nvec, p.tpr);
       const int64_t row_blocks = ceil_div<int64_t>(A, groups_per_block);
-      const unsigned pgrid = (unsigned)std::min<int64_t>(row_blocks, (int64_t)kNumSMs * g_rows_blocks_per_sm);
+      const unsigned pgrid = (unsigned)std::min<int64_t>(
+          row_blocks, std::max<int64_t>(1, (int64_t)kNumSMs * g_rows_blocks_per_sm - g_reserved_blocks));
       if (vpt <= 1)
         return launch_pdl(reduce_short_rows_kernel<T, OP, 1, OutT>, dim3(pgrid), dim3(kBlock), 0, stream, in, out, A, B, p.tpr, g_prefetch_rows);
       else if (vpt == 2)
@@ -724,6 +730,8 @@ using namespace b200;
 // Measurement hook (not part of the drop-in ABI): pins the column plan's threads per slab row
 // (0 = the shape rule).  Workspace sizes follow the pinned plan, so ask for them after calling this.
 extern "C" void b200_reduce_cols_plan_override(int threads_per_row) { g_cols_lpr_override = threads_per_row; }
+
+extern "C" void b200_reduce_reserve_blocks(int blocks) { g_reserved_blocks = blocks > 0 ? blocks : 0; }
 
 extern "C" void b200_reduce_tune(int prefetch_cols, int prefetch_rows, int cols_blocks_per_sm, int rows_blocks_per_sm) {
   g_prefetch_cols = prefetch_cols;

@@ -70,6 +70,15 @@ int b200_reduce_sum_to_f32(int dtype, const void *in, float *out_f32, int64_t A,
                            size_t workspace_bytes, cudaStream_t stream);
 int b200_cast_from_f32(int dtype, const float *in, void *out, int64_t n,
                        cudaStream_t stream);
+/* The reductions size their grids to fill every SM exactly (one wave).  A small
+ * kernel that runs BESIDE them on another stream -- the exchange below is the
+ * case in point -- then takes the place of a block, which runs as a second wave
+ * after all others.  b200_reduce_reserve_blocks(n) makes the following calls of
+ * this process leave n block slots of the wave free (n = 1 is room for
+ * b200_sharded_sum_finish); 0 restores the full wave.  Results do not change
+ * bit for bit for max; for sums the split of the reduced axis, and with it the
+ * order of the f32 additions, follows the grid. */
+void b200_reduce_reserve_blocks(int blocks);
 
 /* The exchange step of a sum whose reduced axis is sharded over `world` GPUs:
  * stands in for nccl.AllReduce(sum) on the f32 partials followed by the cast to the
@@ -90,8 +99,8 @@ int b200_cast_from_f32(int dtype, const float *in, void *out, int64_t n,
  * cannot tell), and zero the flags and counters of every rank again before the
  * next call.  Ranks must not run ahead of each other by more than this call
  * enforces itself (a rank needs every peer's epoch to finish one), so no other
- * synchronisation is needed between steps.  One block does the whole exchange: it
- * is meant for vectors of up to a few thousand elements (the partial sums of a
+ * synchronisation is needed between steps.  One block of 256 threads does the whole
+ * exchange: it is meant for vectors of up to a few thousand elements (the partial sums of a
  * reduction); world <= 16.
  */
 size_t b200_sharded_sum_inbox_bytes(int world, int64_t n);

@@ -137,6 +137,32 @@ def test_reduce_config2_f16_multi_axis(ops):
     assert np.array_equal(_bits(gm), _bits(wm))
 
 
+@pytest.mark.parametrize("reserve", [1, 5])
+def test_reduce_with_block_slots_left_free(ops, reserve):
+    """b200_reduce_reserve_blocks: the one-wave grids leave room for a kernel that runs beside them; the column
+    sum (its split of the reduced axis follows the grid) stays within tolerance, the row max bit-exact"""
+    from byteir_b200 import _native as N
+    rng = np.random.default_rng(31)
+    x = rng.standard_normal((64, 512, 1024), dtype=np.float32).astype(np.float16)
+    x32 = rng.uniform(-1, 1, (1024, 4096)).astype(np.float32)
+    xd, x32d = _to_dev(x), _to_dev(x32)
+    full = _to_host(ops.reduce_max(xd, [2]))
+    try:
+        N.lib().b200_reduce_reserve_blocks(reserve)
+        got = _to_host(ops.reduce_sum(xd, [0, 1])).astype(np.float64)
+        part = _to_host(ops.reduce_sum_to_f32(xd, [0, 1])).astype(np.float64)
+        gm = _to_host(ops.reduce_max(xd, [2]))
+        rows = _to_host(ops.reduce_sum(x32d, [1])).astype(np.float64)
+    finally:
+        N.lib().b200_reduce_reserve_blocks(0)
+    want = O.reduce("sum", x, 1, 64 * 512, 1024).astype(np.float64)
+    np.testing.assert_allclose(got, want, rtol=2e-2, atol=1e-2)
+    ref64 = O.reduce_sum_f64(x, 1, 64 * 512, 1024)
+    assert np.abs(part - ref64).max() <= 1e-5 * np.abs(x.astype(np.float64)).sum(axis=(0, 1)).max()
+    assert np.array_equal(_bits(gm), _bits(full))
+    np.testing.assert_allclose(rows, x32.astype(np.float64).sum(axis=1), rtol=1e-5, atol=1e-4)
+
+
 @pytest.mark.parametrize("dt", ["f32", "f16", "bf16"])
 @pytest.mark.parametrize("op", ["sum", "max"])
 @pytest.mark.parametrize("shape", [(64 * 512, 1024), (20000, 96), (3, 9000, 40), (100000, 7)])
