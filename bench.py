@@ -1311,11 +1311,12 @@ class Bench:
             # Two requests in flight, each on a stream of its own: the upload of one step runs beside the
             # download of the step before (the bus is full duplex), as a serving loop would double-buffer.
             # A module with an exchange keeps one stream: its protocol is one call chain per rank.
-            # Only where both directions carry data: two uploads side by side share one copy engine and
-            # measured slower than one after the other (reductions 51 -> 41 GB/s).
+            # Only where both directions carry megabytes: two uploads side by side share one copy engine and
+            # measured slower than one after the other (reductions 51 -> 41 GB/s), and a step that moves
+            # kilobytes (the decode step) gains nothing from a second stream.
             up = sum(a.nbytes for a in session.args() if binding[a.name][0] == "in")
             down = sum(a.nbytes for a in session.args() if binding[a.name][0] == "out")
-            if min(up, down) * 5 >= max(up, down) and not (world > 1 and isinstance(wl, ReduceC2)):
+            if min(up, down) * 5 >= max(up, down) and min(up, down) >= (8 << 20) and not (world > 1 and isinstance(wl, ReduceC2)):
                 streams = [torch.cuda.Stream(), torch.cuda.Stream()]
             reqs = []
             for k in range(2):
