@@ -17,7 +17,9 @@ measures one of them alone (used for profiling).  One JSON line is printed by ra
             are inside the timed region; two requests are in flight, each on its own stream, so
             that the upload of a step runs beside the download of the step before
   roofline  algorithmic bytes (or FLOPs) of the op over its own event-timed duration, against
-            the measured peak
+            the measured peak; for the attention workloads also `alone`: single steps, each after
+            a pause, which is the regime the burst peak was measured in (back-to-back steps run
+            into the power cap)
   ref_gpu   the reference's own CUDA kernel launcher for the op (compiled for sm_100a into
             oracle/_ref/libref_kernels.so), timed the same way on the same inputs
   cpu_baseline  the CPU oracle (a restatement of the reference's op semantics) on this host's
@@ -1232,6 +1234,20 @@ class Bench:
             # the power cap (see `clocks`), the regime of the sustained figure, reported beside it.
             entry["roofline"]["peak_sustained"] = self.peaks["bf16_tflops_sustained"]
             entry["roofline"]["frac_of_sustained"] = achieved / self.peaks["bf16_tflops_sustained"]
+            # ... and the step timed ALONE, the regime of the burst figure: single steps, each after a pause
+            # that lets the clocks recover, CUDA events around the one step, median of five
+            alone = []
+            for i in range(5):
+                torch.cuda.synchronize()
+                time.sleep(0.25)
+                self.ev0.record()
+                wl.step_gpu(xs[i % n_buf])
+                self.ev1.record()
+                torch.cuda.synchronize()
+                alone.append(self.ev0.elapsed_time(self.ev1))
+            alone_ms = self.max_over_ranks(float(np.median(alone)))
+            a_rate = rate(wl, wl.work() * world, alone_ms * 1e-3)
+            entry["roofline"]["alone"] = {"ms_per_step": alone_ms, "achieved": a_rate / world, "frac": a_rate / world / peak}
 
         # the reference's own GPU kernel on the same inputs
         entry["ref_gpu"] = None
