@@ -1234,17 +1234,19 @@ class Bench:
             # the power cap (see `clocks`), the regime of the sustained figure, reported beside it.
             entry["roofline"]["peak_sustained"] = self.peaks["bf16_tflops_sustained"]
             entry["roofline"]["frac_of_sustained"] = achieved / self.peaks["bf16_tflops_sustained"]
-            # ... and the step timed ALONE, the regime of the burst figure: single steps, each after a pause
-            # that lets the clocks recover, CUDA events around the one step, median of five
+            # ... and the step timed in short bursts, the regime of the burst figure: after a pause that lets
+            # the GPU cool, one untimed step and three timed ones; median of five such bursts
             alone = []
             for i in range(5):
                 torch.cuda.synchronize()
                 time.sleep(0.25)
+                wl.step_gpu(xs[i % n_buf])  # untimed: brings the clocks back up after the pause
                 self.ev0.record()
-                wl.step_gpu(xs[i % n_buf])
+                for j in range(3):
+                    wl.step_gpu(xs[(i + j) % n_buf])
                 self.ev1.record()
                 torch.cuda.synchronize()
-                alone.append(self.ev0.elapsed_time(self.ev1))
+                alone.append(self.ev0.elapsed_time(self.ev1) / 3)
             alone_ms = self.max_over_ranks(float(np.median(alone)))
             a_rate = rate(wl, wl.work() * world, alone_ms * 1e-3)
             entry["roofline"]["alone"] = {"ms_per_step": alone_ms, "achieved": a_rate / world, "frac": a_rate / world / peak}
