@@ -80,7 +80,16 @@ public:
     std::sort(dimensions.begin(), dimensions.end());
     dimensions.erase(std::unique(dimensions.begin(), dimensions.end()), dimensions.end());
     total_ = OpAccessor::GetNumElementsOfShape(shape);
-    std::vector<int64_t> cur(shape.begin(), shape.end());
+    // Dimensions of size 1 are taken out of the shape altogether, so that reduced dimensions with only such
+    // dimensions between them form one group (f16 [128, 2, 1, 21] over all four is one pass, not two).
+    std::vector<int64_t> cur, renumber(shape.size(), -1);
+    for (size_t i = 0; i < shape.size(); ++i)
+      if (shape[i] != 1) {
+        renumber[i] = (int64_t)cur.size();
+        cur.push_back(shape[i]);
+      }
+    for (auto &d : dimensions)
+      d = renumber[d];
     // groups of consecutive dimensions, taken from the back so that the indices in front stay valid
     for (size_t hi = dimensions.size(); hi > 0;) {
       size_t lo = hi - 1;

@@ -37,13 +37,17 @@ def _need_cuda(*ts):
 
 
 def reduce_abc(shape, dimensions):
-    """A x B x C view of reduce_impl.h:28-59."""
-    dims = sorted(d for d in dimensions if shape[d] != 1)
+    """A x B x C view of reduce_impl.h:28-59.  Dimensions of size 1 are taken out of the shape first, so
+    that reduced dimensions with only such dimensions between them count as consecutive."""
+    keep = [i for i, s in enumerate(shape) if s != 1]
+    renumber = {d: k for k, d in enumerate(keep)}
+    dims = sorted({renumber[d] for d in dimensions if shape[d] != 1})
     if not dims:
         n = 1
         for s in shape:
             n *= s
         return 0, 0, n
+    shape = [shape[i] for i in keep]
     for a, b in zip(dims, dims[1:]):
         if b - a != 1:
             raise ValueError("Only consecutive dimensions reduction is supported")

@@ -228,6 +228,9 @@ def test_cuda_reduce_op_validates_shapes_and_consecutive_dims():
     assert s.arg_info(1).dtype == "f32"
     with pytest.raises(brt.BrtError):
         s.load_from_memory(reduce_mlir("ReduceMaxOp_f16_f32", "f16", (4, 5, 6), (6,), "dense<[0, 1]> : tensor<2xi64>", "f32"))
+    # reduced dimensions with only size-1 dimensions between them are one group (the reference, which drops the
+    # size-1 dimension from the list and then finds 0, 1, 3 not consecutive, refuses this one too)
+    s.load_from_memory(reduce_mlir("ReduceSumOp_f16_f16", "f16", (128, 2, 1, 21, 3), (3,), "dense<[0, 1, 2, 3]> : tensor<4xi64>"))
     # unsorted dims are fine (resnet18_fw_bw_host_cuda.mlir:178 has dense<[3, 2]>)
     s.load_from_memory(reduce_mlir("ReduceSumOp_f16_f16", "f16", (2, 3, 4, 5), (2, 3), "dense<[3, 2]> : tensor<2xi64>"))
 
