@@ -154,3 +154,86 @@ def test_transpose_random_shapes_and_permutations(ops, seed):
     got = _to_host(ops.transpose(_to_dev(x), perm))
     assert got.shape == want.shape
     assert np.array_equal(_bits(got), _bits(want))
+
+
+@pytest.mark.parametrize("seed", range(36))
+def test_flash_attn_random_shapes_masks_and_head_dims(ops, seed):
+    """forward and backward of the tcgen05 kernels on drawn shapes: ragged sequence lengths, Sq != Sk, grouped
+    heads, head dims below 128, causal / sliding-window / no mask; tolerances of test_flash_attn_gpu.py"""
+    from test_flash_attn_gpu import _dev, _host, _mk
+    rng = np.random.default_rng(11000 + seed)
+    b = int(rng.integers(1, 3))
+    sq = int(rng.integers(1, 700))
+    sk = sq if rng.random() < 0.4 else int(rng.integers(max(1, sq - 50), sq + 400))
+    hk = int(rng.integers(1, 4))
+    h = hk * int(rng.integers(1, 4))
+    d = [128, 128, 64, 96, 32, 120, 8][int(rng.integers(0, 7))]
+    dt = "bf16" if seed % 2 else "f16"
+    mode = int(rng.integers(0, 4))
+    causal, window = (mode == 1), (-1, -1)
+    if mode == 2:
+        window = (int(rng.integers(0, 300)), int(rng.integers(0, 200)))
+    elif mode == 3:
+        window = (int(rng.integers(0, 300)), 0)
+    q, k, v = _mk(rng, (b, sq, h, d), dt), _mk(rng, (b, sk, hk, d), dt), _mk(rng, (b, sk, hk, d), dt)
+    do = _mk(rng, (b, sq, h, d), dt)
+    scale = float(1.0 / np.sqrt(d))
+    want_o, want_lse = O.flash_attn_fwd(q, k, v, scale, causal, window=window)
+    qd, kd, vd, dod = _dev(q), _dev(k), _dev(v), _dev(do)
+    o, lse = ops.flash_attn_fwd(qd, kd, vd, scale, causal, window=window)
+    dq, dk, dv = ops.flash_attn_bwd(dod, qd, kd, vd, o, lse, scale, causal, window=window)
+    torch.cuda.synchronize()
+    gl = lse.cpu().numpy()
+    seen = np.isfinite(want_lse)  # a row that sees no key: LSE = +inf in both, output zero
+    assert np.array_equal(np.isfinite(gl), seen)
+    np.testing.assert_allclose(gl[seen], want_lse[seen], rtol=1e-3, atol=1e-3)
+    np.testing.assert_allclose(O.to_f32(_host(o)), O.to_f32(want_o), rtol=2e-2, atol=1e-2)
+    wq, wk, wv = O.flash_attn_bwd(do, q, k, v, _host(o), gl, scale, causal, window=window)
+    for name, got, want in (("dq", dq, wq), ("dk", dk, wk), ("dv", dv, wv)):
+        np.testing.assert_allclose(O.to_f32(_host(got)), O.to_f32(want), rtol=2e-2, atol=1e-2, err_msg=name)
+    again = ops.flash_attn_bwd(dod, qd, kd, vd, o, lse, scale, causal, window=window)
+    for a, b_ in zip(again, (dq, dk, dv)):
+        assert torch.equal(a.view(torch.int16), b_.view(torch.int16)), "backward is not deterministic"
+
+
+@pytest.mark.parametrize("seed", range(30))
+def test_flash_attn_kvcache_random_shapes(ops, seed):
+    """the decode step on drawn shapes: batch, rows in use per entry (empty to full), appended rows, query rows,
+    heads per cache head, head dims on both kernels (tensor-core tiles for 64 / 128, the scalar kernel
+    otherwise), causal / window / no mask"""
+    from test_flash_attn_gpu import _dev, _host, _mk
+    rng = np.random.default_rng(12000 + seed)
+    b = int(rng.integers(1, 9))
+    sq = int(rng.integers(1, 5))
+    hk = int(rng.integers(1, 5))
+    h = hk * [1, 1, 2, 4, 8][int(rng.integers(0, 5))]
+    d = [128, 128, 64, 64, 32, 96, 256, 8][int(rng.integers(0, 8))]
+    cap = int(rng.integers(8, 3000))
+    s_new = int(rng.integers(0, min(cap, 5) + 1))
+    dt = "bf16" if seed % 2 else "f16"
+    mode = int(rng.integers(0, 3))
+    causal, window = (mode == 0), (-1, -1)
+    if mode == 2:
+        window = (int(rng.integers(0, 400)), int(rng.integers(0, 4)))
+    lens_h = None
+    if rng.random() < 0.85 or s_new:
+        lens_h = rng.integers(0, cap - s_new + 1, b).astype(np.int32)
+        lens_h[rng.random(b) < 0.15] = 0
+        lens_h[rng.random(b) < 0.15] = cap - s_new
+    q = _mk(rng, (b, sq, h, d), dt)
+    kc, vc = _mk(rng, (b, cap, hk, d), dt), _mk(rng, (b, cap, hk, d), dt)
+    kn = _mk(rng, (b, s_new, hk, d), dt) if s_new else None
+    vn = _mk(rng, (b, s_new, hk, d), dt) if s_new else None
+    scale = float(1.0 / np.sqrt(d))
+    want_k, want_v = kc.copy(), vc.copy()
+    want_o, want_lse = O.flash_attn_kvcache(q, want_k, want_v, kn, vn, lens_h, scale, causal, window)
+    kd, vd = _dev(kc), _dev(vc)
+    o, lse = ops.flash_attn_kvcache(_dev(q), kd, vd, None if kn is None else _dev(kn), None if vn is None else _dev(vn),
+                                    None if lens_h is None else torch.from_numpy(lens_h).cuda(), scale, causal, window)
+    torch.cuda.synchronize()
+    assert np.array_equal(_host(kd), want_k) and np.array_equal(_host(vd), want_v)
+    gl = lse.cpu().numpy()
+    assert np.array_equal(np.isinf(gl), np.isinf(want_lse))
+    fin = np.isfinite(want_lse)
+    np.testing.assert_allclose(gl[fin], want_lse[fin], rtol=1e-3, atol=1e-3)
+    np.testing.assert_allclose(O.to_f32(_host(o)), O.to_f32(want_o), rtol=2e-2, atol=1e-2)
