@@ -15,7 +15,9 @@ and the two updated caches.
 
 It also copies the reference's one ByRE bytecode fixture (runtime/test/test_files/LLJIT/
 Case0_v1_0_0/entry.mlirbc, 447 bytes, byre_serial 1.0.0 in an MLIR 17 container) to
-byre_serial_v1_lljit_case0.mlirbc; its text twin is LLJIT/Case0/entry.mlir.
+byre_serial_v1_lljit_case0.mlirbc; its text twin is LLJIT/Case0/entry.mlir.  The compiler's own end-to-end
+test holds the same module under another producer string (compiler/test/E2E/Host/Case0_Bytecode/
+Output.mlirbc, 448 bytes): copied to byre_serial_v1_host_case0_bytecode.mlirbc.
 
 The reference's three flash-attention test modules (runtime/test/test_files/flash_attn_fwd.mlir,
 flash_attn_bwd.mlir, flash_attn_kvcache.mlir: a few lines of ByRE text each, with the packed
@@ -84,6 +86,10 @@ def main(ref_root: str) -> None:
     bc = (src / "LLJIT" / "Case0_v1_0_0" / "entry.mlirbc").read_bytes()
     assert bc[:4] == b"ML\xefR"
     Path(__file__).with_name("byre_serial_v1_lljit_case0.mlirbc").write_bytes(bc)
+    # the same module as the compiler's end-to-end test writes it (another producer string)
+    bc2 = (src.parents[2] / "compiler" / "test" / "E2E" / "Host" / "Case0_Bytecode" / "Output.mlirbc").read_bytes()
+    assert bc2[:4] == b"ML\xefR"
+    Path(__file__).with_name("byre_serial_v1_host_case0_bytecode.mlirbc").write_bytes(bc2)
     arrays = {}
     for key, fname in NAMES.items():
         vals = np.array((src / fname).read_text().split(), dtype=np.float64)
