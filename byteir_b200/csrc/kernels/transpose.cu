@@ -31,8 +31,8 @@ constexpr int kOutStages = 2;
 // persistent grid, and the width of a panel of the tile order; 0 = the rule in launch_tma.
 // b200_transpose_tune sets them for measurements.  Measured (TB/s of bytes read + written; ring depth /
 // blocks per SM): bf16 8192 x 8192: 2/6 4.3, 3/5 5.2, 4/4 5.4; f16 [32] x 128 x 4096: 2/6 4.2, 3/5 6.4,
-// 4/4 6.2; f32 4096 x 4096: 2/6 3.1, 3/5 4.9, 4/4 4.0; f16 1000 x 30000 (panels of 16): 3/5 5.6, 4/4 5.9,
-// row-major order 4.5 / 4.8.
+// 4/4 6.2; f16 1000 x 30000 (panels of 16): 3/5 5.6, 4/4 5.9, row-major order 4.5 / 4.8; f32 4096 x 4096 with
+// tiles of 64 rows (two output tiles per input tile): 2/6 4.3, 3/5 6.0, 4/4 6.0 (with tiles of 32 rows: 4.9 at best).
 int g_in_stages = 0, g_blocks_per_sm = 0, g_panel = 0;
 
 // byte offset of 16-byte chunk `chunk` (0..7) of tile row `row` in the 128-byte
@@ -45,12 +45,14 @@ template <int ES> // element size: 2 or 4
 __global__ void __launch_bounds__(256)
     transpose_tma_kernel(const __grid_constant__ CUtensorMap in_map,
                          const __grid_constant__ CUtensorMap out_map, int tiles_c, int tiles_r,
-                         int64_t num_tiles, int in_stages, int panel, int *error) {
+                         int64_t num_tiles, int in_stages, int panel, int64_t rows, int *error) {
   constexpr int TC = 128 / ES; // tile columns = elements per 128-byte row
-  constexpr int TR = ES == 2 ? 64 : 32;
+  constexpr int TR = 64;       // tile rows
+  constexpr int TRo = 128 / ES; // elements of an output row that one 128-byte swizzled row holds
+  constexpr int H = TR / TRo;  // output tiles per input tile: TC rows of TRo elements each (1, or 2 for 4-byte elements)
   constexpr uint32_t kInBytes = TR * 128;  // TR rows of 128 bytes
-  constexpr uint32_t kOutBytes = TC * TR * ES; // TC rows of TR elements
-  static_assert(TR * ES == 128, "output tile rows are 128 bytes");
+  constexpr uint32_t kOutHalf = TC * 128;  // TC rows of 128 bytes
+  constexpr uint32_t kOutBytes = H * kOutHalf;
   extern __shared__ __align__(1024) unsigned char smem_raw[];
   // 1024-byte alignment is what the 128-byte swizzle pattern repeats on
   unsigned char *smem = reinterpret_cast<unsigned char *>(
@@ -169,19 +171,26 @@ __global__ void __launch_bounds__(256)
         *reinterpret_cast<uint4 *>(dst + swz(c + 1, warp)) = odd;
       }
     } else {
-      // thread: column c = lane x rows 4 * warp .. 4 * warp + 3
-      const int c = lane, r0 = 4 * warp;
-      uint4 v;
-      v.x = *reinterpret_cast<const uint32_t *>(src + swz(r0 + 0, c >> 2) + ((c & 3) << 2));
-      v.y = *reinterpret_cast<const uint32_t *>(src + swz(r0 + 1, c >> 2) + ((c & 3) << 2));
-      v.z = *reinterpret_cast<const uint32_t *>(src + swz(r0 + 2, c >> 2) + ((c & 3) << 2));
-      v.w = *reinterpret_cast<const uint32_t *>(src + swz(r0 + 3, c >> 2) + ((c & 3) << 2));
-      *reinterpret_cast<uint4 *>(dst + swz(c, warp)) = v;
+      // thread: column c = lane x rows 4 * warp .. 4 * warp + 3 of each 32-row half of the tile
+      const int c = lane;
+#pragma unroll
+      for (int h = 0; h < H; ++h) {
+        const int r0 = h * TRo + 4 * warp;
+        uint4 v;
+        v.x = *reinterpret_cast<const uint32_t *>(src + swz(r0 + 0, c >> 2) + ((c & 3) << 2));
+        v.y = *reinterpret_cast<const uint32_t *>(src + swz(r0 + 1, c >> 2) + ((c & 3) << 2));
+        v.z = *reinterpret_cast<const uint32_t *>(src + swz(r0 + 2, c >> 2) + ((c & 3) << 2));
+        v.w = *reinterpret_cast<const uint32_t *>(src + swz(r0 + 3, c >> 2) + ((c & 3) << 2));
+        *reinterpret_cast<uint4 *>(dst + h * kOutHalf + swz(c, warp)) = v;
+      }
     }
     fence_proxy_async_smem();
     __syncthreads();
     if (threadIdx.x == 32) {
-      tma_store_3d(&out_map, dst, str * TR, stc * TC, sb);
+#pragma unroll
+      for (int h = 0; h < H; ++h)
+        if ((int64_t)str * TR + h * TRo < rows) // a store that would start past the end of the rows is left out
+          tma_store_3d(&out_map, dst + h * kOutHalf, str * TR + h * TRo, stc * TC, sb);
       bulk_commit();
     }
     if (++s == in_stages) {
@@ -197,7 +206,8 @@ template <int ES>
 int launch_tma(const void *in, void *out, int64_t batch, int64_t rows, int64_t cols,
                cudaStream_t stream) {
   constexpr int TC = 128 / ES;
-  constexpr int TR = ES == 2 ? 64 : 32;
+  constexpr int TR = 64;
+  constexpr int TRo = 128 / ES;
   CUtensorMap in_map, out_map;
   const CUtensorMapDataType dt = ES == 2 ? CU_TENSOR_MAP_DATA_TYPE_UINT16 : CU_TENSOR_MAP_DATA_TYPE_UINT32;
   {
@@ -211,16 +221,15 @@ int launch_tma(const void *in, void *out, int64_t batch, int64_t rows, int64_t c
   {
     const uint64_t dims[3] = {(uint64_t)rows, (uint64_t)cols, (uint64_t)batch};
     const uint64_t strides[2] = {(uint64_t)rows * ES, (uint64_t)rows * cols * ES};
-    const uint32_t box[3] = {TR, TC, 1};
+    const uint32_t box[3] = {TRo, TC, 1};
     if (int rc = make_tensor_map(&out_map, dt, 3, out, dims, strides, box, CU_TENSOR_MAP_SWIZZLE_128B))
       return rc;
   }
   const int tiles_c = (int)ceil_div<int64_t>(cols, TC);
   const int tiles_r = (int)ceil_div<int64_t>(rows, TR);
   const int64_t num_tiles = (int64_t)tiles_c * tiles_r * batch;
-  // large matrices of 2-byte elements: four tiles in the ring and four blocks per SM; everything else
-  // three and five
-  const bool deep = ES == 2 && (int64_t)tiles_c * tiles_r >= 4096;
+  // large matrices: four tiles in the ring and four blocks per SM; everything else three and five
+  const bool deep = (int64_t)tiles_c * tiles_r >= 4096;
   const int in_stages = g_in_stages > 0 ? std::max(2, std::min(g_in_stages, kMaxInStages)) : (deep ? 4 : 3);
   const int blocks_per_sm = g_blocks_per_sm > 0 ? g_blocks_per_sm : (deep ? 4 : 5);
   const int panel = std::max(1, std::min(g_panel > 0 ? g_panel : 16, tiles_c));
@@ -231,7 +240,7 @@ int launch_tma(const void *in, void *out, int64_t batch, int64_t rows, int64_t c
     return rc;
   const unsigned grid = (unsigned)std::min<int64_t>(num_tiles, (int64_t)kNumSMs * blocks_per_sm);
   return launch_pdl(transpose_tma_kernel<ES>, dim3(grid), dim3(256), smem, stream, in_map, out_map, tiles_c, tiles_r,
-                    num_tiles, in_stages, panel, (int *)nullptr);
+                    num_tiles, in_stages, panel, rows, (int *)nullptr);
 }
 
 // =============================================================================
