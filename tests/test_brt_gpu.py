@@ -384,6 +384,20 @@ def test_reduce_over_dimensions_that_are_not_consecutive(shape, dims, t, npdt):
     assert np.array_equal(m, x.max(axis=dims))
 
 
+def test_cuda_kernel_plugin_runs():
+    """the plug-in of the integration notes (tests/cpp/cuda_plugin.cc) on configuration 2's sum"""
+    from test_brt_host import cuda_plugin
+    cuda_plugin()
+    x = np.random.default_rng(5).standard_normal((64, 512, 1024), dtype=np.float32).astype(np.float16)
+    text = reduce_mlir("PluginReduceSumOp_f16_f16", "f16", x.shape, (1024,), "dense<[0, 1]> : tensor<2xi64>")
+    got = _run(text, {"Input0": x})["Output0"]
+    want = O.reduce("sum", x, 1, 64 * 512, 1024)
+    np.testing.assert_allclose(got.astype(np.float64), want.astype(np.float64), rtol=2e-2, atol=1e-2)
+    # the same kernels behind the built-in key: the same bits
+    builtin = _run(reduce_mlir("ReduceSumOp_f16_f16", "f16", x.shape, (1024,), "dense<[0, 1]> : tensor<2xi64>"), {"Input0": x})["Output0"]
+    assert np.array_equal(got.view(np.uint16), builtin.view(np.uint16))
+
+
 def test_group_copy_from_bytecode_runs_on_the_gpu(tmp_path):
     from byre_bytecode_writer import write_module
     desc = {"name": "main",

@@ -27,6 +27,40 @@ def plugin():
     return PLUGIN
 
 
+CUDA_PLUGIN = ROOT / "tests" / "cpp" / "_build" / "libcuda_plugin.so"
+_cuda_plugin_registered = False
+
+
+def cuda_plugin():
+    """tests/cpp/cuda_plugin.cc: the kernel plug-in of the integration notes (an Impl class with the contract of
+    the reference's reduce_impl.h, wrapped by CudaOpKernelWithWorkspace, calling the C ABI), built with g++ against
+    this repo's headers and registered once"""
+    global _cuda_plugin_registered
+    src = ROOT / "tests" / "cpp" / "cuda_plugin.cc"
+    CUDA_PLUGIN.parent.mkdir(exist_ok=True)
+    if not CUDA_PLUGIN.exists() or CUDA_PLUGIN.stat().st_mtime < src.stat().st_mtime:
+        cuda_inc = next((p for p in ("/usr/local/cuda/include", "/usr/local/cuda-12.9/include") if Path(p).exists()), None)
+        assert cuda_inc, "no CUDA headers"
+        lib_dir = ROOT / "byteir_b200" / "_lib"
+        subprocess.check_call(["/usr/bin/g++" if Path("/usr/bin/g++").exists() else "g++", "-std=c++17", "-O1", "-fPIC",
+                               "-shared", "-I", str(ROOT / "include"), "-I", cuda_inc, str(src), "-o", str(CUDA_PLUGIN),
+                               "-L", str(lib_dir), "-lb200_kernels", f"-Wl,-rpath,{lib_dir}"])
+    if not _cuda_plugin_registered:
+        brt.lib()
+        brt.register_kernels_from_dynlib(CUDA_PLUGIN)
+        _cuda_plugin_registered = True
+    return CUDA_PLUGIN
+
+
+def test_cuda_kernel_plugin_builds_registers_and_its_key_loads():
+    cuda_plugin()
+    s = _cuda_session()
+    s.load_from_memory(reduce_mlir("PluginReduceSumOp_f16_f16", "f16", (64, 512, 1024), (1024,), "dense<[0, 1]> : tensor<2xi64>"))
+    assert s.arg_info(1).shape == (1024,)
+    with pytest.raises(brt.BrtError, match="consecutive"):  # the plug-in's own check, raised from its constructor
+        s.load_from_memory(reduce_mlir("PluginReduceSumOp_f16_f16", "f16", (4, 5, 6), (5,), "dense<[0, 2]> : tensor<2xi64>"))
+
+
 ADD = """
 module attributes {byre.container_module} {
   func.func @test_add(%arg0 : memref<100x32xf32, "cpu"> {byre.argname = "A", byre.argtype = 1: i32},
