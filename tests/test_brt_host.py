@@ -436,7 +436,11 @@ def test_session_takes_device_memory_from_the_callers_functions():
     assert s.get_input_arg_offsets() == [0] and s.get_output_arg_offsets() == [1]
     assert s.get_static_shape(0) == [64, 32] and s.get_data_type(1) == "f32"
     assert s.get_input_names() == ["Input0"] and s.get_output_names() == ["Output0"]
-    req = s.new_request_context(0x10)  # any non-null stream: nothing is launched here
+    # any non-null stream where there is no device (nothing is launched here); a real one where there is,
+    # since closing the request waits for its stream
+    import torch
+    stream = torch.cuda.Stream().cuda_stream if torch.cuda.is_available() else 0x10
+    req = s.new_request_context(stream)
     req.bind_args([(0, 0x1000)])
     req.finish_io_binding()             # the unbound output is allocated by the caller's function
     assert 64 * 4 in sizes and len(live) >= 1
